@@ -1,0 +1,170 @@
+"""In-tree build of the native parts of monarch_b200.
+
+Two shared objects are produced next to the Python sources (so they are importable
+without installation and are the files a process actually maps):
+
+* ``monarch_b200/ops/_mb200_kernels.so`` -- sm_100a CUDA kernels with a plain C API
+  (loaded with ctypes; no torch headers, so it compiles in seconds).
+* ``monarch_b200/_native.so`` -- the C++ runtime (ndslice, channels, mailboxes,
+  procs, mesh layer, telemetry) with pybind11 bindings.
+* ``monarch_b200/_gradgen.so`` -- the incremental autograd executor (torch extension).
+
+Usage: ``python -m monarch_b200._build [kernels|native|gradgen|all] [--force]``
+"""
+from __future__ import annotations
+
+import concurrent.futures as cf
+import hashlib
+import os
+import shlex
+import subprocess
+import sys
+import sysconfig
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+CSRC = ROOT / "csrc"
+OBJ = ROOT / "build"
+
+NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+CXX = os.environ.get("CXX", "g++")
+
+CUDA_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v",
+]
+
+
+def _run(cmd: list[str], log: Path | None = None) -> str:
+    p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if log is not None:
+        log.write_text(" ".join(shlex.quote(c) for c in cmd) + "\n" + p.stdout)
+    if p.returncode != 0:
+        raise RuntimeError(f"build command failed ({p.returncode}):\n{' '.join(cmd)}\n{p.stdout}")
+    return p.stdout
+
+
+def _stamp(srcs: list[Path], flags: list[str]) -> str:
+    h = hashlib.sha256()
+    for s in sorted(srcs):
+        h.update(str(s).encode())
+        h.update(s.read_bytes())
+    h.update(" ".join(flags).encode())
+    return h.hexdigest()
+
+
+def _deps(dirs: list[Path]) -> list[Path]:
+    out: list[Path] = []
+    for d in dirs:
+        for ext in ("*.h", "*.hpp", "*.cuh", "*.cu", "*.cpp"):
+            out += list(d.rglob(ext))
+    return out
+
+
+def _up_to_date(target: Path, stamp: str) -> bool:
+    sf = target.with_suffix(target.suffix + ".stamp")
+    return target.exists() and sf.exists() and sf.read_text() == stamp
+
+
+def _write_stamp(target: Path, stamp: str) -> None:
+    target.with_suffix(target.suffix + ".stamp").write_text(stamp)
+
+
+def _compile_many(jobs: list[tuple[list[str], Path]]) -> None:
+    with cf.ThreadPoolExecutor(max_workers=min(8, max(1, len(jobs)))) as ex:
+        futs = [ex.submit(_run, cmd, log) for cmd, log in jobs]
+        for f in futs:
+            f.result()
+
+
+def build_kernels(force: bool = False) -> Path:
+    kdir = CSRC / "kernels"
+    target = ROOT / "ops" / "_mb200_kernels.so"
+    srcs = sorted(kdir.glob("*.cu"))
+    stamp = _stamp(_deps([kdir]), CUDA_FLAGS)
+    if not force and _up_to_date(target, stamp):
+        return target
+    odir = OBJ / "kernels"
+    odir.mkdir(parents=True, exist_ok=True)
+    jobs = []
+    objs = []
+    for s in srcs:
+        o = odir / (s.stem + ".o")
+        objs.append(str(o))
+        jobs.append(([NVCC, *CUDA_FLAGS, "-I", str(kdir), "-c", str(s), "-o", str(o)],
+                     odir / (s.stem + ".log")))
+    _compile_many(jobs)
+    _run([NVCC, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", *objs, "-o", str(target)])
+    _write_stamp(target, stamp)
+    return target
+
+
+def _py_includes() -> list[str]:
+    import pybind11
+    return ["-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"]]
+
+
+NATIVE_FLAGS = ["-O2", "-std=c++20", "-fPIC", "-fvisibility=hidden", "-pthread", "-Wall",
+                "-Wno-unused-function"]
+
+
+def build_native(force: bool = False) -> Path:
+    target = ROOT / "_native.so"
+    dirs = [CSRC / d for d in ("ndslice", "actor", "channel", "mesh", "telemetry", "python",
+                               "rdma", "tensor")]
+    srcs = sorted(p for d in dirs for p in d.rglob("*.cpp"))
+    stamp = _stamp(_deps(dirs), NATIVE_FLAGS)
+    if not force and _up_to_date(target, stamp):
+        return target
+    odir = OBJ / "native"
+    odir.mkdir(parents=True, exist_ok=True)
+    jobs = []
+    objs = []
+    for s in srcs:
+        o = odir / (s.parent.name + "_" + s.stem + ".o")
+        objs.append(str(o))
+        jobs.append(([CXX, *NATIVE_FLAGS, "-I", str(CSRC), *_py_includes(), "-c", str(s), "-o",
+                      str(o)], odir / (s.parent.name + "_" + s.stem + ".log")))
+    _compile_many(jobs)
+    _run([CXX, "-shared", "-pthread", *objs, "-o", str(target), "-lrt"])
+    _write_stamp(target, stamp)
+    return target
+
+
+def build_gradgen(force: bool = False) -> Path:
+    """The gradient generator links against libtorch (it drives the autograd engine)."""
+    target = ROOT / "_gradgen.so"
+    src = CSRC / "gradgen" / "gradient_generator.cpp"
+    if not src.exists():
+        return target
+    import torch
+    from torch.utils import cpp_extension as ce
+    flags = ["-O2", "-std=c++17", "-fPIC", "-DTORCH_EXTENSION_NAME=_gradgen",
+             "-D_GLIBCXX_USE_CXX11_ABI=" + str(int(torch._C._GLIBCXX_USE_CXX11_ABI))]
+    stamp = _stamp([src], flags + [torch.__version__])
+    if not force and _up_to_date(target, stamp):
+        return target
+    incs = []
+    for i in ce.include_paths():
+        incs += ["-isystem", i]
+    libdir = os.path.join(os.path.dirname(torch.__file__), "lib")
+    _run([CXX, *flags, *incs, *_py_includes(), "-shared", str(src), "-o", str(target),
+          "-L", libdir, "-Wl,-rpath," + libdir, "-ltorch", "-ltorch_cpu", "-lc10",
+          "-ltorch_python"])
+    _write_stamp(target, stamp)
+    return target
+
+
+def build_all(force: bool = False) -> None:
+    build_kernels(force)
+    build_native(force)
+    build_gradgen(force)
+
+
+if __name__ == "__main__":
+    what = [a for a in sys.argv[1:] if not a.startswith("-")] or ["all"]
+    force = "--force" in sys.argv
+    for w in what:
+        {"kernels": build_kernels, "native": build_native, "gradgen": build_gradgen,
+         "all": build_all}[w](force)
+        print("built", w)

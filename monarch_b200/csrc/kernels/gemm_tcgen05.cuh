@@ -1,0 +1,280 @@
+// Persistent warp-specialised bf16 GEMM for sm_100a.
+//
+//   C[M,N] (bf16) = opA(A) * opB(B) (+ R) (+ C)        fp32 accumulation in TMEM
+//
+// * operands are staged by TMA (cp.async.bulk.tensor.2d, 128-byte swizzle) through a
+//   4-deep mbarrier ring; one elected thread issues tcgen05.mma (128x256x16 per
+//   instruction); the fp32 accumulator lives in TMEM and is double-buffered
+//   (2 x 256 columns) so the epilogue of tile i overlaps the main loop of tile i+1.
+// * either operand may be K-major (row-major [rows,K]) or MN-major (row-major [K,rows]),
+//   which covers forward (X W^T), input-gradient (dY W) and weight-gradient (dY^T X)
+//   products of a linear layer without any transpose pass.
+// * the body is a __device__ function over a *virtual* CTA id so that fused
+//   compute+collective kernels can run it on a subset of the grid while other CTAs
+//   move peer data; the TMA producer can be gated on global "ready" flags per block
+//   of B rows (bounded wait).
+#pragma once
+#include "ptx.cuh"
+
+namespace mb200 {
+
+constexpr int GEMM_BM = 128;
+constexpr int GEMM_BN = 256;
+constexpr int GEMM_BK = 64;
+constexpr int GEMM_STAGES = 4;
+constexpr int GEMM_THREADS = 192;  // warp0: TMA, warp1: MMA, warps 2-5: epilogue
+constexpr int GEMM_A_BYTES = GEMM_BM * GEMM_BK * 2;
+constexpr int GEMM_B_BYTES = GEMM_BN * GEMM_BK * 2;
+constexpr int GEMM_STAGE_BYTES = GEMM_A_BYTES + GEMM_B_BYTES;
+constexpr int GEMM_SMEM_BYTES = GEMM_STAGES * GEMM_STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+
+struct GemmParams {
+  __nv_bfloat16* C;
+  const __nv_bfloat16* R;  // optional residual, same shape as C
+  int M, N, K;
+  int ldc, ldr;
+  int accumulate;  // C += result
+  int* status;
+  // Optional gating of B tiles on readiness flags (fused all-gather -> GEMM):
+  // rows [f*rows_per_flag, (f+1)*rows_per_flag) of B are usable once
+  // b_ready[f] >= b_ready_target.
+  const uint32_t* b_ready;
+  uint32_t b_ready_target;
+  int rows_per_flag;
+  int n_blk_rot;  // rotate the N-block order so locally-owned blocks come first
+};
+
+struct GemmShared {
+  uint64_t full[GEMM_STAGES];
+  uint64_t empty[GEMM_STAGES];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  volatile int abort_word;
+};
+
+template <bool A_MN, bool B_MN>
+__device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tmA, const CUtensorMap* tmB,
+                                              const GemmParams& p, int vcta, int nvcta,
+                                              uint8_t* smem_raw) {
+  // 1024-byte aligned stage buffers (required by the 128-byte swizzle atoms).
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  GemmShared* sh = reinterpret_cast<GemmShared*>(smem + GEMM_STAGES * GEMM_STAGE_BYTES);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m_blocks = (p.M + GEMM_BM - 1) / GEMM_BM;
+  const int n_blocks = (p.N + GEMM_BN - 1) / GEMM_BN;
+  const int k_iters = (p.K + GEMM_BK - 1) / GEMM_BK;
+  const int num_tiles = m_blocks * n_blocks;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < GEMM_STAGES; ++s) {
+      mbar_init(&sh->full[s], 1);
+      mbar_init(&sh->empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&sh->tmem_full[s], 1);
+      mbar_init(&sh->tmem_empty[s], 4);
+    }
+    sh->abort_word = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&sh->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sh->tmem_base;
+  volatile int* abort_word = &sh->abort_word;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(tmA);
+      tma_prefetch_desc(tmB);
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = vcta; t < num_tiles; t += nvcta) {
+        const int m_blk = t % m_blocks;
+        int n_blk = t / m_blocks + p.n_blk_rot;
+        if (n_blk >= n_blocks) n_blk -= n_blocks;
+        const int m0 = m_blk * GEMM_BM, n0 = n_blk * GEMM_BN;
+        if (p.b_ready) {
+          // Both ends of the block: a 256-row block may straddle two flag ranges.
+          const int f0 = n0 / p.rows_per_flag;
+          int last_row = n0 + GEMM_BN - 1;
+          if (last_row >= p.N) last_row = p.N - 1;
+          const int f1 = last_row / p.rows_per_flag;
+          bool ok = true;
+          for (int f = f0; f <= f1 && ok; ++f)
+            ok = flag_wait_ge<false>(p.b_ready + f, p.b_ready_target, p.status);
+          if (!ok) {
+            *abort_word = 1;
+            break;
+          }
+        }
+        bool failed = false;
+        for (int k = 0; k < k_iters; ++k) {
+          if (!mbar_wait(&sh->empty[stage], phase ^ 1, abort_word, p.status)) {
+            failed = true;
+            break;
+          }
+          uint8_t* sa = smem + stage * GEMM_STAGE_BYTES;
+          uint8_t* sb = sa + GEMM_A_BYTES;
+          mbar_expect_tx(&sh->full[stage], GEMM_STAGE_BYTES);
+          const int k0 = k * GEMM_BK;
+          if (A_MN) {
+#pragma unroll
+            for (int j = 0; j < GEMM_BM / 64; ++j)
+              tma_load_2d(sa + j * 8192, tmA, &sh->full[stage], m0 + j * 64, k0);
+          } else {
+            tma_load_2d(sa, tmA, &sh->full[stage], k0, m0);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < GEMM_BN / 64; ++j)
+              tma_load_2d(sb + j * 8192, tmB, &sh->full[stage], n0 + j * 64, k0);
+          } else {
+            tma_load_2d(sb, tmB, &sh->full[stage], k0, n0);
+          }
+          if (++stage == GEMM_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (failed) break;
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(GEMM_BM, GEMM_BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      for (int t = vcta; t < num_tiles; t += nvcta) {
+        if (!mbar_wait(&sh->tmem_empty[acc], acc_phase ^ 1, abort_word, p.status)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * GEMM_BN;
+        bool failed = false;
+        for (int k = 0; k < k_iters; ++k) {
+          if (!mbar_wait(&sh->full[stage], phase, abort_word, p.status)) {
+            failed = true;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * GEMM_STAGE_BYTES);
+          const uint32_t sb = sa + GEMM_A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < GEMM_BK / 16; ++kk) {
+            const uint64_t da = A_MN ? umma_smem_desc_sw128(sa + kk * 2048, 8192, 1024)
+                                     : umma_smem_desc_sw128(sa + kk * 32, 16, 1024);
+            const uint64_t db = B_MN ? umma_smem_desc_sw128(sb + kk * 2048, 8192, 1024)
+                                     : umma_smem_desc_sw128(sb + kk * 32, 16, 1024);
+            umma_f16(d_tmem, da, db, idesc, (k > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(&sh->empty[stage]);  // stage reusable once these MMAs retire
+          if (++stage == GEMM_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (failed) break;
+        umma_commit(&sh->tmem_full[acc]);
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may access
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const bool vec_ok = ((p.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
+                        (!p.R || (((p.ldr & 7) == 0) &&
+                                  ((reinterpret_cast<uintptr_t>(p.R) & 15) == 0)));
+    for (int t = vcta; t < num_tiles; t += nvcta) {
+      const int m_blk = t % m_blocks;
+      int n_blk = t / m_blocks + p.n_blk_rot;
+      if (n_blk >= n_blocks) n_blk -= n_blocks;
+      const int row = m_blk * GEMM_BM + quad * 32 + lane;
+      const int n0 = n_blk * GEMM_BN;
+      if (!mbar_wait(&sh->tmem_full[acc], acc_phase, abort_word, p.status)) break;
+      tc_fence_after();
+      const uint32_t t_base = tmem_base + acc * GEMM_BN + ((uint32_t)(quad * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < GEMM_BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(t_base + c * 32, v);
+        tmem_ld_wait();
+        const int col = n0 + c * 32;
+        if (row < p.M && col < p.N) {
+          __nv_bfloat16* cp = p.C + (size_t)row * p.ldc + col;
+          const __nv_bfloat16* rp = p.R ? p.R + (size_t)row * p.ldr + col : nullptr;
+          if (vec_ok && col + 32 <= p.N) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              float f[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[q * 8 + i]);
+              if (rp) {
+                uint4 r4 = *reinterpret_cast<const uint4*>(rp + q * 8);
+                float2 a = unpack_bf16x2(r4.x), b = unpack_bf16x2(r4.y), c2 = unpack_bf16x2(r4.z),
+                       d = unpack_bf16x2(r4.w);
+                f[0] += a.x; f[1] += a.y; f[2] += b.x; f[3] += b.y;
+                f[4] += c2.x; f[5] += c2.y; f[6] += d.x; f[7] += d.y;
+              }
+              if (p.accumulate) {
+                uint4 r4 = *reinterpret_cast<const uint4*>(cp + q * 8);
+                float2 a = unpack_bf16x2(r4.x), b = unpack_bf16x2(r4.y), c2 = unpack_bf16x2(r4.z),
+                       d = unpack_bf16x2(r4.w);
+                f[0] += a.x; f[1] += a.y; f[2] += b.x; f[3] += b.y;
+                f[4] += c2.x; f[5] += c2.y; f[6] += d.x; f[7] += d.y;
+              }
+              uint4 o;
+              o.x = pack_bf16x2(f[0], f[1]);
+              o.y = pack_bf16x2(f[2], f[3]);
+              o.z = pack_bf16x2(f[4], f[5]);
+              o.w = pack_bf16x2(f[6], f[7]);
+              *reinterpret_cast<uint4*>(cp + q * 8) = o;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              if (col + i < p.N) {
+                float f = __uint_as_float(v[i]);
+                if (rp) f += __bfloat162float(rp[i]);
+                if (p.accumulate) f += __bfloat162float(cp[i]);
+                cp[i] = __float2bfloat16(f);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->tmem_empty[acc]);
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  }
+
+  // Common exit: every role reaches this point (all waits are bounded).
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace mb200

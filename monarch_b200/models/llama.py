@@ -1,0 +1,441 @@
+"""Llama-family decoder with an explicit forward/backward engine.
+
+The training step is written as explicit kernel launches (no autograd graph, no tracing
+compiler): every GEMM is the tcgen05 kernel, every normalisation / activation /
+loss / optimizer op is a hand-written sm_100a kernel, and the backward pass is spelled
+out per layer so that activation checkpointing, parameter gathering and gradient
+reduction can be placed exactly (see :mod:`monarch_b200.parallel`).
+
+Parameters live in one flat bf16 buffer split into *units* (embedding, each decoder
+layer, head); a unit is the granularity of FSDP gathering and gradient reduction.
+Parameter names and shapes match the Hugging Face Llama ``state_dict`` so checkpoints
+interchange with stock torch modules (:func:`to_hf_state_dict`,
+:func:`load_hf_state_dict`).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, Optional
+
+import torch
+
+from .. import ops
+
+bf16 = torch.bfloat16
+
+
+@dataclass
+class LlamaConfig:
+    vocab: int = 128256
+    d: int = 4096
+    n_layers: int = 32
+    n_heads: int = 32
+    n_kv_heads: int = 8
+    ffn: int = 14336
+    eps: float = 1e-5
+    theta: float = 500000.0
+    tie_embeddings: bool = False
+    name: str = "llama"
+
+    @property
+    def hd(self) -> int:
+        return self.d // self.n_heads
+
+    @property
+    def qkv_dim(self) -> int:
+        return (self.n_heads + 2 * self.n_kv_heads) * self.hd
+
+    def n_params(self) -> int:
+        per_layer = (2 * self.d + self.qkv_dim * self.d + self.d * self.d +
+                     2 * self.ffn * self.d + self.d * self.ffn)
+        n = self.vocab * self.d + self.n_layers * per_layer + self.d
+        if not self.tie_embeddings:
+            n += self.vocab * self.d
+        return n
+
+    def flops_per_token(self, seq_len: int, recompute: bool = True) -> float:
+        """Model FLOPs per token for one training step (fwd + bwd [+ recomputed fwd])."""
+        mm = self.n_layers * (self.qkv_dim * self.d + self.d * self.d + 3 * self.ffn * self.d)
+        mm += self.vocab * self.d
+        attn = self.n_layers * 2 * seq_len * self.d / 2  # causal QK^T + PV, per token
+        fwd = 2 * mm + 2 * attn
+        return fwd * (4 if recompute else 3)
+
+
+PRESETS: dict[str, LlamaConfig] = {
+    "llama3-8b": LlamaConfig(128256, 4096, 32, 32, 8, 14336, 1e-5, 500000.0, False, "llama3-8b"),
+    "llama3.2-1b": LlamaConfig(128256, 2048, 16, 32, 8, 8192, 1e-5, 500000.0, True,
+                               "llama3.2-1b"),
+    "llama2-13b": LlamaConfig(32000, 5120, 40, 40, 40, 13824, 1e-5, 10000.0, False, "llama2-13b"),
+    "tiny": LlamaConfig(512, 256, 2, 4, 2, 512, 1e-5, 500000.0, False, "tiny"),
+    "tiny-tied": LlamaConfig(512, 256, 2, 4, 2, 512, 1e-5, 500000.0, True, "tiny-tied"),
+}
+
+
+def _round_up(n: int, m: int) -> int:
+    return (n + m - 1) // m * m
+
+
+@dataclass
+class ParamSpec:
+    name: str
+    shape: tuple
+    offset: int  # element offset inside its unit
+
+
+@dataclass
+class Unit:
+    name: str
+    offset: int  # element offset of the unit inside the flat buffer
+    size: int    # padded size (multiple of ParamLayout.ALIGN)
+    params: list = field(default_factory=list)
+
+
+class ParamLayout:
+    """Flat layout: [embed | layer 0 | ... | layer L-1 | head]; units padded to ALIGN."""
+    ALIGN = 8192  # elements: keeps every 1/8 shard 16-byte aligned with room to spare
+
+    def __init__(self, cfg: LlamaConfig):
+        self.cfg = cfg
+        self.units: list[Unit] = []
+        off = 0
+
+        def add_unit(name, specs):
+            nonlocal off
+            u = Unit(name, off, 0)
+            o = 0
+            for n, shape in specs:
+                u.params.append(ParamSpec(n, tuple(shape), o))
+                numel = 1
+                for s in shape:
+                    numel *= s
+                o += _round_up(numel, 8)
+            u.size = _round_up(o, self.ALIGN)
+            off += u.size
+            self.units.append(u)
+
+        d, F = cfg.d, cfg.ffn
+        add_unit("embed", [("embed", (cfg.vocab, d))])
+        for i in range(cfg.n_layers):
+            add_unit(f"layer{i}", [("attn_norm", (d,)), ("wqkv", (cfg.qkv_dim, d)),
+                                   ("wo", (d, d)), ("mlp_norm", (d,)),
+                                   ("w_gu", (2 * F, d)), ("w_down", (d, F))])
+        head = [("final_norm", (d,))]
+        if not cfg.tie_embeddings:
+            head.append(("lm_head", (cfg.vocab, d)))
+        add_unit("head", head)
+        self.total = off
+
+    def views(self, unit: Unit, flat_unit: torch.Tensor) -> dict:
+        out = {}
+        for p in unit.params:
+            n = 1
+            for s in p.shape:
+                n *= s
+            out[p.name] = flat_unit[p.offset: p.offset + n].view(p.shape)
+        return out
+
+
+class LocalParamStore:
+    """All parameters, gradients and optimizer state resident on one device."""
+
+    def __init__(self, layout: ParamLayout, device, seed: int = 0, init_std: float = 0.02):
+        self.layout = layout
+        self.device = torch.device(device)
+        self.params = torch.empty(layout.total, dtype=bf16, device=device)
+        self.grads = torch.zeros(layout.total, dtype=bf16, device=device)
+        self.master = torch.empty(layout.total, dtype=torch.float32, device=device)
+        self.m = torch.zeros(layout.total, dtype=torch.float32, device=device)
+        self.v = torch.zeros(layout.total, dtype=torch.float32, device=device)
+        init_params_(layout, self.master, seed, init_std)
+        self.params.copy_(self.master)
+        self.step_count = 0
+
+    # --- unit access -----------------------------------------------------------------
+    def unit_params(self, ui: int) -> dict:
+        u = self.layout.units[ui]
+        return self.layout.views(u, self.params[u.offset: u.offset + u.size])
+
+    def unit_grads(self, ui: int) -> dict:
+        u = self.layout.units[ui]
+        return self.layout.views(u, self.grads[u.offset: u.offset + u.size])
+
+    # --- hooks (no-ops for a resident store) -----------------------------------------
+    def begin_step(self):
+        pass
+
+    def pre_forward(self, ui: int):
+        pass
+
+    def post_forward(self, ui: int):
+        pass
+
+    def pre_backward(self, ui: int):
+        pass
+
+    def post_backward(self, ui: int):
+        pass
+
+    def optimizer_step(self, lr, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1, grad_scale=1.0):
+        self.step_count += 1
+        ops.adamw_(self.master, self.m, self.v, self.grads, self.params, lr=lr, beta1=beta1,
+                   beta2=beta2, eps=eps, wd=wd, step=self.step_count, grad_scale=grad_scale)
+
+    def full_params(self) -> torch.Tensor:
+        return self.params
+
+    def load_full_params(self, flat: torch.Tensor) -> None:
+        self.params.copy_(flat)
+        self.master.copy_(flat)
+
+
+def init_params_(layout: ParamLayout, master: torch.Tensor, seed: int, std: float,
+                 lo: int = 0, hi: Optional[int] = None) -> None:
+    """Deterministic init of the flat fp32 master buffer range [lo, hi): N(0, std) for
+    matrices, ones for norm gains, zeros for padding.  Generated per parameter on the
+    buffer's device so a shard-only store initialises just its slice consistently."""
+    hi = layout.total if hi is None else hi
+    for ui, u in enumerate(layout.units):
+        if u.offset + u.size <= lo or u.offset >= hi:
+            continue
+        s, e = max(lo, u.offset), min(hi, u.offset + u.size)
+        master[s - lo: e - lo].zero_()
+        for pi, p in enumerate(u.params):
+            n = 1
+            for x in p.shape:
+                n *= x
+            a, b = u.offset + p.offset, u.offset + p.offset + n
+            s, e = max(a, lo), min(b, hi)
+            if s >= e:
+                continue
+            if len(p.shape) == 1:
+                master[s - lo: e - lo].fill_(1.0)
+                continue
+            # Row-chunked generation keyed by (seed, unit, param, chunk): identical values
+            # whichever slice of the parameter a rank owns.
+            CH = 1 << 22
+            c0 = (s - a) // CH
+            c1 = (e - a + CH - 1) // CH
+            for c in range(c0, c1):
+                g = torch.Generator(device=master.device)
+                g.manual_seed((seed * 1000003 + ui * 1009 + pi * 101 + c) & 0x7FFFFFFF)
+                cn = min(CH, n - c * CH)
+                vals = torch.empty(cn, dtype=torch.float32, device=master.device)
+                vals.normal_(0.0, std, generator=g)
+                ca, cb = a + c * CH, a + c * CH + cn
+                ss, ee = max(ca, s), min(cb, e)
+                master[ss - lo: ee - lo].copy_(vals[ss - ca: ee - ca])
+
+
+class LlamaEngine:
+    """Explicit training engine: ``loss = engine.forward_backward(tokens, targets)``
+    then ``engine.optimizer_step(lr)``.
+
+    ``store`` provides parameters/gradients per unit and receives hooks around each
+    unit's forward and backward so that FSDP / DDP / TP variants only swap the store.
+    """
+
+    def __init__(self, cfg: LlamaConfig, store, seq_len: int, checkpoint: bool = True):
+        self.cfg = cfg
+        self.store = store
+        self.seq_len = seq_len
+        self.checkpoint = checkpoint
+        dev = store.device
+        self.cos, self.sin = ops.reference.rope_tables(seq_len, cfg.hd, cfg.theta, device=dev)
+        self.n_units = cfg.n_layers + 2
+
+    # ------------------------------------------------------------------ layer forward
+    def _layer_fwd(self, w: dict, x: torch.Tensor, B: int, S: int, keep: bool):
+        cfg = self.cfg
+        h1, rstd1 = ops.rmsnorm_fwd(x, w["attn_norm"], cfg.eps)
+        qkv = ops.gemm(h1, w["wqkv"])
+        ops.rope_(qkv, self.cos, self.sin, S, cfg.n_heads + cfg.n_kv_heads, cfg.hd)
+        attn, actx = ops.attention_fwd(qkv, B, S, cfg.n_heads, cfg.n_kv_heads, cfg.hd,
+                                       need_bwd=keep)
+        x2 = ops.gemm(attn, w["wo"], residual=x)
+        h2, rstd2 = ops.rmsnorm_fwd(x2, w["mlp_norm"], cfg.eps)
+        gu = ops.gemm(h2, w["w_gu"])
+        hmid = ops.swiglu_fwd(gu)
+        y = ops.gemm(hmid, w["w_down"], residual=x2)
+        saved = (x, rstd1, h1, actx, attn, x2, rstd2, h2, gu, hmid) if keep else None
+        return y, saved
+
+    def _layer_bwd(self, w: dict, g: dict, saved, dy: torch.Tensor):
+        cfg = self.cfg
+        x, rstd1, h1, actx, attn, x2, rstd2, h2, gu, hmid = saved
+        d_hmid = ops.gemm(dy, w["w_down"], b_mn=True)
+        ops.gemm(dy, hmid, a_mn=True, b_mn=True, out=g["w_down"])
+        d_gu = ops.swiglu_bwd(gu, d_hmid)
+        del d_hmid
+        d_h2 = ops.gemm(d_gu, w["w_gu"], b_mn=True)
+        ops.gemm(d_gu, h2, a_mn=True, b_mn=True, out=g["w_gu"])
+        del d_gu
+        d_x2 = ops.rmsnorm_bwd(d_h2, x2, w["mlp_norm"], rstd2, g["mlp_norm"], dres=dy)
+        d_attn = ops.gemm(d_x2, w["wo"], b_mn=True)
+        ops.gemm(d_x2, attn, a_mn=True, b_mn=True, out=g["wo"])
+        d_qkv = ops.attention_bwd(actx, d_attn)
+        ops.rope_(d_qkv, self.cos, self.sin, actx.S, cfg.n_heads + cfg.n_kv_heads, cfg.hd,
+                  inverse=True)
+        d_h1 = ops.gemm(d_qkv, w["wqkv"], b_mn=True)
+        ops.gemm(d_qkv, h1, a_mn=True, b_mn=True, out=g["wqkv"])
+        dx = ops.rmsnorm_bwd(d_h1, x, w["attn_norm"], rstd1, g["attn_norm"], dres=d_x2)
+        return dx
+
+    # ------------------------------------------------------------------------- step
+    def forward_backward(self, tokens: torch.Tensor, targets: torch.Tensor,
+                         loss_scale: Optional[float] = None) -> torch.Tensor:
+        """tokens/targets: [B, S] int64 on the engine's device.  Returns the mean
+        token loss as a 0-d fp32 device tensor; gradients are left in the store."""
+        cfg, st = self.cfg, self.store
+        B, S = tokens.shape
+        T = B * S
+        L = cfg.n_layers
+        ids = tokens.reshape(-1)
+        tg = targets.reshape(-1)
+        st.begin_step()
+
+        # ---- forward
+        st.pre_forward(0)
+        x = ops.embedding_fwd(st.unit_params(0)["embed"], ids)
+        st.post_forward(0)
+        ckpt = []
+        saved_all = []
+        for i in range(L):
+            st.pre_forward(1 + i)
+            w = st.unit_params(1 + i)
+            ckpt.append(x)
+            x, saved = self._layer_fwd(w, x, B, S, keep=not self.checkpoint)
+            saved_all.append(saved)
+            st.post_forward(1 + i)
+
+        # ---- head: final norm, logits, loss, and its backward
+        hu = L + 1
+        st.pre_forward(hu)
+        st.pre_backward(hu)
+        wh = st.unit_params(hu)
+        gh = st.unit_grads(hu)
+        if cfg.tie_embeddings:
+            st.pre_backward(0)
+            w_out = st.unit_params(0)["embed"]
+            g_out = st.unit_grads(0)["embed"]
+        else:
+            w_out, g_out = wh["lm_head"], gh["lm_head"]
+        hf, rstdf = ops.rmsnorm_fwd(x, wh["final_norm"], cfg.eps)
+        logits = ops.gemm(hf, w_out)
+        scale = (1.0 / T) if loss_scale is None else loss_scale
+        loss_rows = ops.cross_entropy_(logits, tg, scale)
+        loss = loss_rows.mean()
+        d_hf = ops.gemm(logits, w_out, b_mn=True)
+        ops.gemm(logits, hf, a_mn=True, b_mn=True, out=g_out)
+        del logits
+        dx = ops.rmsnorm_bwd(d_hf, x, wh["final_norm"], rstdf, gh["final_norm"])
+        del d_hf, hf
+        st.post_forward(hu)
+        st.post_backward(hu)
+
+        # ---- layers backward (recompute from the checkpoint when enabled)
+        for i in reversed(range(L)):
+            st.pre_backward(1 + i)
+            w = st.unit_params(1 + i)
+            g = st.unit_grads(1 + i)
+            if self.checkpoint:
+                _, saved = self._layer_fwd(w, ckpt[i], B, S, keep=True)
+            else:
+                saved = saved_all[i]
+                saved_all[i] = None
+            dx = self._layer_bwd(w, g, saved, dx)
+            ckpt[i] = None
+            del saved
+            st.post_backward(1 + i)
+
+        # ---- embedding backward
+        if not cfg.tie_embeddings:
+            st.pre_backward(0)
+            st.unit_grads(0)["embed"].zero_()
+        ops.embedding_bwd_(dx, ids, st.unit_grads(0)["embed"])
+        st.post_backward(0)
+        return loss
+
+    def forward_loss(self, tokens, targets) -> torch.Tensor:
+        """Forward only (evaluation): mean token loss."""
+        cfg, st = self.cfg, self.store
+        B, S = tokens.shape
+        st.begin_step()
+        st.pre_forward(0)
+        x = ops.embedding_fwd(st.unit_params(0)["embed"], tokens.reshape(-1))
+        st.post_forward(0)
+        for i in range(cfg.n_layers):
+            st.pre_forward(1 + i)
+            x, _ = self._layer_fwd(st.unit_params(1 + i), x, B, S, keep=False)
+            st.post_forward(1 + i)
+        hu = cfg.n_layers + 1
+        st.pre_forward(hu)
+        wh = st.unit_params(hu)
+        if cfg.tie_embeddings:
+            st.pre_forward(0)
+            w_out = st.unit_params(0)["embed"]
+        else:
+            w_out = wh["lm_head"]
+        hf, _ = ops.rmsnorm_fwd(x, wh["final_norm"], cfg.eps)
+        logits = ops.gemm(hf, w_out)
+        loss = ops.cross_entropy_(logits, targets.reshape(-1), 0.0).mean()
+        st.post_forward(hu)
+        return loss
+
+    def optimizer_step(self, lr: float, **kw):
+        self.store.optimizer_step(lr, **kw)
+
+
+# ------------------------------------------------------------------ state_dict interchange
+def to_hf_state_dict(cfg: LlamaConfig, layout: ParamLayout, flat: torch.Tensor) -> dict:
+    """Full flat parameter buffer -> Hugging Face Llama ``state_dict`` (tensor views are
+    cloned so the result is an ordinary, independently owned state_dict)."""
+    sd = {}
+    hd, Hq, Hkv, F = cfg.hd, cfg.n_heads, cfg.n_kv_heads, cfg.ffn
+    for ui, u in enumerate(layout.units):
+        v = layout.views(u, flat[u.offset: u.offset + u.size])
+        if u.name == "embed":
+            sd["model.embed_tokens.weight"] = v["embed"].clone()
+        elif u.name == "head":
+            sd["model.norm.weight"] = v["final_norm"].clone()
+            sd["lm_head.weight"] = (v["lm_head"] if "lm_head" in v
+                                    else sd["model.embed_tokens.weight"]).clone()
+        else:
+            i = ui - 1
+            p = f"model.layers.{i}."
+            sd[p + "input_layernorm.weight"] = v["attn_norm"].clone()
+            sd[p + "post_attention_layernorm.weight"] = v["mlp_norm"].clone()
+            q, k, vv = v["wqkv"].split([Hq * hd, Hkv * hd, Hkv * hd], dim=0)
+            sd[p + "self_attn.q_proj.weight"] = q.clone()
+            sd[p + "self_attn.k_proj.weight"] = k.clone()
+            sd[p + "self_attn.v_proj.weight"] = vv.clone()
+            sd[p + "self_attn.o_proj.weight"] = v["wo"].clone()
+            gate, up = v["w_gu"].split([F, F], dim=0)
+            sd[p + "mlp.gate_proj.weight"] = gate.clone()
+            sd[p + "mlp.up_proj.weight"] = up.clone()
+            sd[p + "mlp.down_proj.weight"] = v["w_down"].clone()
+    return sd
+
+
+def load_hf_state_dict(cfg: LlamaConfig, layout: ParamLayout, sd: dict,
+                       flat: torch.Tensor) -> None:
+    """Inverse of :func:`to_hf_state_dict`: fill a full flat buffer from HF names."""
+    for ui, u in enumerate(layout.units):
+        v = layout.views(u, flat[u.offset: u.offset + u.size])
+        if u.name == "embed":
+            v["embed"].copy_(sd["model.embed_tokens.weight"])
+        elif u.name == "head":
+            v["final_norm"].copy_(sd["model.norm.weight"])
+            if "lm_head" in v:
+                v["lm_head"].copy_(sd["lm_head.weight"])
+        else:
+            p = f"model.layers.{ui - 1}."
+            v["attn_norm"].copy_(sd[p + "input_layernorm.weight"])
+            v["mlp_norm"].copy_(sd[p + "post_attention_layernorm.weight"])
+            v["wqkv"].copy_(torch.cat([sd[p + "self_attn.q_proj.weight"],
+                                       sd[p + "self_attn.k_proj.weight"],
+                                       sd[p + "self_attn.v_proj.weight"]], dim=0))
+            v["wo"].copy_(sd[p + "self_attn.o_proj.weight"])
+            v["w_gu"].copy_(torch.cat([sd[p + "mlp.gate_proj.weight"],
+                                       sd[p + "mlp.up_proj.weight"]], dim=0))
+            v["w_down"].copy_(sd[p + "mlp.down_proj.weight"])

@@ -1,0 +1,128 @@
+"""ctypes binding of the sm_100a kernel library (``_mb200_kernels.so``).
+
+The library is built in-tree by :mod:`monarch_b200._build`.  On a machine with a GPU a
+missing or unloadable library is an error (never a silent PyTorch fallback); without a
+GPU the pure-PyTorch reference implementations in :mod:`monarch_b200.ops.reference`
+are used so that the host-side logic stays testable.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from pathlib import Path
+from typing import Optional
+
+import torch
+
+_SO = Path(__file__).resolve().parent / "_mb200_kernels.so"
+_lib: Optional[ctypes.CDLL] = None
+_status: dict[int, torch.Tensor] = {}
+
+#: number of kernels of this library launched since import (bench.py reports the delta)
+launch_count = 0
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not _SO.exists():
+            if os.environ.get("MB200_NO_AUTOBUILD") != "1":
+                from .. import _build
+                _build.build_kernels()
+        if not _SO.exists():
+            raise KernelError(f"{_SO} is missing: run `python -m monarch_b200._build kernels`")
+        _lib = ctypes.CDLL(str(_SO))
+        _declare(_lib)
+    return _lib
+
+
+def available() -> bool:
+    """True when the CUDA kernels can run (GPU present).  Raises if a GPU is present
+    but the library cannot be loaded."""
+    if not torch.cuda.is_available():
+        return False
+    lib()
+    return True
+
+
+_vp, _i, _f, _i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_int64
+
+
+def _declare(l: ctypes.CDLL) -> None:
+    l.mb200_gemm_bf16.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp,
+                                  _vp]
+    l.mb200_rmsnorm_fwd.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _f, _vp]
+    l.mb200_rmsnorm_bwd_blocks.argtypes = [_i]
+    l.mb200_rmsnorm_bwd.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]
+    l.mb200_rope_inplace.argtypes = [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]
+    l.mb200_swiglu_fwd.argtypes = [_vp, _vp, _i, _i, _vp]
+    l.mb200_swiglu_bwd.argtypes = [_vp, _vp, _vp, _i, _i, _vp]
+    l.mb200_cross_entropy_fwd_bwd.argtypes = [_vp, _vp, _vp, _i, _i, _i, _f, _vp]
+    l.mb200_adamw.argtypes = [_vp, _vp, _vp, _vp, _vp, _i64, _i, _f, _f, _f, _f, _f, _i, _f, _vp]
+    l.mb200_embedding_fwd.argtypes = [_vp, _vp, _vp, _i, _i, _vp]
+    l.mb200_embedding_bwd.argtypes = [_vp, _vp, _vp, _i, _i, _vp]
+    l.mb200_sumsq.argtypes = [_vp, _i64, _i, _vp, _vp]
+    for n in ("mb200_gemm_bf16", "mb200_rmsnorm_fwd", "mb200_rmsnorm_bwd_blocks",
+              "mb200_rmsnorm_bwd", "mb200_rope_inplace", "mb200_swiglu_fwd", "mb200_swiglu_bwd",
+              "mb200_cross_entropy_fwd_bwd", "mb200_adamw", "mb200_embedding_fwd",
+              "mb200_embedding_bwd", "mb200_sumsq"):
+        getattr(l, n).restype = _i
+    for n, args in _OPTIONAL.items():
+        if hasattr(l, n):
+            getattr(l, n).argtypes = args
+            getattr(l, n).restype = _i
+
+
+_OPTIONAL: dict[str, list] = {
+    "mb200_attn_fwd": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _vp],
+    "mb200_attn_bwd": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
+                       _i, _i, _f, _vp, _vp],
+    "mb200_peer_copy": [_vp, _vp, _i64, _i, _vp],
+    "mb200_barrier": [_vp, _i, _i, ctypes.c_uint32, _vp, _vp],
+    "mb200_allreduce_scale_cast": [_vp, _vp, _vp, _i64, _i, _i, _f, _i, _i, _vp, ctypes.c_uint32,
+                                   _vp, _vp],
+    "mb200_allgather_pull": [_vp, _vp, _i64, _i, _i, _i, _vp],
+    "mb200_rs_adamw": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i, _i, _f, _f, _f, _f, _f, _i, _f,
+                       _i, _vp],
+    "mb200_ag_gemm": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp,
+                      ctypes.c_uint32, _i, _vp, _vp],
+}
+
+
+def status_word(device: torch.device | int | None = None) -> torch.Tensor:
+    """Per-device int32 status word written by kernels whose bounded waits ran out."""
+    idx = torch.cuda.current_device() if device is None else torch.device(device).index or 0
+    t = _status.get(idx)
+    if t is None:
+        t = torch.zeros(4, dtype=torch.int32, device=f"cuda:{idx}")
+        _status[idx] = t
+    return t
+
+
+def check_status(device=None) -> None:
+    """Synchronising check of the status word; raises KernelError on a recorded timeout."""
+    t = status_word(device)
+    v = int(t[0].item())
+    if v != 0:
+        t.zero_()
+        raise KernelError({1: "mbarrier wait timed out inside a kernel",
+                           2: "wait on a peer/ready flag timed out inside a kernel",
+                           3: "kernel rejected its arguments"}.get(v, f"kernel status {v}"))
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def check(rc: int, what: str, n_launch: int = 1) -> None:
+    global launch_count
+    if rc != 0:
+        msg = f"{what}: error {rc}"
+        if rc < 1000:
+            msg += f" ({torch.cuda.cudart().cudaGetErrorString(rc) if hasattr(torch.cuda.cudart(), 'cudaGetErrorString') else 'cuda error'})"
+        raise KernelError(msg)
+    launch_count += n_launch

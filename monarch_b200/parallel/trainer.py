@@ -1,0 +1,96 @@
+"""User-facing training driver: one object per rank that owns the model engine, the
+parameter store for the chosen parallelism and the host<->device staging.
+
+``Trainer.step(tokens, targets)`` is the call a user makes every iteration: it takes
+*host* tensors (pinned or not), copies them to the device, runs forward + backward +
+optimizer through the hand-written kernels and returns the loss as a Python float.
+"""
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import torch
+
+from ..models.llama import PRESETS, LlamaConfig, LlamaEngine, LocalParamStore, ParamLayout
+
+
+def _dist_info():
+    import torch.distributed as dist
+    if dist.is_available() and dist.is_initialized():
+        return dist.get_rank(), dist.get_world_size()
+    return 0, 1
+
+
+class Trainer:
+    def __init__(self, model: str | LlamaConfig = "llama3-8b", seq_len: int = 8192,
+                 micro_batch: int = 1, parallelism: str = "auto", device=None,
+                 checkpoint: bool = True, lr: float = 3e-4, seed: int = 0,
+                 comm: str = "fused"):
+        self.cfg = PRESETS[model] if isinstance(model, str) else model
+        self.seq_len = seq_len
+        self.micro_batch = micro_batch
+        self.lr = lr
+        rank, world = _dist_info()
+        self.rank, self.world = rank, world
+        if device is None:
+            if torch.cuda.is_available():
+                device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
+                torch.cuda.set_device(device)
+            else:
+                device = torch.device("cpu")
+        self.device = torch.device(device)
+        if parallelism == "auto":
+            parallelism = "single" if world == 1 else "fsdp"
+        self.parallelism = parallelism
+        self.layout = ParamLayout(self.cfg)
+        if parallelism == "single":
+            self.store = LocalParamStore(self.layout, self.device, seed=seed)
+        elif parallelism == "fsdp":
+            from .fsdp import FSDPParamStore
+            self.store = FSDPParamStore(self.layout, self.device, seed=seed, comm=comm)
+        elif parallelism == "ddp":
+            from .ddp import DDPParamStore
+            self.store = DDPParamStore(self.layout, self.device, seed=seed, comm=comm)
+        else:
+            raise ValueError(f"unknown parallelism {parallelism!r}")
+        self.engine = LlamaEngine(self.cfg, self.store, seq_len, checkpoint=checkpoint)
+        shape = (micro_batch, seq_len)
+        self._tok_dev = torch.empty(shape, dtype=torch.int64, device=self.device)
+        self._tgt_dev = torch.empty(shape, dtype=torch.int64, device=self.device)
+
+    # -------------------------------------------------------------------------------
+    def step_device(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        """One optimizer step on device-resident inputs; returns the device loss tensor."""
+        loss = self.engine.forward_backward(tokens, targets)
+        self.engine.optimizer_step(self.lr)
+        return loss
+
+    def step(self, tokens: torch.Tensor, targets: torch.Tensor) -> float:
+        """One optimizer step on host inputs ([micro_batch, seq_len] int64).  Copies the
+        batch to the device, runs the step and reads the loss back."""
+        self._tok_dev.copy_(tokens, non_blocking=True)
+        self._tgt_dev.copy_(targets, non_blocking=True)
+        loss = self.step_device(self._tok_dev, self._tgt_dev)
+        return float(loss.item())
+
+    @property
+    def h2d_bytes_per_step(self) -> int:
+        return 2 * self._tok_dev.numel() * self._tok_dev.element_size()
+
+    @property
+    def d2h_bytes_per_step(self) -> int:
+        return 4
+
+    # ---------------------------------------------------------------- checkpointing
+    def state_dict(self) -> dict:
+        """Hugging Face-named model ``state_dict`` (full tensors, on every rank)."""
+        from ..models.llama import to_hf_state_dict
+        return to_hf_state_dict(self.cfg, self.layout, self.store.full_params())
+
+    def load_state_dict(self, sd: dict) -> None:
+        from ..models.llama import load_hf_state_dict
+        flat = torch.empty(self.layout.total, dtype=torch.bfloat16, device=self.device)
+        flat.zero_()
+        load_hf_state_dict(self.cfg, self.layout, sd, flat)
+        self.store.load_full_params(flat)

@@ -1,0 +1,182 @@
+"""Numerics of every sm_100a kernel against the plain-PyTorch fp32 reference of the
+same op (monarch_b200.ops.reference)."""
+import pytest
+import torch
+
+from monarch_b200 import ops
+from monarch_b200.ops import kernels as K
+from monarch_b200.ops import reference as R
+
+pytestmark = pytest.mark.gpu
+bf16 = torch.bfloat16
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    yield
+    torch.cuda.synchronize()
+    K.check_status()
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K_", [(128, 256, 64), (256, 512, 256), (384, 768, 1024),
+                                    (304, 520, 200), (8, 24, 72), (1024, 4096, 4096)])
+def test_gemm_matches_fp32(a_mn, b_mn, M, N, K_):
+    torch.manual_seed(0)
+    a = torch.randn((K_, M) if a_mn else (M, K_), device="cuda", dtype=bf16)
+    b = torch.randn((K_, N) if b_mn else (N, K_), device="cuda", dtype=bf16)
+    c = ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    ref = R.gemm(a, b, a_mn, b_mn)
+    assert c.shape == (M, N)
+    assert _rel(c, ref) < 5e-3, _rel(c, ref)
+
+
+def test_gemm_residual_and_accumulate():
+    torch.manual_seed(1)
+    M, N, K_ = 512, 1024, 512
+    a = torch.randn(M, K_, device="cuda", dtype=bf16)
+    b = torch.randn(N, K_, device="cuda", dtype=bf16)
+    r = torch.randn(M, N, device="cuda", dtype=bf16)
+    c = ops.gemm(a, b, residual=r)
+    assert _rel(c, R.gemm(a, b, residual=r)) < 5e-3
+    c0 = torch.randn(M, N, device="cuda", dtype=bf16)
+    c1 = c0.clone()
+    ops.gemm(a, b, out=c1, accumulate=True)
+    assert _rel(c1, R.gemm(a, b, accumulate_into=c0)) < 5e-3
+
+
+def test_gemm_strided_views():
+    torch.manual_seed(2)
+    big = torch.randn(512, 1024, device="cuda", dtype=bf16)
+    a = big[:, 256:768]           # [512, 512], ld 1024
+    b = torch.randn(256, 512, device="cuda", dtype=bf16)
+    out_big = torch.zeros(512, 512, device="cuda", dtype=bf16)
+    out = out_big[:, 128:384]
+    ops.gemm(a, b, out=out)
+    assert _rel(out, R.gemm(a, b)) < 5e-3
+    assert out_big[:, :128].abs().max() == 0 and out_big[:, 384:].abs().max() == 0
+
+
+def test_gemm_many_tiles_persistent():
+    # more tiles than SMs: exercises the persistent loop and TMEM double buffering
+    torch.manual_seed(3)
+    M, N, K_ = 4096, 4096, 512
+    a = torch.randn(M, K_, device="cuda", dtype=bf16)
+    b = torch.randn(N, K_, device="cuda", dtype=bf16)
+    c = ops.gemm(a, b)
+    ref = (a.float() @ b.float().t())
+    assert _rel(c, ref) < 5e-3
+
+
+@pytest.mark.parametrize("rows,d", [(64, 256), (1000, 2048), (512, 4096), (33, 8192)])
+def test_rmsnorm(rows, d):
+    torch.manual_seed(0)
+    x = torch.randn(rows, d, device="cuda", dtype=bf16)
+    w = (1 + 0.1 * torch.randn(d, device="cuda")).to(bf16)
+    y, rstd = ops.rmsnorm_fwd(x, w, 1e-5)
+    yr, rstdr = R.rmsnorm_fwd(x, w, 1e-5)
+    assert _rel(y, yr) < 5e-3 and _rel(rstd, rstdr) < 1e-5
+    dy = torch.randn(rows, d, device="cuda", dtype=bf16)
+    dres = torch.randn(rows, d, device="cuda", dtype=bf16)
+    dw = torch.zeros(d, device="cuda", dtype=bf16)
+    dx = ops.rmsnorm_bwd(dy, x, w, rstd, dw, dres=dres)
+    dxr, dwr = R.rmsnorm_bwd(dy, x, w, rstdr)
+    assert _rel(dx, dxr + dres.float()) < 6e-3
+    assert _rel(dw, dwr) < 6e-3
+    # second call reuses the scratch buffer and accumulates
+    ops.rmsnorm_bwd(dy, x, w, rstd, dw, accumulate=True)
+    assert _rel(dw, 2 * dwr) < 1e-2
+
+
+def test_rope_forward_inverse():
+    torch.manual_seed(0)
+    S, Hq, Hkv, hd, B = 64, 4, 2, 128, 2
+    cos, sin = R.rope_tables(S, hd, 500000.0, device="cuda")
+    qkv = torch.randn(B * S, (Hq + 2 * Hkv) * hd, device="cuda", dtype=bf16)
+    orig = qkv.clone()
+    ops.rope_(qkv, cos, sin, S, Hq + Hkv, hd)
+    ref = R.rope(orig[:, : (Hq + Hkv) * hd].float().reshape(B * S, Hq + Hkv, hd), cos, sin, S)
+    assert _rel(qkv[:, : (Hq + Hkv) * hd], ref.reshape(B * S, -1)) < 5e-3
+    assert torch.equal(qkv[:, (Hq + Hkv) * hd:], orig[:, (Hq + Hkv) * hd:])
+    ops.rope_(qkv, cos, sin, S, Hq + Hkv, hd, inverse=True)
+    assert _rel(qkv, orig) < 1e-2
+
+
+def test_swiglu():
+    torch.manual_seed(0)
+    gu = torch.randn(300, 2 * 1024, device="cuda", dtype=bf16)
+    dh = torch.randn(300, 1024, device="cuda", dtype=bf16)
+    assert _rel(ops.swiglu_fwd(gu), R.swiglu_fwd(gu)) < 5e-3
+    assert _rel(ops.swiglu_bwd(gu, dh), R.swiglu_bwd(gu, dh)) < 5e-3
+
+
+@pytest.mark.parametrize("rows,V", [(64, 512), (37, 32000), (16, 128256)])
+def test_cross_entropy(rows, V):
+    torch.manual_seed(0)
+    logits = (3 * torch.randn(rows, V, device="cuda")).to(bf16)
+    tg = torch.randint(0, V, (rows,), device="cuda")
+    lr, gr = R.cross_entropy(logits, tg, 1.0 / rows)
+    loss = ops.cross_entropy_(logits, tg, 1.0 / rows)
+    assert torch.allclose(loss, lr, atol=2e-3, rtol=1e-3)
+    assert _rel(logits, gr) < 1e-2
+
+
+def test_adamw_matches_reference():
+    torch.manual_seed(0)
+    n = 100003
+    p = torch.randn(n, device="cuda")
+    m = torch.zeros(n, device="cuda")
+    v = torch.zeros(n, device="cuda")
+    pb = torch.empty(n, device="cuda", dtype=bf16)
+    pr, mr, vr = p.clone(), m.clone(), v.clone()
+    for step in range(1, 4):
+        g = torch.randn(n, device="cuda").to(bf16)
+        ops.adamw_(p, m, v, g, pb, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1, step=step)
+        pr, mr, vr = R.adamw(pr, mr, vr, g, 1e-2, 0.9, 0.95, 1e-8, 0.1, step)
+    assert torch.allclose(p, pr, atol=1e-5) and torch.allclose(m, mr, atol=1e-6)
+    assert torch.allclose(v, vr, atol=1e-6)
+    assert torch.equal(pb, p.to(bf16))
+
+
+def test_embedding():
+    torch.manual_seed(0)
+    table = torch.randn(1000, 256, device="cuda", dtype=bf16)
+    ids = torch.randint(0, 1000, (777,), device="cuda")
+    assert torch.equal(ops.embedding_fwd(table, ids), table[ids])
+    dout = torch.randn(777, 256, device="cuda", dtype=bf16)
+    dt = torch.zeros(1000, 256, device="cuda", dtype=bf16)
+    ops.embedding_bwd_(dout, ids, dt)
+    ref = torch.zeros(1000, 256, device="cuda").index_add_(0, ids, dout.float())
+    assert _rel(dt, ref) < 1e-2
+
+
+def test_sumsq():
+    x = torch.randn(1 << 20, device="cuda", dtype=bf16)
+    s = ops.sumsq(x)
+    assert abs(s.item() - x.float().pow(2).sum().item()) / s.item() < 1e-3
+
+
+def test_engine_gpu_matches_cpu_fp32():
+    """The whole explicit step on the GPU kernels (bf16) against the same engine run with
+    the fp32 CPU reference ops."""
+    from monarch_b200.models import PRESETS, LlamaEngine, LocalParamStore, ParamLayout
+    cfg = PRESETS["tiny"]
+    layout = ParamLayout(cfg)
+    g_st = LocalParamStore(layout, "cuda", seed=5, init_std=0.05)
+    c_st = LocalParamStore(layout, "cpu", seed=5, init_std=0.05)
+    c_st.master.copy_(g_st.master.cpu())
+    c_st.params = g_st.params.cpu().float()
+    c_st.grads = torch.zeros(layout.total)
+    S = 128
+    torch.manual_seed(0)
+    tokens = torch.randint(0, cfg.vocab, (2, S))
+    targets = torch.randint(0, cfg.vocab, (2, S))
+    lg = LlamaEngine(cfg, g_st, S).forward_backward(tokens.cuda(), targets.cuda())
+    lc = LlamaEngine(cfg, c_st, S).forward_backward(tokens, targets)
+    assert abs(lg.item() - lc.item()) < 3e-2, (lg.item(), lc.item())
+    assert _rel(g_st.grads.cpu(), c_st.grads) < 5e-2, _rel(g_st.grads.cpu(), c_st.grads)
+    assert K.launch_count > 0
