@@ -113,6 +113,8 @@ def build_native(force: bool = False) -> Path:
     dirs = [CSRC / d for d in ("ndslice", "actor", "channel", "mesh", "telemetry", "python",
                                "rdma", "tensor")]
     srcs = sorted(p for d in dirs for p in d.rglob("*.cpp"))
+    if not (CSRC / "python" / "module.cpp").exists():
+        return target
     stamp = _stamp(_deps(dirs), NATIVE_FLAGS)
     if not force and _up_to_date(target, stamp):
         return target
