@@ -1,0 +1,95 @@
+#!/usr/bin/env python
+"""Small, self-terminating cases of each hand-written kernel for `ncu` captures.
+
+    python benchmarks/profile_case.py gemm            # 3 launches of one 8192x4096x4096 GEMM
+    python benchmarks/profile_case.py elementwise     # one launch of each memory-bound kernel
+    python benchmarks/profile_case.py step            # 2-layer Llama-3-8B-shaped training steps
+
+Inputs are larger than the 126 MB L2 but only a few hundred MB, so a multi-pass capture
+finishes in about a minute.
+"""
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from monarch_b200 import ops  # noqa: E402
+from monarch_b200.ops import kernels as K  # noqa: E402
+from monarch_b200.ops import reference as R  # noqa: E402
+
+bf16 = torch.bfloat16
+
+
+def gemm_case(variant="nt"):
+    T, N, Kd = 8192, 4096, 4096
+    a_mn, b_mn = {"nt": (False, False), "nn": (False, True), "tn": (True, True)}[variant]
+    a = torch.randn((Kd, T) if a_mn else (T, Kd), device="cuda", dtype=bf16)
+    b = torch.randn((Kd, N) if b_mn else (N, Kd), device="cuda", dtype=bf16)
+    out = torch.empty(T, N, device="cuda", dtype=bf16)
+    for _ in range(3):
+        ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out)
+    torch.cuda.synchronize()
+
+
+def elementwise_case():
+    T, d, F, V = 8192, 4096, 14336, 32064
+    x = torch.randn(T, d, device="cuda", dtype=bf16)
+    w = torch.ones(d, device="cuda", dtype=bf16)
+    y, rstd = ops.rmsnorm_fwd(x, w)
+    dw = torch.zeros(d, device="cuda", dtype=bf16)
+    ops.rmsnorm_bwd(y, x, w, rstd, dw, dres=x)
+    gu = torch.randn(T, 2 * F, device="cuda", dtype=bf16)
+    h = ops.swiglu_fwd(gu)
+    ops.swiglu_bwd(gu, h)
+    cos, sin = R.rope_tables(T, 128, 500000.0, device="cuda")
+    qkv = torch.randn(T, 6144, device="cuda", dtype=bf16)
+    ops.rope_(qkv, cos, sin, T, 40, 128)
+    logits = torch.randn(T, V, device="cuda", dtype=bf16)
+    tg = torch.randint(0, V, (T,), device="cuda")
+    ops.cross_entropy_(logits, tg, 1.0 / T)
+    n = 64 << 20
+    p = torch.randn(n, device="cuda")
+    m = torch.zeros(n, device="cuda")
+    v = torch.zeros(n, device="cuda")
+    g = torch.randn(n, device="cuda", dtype=bf16)
+    pb = torch.empty(n, device="cuda", dtype=bf16)
+    ops.adamw_(p, m, v, g, pb, lr=1e-3, step=1)
+    torch.cuda.synchronize()
+
+
+def attn_case():
+    B, S, Hq, Hkv, hd = 1, 8192, 32, 8, 128
+    qkv = torch.randn(B * S, (Hq + 2 * Hkv) * hd, device="cuda", dtype=bf16)
+    o, ctx = ops.attention_fwd(qkv, B, S, Hq, Hkv, hd)
+    do = torch.randn_like(o)
+    ops.attention_bwd(ctx, do)
+    torch.cuda.synchronize()
+
+
+def step_case(layers=2, steps=2):
+    from dataclasses import replace
+    from monarch_b200.models import PRESETS, LlamaEngine, LocalParamStore, ParamLayout
+    cfg = replace(PRESETS["llama3-8b"], n_layers=layers, vocab=32064)
+    layout = ParamLayout(cfg)
+    st = LocalParamStore(layout, "cuda", seed=0)
+    eng = LlamaEngine(cfg, st, 8192)
+    tok = torch.randint(0, cfg.vocab, (1, 8192), device="cuda")
+    for _ in range(steps):
+        eng.forward_backward(tok, tok)
+        eng.optimizer_step(1e-4)
+    torch.cuda.synchronize()
+
+
+if __name__ == "__main__":
+    what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
+    if what == "gemm":
+        gemm_case(sys.argv[2] if len(sys.argv) > 2 else "nt")
+    elif what == "elementwise":
+        elementwise_case()
+    elif what == "attn":
+        attn_case()
+    elif what == "step":
+        step_case()
+    K.check_status()
+    print("ok", what)
