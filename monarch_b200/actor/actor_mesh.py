@@ -1,0 +1,655 @@
+"""Actors, endpoints, actor meshes, ports and value meshes.
+
+Parity: python/monarch/_src/actor/actor_mesh.py (Actor, ActorMesh, _Actor.handle dispatch,
+Port/PortReceiver/Channel, ValueMesh, Accumulator, ActorError, context()),
+python/monarch/_src/actor/endpoint.py (adverbs call / call_one / choose / stream /
+broadcast / rref, ``@endpoint``), monarch_hyperactor/src/actor.rs (PythonActor bridge,
+PythonMessage kinds).
+
+Every message to an actor mesh -- including single-actor sends -- goes through the native
+cast tree (``_native.cast``), so casts and sends from one sender stay in FIFO order.
+Replies go straight to the caller's port.
+"""
+from __future__ import annotations
+
+import asyncio
+import contextvars
+import functools
+import inspect
+import json
+import random
+import threading
+import time
+import traceback
+from typing import (Any, Callable, Dict, Generic, Iterator, List, Optional, Tuple, Type,
+                    TypeVar)
+
+from .. import _native as N
+from .future import Future
+from .pickle import flatten, unflatten
+from .shape import Extent, MeshTrait, Point, Shape
+
+R = TypeVar("R")
+T = TypeVar("T")
+
+
+# ----------------------------------------------------------------------------- errors --
+class ActorError(Exception):
+    """An endpoint raised; carries the remote exception and its formatted traceback."""
+
+    def __init__(self, exception: BaseException, message: str = "A remote actor call has failed.",
+                 frames: Optional[str] = None):
+        self.exception = exception
+        self.message = message
+        self.actor_mesh_ref_frames = frames if frames is not None else "".join(
+            traceback.format_exception(type(exception), exception, exception.__traceback__))
+        super().__init__(str(self))
+
+    def __str__(self) -> str:
+        return (f"{self.message}\n Traceback of where the remote call failed "
+                f"(most recent call last):\n{self.actor_mesh_ref_frames}")
+
+    def __reduce__(self):
+        exc = self.exception
+        try:
+            import cloudpickle
+            cloudpickle.dumps(exc)
+        except Exception:  # unpicklable exception objects degrade to their text
+            exc = RuntimeError(f"{type(self.exception).__name__}: {self.exception}")
+        return (ActorError, (exc, self.message, self.actor_mesh_ref_frames))
+
+
+class SupervisionError(RuntimeError):
+    """The actor mesh (or the procs under it) failed; raised on pending and later calls."""
+
+
+# ---------------------------------------------------------------------------- context --
+class ActorInstance:
+    """What ``context().actor_instance`` exposes."""
+
+    def __init__(self, native: "N.Instance", proc_mesh=None, rank_point: Optional[Point] = None):
+        self._native = native
+        self.proc_mesh = proc_mesh
+        self._rank_point = rank_point
+
+    @property
+    def actor_id(self) -> str:
+        return self._native.actor_id
+
+    @property
+    def proc_id(self) -> str:
+        return self._native.proc_id
+
+    @property
+    def rank(self) -> Point:
+        return self._rank_point if self._rank_point is not None else Point(0, Extent([], []))
+
+    @property
+    def proc(self):
+        return self._native.proc
+
+    @property
+    def name(self) -> str:
+        return self._native.name
+
+
+class Context:
+    def __init__(self, actor_instance: ActorInstance, message_rank: Point):
+        self.actor_instance = actor_instance
+        self.message_rank = message_rank
+
+    @staticmethod
+    def _root() -> "Context":
+        return _root_context()
+
+
+_context: contextvars.ContextVar[Optional[Context]] = contextvars.ContextVar("mb_ctx", default=None)
+_tls = threading.local()
+_root_lock = threading.Lock()
+_root_ctx: Optional[Context] = None
+
+
+def _root_context() -> Context:
+    global _root_ctx
+    with _root_lock:
+        if _root_ctx is None:
+            inst = N.client_proc().attach("root_client")
+            _root_ctx = Context(ActorInstance(inst), Point(0, Extent([], [])))
+        return _root_ctx
+
+
+def context() -> Context:
+    """The current actor's context, or the root client's outside any actor."""
+    c = getattr(_tls, "ctx", None)
+    if c is not None:
+        return c
+    c = _context.get()
+    return c if c is not None else _root_context()
+
+
+def current_rank() -> Point:
+    return context().message_rank
+
+
+def current_size() -> Dict[str, int]:
+    r = context().message_rank
+    return dict(zip(r.extent.labels, r.extent.sizes))
+
+
+def current_actor_name() -> str:
+    return context().actor_instance.actor_id
+
+
+# ------------------------------------------------------------------------------ ports --
+_KIND_RESULT = "result"
+_KIND_EXCEPTION = "exception"
+
+
+class Port(Generic[R]):
+    """Send side of a port; picklable and usable from any actor."""
+
+    def __init__(self, port_id: str, rank: Optional[int] = None):
+        self._port_id = port_id
+        self._rank = rank
+
+    def _post(self, kind: str, obj: Any) -> None:
+        body, parts = flatten((kind, self._rank, obj))
+        context().actor_instance._native.send(self._port_id, body,
+                                              {"kind": kind, "no_return": "1"}, parts)
+
+    def send(self, obj: R) -> None:
+        self._post(_KIND_RESULT, obj)
+
+    def exception(self, obj: BaseException) -> None:
+        if not isinstance(obj, ActorError):
+            obj = ActorError(obj)
+        self._post(_KIND_EXCEPTION, obj)
+
+    def __reduce__(self):
+        return (Port, (self._port_id, self._rank))
+
+
+class DroppingPort:
+    """Used when the caller did not ask for a response: results vanish, exceptions crash
+    the actor (and reach its supervisor)."""
+
+    def send(self, obj: Any) -> None:
+        pass
+
+    def exception(self, obj: BaseException) -> None:
+        raise obj if not isinstance(obj, ActorError) else obj.exception
+
+
+class _Health:
+    """Failure state of one proc mesh, shared by its actor meshes."""
+
+    def __init__(self):
+        self.lock = threading.Lock()
+        self.mesh_error: Optional[str] = None
+        self.actor_errors: Dict[str, str] = {}
+        self.stopped = False
+
+    def error_for(self, actor_name: str) -> Optional[str]:
+        with self.lock:
+            if actor_name in self.actor_errors:
+                return self.actor_errors[actor_name]
+            return self.mesh_error
+
+
+def _recv_checked(receiver, health: Optional[_Health], actor_name: str,
+                  deadline: Optional[float]):
+    """Wait for the next envelope, waking regularly to notice supervision failures."""
+    while True:
+        env = receiver.recv(50)
+        if env is not None:
+            return env
+        if health is not None:
+            err = health.error_for(actor_name)
+            if err is not None:
+                raise SupervisionError(f"actor mesh '{actor_name}' is unhealthy: {err}")
+        if deadline is not None and time.monotonic() > deadline:
+            raise TimeoutError("timed out waiting for a reply")
+
+
+class PortReceiver(Generic[R]):
+    def __init__(self, native_receiver, port_id: str, instance, health: Optional[_Health] = None,
+                 actor_name: str = ""):
+        self._rx = native_receiver
+        self._port_id = port_id
+        self._instance = instance
+        self._health = health
+        self._actor_name = actor_name
+
+    def _next(self, timeout: Optional[float]) -> Tuple[Optional[int], Any]:
+        deadline = None if timeout is None else time.monotonic() + timeout
+        env = _recv_checked(self._rx, self._health, self._actor_name, deadline)
+        kind, rank, obj = unflatten(env.data, env.parts)
+        if kind == _KIND_EXCEPTION:
+            raise obj
+        return rank, obj
+
+    def recv(self) -> Future[R]:
+        return Future(lambda timeout: self._next(timeout)[1])
+
+    def ranked(self) -> "RankedPortReceiver[R]":
+        return RankedPortReceiver(self)
+
+    def close(self) -> None:
+        self._instance.close_port(self._port_id)
+
+
+class RankedPortReceiver(Generic[R]):
+    def __init__(self, inner: PortReceiver):
+        self._inner = inner
+
+    def recv(self) -> Future[Tuple[int, R]]:
+        return Future(lambda timeout: self._inner._next(timeout))
+
+
+class Channel(Generic[R]):
+    @staticmethod
+    def open(once: bool = False, _health=None, _actor_name="") -> Tuple[Port, PortReceiver]:
+        inst = context().actor_instance._native
+        port_id, rx = inst.open_port(once)
+        return Port(port_id), PortReceiver(rx, port_id, inst, _health, _actor_name)
+
+
+# ------------------------------------------------------------------------- value mesh --
+class ValueMesh(MeshTrait, Generic[R]):
+    """The per-actor results of a ``call``, laid out like the mesh that was called."""
+
+    def __init__(self, shape: Shape, values: List[R]):
+        self._shape_ = shape
+        self._values = values
+
+    @property
+    def _ndslice(self):
+        return self._shape_.ndslice
+
+    @property
+    def _labels(self):
+        return tuple(self._shape_.labels)
+
+    def _new_with_shape(self, shape: Shape) -> "ValueMesh[R]":
+        base = self._shape_.ndslice
+        return ValueMesh(shape_normalised(shape), [self._values[base.index(r)] for r in
+                                                   shape.ndslice.ranks()])
+
+    def item(self, **kwargs) -> R:
+        coords = [kwargs[l] for l in self._labels]
+        if len(kwargs) != len(self._labels):
+            raise KeyError(f"expected coordinates for {self._labels}, got {tuple(kwargs)}")
+        sl = self._shape_.ndslice
+        return self._values[sl.index(sl.nditem(coords))]
+
+    def items(self) -> Iterator[Tuple[Point, R]]:
+        ext = self.extent
+        for i, v in enumerate(self._values):
+            yield Point(i, ext), v
+
+    def values(self) -> List[R]:
+        return list(self._values)
+
+    def __iter__(self):
+        return self.items()
+
+    def __len__(self) -> int:
+        return len(self._values)
+
+    def __repr__(self) -> str:
+        return f"ValueMesh({self.extent}, {self._values!r})"
+
+
+def shape_normalised(shape: Shape) -> Shape:
+    """Same labels/sizes, dense row-major ranks 0..n-1 (a ValueMesh owns its values)."""
+    return Shape(shape.labels, N.Slice.new_row_major(shape.ndslice.sizes))
+
+
+# -------------------------------------------------------------------------- endpoints --
+class EndpointProperty:
+    """What ``@endpoint`` leaves on the class: resolved to an :class:`Endpoint` when read
+    from an :class:`ActorMesh`, to the plain bound method when read from the actor."""
+
+    def __init__(self, fn: Callable, propagate=None, explicit_response_port: bool = False):
+        self._fn = fn
+        self._propagate = propagate
+        self._explicit_response_port = explicit_response_port
+        functools.update_wrapper(self, fn)
+
+    def __set_name__(self, owner, name):
+        self._name = name
+
+    def __get__(self, obj, objtype=None):
+        if obj is None:
+            return self
+        return functools.partial(self._fn, obj)
+
+    def __call__(self, *a, **kw):  # pragma: no cover - guidance only
+        raise RuntimeError("an endpoint is invoked through an actor mesh: "
+                           "mesh.name.call(...), .call_one(...), .choose(...), .broadcast(...)")
+
+
+def endpoint(fn: Optional[Callable] = None, *, propagate=None,
+             explicit_response_port: bool = False):
+    """Mark a method of an :class:`Actor` as remotely callable."""
+    if fn is None:
+        return lambda f: EndpointProperty(f, propagate, explicit_response_port)
+    return EndpointProperty(fn, propagate, explicit_response_port)
+
+
+class Endpoint(Generic[R]):
+    def __init__(self, mesh: "ActorMesh", name: str, fn: Optional[Callable],
+                 explicit_response_port: bool = False, propagate=None):
+        self._mesh = mesh
+        self._name = name
+        self._fn = fn
+        self._explicit = explicit_response_port
+        self._propagate = propagate
+
+    # -- plumbing ---------------------------------------------------------------------
+    def _check_signature(self, args, kwargs) -> None:
+        if self._fn is None:
+            return
+        sig = inspect.signature(self._fn)
+        extra = [None] * (2 if self._explicit else 1)  # self (+ port)
+        try:
+            sig.bind(*extra, *args, **kwargs)
+        except TypeError as e:
+            raise TypeError(f"{self._mesh._class_name}.{self._name}: {e}") from None
+
+    def _send(self, args, kwargs, port: Optional[Port], ranks: Optional[List[int]] = None) -> None:
+        self._check_signature(args, kwargs)
+        self._mesh._cast(("call", self._name, args, kwargs, port), ranks)
+
+    def _open(self, once: bool = False) -> Tuple[Port, PortReceiver]:
+        return Channel.open(once, _health=self._mesh._health, _actor_name=self._mesh._name)
+
+    # -- adverbs ----------------------------------------------------------------------
+    def call(self, *args, **kwargs) -> Future[ValueMesh[R]]:
+        self._mesh._raise_if_unhealthy()
+        port, rx = self._open()
+        n = len(self._mesh)
+        self._send(args, kwargs, port)
+        shape = shape_normalised(self._mesh._shape)
+
+        def wait(timeout: Optional[float]) -> ValueMesh[R]:
+            deadline = None if timeout is None else time.monotonic() + timeout
+            out: List[Any] = [None] * n
+            try:
+                for _ in range(n):
+                    left = None if deadline is None else max(deadline - time.monotonic(), 0.0)
+                    rank, v = rx._next(left)
+                    out[rank] = v
+            finally:
+                rx.close()
+            return ValueMesh(shape, out)
+
+        return Future(wait)
+
+    def call_one(self, *args, **kwargs) -> Future[R]:
+        if len(self._mesh) != 1:
+            raise ValueError(f"Can only use 'call_one' on a single Actor but this actor has shape "
+                             f"{self._mesh._shape}")
+        self._mesh._raise_if_unhealthy()
+        port, rx = self._open(once=True)
+        self._send(args, kwargs, port)
+        return Future(lambda timeout: rx._next(timeout)[1])
+
+    def choose(self, *args, **kwargs) -> Future[R]:
+        """Load-balanced call to one actor of the mesh, picked by a deterministic PRNG."""
+        self._mesh._raise_if_unhealthy()
+        port, rx = self._open(once=True)
+        ranks = self._mesh._shape.ndslice.ranks()
+        self._send(args, kwargs, port, [_choose_rng.choice(ranks)])
+        return Future(lambda timeout: rx._next(timeout)[1])
+
+    def stream(self, *args, **kwargs) -> Iterator[Future[R]]:
+        self._mesh._raise_if_unhealthy()
+        port, rx = self._open()
+        n = len(self._mesh)
+        self._send(args, kwargs, port)
+        for _ in range(n):
+            yield Future(lambda timeout: rx._next(timeout)[1])
+
+    def broadcast(self, *args, **kwargs) -> None:
+        """Fire and forget; an exception in the endpoint crashes the actor."""
+        self._mesh._raise_if_unhealthy()
+        self._send(args, kwargs, None)
+
+    def rref(self, *args, **kwargs):
+        from ..tensor_engine.actor_bridge import endpoint_rref
+        return endpoint_rref(self, args, kwargs)
+
+    def _port_call(self, args, kwargs, port: Port, ranks=None) -> None:
+        """``send(endpoint, args, kwargs, port, selection)``: replies go to ``port``."""
+        self._send(args, kwargs, port, ranks)
+
+
+_choose_rng = random.Random(4)
+
+
+def send(endpoint_: Endpoint, args: Tuple, kwargs: Dict, port: Optional[Port] = None,
+         selection: str = "all") -> None:
+    """Low-level send: deliver to all actors (``"all"``) or one (``"choose"``)."""
+    ranks = None
+    if selection == "choose":
+        ranks = [_choose_rng.choice(endpoint_._mesh._shape.ndslice.ranks())]
+    elif selection != "all":
+        raise ValueError(f"invalid selection: {selection}")
+    endpoint_._send(args, kwargs, port, ranks)
+
+
+def as_endpoint(bound_method, *, propagate=None, explicit_response_port=False) -> Endpoint:
+    """Treat ``mesh.method`` of an undecorated method as an endpoint."""
+    if isinstance(bound_method, Endpoint):
+        return bound_method
+    if isinstance(bound_method, _NotAnEndpoint):
+        return Endpoint(bound_method.mesh, bound_method.name, bound_method.fn,
+                        explicit_response_port, propagate)
+    raise ValueError("as_endpoint expects an attribute read from an actor mesh")
+
+
+class _NotAnEndpoint:
+    def __init__(self, mesh, name, fn):
+        self.mesh, self.name, self.fn = mesh, name, fn
+
+    def _fail(self, *a, **k):
+        raise RuntimeError(
+            f"Actor {self.mesh._class_name}.{self.name} is not annotated as an endpoint. To call "
+            f"it as one, add a @endpoint decorator to it, or wrap it using "
+            f"as_endpoint(obj.{self.name})")
+
+    call = call_one = choose = stream = broadcast = rref = __call__ = _fail
+
+
+class Accumulator(Generic[T, R]):
+    """Fold the per-actor results of an endpoint: ``Accumulator(ep, identity,
+    combine).accumulate(*args)`` -> Future of the combined value."""
+
+    def __init__(self, endpoint_: Endpoint, identity: T, combine: Callable[[T, R], T]):
+        self._endpoint = endpoint_
+        self._identity = identity
+        self._combine = combine
+
+    def accumulate(self, *args, **kwargs) -> Future[T]:
+        gen = self._endpoint.stream(*args, **kwargs)
+
+        def wait(timeout):
+            acc = self._identity
+            deadline = None if timeout is None else time.monotonic() + timeout
+            for f in gen:
+                left = None if deadline is None else max(deadline - time.monotonic(), 0.0)
+                acc = self._combine(acc, f.get(left))
+            return acc
+
+        return Future(wait)
+
+
+# ------------------------------------------------------------------------------ actor --
+class Actor:
+    """Base class of user actors.  Methods decorated with :func:`endpoint` are callable
+    through the :class:`ActorMesh` returned by ``ProcMesh.spawn``."""
+
+    def _handle_undeliverable_message(self, envelope, reason: str) -> bool:
+        """Return True to swallow a returned message; the default fails the actor."""
+        return False
+
+
+class ActorMesh(MeshTrait, Generic[T]):
+    def __init__(self, cls: Type[T], name: str, world: str, shape: Shape, proc_mesh=None,
+                 health: Optional[_Health] = None):
+        self._class = cls
+        self._class_name = getattr(cls, "__name__", str(cls))
+        self._name = name
+        self._world = world
+        self._shape_ = shape
+        self._proc_mesh = proc_mesh
+        self._health = health
+
+    # MeshTrait ------------------------------------------------------------------------
+    @property
+    def _ndslice(self):
+        return self._shape_.ndslice
+
+    @property
+    def _labels(self):
+        return tuple(self._shape_.labels)
+
+    @property
+    def _shape(self) -> Shape:
+        return self._shape_
+
+    def _new_with_shape(self, shape: Shape) -> "ActorMesh[T]":
+        return ActorMesh(self._class, self._name, self._world, shape, self._proc_mesh,
+                         self._health)
+
+    # endpoints ------------------------------------------------------------------------
+    def __getattr__(self, name: str):
+        if name.startswith("__") or name in ("_class", "_shape_", "_name"):
+            raise AttributeError(name)
+        attr = getattr(self._class, name, None)
+        if isinstance(attr, EndpointProperty):
+            return Endpoint(self, name, attr._fn, attr._explicit_response_port, attr._propagate)
+        if attr is None:
+            raise AttributeError(f"{self._class_name} has no attribute {name!r}")
+        return _NotAnEndpoint(self, name, attr if callable(attr) else None)
+
+    def _raise_if_unhealthy(self) -> None:
+        if self._health is not None:
+            err = self._health.error_for(self._name)
+            if err is not None:
+                raise SupervisionError(f"actor mesh '{self._name}' is unhealthy: {err}")
+
+    def _cast(self, message: Tuple, ranks: Optional[List[int]] = None) -> None:
+        body, parts = flatten(message)
+        sl = self._shape_.ndslice
+        sel = N.Selection.all() if ranks is None else N.Selection.of_ranks(sl, ranks)
+        headers = {"cast_shape": json.dumps([self._shape_.labels, list(sl.sizes)])}
+        inst = context().actor_instance._native
+        N.cast(inst, self._world, self._name, sl, sel, body, headers, parts, sl)
+
+    def stop(self) -> Future[None]:
+        pm = self._proc_mesh
+        if pm is None:
+            raise NotImplementedError("stopping an actor mesh needs its owning proc mesh")
+        return Future(lambda timeout: pm._native.stop_actor(self._name,
+                                                            int((timeout or 5) * 1000)))
+
+    def __reduce__(self):
+        return (ActorMesh, (self._class, self._name, self._world, self._shape_))
+
+    def __repr__(self) -> str:
+        return f"ActorMesh({self._class_name}, '{self._name}', {self._shape_})"
+
+
+# -------------------------------------------------------------- worker-side dispatch ----
+class _ActorState:
+    """Per-actor state on the hosting proc: the user object, its event loop, dispatch."""
+
+    def __init__(self, proc, name: str, params: bytes):
+        self.proc = proc
+        self.name = name
+        (self.cls, self.args, self.kwargs, self.meta) = unflatten(params, [])
+        self.obj: Any = None
+        self.loop: Optional[asyncio.AbstractEventLoop] = None
+        self.instance_info: Optional[ActorInstance] = None
+
+    def _ensure(self, instance) -> None:
+        if self.instance_info is None:
+            labels, sizes = self.meta["labels"], self.meta["sizes"]
+            ext = Extent(labels, sizes)
+            rank_in_mesh = self.meta["ranks"].index(instance.rank)
+            self.instance_info = ActorInstance(instance, proc_mesh=self.meta.get("proc_mesh_ref"),
+                                               rank_point=Point(rank_in_mesh, ext))
+        if self.obj is None:
+            ctx = Context(self.instance_info, self.instance_info.rank)
+            _tls.ctx = ctx
+            self.obj = self.cls(*self.args, **self.kwargs)
+
+    def _run(self, fn, args, kwargs):
+        r = fn(*args, **kwargs)
+        if inspect.iscoroutine(r):
+            if self.loop is None:
+                self.loop = asyncio.new_event_loop()
+            asyncio.set_event_loop(self.loop)
+            r = self.loop.run_until_complete(r)
+        return r
+
+    def on_message(self, instance, env) -> None:
+        t0 = time.perf_counter()
+        msg = unflatten(env.data, env.parts, getattr(self, "_extra_load", None))
+        kind = msg[0]
+        cast_rank = int(env.headers.get("cast_rank", "0"))
+        shape_hdr = env.headers.get("cast_shape")
+        if shape_hdr:
+            labels, sizes = json.loads(shape_hdr)
+            point = Point(cast_rank, Extent(labels, sizes))
+        else:
+            point = Point(0, Extent([], []))
+        try:
+            self._ensure(instance)
+        except BaseException:
+            _tls.ctx = None
+            raise
+        _tls.ctx = Context(self.instance_info, point)
+        try:
+            if kind == "init":
+                return
+            _, method, args, kwargs, port = msg
+            if port is not None:
+                port = Port(port._port_id, cast_rank)
+            response = port if port is not None else DroppingPort()
+            prop = getattr(self.cls, method, None)
+            explicit = isinstance(prop, EndpointProperty) and prop._explicit_response_port
+            fn = prop._fn if isinstance(prop, EndpointProperty) else getattr(self.cls, method)
+            try:
+                if explicit:
+                    self._run(fn, (self.obj, response, *args), kwargs)
+                else:
+                    response.send(self._run(fn, (self.obj, *args), kwargs))
+            except Exception as e:  # noqa: BLE001
+                response.exception(ActorError(e))
+            N.metrics_counter_add("py_messages_handled", 1)
+        finally:
+            _tls.ctx = None
+            N.metrics_histogram_record("py_endpoint_us", (time.perf_counter() - t0) * 1e6)
+
+    def on_undeliverable(self, instance, env, reason: str) -> bool:
+        if self.obj is None:
+            return False
+        return bool(self.obj._handle_undeliverable_message(env, reason))
+
+    def on_stop(self, instance) -> None:
+        if self.loop is not None:
+            try:
+                self.loop.close()
+            except Exception:  # noqa: BLE001
+                pass
+
+
+def _python_actor_factory(proc, name: str, params: bytes):
+    st = _ActorState(proc, name, params)
+    return (st.on_message, None, st.on_undeliverable, st.on_stop)
+
+
+N.register_python_actor_type("python", _python_actor_factory)

@@ -1,0 +1,84 @@
+"""Message serialisation: cloudpickle with large tensors carried out of band.
+
+Parity: python/monarch/_src/actor/pickle.py (flatten/unflatten; tensors are loaded on the
+CPU).  The pickled body travels as the envelope's data, tensor payloads as separate
+frame parts that the channel writes with scatter-gather IO (no copy into the body).
+"""
+from __future__ import annotations
+
+import io
+import pickle
+import sys
+from typing import Any, Callable, List, Optional, Tuple
+
+import cloudpickle
+
+_OOB_MIN_BYTES = 4096
+
+
+def _torch():
+    return sys.modules.get("torch")
+
+
+class _Pickler(cloudpickle.Pickler):
+    def __init__(self, f, parts: List[bytes], extra_pid: Optional[Callable[[Any], Any]]):
+        super().__init__(f, protocol=pickle.HIGHEST_PROTOCOL)
+        self._parts = parts
+        self._extra = extra_pid
+
+    def persistent_id(self, obj):
+        if self._extra is not None:
+            r = self._extra(obj)
+            if r is not None:
+                return ("x", r)
+        torch = _torch()
+        if torch is not None and type(obj) is torch.Tensor and obj.layout == torch.strided \
+                and not getattr(obj, "is_meta", False):
+            t = obj.detach()
+            if t.device.type != "cpu":
+                t = t.cpu()
+            t = t.contiguous()
+            nbytes = t.numel() * t.element_size()
+            if nbytes >= _OOB_MIN_BYTES:
+                raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if nbytes else b""
+                self._parts.append(raw)
+                return ("t", len(self._parts) - 1, str(t.dtype).split(".")[-1], tuple(t.shape),
+                        bool(obj.requires_grad))
+        return None
+
+
+class _Unpickler(pickle.Unpickler):
+    def __init__(self, f, parts: List[bytes], extra_load: Optional[Callable[[Any], Any]]):
+        super().__init__(f)
+        self._parts = parts
+        self._extra = extra_load
+
+    def persistent_load(self, pid):
+        if pid[0] == "x":
+            if self._extra is None:
+                raise pickle.UnpicklingError("message carries references this context cannot resolve")
+            return self._extra(pid[1])
+        if pid[0] == "t":
+            import torch
+            _, idx, dtype, shape, req = pid
+            raw = self._parts[idx]
+            dt = getattr(torch, dtype)
+            if len(raw) == 0:
+                t = torch.empty(shape, dtype=dt)
+            else:
+                t = torch.frombuffer(bytearray(raw), dtype=torch.uint8).view(dt).reshape(shape)
+            return t.requires_grad_(req) if req else t
+        raise pickle.UnpicklingError(f"unknown persistent id {pid!r}")
+
+
+def flatten(obj: Any, extra_pid: Optional[Callable[[Any], Any]] = None) -> Tuple[bytes, List[bytes]]:
+    """Serialise ``obj``; returns (body, out-of-band parts)."""
+    parts: List[bytes] = []
+    f = io.BytesIO()
+    _Pickler(f, parts, extra_pid).dump(obj)
+    return f.getvalue(), parts
+
+
+def unflatten(body: bytes, parts: List[bytes],
+              extra_load: Optional[Callable[[Any], Any]] = None) -> Any:
+    return _Unpickler(io.BytesIO(body), list(parts), extra_load).load()

@@ -285,7 +285,7 @@ Sel Selection::t() { static Sel s = mk(True_); return s; }
 Sel Selection::all(Sel inner) { return mk(All, std::move(inner)); }
 Sel Selection::first(Sel inner) { return mk(First, std::move(inner)); }
 Sel Selection::any(Sel inner) { return mk(Any, std::move(inner)); }
-Sel Selection::range(Range r, Sel inner) {
+Sel Selection::range_of(Range r, Sel inner) {
   auto s = std::make_shared<Selection>();
   s->kind = RangeK;
   s->range = r;
@@ -408,7 +408,7 @@ struct Parser {
         r.begin = *b;
         r.end = *b + 1;
       }
-      w = [r](Sel in) { return Selection::range(r, in); };
+      w = [r](Sel in) { return Selection::range_of(r, in); };
     }
     if (eat(',')) return w(chain());
     return w(Selection::t());
@@ -429,7 +429,7 @@ Sel Selection::of_ranks(const Slice& slice, const std::vector<size_t>& ranks) {
   for (size_t r : ranks) {
     auto c = slice.coordinates(r);
     Sel s = t();
-    for (size_t d = c.size(); d-- > 0;) s = range(Range{c[d], c[d] + 1, 1}, s);
+    for (size_t d = c.size(); d-- > 0;) s = range_of(Range{c[d], c[d] + 1, 1}, s);
     acc = union_(acc, s);
   }
   return acc;

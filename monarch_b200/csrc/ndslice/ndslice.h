@@ -122,7 +122,7 @@ struct Selection {
   static Sel all(Sel inner);
   static Sel first(Sel inner);
   static Sel any(Sel inner);
-  static Sel range(Range r, Sel inner);
+  static Sel range_of(Range r, Sel inner);
   static Sel label(std::vector<std::string> l, Sel inner);
   static Sel intersection(Sel x, Sel y);
   static Sel union_(Sel x, Sel y);
