@@ -27,7 +27,9 @@ CSRC = ROOT / "csrc"
 OBJ = ROOT / "build"
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-CXX = os.environ.get("CXX", "g++")
+# The system compiler, not $CXX: a toolchain that links its own libstdc++ statically
+# clashes with the libstdc++ that numpy/torch have already loaded into the process.
+CXX = os.environ.get("MB200_CXX", "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++")
 
 CUDA_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -362,6 +362,22 @@ struct Parser {
     i = j;
     return v;
   }
+  // Replace the terminal `true` leaves of `s` by `cont`.
+  static Sel append(const Sel& s, const Sel& cont) {
+    switch (s->kind) {
+      case Selection::True_: return cont;
+      case Selection::False_: return s;
+      case Selection::All: return Selection::all(append(s->a, cont));
+      case Selection::First: return Selection::first(append(s->a, cont));
+      case Selection::Any: return Selection::any(append(s->a, cont));
+      case Selection::RangeK: return Selection::range_of(s->range, append(s->a, cont));
+      case Selection::Label: return Selection::label(s->labels, append(s->a, cont));
+      case Selection::Union: return Selection::union_(append(s->a, cont), append(s->b, cont));
+      case Selection::Intersection:
+        return Selection::intersection(append(s->a, cont), append(s->b, cont));
+    }
+    return s;
+  }
   // Applies `inner` to a parsed dimension atom.
   using Wrap = std::function<Sel(Sel)>;
   Sel expr() {
@@ -379,6 +395,8 @@ struct Parser {
     if (eat('(')) {
       Sel e = expr();
       if (!eat(')')) fail("expected ')'");
+      // "(a|b),rest": the continuation applies below every branch of the group
+      if (eat(',')) return append(e, chain());
       return e;
     }
     Wrap w;

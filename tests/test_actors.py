@@ -1,0 +1,254 @@
+"""Actor API semantics: endpoints and adverbs, value meshes, ports, ordering, context.
+Modelled on python/tests/test_python_actors.py of the reference."""
+import asyncio
+import pickle
+import threading
+import time
+
+import pytest
+
+from monarch_b200.actor import (Accumulator, Actor, ActorError, Channel, Future, Point, Port,
+                                ValueMesh, as_endpoint, context, current_rank, current_size,
+                                endpoint, fake_in_process_host, get_or_spawn_controller,
+                                local_proc_mesh, send, this_host, this_proc)
+
+
+class Counter(Actor):
+    def __init__(self, v: int):
+        self.v = v
+
+    @endpoint
+    def incr(self):
+        self.v += 1
+
+    @endpoint
+    def value(self) -> int:
+        return self.v
+
+    @endpoint
+    async def value_async(self) -> int:
+        await asyncio.sleep(0)
+        return self.v
+
+    def not_an_endpoint(self):
+        return self.v * 100
+
+    @endpoint
+    def rank_info(self):
+        return (current_rank().rank, dict(current_rank()), current_size(),
+                context().actor_instance.rank.rank)
+
+
+class Indirect(Actor):
+    @endpoint
+    def call_value(self, c: Counter):
+        return c.value.choose().get()
+
+    @endpoint
+    def fan_in(self, c):
+        return sum(v for _, v in c.value.call().get())
+
+
+@pytest.fixture(scope="module")
+def pm():
+    m = local_proc_mesh(gpus=4)
+    yield m
+    m.stop().get()
+
+
+def test_call_broadcast_choose_call_one(pm):
+    c = pm.spawn("counter_a", Counter, 3)
+    c.incr.broadcast()
+    c.incr.broadcast()
+    vm = c.value.call().get()
+    assert isinstance(vm, ValueMesh) and vm.values() == [5, 5, 5, 5]
+    assert c.value.choose().get() == 5
+    assert c.slice(gpus=2).value.call_one().get() == 5
+    with pytest.raises(ValueError, match="call_one"):
+        c.value.call_one()
+    assert c.value_async.call().get().values() == [5] * 4
+    assert [f.get() for f in c.value.stream()] == [5] * 4
+
+
+def test_value_mesh_items_and_points(pm):
+    c = pm.spawn("counter_b", Counter, 1)
+    vm = c.rank_info.call().get()
+    for point, (cast_rank, coords, size, own_rank) in vm.items():
+        assert isinstance(point, Point)
+        assert point.rank == cast_rank == own_rank
+        assert coords == dict(point) and size == {"hosts": 1, "gpus": 4}
+    assert vm.item(hosts=0, gpus=3)[0] == 3
+    assert str(Point(1, vm.extent)) == "{'hosts': 0/1, 'gpus': 1/4}"
+    sub = c.slice(gpus=slice(2, 4)).rank_info.call().get()
+    # the rank inside a cast is relative to the slice that was called
+    assert [v[0] for v in sub.values()] == [0, 1]
+    assert [v[3] for v in sub.values()] == [2, 3]
+    assert [v[2] for v in sub.values()] == [{"hosts": 1, "gpus": 2}] * 2
+
+
+def test_sends_are_ordered_per_sender(pm):
+    c = pm.spawn("counter_c", Counter, 0)
+    for _ in range(100):
+        c.incr.broadcast()
+    assert c.value.call().get().values() == [100] * 4
+    one = c.slice(gpus=1)
+    for _ in range(50):
+        one.incr.broadcast()
+    c.incr.broadcast()
+    assert one.value.call_one().get() == 151
+
+
+def test_actor_refs_travel_in_messages(pm):
+    c = pm.spawn("counter_d", Counter, 7)
+    ind = pm.spawn("indirect", Indirect)
+    assert ind.call_value.call(c).get().values() == [7] * 4
+    assert ind.slice(gpus=0).fan_in.call_one(c).get() == 28
+
+
+def test_non_endpoint_attribute_and_as_endpoint(pm):
+    c = pm.spawn("counter_e", Counter, 2)
+    with pytest.raises(RuntimeError, match="not annotated as an endpoint"):
+        c.not_an_endpoint.call()
+    assert as_endpoint(c.not_an_endpoint).call().get().values() == [200] * 4
+    with pytest.raises(TypeError):
+        c.value.call(1, 2, 3)  # signature is checked at the call site
+
+
+def test_ports_and_channels(pm):
+    class Producer(Actor):
+        @endpoint
+        def produce(self, port: Port, n: int):
+            for i in range(n):
+                port.send((current_rank().rank, i))
+
+        @endpoint(explicit_response_port=True)
+        def explicit(self, port, x):
+            port.send(x * 2)
+
+    p = pm.spawn("producer", Producer)
+    port, rx = Channel.open()
+    p.produce.broadcast(port, 3)
+    got = sorted(rx.recv().get(timeout=10) for _ in range(12))
+    assert got == sorted((r, i) for r in range(4) for i in range(3))
+    assert p.explicit.call(21).get().values() == [42] * 4
+    port2, rx2 = Channel.open(once=True)
+    send(p.explicit, (5,), {}, port=port2, selection="choose")
+    assert rx2.recv().get(timeout=10) == 10
+    assert pickle.loads(pickle.dumps(port))._port_id == port._port_id
+
+
+def test_accumulator(pm):
+    c = pm.spawn("counter_f", Counter, 10)
+    acc = Accumulator(c.value, 0, lambda a, b: a + b)
+    assert acc.accumulate().get() == 40
+
+
+def test_future_timeout_and_await(pm):
+    class Slow(Actor):
+        @endpoint
+        def nap(self, s):
+            time.sleep(s)
+            return s
+
+    s = pm.spawn("slow", Slow)
+    with pytest.raises(TimeoutError):
+        s.slice(gpus=0).nap.call_one(0.5).get(timeout=0.05)
+
+    async def main():
+        return await s.slice(gpus=1).nap.call_one(0.01)
+
+    assert asyncio.run(main()) == 0.01
+    assert Future.ready(3).get() == 3
+
+
+def test_one_message_at_a_time_but_actors_run_concurrently(pm):
+    class Busy(Actor):
+        def __init__(self):
+            self.active = 0
+            self.max_active = 0
+
+        @endpoint
+        def work(self):
+            self.active += 1
+            self.max_active = max(self.max_active, self.active)
+            time.sleep(0.02)
+            self.active -= 1
+            return threading.get_ident()
+
+        @endpoint
+        def peak(self):
+            return self.max_active
+
+    b = pm.spawn("busy", Busy)
+    futs = [b.work.call() for _ in range(3)]
+    tids = [set(f.get().values()) for f in futs]
+    assert b.peak.call().get().values() == [1] * 4
+    assert len(tids[0]) == 4  # four actors, four threads
+
+
+def test_endpoint_exception_reaches_caller_only(pm):
+    class Faulty(Actor):
+        @endpoint
+        def boom(self):
+            raise ValueError("kaboom")
+
+        @endpoint
+        def ok(self):
+            return "fine"
+
+    f = pm.spawn("faulty", Faulty)
+    with pytest.raises(ActorError, match="kaboom") as ei:
+        f.boom.call().get()
+    assert isinstance(ei.value.exception, ValueError)
+    assert "boom" in ei.value.actor_mesh_ref_frames
+    assert f.ok.call().get().values() == ["fine"] * 4  # the actor survives
+
+
+def test_spawn_on_slice_and_after_stop_rejected():
+    m = fake_in_process_host().spawn_procs(per_host={"gpus": 2})
+    with pytest.raises(NotImplementedError):
+        m.slice(gpus=0).spawn("x", Counter, 0)
+    with pytest.raises(ValueError):
+        fake_in_process_host().spawn_procs(per_host={"hosts": 2})
+    m.stop().get()
+    with pytest.raises(RuntimeError, match="stopped"):
+        m.spawn("y", Counter, 0)
+
+
+def test_this_proc_and_controllers():
+    c = this_proc().spawn("tp_counter", Counter, 9)
+    assert c.value.call_one().get() == 9
+    a = get_or_spawn_controller("the_one", Counter, 5).get()
+    a.incr.broadcast()
+    b = get_or_spawn_controller("the_one", Counter, 1000).get()
+    assert b.value.call_one().get() == 6  # same singleton, constructor args of the first win
+
+
+def test_sim_mesh_cast_tree_large():
+    from monarch_b200.actor import sim_proc_mesh
+    m = sim_proc_mesh(gpus=8, hosts=4, racks=2)
+    c = m.spawn("many", Counter, 1)
+    assert len(c) == 64 and sum(c.value.call().get().values()) == 64
+    assert c.slice(racks=1, hosts=2).value.call().get().values() == [1] * 8
+    m.stop().get()
+
+
+def test_subprocess_mesh_end_to_end():
+    m = this_host().spawn_procs(per_host={"gpus": 2})
+    try:
+        c = m.spawn("counter_proc", Counter, 11)
+        c.incr.broadcast()
+        vm = c.value.call().get(timeout=30)
+        assert vm.values() == [12, 12] and vm.sizes == {"hosts": 1, "gpus": 2}
+
+        class Pid(Actor):
+            @endpoint
+            def pid(self):
+                import os
+                return os.getpid()
+
+        pids = m.spawn("pid", Pid).pid.call().get(timeout=30).values()
+        import os
+        assert len(set(pids)) == 2 and os.getpid() not in pids
+    finally:
+        m.stop().get()
