@@ -1,0 +1,409 @@
+// NVLink / NVSwitch collectives written as plain CUDA kernels over peer-mapped
+// ("symmetric") memory: every rank passes the base pointers of all ranks' buffers and the
+// kernels issue ordinary ld/st.global on peer addresses.  Each collective is fused with
+// the compute that follows it:
+//
+//   * rs_adamw      reduce-scatter of bf16 gradients (fp32 accumulation) + AdamW on the
+//                   rank's fp32 master/moment shard + bf16 cast of the updated shard
+//   * allreduce     two-shot in-place all-reduce fused with the 1/N scale and the bf16
+//                   cast (fp32 or bf16 in, bf16 out)
+//   * allgather     pull of every rank's shard into a local buffer, optionally
+//                   publishing per-chunk ready flags that a GEMM's TMA producer waits on
+//   * peer_copy     one-sided put/get between two GPUs with a completion flag
+//   * barrier       flag barrier
+//
+// Cross-rank ordering uses monotonically increasing epochs in per-rank flag arrays
+// (flags[slot * kMaxRanks + source_rank]); every wait is bounded and reports through the
+// status word instead of hanging.  No TMA, no multicast loads: peer data moves with
+// per-thread 16-byte loads and stores.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "mb200.h"
+#include "ptx.cuh"
+
+namespace mb200 {
+
+constexpr int kMaxRanks = 8;
+struct Peers {
+  void* p[kMaxRanks];
+};
+
+__device__ __forceinline__ uint32_t* flag_ptr(void* base, int slot, int src_rank) {
+  return reinterpret_cast<uint32_t*>(base) + (size_t)slot * kMaxRanks + src_rank;
+}
+
+// Publish `epoch` in slot `slot` of every rank's flag array (called by <= kMaxRanks
+// threads of one block after the data it announces has been written).
+__device__ __forceinline__ void signal_all(const Peers& flags, int world, int rank, int slot,
+                                           uint32_t epoch, int tid) {
+  if (tid < world) {
+    __threadfence_system();
+    st_release_sys(flag_ptr(flags.p[tid], slot, rank), epoch);
+  }
+}
+
+// Wait until every rank has published >= epoch in `slot` of *my* flag array.
+__device__ __forceinline__ bool wait_all(void* my_flags, int world, int slot, uint32_t epoch,
+                                         int* status) {
+  bool ok = true;
+  for (int r = 0; r < world && ok; ++r)
+    ok = flag_wait_ge<true>(flag_ptr(my_flags, slot, r), epoch, status);
+  return ok;
+}
+
+// Block-wide: thread 0 waits, everyone learns the outcome.
+__device__ __forceinline__ bool block_wait_all(void* my_flags, int world, int slot,
+                                               uint32_t epoch, int* status, int* sh_ok) {
+  if (threadIdx.x == 0) *sh_ok = wait_all(my_flags, world, slot, epoch, status) ? 1 : 0;
+  __syncthreads();
+  return *sh_ok != 0;
+}
+
+// "Last block out" notification: returns true in exactly one block (the one finishing
+// last), after all other blocks' writes are visible.
+__device__ __forceinline__ bool last_block_done(unsigned int* counter) {
+  __shared__ bool is_last;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned int prev = atomicAdd(counter, 1u);
+    is_last = (prev == gridDim.x - 1);
+    if (is_last) *counter = 0;  // ready for the next launch
+  }
+  __syncthreads();
+  return is_last;
+}
+
+__device__ __forceinline__ void acc8(float (&a)[8], uint4 u) {
+  float2 x = unpack_bf16x2(u.x), y = unpack_bf16x2(u.y), z = unpack_bf16x2(u.z),
+         w = unpack_bf16x2(u.w);
+  a[0] += x.x; a[1] += x.y; a[2] += y.x; a[3] += y.y;
+  a[4] += z.x; a[5] += z.y; a[6] += w.x; a[7] += w.y;
+}
+__device__ __forceinline__ uint4 ld_nc_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.relaxed.sys.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+
+// ------------------------------------------------------------------------ barrier --
+__global__ void barrier_kernel(Peers flags, int rank, int world, int slot, uint32_t epoch,
+                               int* status) {
+  signal_all(flags, world, rank, slot, epoch, threadIdx.x);
+  __syncthreads();
+  if (threadIdx.x == 0) wait_all(flags.p[rank], world, slot, epoch, status);
+}
+
+__global__ void wait_kernel(void* my_flags, int world, int slot, uint32_t epoch, int* status) {
+  if (threadIdx.x == 0) wait_all(my_flags, world, slot, epoch, status);
+}
+
+// ---------------------------------------------------------------------- all-gather --
+// dst[p * shard_elems + i] = src_p[i] for every rank p; 16-byte vectors of bf16.
+// If wait_epoch != 0 the kernel first waits until every rank published wait_epoch in
+// wait_slot ("my shard is up to date").  If chunk_flags != nullptr, blocks copy whole
+// chunks of `chunk_elems` and publish chunk_epoch in chunk_flags[chunk] when done.
+__global__ void __launch_bounds__(256)
+    allgather_pull_kernel(__nv_bfloat16* __restrict__ dst, Peers src, int64_t shard_elems,
+                          int rank, int world, void* my_flags, int wait_slot,
+                          uint32_t wait_epoch, uint32_t* chunk_flags, int64_t chunk_elems,
+                          uint32_t chunk_epoch, int* status) {
+  __shared__ int sh_ok;
+  if (wait_epoch) {
+    if (!block_wait_all(my_flags, world, wait_slot, wait_epoch, status, &sh_ok)) return;
+  }
+  if (chunk_flags == nullptr) {
+    const int64_t vec_per_shard = shard_elems >> 3;
+    const int64_t total = vec_per_shard * world;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+      const int k = (int)(i / vec_per_shard);
+      const int p = (rank + k) % world;  // start with the local shard, stagger peers
+      const int64_t v = i - (int64_t)k * vec_per_shard;
+      const uint4 val = ld_nc_v4(reinterpret_cast<const uint4*>(src.p[p]) + v);
+      reinterpret_cast<uint4*>(dst + (int64_t)p * shard_elems)[v] = val;
+    }
+    return;
+  }
+  // chunked mode: chunk c covers dst elements [c*chunk_elems, (c+1)*chunk_elems)
+  const int64_t total_elems = shard_elems * world;
+  const int64_t n_chunks = (total_elems + chunk_elems - 1) / chunk_elems;
+  const int64_t my_first = ((int64_t)rank * shard_elems) / chunk_elems;
+  for (int64_t cc = blockIdx.x; cc < n_chunks; cc += gridDim.x) {
+    const int64_t c = (my_first + cc) % n_chunks;  // local chunks first
+    const int64_t e0 = c * chunk_elems;
+    int64_t e1 = e0 + chunk_elems;
+    if (e1 > total_elems) e1 = total_elems;
+    for (int64_t e = e0 + (int64_t)threadIdx.x * 8; e < e1; e += (int64_t)blockDim.x * 8) {
+      const int p = (int)(e / shard_elems);
+      const int64_t off = e - (int64_t)p * shard_elems;
+      const uint4 val = ld_nc_v4(reinterpret_cast<const __nv_bfloat16*>(src.p[p]) + off);
+      *reinterpret_cast<uint4*>(dst + e) = val;
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) st_release_gpu(chunk_flags + c, chunk_epoch);
+  }
+}
+
+// -------------------------------------------------------- reduce-scatter + AdamW ----
+// grads.p[r] points at rank r's gradient buffer for this unit (bf16, `unit_elems` long,
+// unit_elems = world * shard_elems).  This rank owns elements [rank*shard, (rank+1)*shard).
+__global__ void __launch_bounds__(256)
+    rs_adamw_kernel(Peers grads, Peers flags, float* __restrict__ master, float* __restrict__ m,
+                    float* __restrict__ v, __nv_bfloat16* __restrict__ param_shard,
+                    int64_t shard_elems, int rank, int world, int grad_slot, int param_slot,
+                    uint32_t epoch, float lr, float beta1, float beta2, float eps, float wd,
+                    float inv_bc1, float inv_sqrt_bc2, float grad_scale, unsigned int* counter,
+                    int* status) {
+  __shared__ int sh_ok;
+  // My gradients for this unit are complete (stream order): tell everyone, then wait for
+  // everyone else's.
+  if (blockIdx.x == 0) signal_all(flags, world, rank, grad_slot, epoch, threadIdx.x);
+  if (!block_wait_all(flags.p[rank], world, grad_slot, epoch, status, &sh_ok)) return;
+
+  const int64_t base = (int64_t)rank * shard_elems;
+  const int64_t nvec = shard_elems >> 3;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    uint4 raw[kMaxRanks];
+#pragma unroll
+    for (int k = 0; k < kMaxRanks; ++k) {
+      if (k < world) {
+        const int p = (rank + k) % world;
+        raw[k] = ld_nc_v4(reinterpret_cast<const __nv_bfloat16*>(grads.p[p]) + base + i * 8);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < kMaxRanks; ++k)
+      if (k < world) acc8(g, raw[k]);
+    float4 p0 = reinterpret_cast<float4*>(master)[i * 2], p1 = reinterpret_cast<float4*>(master)[i * 2 + 1];
+    float4 m0 = reinterpret_cast<float4*>(m)[i * 2], m1 = reinterpret_cast<float4*>(m)[i * 2 + 1];
+    float4 v0 = reinterpret_cast<float4*>(v)[i * 2], v1 = reinterpret_cast<float4*>(v)[i * 2 + 1];
+    float pv[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+    float mv[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+    float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float gg = g[k] * grad_scale;
+      pv[k] *= (1.f - lr * wd);
+      mv[k] = beta1 * mv[k] + (1.f - beta1) * gg;
+      vv[k] = beta2 * vv[k] + (1.f - beta2) * gg * gg;
+      pv[k] -= lr * inv_bc1 * mv[k] / (sqrtf(vv[k]) * inv_sqrt_bc2 + eps);
+    }
+    reinterpret_cast<float4*>(master)[i * 2] = make_float4(pv[0], pv[1], pv[2], pv[3]);
+    reinterpret_cast<float4*>(master)[i * 2 + 1] = make_float4(pv[4], pv[5], pv[6], pv[7]);
+    reinterpret_cast<float4*>(m)[i * 2] = make_float4(mv[0], mv[1], mv[2], mv[3]);
+    reinterpret_cast<float4*>(m)[i * 2 + 1] = make_float4(mv[4], mv[5], mv[6], mv[7]);
+    reinterpret_cast<float4*>(v)[i * 2] = make_float4(vv[0], vv[1], vv[2], vv[3]);
+    reinterpret_cast<float4*>(v)[i * 2 + 1] = make_float4(vv[4], vv[5], vv[6], vv[7]);
+    uint4 o;
+    o.x = pack_bf16x2(pv[0], pv[1]);
+    o.y = pack_bf16x2(pv[2], pv[3]);
+    o.z = pack_bf16x2(pv[4], pv[5]);
+    o.w = pack_bf16x2(pv[6], pv[7]);
+    reinterpret_cast<uint4*>(param_shard)[i] = o;
+  }
+  // The updated bf16 shard is what peers gather next step: announce it once every block
+  // of this launch has finished.
+  if (last_block_done(counter)) signal_all(flags, world, rank, param_slot, epoch, threadIdx.x);
+}
+
+// -------------------------------------------- all-reduce + scale + cast (two-shot) ----
+// in.p[r] / out.p[r]: rank r's input / output buffers (may alias for bf16 in place).
+// Rank r reduces elements [r*n/world, (r+1)*n/world) over all ranks and stores the scaled
+// bf16 result into every rank's output.
+template <bool kInFp32>
+__global__ void __launch_bounds__(256)
+    allreduce_kernel(Peers in, Peers out, Peers flags, int64_t n, int rank, int world, float scale,
+                     int slot, uint32_t epoch, unsigned int* counter, int* status) {
+  __shared__ int sh_ok;
+  if (blockIdx.x == 0) signal_all(flags, world, rank, slot, epoch, threadIdx.x);
+  if (!block_wait_all(flags.p[rank], world, slot, epoch, status, &sh_ok)) return;
+  const int64_t nvec = n >> 3;
+  const int64_t per = (nvec + world - 1) / world;
+  const int64_t v0 = per * rank;
+  int64_t v1 = v0 + per;
+  if (v1 > nvec) v1 = nvec;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = v0 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < v1; i += stride) {
+    float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (kInFp32) {
+#pragma unroll
+      for (int k = 0; k < kMaxRanks; ++k) {
+        if (k < world) {
+          const int p = (rank + k) % world;
+          const uint4 a = ld_nc_v4(reinterpret_cast<const float*>(in.p[p]) + i * 8);
+          const uint4 b = ld_nc_v4(reinterpret_cast<const float*>(in.p[p]) + i * 8 + 4);
+          g[0] += __uint_as_float(a.x); g[1] += __uint_as_float(a.y);
+          g[2] += __uint_as_float(a.z); g[3] += __uint_as_float(a.w);
+          g[4] += __uint_as_float(b.x); g[5] += __uint_as_float(b.y);
+          g[6] += __uint_as_float(b.z); g[7] += __uint_as_float(b.w);
+        }
+      }
+    } else {
+      uint4 raw[kMaxRanks];
+#pragma unroll
+      for (int k = 0; k < kMaxRanks; ++k)
+        if (k < world)
+          raw[k] = ld_nc_v4(reinterpret_cast<const __nv_bfloat16*>(in.p[(rank + k) % world]) + i * 8);
+#pragma unroll
+      for (int k = 0; k < kMaxRanks; ++k)
+        if (k < world) acc8(g, raw[k]);
+    }
+    uint4 o;
+    o.x = pack_bf16x2(g[0] * scale, g[1] * scale);
+    o.y = pack_bf16x2(g[2] * scale, g[3] * scale);
+    o.z = pack_bf16x2(g[4] * scale, g[5] * scale);
+    o.w = pack_bf16x2(g[6] * scale, g[7] * scale);
+#pragma unroll
+    for (int k = 0; k < kMaxRanks; ++k)
+      if (k < world)
+        reinterpret_cast<uint4*>(out.p[(rank + k) % world])[i] = o;
+  }
+  if (last_block_done(counter)) signal_all(flags, world, rank, slot + 1, epoch, threadIdx.x);
+}
+
+// ----------------------------------------------------------------------- peer copy ----
+// One-sided transfer: either pointer may be a peer mapping.  After the data is written a
+// completion word is published (system scope) at `done_flag` (may live on the peer).
+__global__ void __launch_bounds__(256)
+    peer_copy_kernel(uint8_t* __restrict__ dst, const uint8_t* __restrict__ src, int64_t nbytes,
+                     uint32_t* done_flag, uint32_t done_value, unsigned int* counter) {
+  const int64_t nvec = nbytes >> 4;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src)) & 15) == 0;
+  if (aligned) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride)
+      reinterpret_cast<uint4*>(dst)[i] = ld_nc_v4(reinterpret_cast<const uint4*>(src) + i);
+    for (int64_t b = (nvec << 4) + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; b < nbytes;
+         b += stride)
+      dst[b] = src[b];
+  } else {
+    for (int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; b < nbytes; b += stride)
+      dst[b] = src[b];
+  }
+  if (done_flag && last_block_done(counter)) {
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      st_release_sys(done_flag, done_value);
+    }
+  }
+}
+
+// Bounded wait for a completion word (used by the receiver of a put, or by tests that
+// withhold the signal to exercise the timeout path).  limit_ms bounds the spin.
+__global__ void wait_flag_kernel(const uint32_t* flag, uint32_t value, int limit_ms, int* status) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    // ~2e6 cycles per ms at the upper end of the SM clock range
+    flag_wait_ge<true>(flag, value, status, (long long)limit_ms * 2000000LL);
+  }
+}
+
+static Peers make_peers(const void* const* ptrs, int world) {
+  Peers p{};
+  for (int i = 0; i < world && i < kMaxRanks; ++i) p.p[i] = const_cast<void*>(ptrs[i]);
+  return p;
+}
+
+static int comm_grid(int64_t work_items, int per_block, int cap) {
+  int64_t b = (work_items + per_block - 1) / per_block;
+  if (b < 1) b = 1;
+  return (int)(b < cap ? b : cap);
+}
+
+}  // namespace mb200
+
+using namespace mb200;
+#define ST(s) reinterpret_cast<cudaStream_t>(s)
+
+extern "C" int mb200_comm_max_ranks() { return kMaxRanks; }
+
+extern "C" int mb200_barrier(const void* const* flag_ptrs, int rank, int world, int slot,
+                             uint32_t epoch, int* status, void* stream) {
+  if (world > kMaxRanks) return 1001;
+  barrier_kernel<<<1, 32, 0, ST(stream)>>>(make_peers(flag_ptrs, world), rank, world, slot, epoch,
+                                            status);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int mb200_wait_flags(void* my_flags, int world, int slot, uint32_t epoch, int* status,
+                                void* stream) {
+  wait_kernel<<<1, 32, 0, ST(stream)>>>(my_flags, world, slot, epoch, status);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int mb200_allgather_pull(void* dst, const void* const* src_ptrs, int64_t shard_elems,
+                                    int rank, int world, void* my_flags, int wait_slot,
+                                    uint32_t wait_epoch, uint32_t* chunk_flags,
+                                    int64_t chunk_elems, uint32_t chunk_epoch, int n_blocks,
+                                    int* status, void* stream) {
+  if (world > kMaxRanks || (shard_elems & 7)) return 1001;
+  if (chunk_flags && (chunk_elems & 7)) return 1001;
+  const int grid = n_blocks > 0 ? n_blocks : comm_grid(shard_elems * world / 8, 256 * 8, 296);
+  allgather_pull_kernel<<<grid, 256, 0, ST(stream)>>>(
+      reinterpret_cast<__nv_bfloat16*>(dst), make_peers(src_ptrs, world), shard_elems, rank, world,
+      my_flags, wait_slot, wait_epoch, chunk_flags, chunk_elems, chunk_epoch, status);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int mb200_rs_adamw(const void* const* grad_ptrs, const void* const* flag_ptrs,
+                              float* master, float* m, float* v, void* param_shard,
+                              int64_t shard_elems, int rank, int world, int grad_slot,
+                              int param_slot, uint32_t epoch, float lr, float beta1, float beta2,
+                              float eps, float wd, int step, float grad_scale,
+                              unsigned int* counter, int n_blocks, int* status, void* stream) {
+  if (world > kMaxRanks || (shard_elems & 7)) return 1001;
+  const double bc1 = 1.0 - pow((double)beta1, (double)step);
+  const double bc2 = 1.0 - pow((double)beta2, (double)step);
+  const int grid = n_blocks > 0 ? n_blocks : comm_grid(shard_elems / 8, 256 * 4, 592);
+  rs_adamw_kernel<<<grid, 256, 0, ST(stream)>>>(
+      make_peers(grad_ptrs, world), make_peers(flag_ptrs, world), master, m, v,
+      reinterpret_cast<__nv_bfloat16*>(param_shard), shard_elems, rank, world, grad_slot,
+      param_slot, epoch, lr, beta1, beta2, eps, wd, (float)(1.0 / bc1), (float)(1.0 / sqrt(bc2)),
+      grad_scale, counter, status);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int mb200_allreduce_scale_cast(const void* const* in_ptrs, const void* const* out_ptrs,
+                                          const void* const* flag_ptrs, int64_t n, int in_fp32,
+                                          int rank, int world, float scale, int slot,
+                                          uint32_t epoch, unsigned int* counter, int n_blocks,
+                                          int* status, void* stream) {
+  if (world > kMaxRanks || (n & 7)) return 1001;
+  const int grid = n_blocks > 0 ? n_blocks : comm_grid(n / 8 / world, 256 * 4, 296);
+  Peers in = make_peers(in_ptrs, world), out = make_peers(out_ptrs, world),
+        fl = make_peers(flag_ptrs, world);
+  if (in_fp32)
+    allreduce_kernel<true><<<grid, 256, 0, ST(stream)>>>(in, out, fl, n, rank, world, scale, slot,
+                                                          epoch, counter, status);
+  else
+    allreduce_kernel<false><<<grid, 256, 0, ST(stream)>>>(in, out, fl, n, rank, world, scale, slot,
+                                                           epoch, counter, status);
+  // Results from every rank must have landed before a consumer on this stream reads them.
+  wait_kernel<<<1, 32, 0, ST(stream)>>>(fl.p[rank], world, slot + 1, epoch, status);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int mb200_peer_copy(void* dst, const void* src, int64_t nbytes, uint32_t* done_flag,
+                               uint32_t done_value, unsigned int* counter, int n_blocks,
+                               void* stream) {
+  if (nbytes <= 0 && !done_flag) return 0;
+  const int grid = n_blocks > 0 ? n_blocks : comm_grid(nbytes / 16 + 1, 256 * 8, 296);
+  peer_copy_kernel<<<grid, 256, 0, ST(stream)>>>(reinterpret_cast<uint8_t*>(dst),
+                                                 reinterpret_cast<const uint8_t*>(src), nbytes,
+                                                 done_flag, done_value, counter);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int mb200_wait_flag(const uint32_t* flag, uint32_t value, int limit_ms, int* status,
+                               void* stream) {
+  wait_flag_kernel<<<1, 32, 0, ST(stream)>>>(flag, value, limit_ms, status);
+  return (int)cudaGetLastError();
+}

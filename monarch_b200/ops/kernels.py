@@ -81,13 +81,16 @@ _OPTIONAL: dict[str, list] = {
     "mb200_attn_fwd": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _vp],
     "mb200_attn_bwd": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
                        _i, _i, _f, _vp, _vp],
-    "mb200_peer_copy": [_vp, _vp, _i64, _i, _vp],
-    "mb200_barrier": [_vp, _i, _i, ctypes.c_uint32, _vp, _vp],
-    "mb200_allreduce_scale_cast": [_vp, _vp, _vp, _i64, _i, _i, _f, _i, _i, _vp, ctypes.c_uint32,
-                                   _vp, _vp],
-    "mb200_allgather_pull": [_vp, _vp, _i64, _i, _i, _i, _vp],
-    "mb200_rs_adamw": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i, _i, _f, _f, _f, _f, _f, _i, _f,
-                       _i, _vp],
+    "mb200_barrier": [_vp, _i, _i, _i, ctypes.c_uint32, _vp, _vp],
+    "mb200_wait_flags": [_vp, _i, _i, ctypes.c_uint32, _vp, _vp],
+    "mb200_allgather_pull": [_vp, _vp, _i64, _i, _i, _vp, _i, ctypes.c_uint32, _vp, _i64,
+                             ctypes.c_uint32, _i, _vp, _vp],
+    "mb200_rs_adamw": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, ctypes.c_uint32, _f, _f,
+                       _f, _f, _f, _i, _f, _vp, _i, _vp, _vp],
+    "mb200_allreduce_scale_cast": [_vp, _vp, _vp, _i64, _i, _i, _i, _f, _i, ctypes.c_uint32, _vp,
+                                   _i, _vp, _vp],
+    "mb200_peer_copy": [_vp, _vp, _i64, _vp, ctypes.c_uint32, _vp, _i, _vp],
+    "mb200_wait_flag": [_vp, ctypes.c_uint32, _i, _vp, _vp],
     "mb200_ag_gemm": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp,
                       ctypes.c_uint32, _i, _vp, _vp],
 }

@@ -1,0 +1,248 @@
+"""Multi-GPU self-test of the NVLink kernels and the fused FSDP/DDP stores.
+
+Run one process per GPU:
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 \
+        --master-port 29511 -m monarch_b200.parallel.selftest [--bench]
+
+Each check compares the hand-written kernel against a torch.distributed (NCCL) or plain
+PyTorch fp32 computation of the same thing.  ``--bench`` also prints device-timed
+bandwidths (max over ranks) next to NCCL's.
+"""
+from __future__ import annotations
+
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+from ..ops import kernels as K
+from ..ops import reference as R
+from .symm import FlagArray, SymmBuffer, ptr_array
+
+bf16 = torch.bfloat16
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+def _max_over_ranks(ms: float, dev) -> float:
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def _time(fn, dev, iters=10, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return _max_over_ranks(e0.elapsed_time(e1) / iters, dev)
+
+
+def main() -> int:
+    rank = int(os.environ["RANK"])
+    world = int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    bench = "--bench" in sys.argv
+    lib = K.lib()
+    status = K.status_word(dev)
+    results = {}
+
+    flags = FlagArray(16, dev)
+    # ---------------------------------------------------------------- barrier -------
+    for _ in range(3):
+        flags.barrier(0)
+    torch.cuda.synchronize()
+    K.check_status()
+
+    # -------------------------------------------------------------- all-gather ------
+    shard = 1 << 20
+    src = SymmBuffer(shard, bf16, dev, zero=False)
+    torch.manual_seed(rank)
+    src.tensor.copy_(torch.randn(shard, device=dev).to(bf16))
+    torch.cuda.synchronize()
+    dist.barrier()
+    dst = torch.empty(shard * world, dtype=bf16, device=dev)
+    K.check(lib.mb200_allgather_pull(dst.data_ptr(), src.ptrs_at(0), shard, rank, world,
+                                     flags.my_ptr, 0, 0, None, 0, 0, 0, status.data_ptr(),
+                                     K.stream_ptr()), "allgather")
+    ref = torch.empty_like(dst)
+    dist.all_gather_into_tensor(ref, src.tensor)
+    torch.cuda.synchronize()
+    assert torch.equal(dst, ref), "allgather_pull mismatch"
+    # chunked variant publishes ready flags
+    chunk = 1 << 16
+    n_chunks = shard * world // chunk
+    cflags = torch.zeros(n_chunks, dtype=torch.int32, device=dev)
+    dst.zero_()
+    K.check(lib.mb200_allgather_pull(dst.data_ptr(), src.ptrs_at(0), shard, rank, world,
+                                     flags.my_ptr, 0, 0, cflags.data_ptr(), chunk, 7, 0,
+                                     status.data_ptr(), K.stream_ptr()), "allgather chunked")
+    torch.cuda.synchronize()
+    assert torch.equal(dst, ref) and bool((cflags == 7).all()), "chunked allgather mismatch"
+
+    # -------------------------------------------------------------- all-reduce ------
+    n = 1 << 22
+    buf = SymmBuffer(n, bf16, dev, zero=False)
+    torch.manual_seed(100 + rank)
+    x = torch.randn(n, device=dev).to(bf16)
+    buf.tensor.copy_(x)
+    expect = x.float().clone()
+    dist.all_reduce(expect)
+    expect /= world
+    torch.cuda.synchronize()
+    dist.barrier()
+    K.check(lib.mb200_allreduce_scale_cast(buf.ptrs_at(0), buf.ptrs_at(0), flags.ptrs, n, 0, rank,
+                                           world, 1.0 / world, 2, 1, flags.counter.data_ptr(), 0,
+                                           status.data_ptr(), K.stream_ptr()), "allreduce", 2)
+    torch.cuda.synchronize()
+    K.check_status()
+    assert _rel(buf.tensor, expect) < 5e-3, _rel(buf.tensor, expect)
+    # fp32 in -> bf16 out
+    fin = SymmBuffer(n, torch.float32, dev, zero=False)
+    fin.tensor.copy_(x.float())
+    torch.cuda.synchronize()
+    dist.barrier()
+    K.check(lib.mb200_allreduce_scale_cast(fin.ptrs_at(0), buf.ptrs_at(0), flags.ptrs, n, 1, rank,
+                                           world, 1.0 / world, 2, 2, flags.counter.data_ptr(), 0,
+                                           status.data_ptr(), K.stream_ptr()), "allreduce fp32", 2)
+    torch.cuda.synchronize()
+    assert _rel(buf.tensor, expect) < 5e-3
+
+    # ----------------------------------------------------- reduce-scatter + AdamW ----
+    s = 1 << 18
+    g = SymmBuffer(s * world, bf16, dev, zero=False)
+    torch.manual_seed(200 + rank)
+    gl = torch.randn(s * world, device=dev).to(bf16)
+    g.tensor.copy_(gl)
+    gsum = gl.float().clone()
+    dist.all_reduce(gsum)
+    master = torch.randn(s, device=dev)
+    m = torch.zeros(s, device=dev)
+    v = torch.zeros(s, device=dev)
+    pshard = torch.empty(s, dtype=bf16, device=dev)
+    pr, mr, vr = R.adamw(master.clone(), m.clone(), v.clone(), gsum[rank * s:(rank + 1) * s], 1e-2,
+                         0.9, 0.95, 1e-8, 0.1, 1, 1.0 / world)
+    torch.cuda.synchronize()
+    dist.barrier()
+    K.check(lib.mb200_rs_adamw(g.ptrs_at(0), flags.ptrs, master.data_ptr(), m.data_ptr(),
+                               v.data_ptr(), pshard.data_ptr(), s, rank, world, 4, 5, 1, 1e-2, 0.9,
+                               0.95, 1e-8, 0.1, 1, 1.0 / world, flags.counter.data_ptr(), 0,
+                               status.data_ptr(), K.stream_ptr()), "rs_adamw")
+    torch.cuda.synchronize()
+    K.check_status()
+    assert torch.allclose(master, pr, atol=2e-5), (master - pr).abs().max()
+    assert torch.allclose(m, mr, atol=1e-5) and torch.allclose(v, vr, atol=1e-5)
+    assert torch.equal(pshard, master.to(bf16))
+
+    # ------------------------------------------- fused FSDP == library-collective FSDP --
+    from ..models import PRESETS, LlamaEngine, ParamLayout
+    from .fsdp import FSDPParamStore
+    cfg = PRESETS["tiny"]
+    layout = ParamLayout(cfg)
+    S = 128
+    gen = torch.Generator().manual_seed(1000 + rank)
+    toks = torch.randint(0, cfg.vocab, (4, 2, S), generator=gen).to(dev)
+    outs = {}
+    for mode in ("fused", "nccl"):
+        st = FSDPParamStore(layout, dev, seed=3, init_std=0.05, comm=mode)
+        eng = LlamaEngine(cfg, st, S)
+        losses = []
+        for step in range(3):
+            st.set_hyper(lr=1e-2)
+            losses.append(eng.forward_backward(toks[step], toks[step + 1]))
+            eng.optimizer_step(1e-2)
+        torch.cuda.synchronize()
+        K.check_status()
+        outs[mode] = (st.full_params().float(), [float(l) for l in losses])
+    rel = _rel(outs["fused"][0], outs["nccl"][0])
+    assert rel < 2e-2, f"fused FSDP diverges from the NCCL path: {rel}"
+    results["fsdp_rel_diff"] = rel
+    results["fsdp_losses"] = outs["fused"][1]
+
+    # --------------------------------------------------------- DDP fused == library ----
+    try:
+        from .ddp import DDPParamStore
+        outs = {}
+        for mode in ("fused", "nccl"):
+            st = DDPParamStore(layout, dev, seed=3, init_std=0.05, comm=mode, bucket_bytes=1 << 18)
+            eng = LlamaEngine(cfg, st, S)
+            for step in range(3):
+                eng.forward_backward(toks[step], toks[step + 1])
+                eng.optimizer_step(1e-2)
+            torch.cuda.synchronize()
+            K.check_status()
+            outs[mode] = st.full_params().float()
+        rel = _rel(outs["fused"], outs["nccl"])
+        assert rel < 2e-2, f"fused DDP diverges from the NCCL path: {rel}"
+        results["ddp_rel_diff"] = rel
+    except ImportError:
+        pass
+
+    # ------------------------------------------------------------------ bandwidths ----
+    if bench:
+        sizes = [1 << 20, 1 << 24, 1 << 27]  # bf16 elements per rank buffer
+        rows = []
+        for n in sizes:
+            buf = SymmBuffer(n, bf16, dev)
+            out = torch.empty(n, dtype=bf16, device=dev)
+            ep = [10]
+
+            def ours_ar():
+                ep[0] += 1
+                K.check(lib.mb200_allreduce_scale_cast(
+                    buf.ptrs_at(0), buf.ptrs_at(0), flags.ptrs, n, 0, rank, world, 1.0 / world, 6,
+                    ep[0], flags.counter.data_ptr(), 0, status.data_ptr(), K.stream_ptr()),
+                    "allreduce", 2)
+
+            def nccl_ar():
+                dist.all_reduce(buf.tensor)
+
+            t_o = _time(ours_ar, dev)
+            t_n = _time(nccl_ar, dev)
+            bus = lambda ms: 2 * (world - 1) / world * n * 2 / (ms / 1e3) / 1e9
+            shard_n = n // world
+            full = torch.empty(shard_n * world, dtype=bf16, device=dev)
+
+            def ours_ag():
+                K.check(lib.mb200_allgather_pull(full.data_ptr(), buf.ptrs_at(0), shard_n, rank,
+                                                 world, flags.my_ptr, 0, 0, None, 0, 0, 0,
+                                                 status.data_ptr(), K.stream_ptr()), "ag")
+
+            def nccl_ag():
+                dist.all_gather_into_tensor(full, buf.tensor[:shard_n])
+
+            t_oag = _time(ours_ag, dev)
+            t_nag = _time(nccl_ag, dev)
+            agbw = lambda ms: (world - 1) / world * shard_n * world * 2 / (ms / 1e3) / 1e9
+            rows.append({"bytes": n * 2, "allreduce_ms": t_o, "allreduce_busbw_gbs": bus(t_o),
+                         "nccl_allreduce_ms": t_n, "nccl_busbw_gbs": bus(t_n),
+                         "allgather_ms": t_oag, "allgather_rx_gbs": agbw(t_oag),
+                         "nccl_allgather_ms": t_nag, "nccl_allgather_rx_gbs": agbw(t_nag)})
+            del buf
+        results["bandwidth"] = rows
+        K.check_status()
+
+    torch.cuda.synchronize()
+    dist.barrier()
+    if rank == 0:
+        print("SELFTEST OK " + json.dumps(results))
+    dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,76 @@
+"""Peer-mapped ("symmetric") device memory and the flag arrays the NVLink kernels use.
+
+Every rank allocates a buffer of the same size; after the rendezvous each rank holds the
+device addresses of all ranks' buffers, so kernels can issue plain loads/stores on peer
+memory over NVLink.  Allocation and handle exchange use torch's symmetric-memory
+allocator (CUDA VMM + fd passing over the process group's store); everything that
+touches the memory afterwards is this package's own kernels.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import kernels as K
+
+MAX_RANKS = 8
+
+
+def ptr_array(ptrs: List[int]):
+    return (ctypes.c_void_p * len(ptrs))(*ptrs)
+
+
+class SymmBuffer:
+    """A tensor whose storage is mapped on every rank of ``group``."""
+
+    def __init__(self, numel: int, dtype: torch.dtype, device: torch.device,
+                 group: Optional[dist.ProcessGroup] = None, zero: bool = True):
+        import torch.distributed._symmetric_memory as symm_mem
+        group = group or dist.group.WORLD
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        if self.world > MAX_RANKS:
+            raise ValueError(f"at most {MAX_RANKS} ranks per NVLink domain")
+        self.tensor = symm_mem.empty(numel, dtype=dtype, device=device)
+        if zero:
+            self.tensor.zero_()
+        self.handle = symm_mem.rendezvous(self.tensor, group)
+        self.ptrs: List[int] = [int(p) for p in self.handle.buffer_ptrs]
+        assert self.ptrs[self.rank] == self.tensor.data_ptr()
+        self.multicast_ptr: int = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+        self._elt = self.tensor.element_size()
+
+    def ptrs_at(self, elem_offset: int):
+        """ctypes array of every rank's address of element ``elem_offset``."""
+        off = elem_offset * self._elt
+        return ptr_array([p + off for p in self.ptrs])
+
+    def peer_view(self, rank: int, numel: int, offset: int = 0) -> torch.Tensor:
+        return self.handle.get_buffer(rank, (numel,), self.tensor.dtype, offset)
+
+
+class FlagArray:
+    """Per-rank array of epoch flags: ``flags[slot * MAX_RANKS + source_rank]``."""
+
+    def __init__(self, n_slots: int, device: torch.device, group=None):
+        self.n_slots = n_slots
+        self.buf = SymmBuffer(n_slots * MAX_RANKS, torch.int32, device, group)
+        self.rank, self.world = self.buf.rank, self.buf.world
+        self.ptrs = ptr_array(self.buf.ptrs)
+        self.my_ptr = self.buf.ptrs[self.rank]
+        self.counter = torch.zeros(8, dtype=torch.int32, device=device)
+        self._barrier_epoch = 0
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group or dist.group.WORLD)
+
+    def barrier(self, slot: int) -> None:
+        """Device-side flag barrier on the current stream (bounded wait)."""
+        self._barrier_epoch += 1
+        K.check(K.lib().mb200_barrier(self.ptrs, self.rank, self.world, slot,
+                                      self._barrier_epoch,
+                                      K.status_word(self.buf.tensor.device).data_ptr(),
+                                      K.stream_ptr()), "barrier")

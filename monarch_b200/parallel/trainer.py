@@ -62,6 +62,8 @@ class Trainer:
     # -------------------------------------------------------------------------------
     def step_device(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         """One optimizer step on device-resident inputs; returns the device loss tensor."""
+        if hasattr(self.store, "set_hyper"):
+            self.store.set_hyper(lr=self.lr)  # sharded stores update inside backward
         loss = self.engine.forward_backward(tokens, targets)
         self.engine.optimizer_step(self.lr)
         return loss
