@@ -169,6 +169,33 @@ class Port(Generic[R]):
         return (Port, (self._port_id, self._rank))
 
 
+class ReducePort(Port):
+    """Send side of a native accumulating port: tensors are posted as raw bytes and folded
+    by the C++ reducer of the receiving mailbox (no unpickling on the reduce path);
+    exceptions go to a separate ordinary port."""
+
+    def __init__(self, port_id: str, error_port_id: str, rank: Optional[int] = None):
+        super().__init__(port_id, rank)
+        self._error_port_id = error_port_id
+
+    def send(self, obj) -> None:
+        import numpy as np
+        arr = obj.detach().cpu().contiguous().numpy() if hasattr(obj, "detach") else \
+            np.ascontiguousarray(obj)
+        context().actor_instance._native.send(self._port_id, arr.tobytes(),
+                                              {"kind": "reduce", "no_return": "1"}, [])
+
+    def exception(self, obj: BaseException) -> None:
+        if not isinstance(obj, ActorError):
+            obj = ActorError(obj)
+        body, parts = flatten((_KIND_EXCEPTION, self._rank, obj))
+        context().actor_instance._native.send(self._error_port_id, body,
+                                              {"kind": _KIND_EXCEPTION, "no_return": "1"}, parts)
+
+    def __reduce__(self):
+        return (ReducePort, (self._port_id, self._error_port_id, self._rank))
+
+
 class DroppingPort:
     """Used when the caller did not ask for a response: results vanish, exceptions crash
     the actor (and reach its supervisor)."""
@@ -411,6 +438,38 @@ class Endpoint(Generic[R]):
         for _ in range(n):
             yield Future(lambda timeout: rx._next(timeout)[1])
 
+    def reduce(self, *args, reducer: str = "sum_f32", **kwargs) -> Future:
+        """Call every actor and fold the returned tensors element-wise in the native
+        mailbox (``sum_f32``, ``sum_f64``, ``max_f64``, ``min_f64``, ``sum_i64``).  The
+        future yields the folded values as a 1-D tensor."""
+        self._mesh._raise_if_unhealthy()
+        inst = context().actor_instance._native
+        port_id, acc = inst.open_accum_port(reducer, b"")
+        err_port, err_rx = self._open()
+        n = len(self._mesh)
+        self._send(args, kwargs, ReducePort(port_id, err_port._port_id))
+        mesh = self._mesh
+
+        def wait(timeout: Optional[float]):
+            import numpy as np
+            import torch
+            deadline = None if timeout is None else time.monotonic() + timeout
+            try:
+                while not acc.wait_count(n, 20):
+                    env = err_rx._rx.try_recv()
+                    if env is not None:
+                        raise unflatten(env.data, env.parts)[2]
+                    mesh._raise_if_unhealthy()
+                    if deadline is not None and time.monotonic() > deadline:
+                        raise TimeoutError("timed out waiting for the reduction")
+            finally:
+                inst.close_port(port_id)
+                err_rx.close()
+            dt = {"f32": np.float32, "f64": np.float64, "i64": np.int64}[reducer.split("_")[-1]]
+            return torch.from_numpy(np.frombuffer(acc.state(), dtype=dt).copy())
+
+        return Future(wait)
+
     def broadcast(self, *args, **kwargs) -> None:
         """Fire and forget; an exception in the endpoint crashes the actor."""
         self._mesh._raise_if_unhealthy()
@@ -616,7 +675,9 @@ class _ActorState:
             if kind == "init":
                 return
             _, method, args, kwargs, port = msg
-            if port is not None:
+            if isinstance(port, ReducePort):
+                port = ReducePort(port._port_id, port._error_port_id, cast_rank)
+            elif port is not None:
                 port = Port(port._port_id, cast_rank)
             response = port if port is not None else DroppingPort()
             prop = getattr(self.cls, method, None)

@@ -1,0 +1,262 @@
+"""RDMABuffer: one-sided reads and writes of another actor's memory.
+
+Parity: python/monarch/_src/tensor_engine/rdma.py (RDMABuffer.read_into / write_from /
+drop, picklable handles that travel in ordinary actor messages, default timeout 3 s),
+monarch_rdma (per-proc manager actor, buffer registry).  The reference moves bytes with
+ibverbs queue pairs and bounces GPU tensors through the host; here
+
+* GPU buffers are first class: the owner exports a CUDA IPC handle, the peer maps it and a
+  hand-written copy kernel moves the bytes with in-kernel NVLink loads/stores
+  (``peer_copy``), publishing a completion flag; no host bounce;
+* host buffers in the same process are copied directly; across processes the owner's
+  manager actor serves the bytes as out-of-band frame parts over the actor channels
+  (no ibverbs device exists on this class of box).
+"""
+from __future__ import annotations
+
+import itertools
+import pickle
+import threading
+import time
+import warnings
+from typing import Any, Dict, Optional, Tuple
+
+import torch
+
+from ..actor.actor_mesh import context
+from ..actor.future import Future
+from ..actor.pickle import flatten, unflatten
+
+_MANAGER_NAME = "rdma_manager"
+_lock = threading.Lock()
+_managers: Dict[str, "_Manager"] = {}   # proc id -> manager (this process)
+_ids = itertools.count(1)
+
+
+class RDMAError(RuntimeError):
+    pass
+
+
+def is_available() -> bool:
+    return True
+
+
+class _Manager:
+    """Per-proc registry of exported buffers plus the actor that serves remote requests."""
+
+    def __init__(self, proc):
+        self.proc = proc
+        self.proc_id = proc.proc_id
+        self.buffers: Dict[int, torch.Tensor] = {}
+        self.instance = proc.spawn(_MANAGER_NAME, self._on_message,
+                                   on_undeliverable=lambda *a: True)
+        self.actor_id = self.instance.actor_id
+
+    def register(self, t: torch.Tensor) -> int:
+        bid = next(_ids)
+        self.buffers[bid] = t
+        return bid
+
+    def _on_message(self, inst, env) -> None:
+        req = unflatten(env.data, env.parts)
+        op, bid, reply = req[0], req[1], req[-1]
+        try:
+            t = self.buffers.get(bid)
+            if t is None:
+                raise RDMAError(f"buffer {bid} is not registered on {self.proc_id} (dropped?)")
+            raw = _as_bytes(t)
+            if op == "read":
+                _, _, off, n, _ = req
+                _check_range(raw, off, n)
+                body, parts = flatten(("ok", raw[off: off + n].cpu()))
+            elif op == "write":
+                _, _, off, data, _ = req
+                _check_range(raw, off, data.numel())
+                raw[off: off + data.numel()].copy_(data)
+                body, parts = flatten(("ok", None))
+            elif op == "cuda_handle":
+                from torch.multiprocessing.reductions import reduce_tensor
+                fn, args = reduce_tensor(raw)
+                body, parts = flatten(("ok", (fn, args)))
+            elif op == "drop":
+                self.buffers.pop(bid, None)
+                body, parts = flatten(("ok", None))
+            else:
+                raise RDMAError(f"unknown rdma op {op!r}")
+        except Exception as e:  # noqa: BLE001 - reported to the requester
+            body, parts = flatten(("err", f"{type(e).__name__}: {e}"))
+        inst.send(reply, body, {"kind": "rdma_reply", "no_return": "1"}, parts)
+
+
+def _as_bytes(t: torch.Tensor) -> torch.Tensor:
+    if not t.is_contiguous():
+        raise ValueError("RDMABuffer needs a contiguous tensor")
+    return t.reshape(-1).view(torch.uint8)
+
+
+def _check_range(raw: torch.Tensor, off: int, n: int) -> None:
+    if off < 0 or n < 0 or off + n > raw.numel():
+        raise RDMAError(f"range [{off}, {off + n}) outside a buffer of {raw.numel()} bytes")
+
+
+def _manager_for_current_proc() -> _Manager:
+    proc = context().actor_instance.proc
+    with _lock:
+        m = _managers.get(proc.proc_id)
+        if m is None:
+            m = _Manager(proc)
+            _managers[proc.proc_id] = m
+        return m
+
+
+_peer_cache: Dict[Tuple[str, int], torch.Tensor] = {}
+_copy_state: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
+
+
+def _device_copy(dst: torch.Tensor, src: torch.Tensor) -> None:
+    """dst <- src with the peer-copy kernel (either side may be a peer mapping)."""
+    from ..ops import kernels as K
+    dev = dst.device if dst.is_cuda else src.device
+    idx = dev.index or 0
+    st = _copy_state.get(idx)
+    if st is None:
+        st = (torch.zeros(4, dtype=torch.int32, device=dev),
+              torch.zeros(4, dtype=torch.int32, device=dev))
+        _copy_state[idx] = st
+    done, counter = st
+    with torch.cuda.device(dev):
+        done.zero_()
+        K.check(K.lib().mb200_peer_copy(dst.data_ptr(), src.data_ptr(), dst.numel(),
+                                        done.data_ptr(), 1, counter.data_ptr(), 0,
+                                        K.stream_ptr()), "peer_copy")
+        torch.cuda.current_stream().synchronize()
+        if int(done[0].item()) != 1:
+            raise RDMAError("peer copy did not publish its completion flag")
+
+
+class RDMABuffer:
+    """A handle to ``data``'s memory that other actors can read from and write into."""
+
+    def __init__(self, data: torch.Tensor):
+        if data.dim() != 1 or data.dtype != torch.uint8:
+            data = data.reshape(-1).view(torch.uint8) if data.is_contiguous() else None
+            if data is None:
+                raise ValueError("RDMABuffer needs a contiguous tensor (viewed as 1-D uint8)")
+        mgr = _manager_for_current_proc()
+        self._owner = mgr.actor_id
+        self._owner_proc = mgr.proc_id
+        self._id = mgr.register(data)
+        self._nbytes = data.numel()
+        self._cuda = data.is_cuda
+        self._device_index = data.device.index if data.is_cuda else None
+
+    # handles travel by value; the memory stays with the owner
+    def __reduce__(self):
+        return (_rebuild, (self._owner, self._owner_proc, self._id, self._nbytes, self._cuda,
+                           self._device_index))
+
+    @property
+    def nbytes(self) -> int:
+        return self._nbytes
+
+    # ------------------------------------------------------------------------------
+    def _local_tensor(self) -> Optional[torch.Tensor]:
+        m = _managers.get(self._owner_proc)
+        if m is not None and self._id in m.buffers:
+            return _as_bytes(m.buffers[self._id])
+        return None
+
+    def _request(self, msg: tuple, timeout: float) -> Any:
+        inst = context().actor_instance._native
+        port, rx = inst.open_port(True)
+        body, parts = flatten((*msg, port))
+        inst.send(self._owner + "[0]", body, {"kind": "rdma"}, parts)
+        env = rx.recv(int(timeout * 1000))
+        if env is None:
+            inst.close_port(port)
+            raise TimeoutError(f"RDMA operation on {self._owner} timed out after {timeout} s")
+        status, payload = unflatten(env.data, env.parts)
+        if status != "ok":
+            raise RDMAError(payload)
+        return payload
+
+    def _peer_mapping(self, timeout: float) -> torch.Tensor:
+        key = (self._owner, self._id)
+        t = _peer_cache.get(key)
+        if t is None:
+            fn, args = self._request(("cuda_handle", self._id), timeout)
+            t = fn(*args)
+            _peer_cache[key] = t
+        return t
+
+    def read_into(self, dst: torch.Tensor, offset: int = 0, timeout: float = 3) -> Future[None]:
+        """Copy ``dst.nbytes`` bytes starting at ``offset`` of the remote buffer into ``dst``."""
+        d = _as_bytes(dst)
+
+        def run(_t):
+            n = d.numel()
+            if offset < 0 or offset + n > self._nbytes:
+                raise RDMAError(f"range [{offset}, {offset + n}) outside a buffer of "
+                                f"{self._nbytes} bytes")
+            local = self._local_tensor()
+            if local is not None:
+                src = local[offset: offset + n]
+                if src.is_cuda or d.is_cuda:
+                    if src.is_cuda and d.is_cuda:
+                        _device_copy(d, src)
+                    else:
+                        d.copy_(src)
+                else:
+                    d.copy_(src)
+                return None
+            if self._cuda and d.is_cuda:
+                _device_copy(d, self._peer_mapping(timeout)[offset: offset + n])
+                return None
+            data = self._request(("read", self._id, offset, n), timeout)
+            d.copy_(data)
+            return None
+
+        return Future(run)
+
+    def write_from(self, src: torch.Tensor, offset: int = 0, timeout: float = 3) -> Future[None]:
+        """Copy ``src`` into the remote buffer starting at ``offset``."""
+        s = _as_bytes(src)
+
+        def run(_t):
+            n = s.numel()
+            if offset < 0 or offset + n > self._nbytes:
+                raise RDMAError(f"range [{offset}, {offset + n}) outside a buffer of "
+                                f"{self._nbytes} bytes")
+            local = self._local_tensor()
+            if local is not None:
+                dst = local[offset: offset + n]
+                if dst.is_cuda and s.is_cuda:
+                    _device_copy(dst, s)
+                else:
+                    dst.copy_(s)
+                return None
+            if self._cuda and s.is_cuda:
+                _device_copy(self._peer_mapping(timeout)[offset: offset + n], s)
+                return None
+            self._request(("write", self._id, offset, s.cpu()), timeout)
+            return None
+
+        return Future(run)
+
+    def drop(self) -> Future[None]:
+        def run(_t):
+            m = _managers.get(self._owner_proc)
+            if m is not None:
+                m.buffers.pop(self._id, None)
+            else:
+                self._request(("drop", self._id), 3)
+            _peer_cache.pop((self._owner, self._id), None)
+            return None
+        return Future(run)
+
+
+def _rebuild(owner, owner_proc, bid, nbytes, cuda, device_index) -> RDMABuffer:
+    b = RDMABuffer.__new__(RDMABuffer)
+    b._owner, b._owner_proc, b._id, b._nbytes = owner, owner_proc, bid, nbytes
+    b._cuda, b._device_index = cuda, device_index
+    return b
