@@ -556,7 +556,7 @@ class Actor:
 
 class ActorMesh(MeshTrait, Generic[T]):
     def __init__(self, cls: Type[T], name: str, world: str, shape: Shape, proc_mesh=None,
-                 health: Optional[_Health] = None):
+                 health: Optional[_Health] = None, root_slice=None):
         self._class = cls
         self._class_name = getattr(cls, "__name__", str(cls))
         self._name = name
@@ -564,6 +564,9 @@ class ActorMesh(MeshTrait, Generic[T]):
         self._shape_ = shape
         self._proc_mesh = proc_mesh
         self._health = health
+        # the slice the mesh was spawned over: every cast, whatever sub-slice it targets,
+        # is routed through this tree so that one sender's messages keep their order
+        self._root_slice = root_slice if root_slice is not None else shape.ndslice
 
     # MeshTrait ------------------------------------------------------------------------
     @property
@@ -580,7 +583,7 @@ class ActorMesh(MeshTrait, Generic[T]):
 
     def _new_with_shape(self, shape: Shape) -> "ActorMesh[T]":
         return ActorMesh(self._class, self._name, self._world, shape, self._proc_mesh,
-                         self._health)
+                         self._health, self._root_slice)
 
     # endpoints ------------------------------------------------------------------------
     def __getattr__(self, name: str):
@@ -602,10 +605,14 @@ class ActorMesh(MeshTrait, Generic[T]):
     def _cast(self, message: Tuple, ranks: Optional[List[int]] = None) -> None:
         body, parts = flatten(message)
         sl = self._shape_.ndslice
-        sel = N.Selection.all() if ranks is None else N.Selection.of_ranks(sl, ranks)
+        root = self._root_slice
+        if ranks is None and sl == root:
+            sel = N.Selection.all()
+        else:
+            sel = N.Selection.of_ranks(root, sl.ranks() if ranks is None else ranks)
         headers = {"cast_shape": json.dumps([self._shape_.labels, list(sl.sizes)])}
         inst = context().actor_instance._native
-        N.cast(inst, self._world, self._name, sl, sel, body, headers, parts, sl)
+        N.cast(inst, self._world, self._name, root, sel, body, headers, parts, sl)
 
     def stop(self) -> Future[None]:
         pm = self._proc_mesh
@@ -615,7 +622,8 @@ class ActorMesh(MeshTrait, Generic[T]):
                                                             int((timeout or 5) * 1000)))
 
     def __reduce__(self):
-        return (ActorMesh, (self._class, self._name, self._world, self._shape_))
+        return (ActorMesh, (self._class, self._name, self._world, self._shape_, None, None,
+                            self._root_slice))
 
     def __repr__(self) -> str:
         return f"ActorMesh({self._class_name}, '{self._name}', {self._shape_})"

@@ -451,7 +451,7 @@ class _ControllerController(Actor):
         if name not in self._controllers:
             self._controllers[name] = _controller_procs().spawn(name, cls, *args, **kwargs)
         m = self._controllers[name]
-        return ActorMesh(m._class, m._name, m._world, m._shape_)
+        return ActorMesh(m._class, m._name, m._world, m._shape_, None, None, m._root_slice)
 
 
 _cc_lock = threading.Lock()
@@ -479,7 +479,8 @@ def _controller_controller() -> ActorMesh:
             import base64
             import pickle
             os.environ["MB200_CONTROLLER_REF"] = base64.b64encode(pickle.dumps(
-                ActorMesh(_cc_mesh._class, _cc_mesh._name, _cc_mesh._world, _cc_mesh._shape_))).decode()
+                ActorMesh(_cc_mesh._class, _cc_mesh._name, _cc_mesh._world, _cc_mesh._shape_, None,
+                          None, _cc_mesh._root_slice))).decode()
         return _cc_mesh
 
 

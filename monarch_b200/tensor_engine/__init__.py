@@ -4,3 +4,14 @@ Parity: python/monarch/tensor_engine/__init__.py (RDMABuffer, is_available)."""
 from .rdma import RDMABuffer, RDMAError, is_available
 
 __all__ = ["RDMABuffer", "RDMAError", "is_available"]
+
+from .device_mesh import (Borrow, DeviceMesh, RemoteException, Stream, Tensor,  # noqa: E402
+                          get_active_mesh, get_active_stream, no_mesh, reduce, reduce_,
+                          slice_mesh, spawn_tensor_engine, to_mesh)
+from .remote import (Remote, call_on_shard_and_fetch, coalescing, fetch_shard,  # noqa: E402
+                     inspect, remote, show)
+
+__all__ += ["Borrow", "DeviceMesh", "RemoteException", "Stream", "Tensor", "get_active_mesh",
+            "get_active_stream", "no_mesh", "reduce", "reduce_", "slice_mesh",
+            "spawn_tensor_engine", "to_mesh", "Remote", "call_on_shard_and_fetch", "coalescing",
+            "fetch_shard", "inspect", "remote", "show"]

@@ -1,0 +1,720 @@
+"""Controller side of the tensor engine: distributed ``Tensor``s on a ``DeviceMesh``.
+
+Parity: python/monarch/common/tensor.py (Tensor wrapper subclass whose
+``__torch_dispatch__`` turns every torch op into a worker message; ``reduce`` /
+``reduce_`` / ``to_mesh`` / ``slice_mesh``), device_mesh.py (DeviceMesh.activate, slice /
+split / rename / flatten, ``rank``), remote.py (``remote`` functions with shape
+propagation, ``fetch_shard``, ``inspect``, ``call_on_shard_and_fetch``), client.py (seq
+numbers, refs, deferred deletes), _coalescing.py (batched sends), stream.py / borrows.py
+(streams and borrows), mesh_controller.py (RemoteException).
+
+Shapes are propagated on FakeTensors in the controller; each op allocates result refs
+and casts one ``call`` message to the workers of the active mesh (or appends it to the
+open coalescing block).  Failures never kill a worker: the failing op's results carry
+the error, dependants inherit it, and it surfaces as ``RemoteException`` on fetch.
+"""
+from __future__ import annotations
+
+import contextlib
+import itertools
+import socket
+import threading
+import warnings
+from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
+
+import torch
+from torch._subclasses.fake_tensor import FakeTensorMode
+from torch.utils._python_dispatch import TorchDispatchMode
+
+from ..actor import Channel, Future
+from ..actor.shape import MeshTrait, Shape
+from .worker import Ref, TensorWorker, _map_refs
+
+_fake_mode = FakeTensorMode(allow_non_fake_inputs=True)
+
+
+class RemoteException(Exception):
+    """An op failed on a worker; raised when a value depending on it is fetched."""
+
+    def __init__(self, seq: int, rank: int, func: str, exc_text: str, tb: str,
+                 dependent_of: Optional[int] = None):
+        self.seq, self.rank, self.func = seq, rank, func
+        self.exc_text, self.worker_traceback, self.dependent_of = exc_text, tb, dependent_of
+        dep = f" (caused by failed op {dependent_of})" if dependent_of is not None else ""
+        super().__init__(f"remote function '{func}' failed on rank {rank}{dep}: {exc_text}\n"
+                         f"Worker traceback:\n{tb}")
+
+
+# ---------------------------------------------------------------------------- streams --
+class Stream:
+    _ids = itertools.count(1)
+
+    def __init__(self, name: str, _default: bool = False):
+        self.name = name
+        self.id = 0 if _default else next(Stream._ids)
+        self._default = _default
+        self._created_on: set = set()
+
+    def activate(self):
+        return _activate_stream(self)
+
+    def borrow(self, t: "Tensor", mutable: bool = False) -> Tuple["Tensor", "Borrow"]:
+        """Make ``t`` usable on this stream.  Until the borrow is dropped the origin stream
+        may not write (immutable borrow) or touch (mutable borrow) the tensor."""
+        client = t.mesh.client
+        client._ensure_stream(self)
+        b = Borrow(next(Borrow._ids), t, self, mutable)
+        out = Tensor(t._fake, t.mesh, self)
+        client.send(t.mesh, ("borrow_create", b.id, Ref(t.ref), t.stream.id, self.id, Ref(out.ref)))
+        t._borrowed_by.append(b)
+        b._result = out
+        return out, b
+
+    def __repr__(self):
+        return f"<Stream {self.name!r}>"
+
+
+_main_stream = Stream("main", _default=True)
+_tls = threading.local()
+
+
+def get_active_stream() -> Stream:
+    return getattr(_tls, "stream", _main_stream)
+
+
+@contextlib.contextmanager
+def _activate_stream(s: Stream):
+    prev = get_active_stream()
+    _tls.stream = s
+    try:
+        yield
+    finally:
+        _tls.stream = prev
+
+
+class Borrow:
+    _ids = itertools.count(1)
+
+    def __init__(self, id: int, origin: "Tensor", stream: Stream, mutable: bool):
+        self.id, self.origin, self.stream, self.mutable = id, origin, stream, mutable
+        self._dropped = False
+        self._result: Optional[Tensor] = None
+
+    def drop(self) -> None:
+        if self._dropped:
+            return
+        self._dropped = True
+        self.origin.mesh.client.send(self.origin.mesh, ("borrow_drop", self.id))
+        if self in self.origin._borrowed_by:
+            self.origin._borrowed_by.remove(self)
+        if self._result is not None:
+            self._result._dropped = True
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.drop()
+
+    def __del__(self):
+        if not self._dropped:
+            warnings.warn("borrow was never dropped; dropping it now", stacklevel=2)
+            try:
+                self.drop()
+            except Exception:  # noqa: BLE001
+                pass
+
+
+# ----------------------------------------------------------------------------- client --
+class Client:
+    """Sequencing, ref allocation, batching and fetches for one tensor engine."""
+
+    def __init__(self, proc_mesh, workers, use_cuda: bool):
+        self.proc_mesh = proc_mesh
+        self.workers = workers
+        self.use_cuda = use_cuda
+        self._seq = itertools.count(1)
+        self._ref = itertools.count(1)
+        self._lock = threading.RLock()
+        self._pending_deletes: List[int] = []
+        self._coalesce: Optional[List[Tuple[Any, tuple]]] = None
+        self._recording: Optional[List[tuple]] = None
+        self._pg_init = False
+        self._comms: set = set()
+        self._streams_made: set = {0}
+        self.errors: List[tuple] = []
+        port, self._err_rx = Channel.open()
+        workers.configure.call(port).get(timeout=60)
+        self._closed = False
+
+    def new_seq(self) -> int:
+        return next(self._seq)
+
+    def new_ref(self) -> int:
+        return next(self._ref)
+
+    def delete_ref(self, ref: int) -> None:
+        with self._lock:
+            self._pending_deletes.append(ref)
+
+    def _send_deletes(self) -> None:
+        """Refs are dropped on every worker, whichever sub-mesh the next message goes to."""
+        d = self._flush_deletes(None)
+        if d:
+            self.root_mesh._workers.run.broadcast(d)
+
+    def _flush_deletes(self, mesh) -> List[tuple]:
+        with self._lock:
+            if not self._pending_deletes:
+                return []
+            ids, self._pending_deletes = self._pending_deletes, []
+        return [("delete", ids)]
+
+    def send(self, mesh: "DeviceMesh", msg: tuple) -> None:
+        """Queue ``msg`` for the workers of ``mesh`` (cast now, or at the end of the open
+        coalescing block)."""
+        if self._closed:
+            raise RuntimeError("the tensor engine was shut down")
+        if self._coalesce is not None:
+            self._coalesce.append((mesh, msg))
+            return
+        self._send_deletes()
+        mesh._workers.run.broadcast([msg])
+
+    def _ensure_stream(self, s: Stream) -> None:
+        if s.id not in self._streams_made:
+            self._streams_made.add(s.id)
+            self.send(self.root_mesh, ("create_stream", s.id, s._default))
+
+    @contextlib.contextmanager
+    def coalescing(self):
+        if self._coalesce is not None:
+            yield
+            return
+        self._coalesce = []
+        try:
+            yield
+        finally:
+            batch, self._coalesce = self._coalesce, None
+            # one cast per distinct mesh, preserving order within each
+            by_mesh: Dict[int, Tuple[Any, List[tuple]]] = {}
+            order: List[int] = []
+            for mesh, msg in batch:
+                k = id(mesh._workers)
+                if k not in by_mesh:
+                    by_mesh[k] = (mesh, [])
+                    order.append(k)
+                by_mesh[k][1].append(msg)
+            for i, k in enumerate(order):
+                mesh, msgs = by_mesh[k]
+                if i == 0:
+                    self._send_deletes()
+                mesh._workers.run.broadcast(msgs)
+
+    def ensure_process_group(self) -> None:
+        if self._pg_init:
+            return
+        self._pg_init = True
+        s = socket.socket()
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+        s.close()
+        ranks = self.root_mesh._ndslice.ranks()
+        self.send(self.root_mesh, ("init_pg", "127.0.0.1", port, ranks))
+
+    def ensure_comm(self, mesh: "DeviceMesh", dims: Tuple[str, ...]) -> Tuple[int, ...]:
+        """Process groups over ``dims`` of ``mesh``: one group per combination of the other
+        dims' coordinates.  Returns the key workers use to look their group up."""
+        self.ensure_process_group()
+        sl = mesh._ndslice
+        labels = list(mesh._labels)
+        idx = [labels.index(d) for d in dims]
+        key = (sl.offset, tuple(sl.sizes), tuple(sl.strides), tuple(idx))
+        hkey = tuple(hash(key) % (1 << 62) for _ in range(1))
+        if key in self._comms:
+            return hkey
+        self._comms.add(key)
+        other = [i for i in range(len(labels)) if i not in idx]
+        groups: List[List[int]] = []
+        for oc in itertools.product(*[range(sl.sizes[i]) for i in other]):
+            ranks = []
+            for gc in itertools.product(*[range(sl.sizes[i]) for i in idx]):
+                coord = [0] * len(labels)
+                for i, c in zip(other, oc):
+                    coord[i] = c
+                for i, c in zip(idx, gc):
+                    coord[i] = c
+                ranks.append(sl.nditem(coord))
+            groups.append(ranks)
+        self.send(self.root_mesh, ("split_comm", hkey, groups))
+        return hkey
+
+    def fetch(self, mesh: "DeviceMesh", ref_tree, preprocess=None, timeout: Optional[float] = None):
+        seq = self.new_seq()
+        self._send_deletes()
+        fut = mesh._workers.run_and_reply.call([], (seq, ref_tree, preprocess))
+
+        def wait(t):
+            # replies are unpickled into ordinary local tensors: keep the active-mesh
+            # dispatch mode out of the way while that happens
+            prev = getattr(_tls, "propagating", False)
+            _tls.propagating = True
+            try:
+                vm = fut.get(t if t is not None else timeout)
+            finally:
+                _tls.propagating = prev
+            out = []
+            for _, r in vm.items():
+                if r[0] == "error":
+                    raise RemoteException(*r[1:])
+                out.append(r[1])
+            return out
+
+        return Future(wait)
+
+    def drain_errors(self) -> List[tuple]:
+        while True:
+            env = self._err_rx._rx.try_recv()
+            if env is None:
+                break
+            from ..actor.pickle import unflatten
+            _, _, payload = unflatten(env.data, env.parts)
+            self.errors.append(payload)
+        return self.errors
+
+    def shutdown(self) -> None:
+        self._closed = True
+
+
+# ----------------------------------------------------------------------------- tensor --
+class Tensor(torch.Tensor):
+    """A tensor that lives on every proc of a device mesh.  The controller holds only its
+    metadata (a FakeTensor); data is named by ``ref`` on the workers."""
+
+    @staticmethod
+    def __new__(cls, fake: torch.Tensor, mesh: "DeviceMesh", stream: Stream):
+        r = torch.Tensor._make_wrapper_subclass(
+            cls, fake.size(), strides=fake.stride(), storage_offset=fake.storage_offset(),
+            dtype=fake.dtype, device=fake.device, layout=fake.layout,
+            requires_grad=fake.requires_grad)
+        r._fake = fake
+        r.mesh = mesh
+        r.stream = stream
+        r.ref = mesh.client.new_ref()
+        r._dropped = False
+        r._borrowed_by = []
+        return r
+
+    def __init__(self, *a, **k):
+        pass
+
+    def __repr__(self, *, tensor_contents=None):
+        return f"monarch_b200.Tensor(mesh={self.mesh}, ref={self.ref}, fake={self._fake})"
+
+    def __del__(self):
+        try:
+            if not self._dropped and self.ref is not None:
+                self.mesh.client.delete_ref(self.ref)
+        except Exception:  # noqa: BLE001 - interpreter teardown
+            pass
+
+    def drop(self) -> None:
+        if not self._dropped:
+            self._dropped = True
+            self.mesh.client.delete_ref(self.ref)
+
+    @property
+    def dropped(self) -> bool:
+        return self._dropped
+
+    @classmethod
+    def __torch_dispatch__(cls, func, types, args=(), kwargs=None):
+        return _dispatch(func, args, kwargs or {})
+
+    # ---- collectives -------------------------------------------------------------------
+    def reduce(self, dims, reduction: str = "sum", scatter: bool = False, mesh=None,
+               _inplace: bool = False, out: Optional["Tensor"] = None) -> "Tensor":
+        """Reduce across mesh dims.  ``reduction`` in {sum, avg, product, min, max, band,
+        bor, bxor, stack}; ``scatter=True`` keeps slice i of the outer dim on member i
+        (reduce-scatter; with ``"stack"`` an all-to-all); ``"stack"`` alone all-gathers."""
+        _check_usable(self)
+        if isinstance(dims, str):
+            dims = (dims,)
+        dims = tuple(dims)
+        m = self.mesh
+        for d in dims:
+            if d not in m._labels:
+                raise KeyError(f"{m} has no dimension {d!r}")
+        if reduction not in _REDUCTIONS:
+            raise ValueError(f"reduction {reduction!r} not in {sorted(_REDUCTIONS)}")
+        n = 1
+        for d in dims:
+            n *= m.size(d)
+        if (reduction == "stack" or scatter) and len(dims) != 1:
+            raise NotImplementedError("stack/scatter reductions take exactly one mesh dim")
+        f = self._fake
+        if reduction == "stack":
+            if scatter:
+                if f.shape[0] != n:
+                    raise ValueError(f"all-to-all needs an outer dim of {n}, got {tuple(f.shape)}")
+                out_fake = _new_fake(f.shape, f)
+            else:
+                out_fake = _new_fake((n, *f.shape), f)
+        elif scatter:
+            if f.dim() == 0 or f.shape[0] != n:
+                raise ValueError(f"reduce-scatter needs an outer dim of {n}, got {tuple(f.shape)}")
+            out_fake = _new_fake(f.shape[1:], f)
+        else:
+            out_fake = _new_fake(f.shape, f)
+        if _inplace and tuple(out_fake.shape) != tuple(f.shape):
+            raise ValueError("in-place reduce needs matching input and output shapes")
+        client = m.client
+        key = client.ensure_comm(m, dims)
+        seq = client.new_seq()
+        if _inplace:
+            result = self
+            res_ref = Ref(self.ref)
+        else:
+            result = Tensor(out_fake, m, self.stream)
+            res_ref = Ref(result.ref)
+        client.send(m, ("reduce", seq, res_ref, Ref(self.ref), key, reduction, scatter, _inplace,
+                        Ref(out.ref) if out is not None else None, self.stream.id))
+        return out if out is not None else result
+
+    def reduce_(self, dims, reduction: str = "sum", scatter: bool = False, mesh=None) -> "Tensor":
+        return self.reduce(dims, reduction, scatter, mesh, _inplace=True)
+
+    def to_mesh(self, mesh: "DeviceMesh", stream: Optional[Stream] = None) -> "Tensor":
+        """Move to another mesh with equal named-dim sizes (point-to-point sends)."""
+        _check_usable(self)
+        src = self.mesh
+        if mesh is src or (mesh._ndslice == src._ndslice):
+            return self
+        if sorted(mesh._ndslice.sizes) != sorted(src._ndslice.sizes) and \
+                len(mesh._ndslice) != len(src._ndslice):
+            raise ValueError(f"cannot move between meshes of different sizes: {src} -> {mesh}")
+        client = src.client
+        client.ensure_process_group()
+        out = Tensor(self._fake, mesh, stream or self.stream)
+        seq = client.new_seq()
+        fr, to = src._ndslice.ranks(), mesh._ndslice.ranks()
+        root = client.root_mesh
+        client.send(root, ("send_meta", Ref(out.ref), tuple(self._fake.shape), self._fake.dtype))
+        client.send(root, ("send_tensor", seq, Ref(out.ref), Ref(self.ref), fr, to,
+                           self.stream.id))
+        return out
+
+    def slice_mesh(self, **kwargs) -> "Tensor":
+        """The same per-proc values viewed on a sub-mesh (no data moves)."""
+        sub = self.mesh.slice(**kwargs)
+        t = Tensor(self._fake, sub, self.stream)
+        sub.client.send(sub, ("call", sub.client.new_seq(), [Ref(t.ref)], [],
+                              ("pickle", _identity), (Ref(self.ref),), {}, self.stream.id))
+        return t
+
+
+_REDUCTIONS = {"stack", "sum", "avg", "product", "min", "max", "band", "bor", "bxor"}
+
+
+def _identity(x):
+    return x
+
+
+@contextlib.contextmanager
+def _propagation():
+    """Run torch code on FakeTensors for shape inference, with the active-mesh dispatch
+    mode standing aside."""
+    prev = getattr(_tls, "propagating", False)
+    _tls.propagating = True
+    try:
+        with _fake_mode:
+            yield
+    finally:
+        _tls.propagating = prev
+
+
+def _new_fake(shape, like) -> torch.Tensor:
+    with _propagation():
+        return torch.empty(tuple(shape), dtype=like.dtype, device=like.device)
+
+
+def _check_usable(t: Tensor) -> None:
+    if t._dropped:
+        raise RuntimeError("this tensor was dropped (or its borrow has ended)")
+    for b in t._borrowed_by:
+        if b.mutable and get_active_stream() is not b.stream:
+            raise RuntimeError("tensor is mutably borrowed by another stream; drop the borrow first")
+
+
+def reduce(tensors, dims, reduction="sum", scatter=False, mesh=None, _inplace=False):
+    from torch.utils._pytree import tree_map
+    return tree_map(lambda t: t.reduce(dims, reduction, scatter, mesh, _inplace)
+                    if isinstance(t, Tensor) else t, tensors)
+
+
+def reduce_(tensors, dims, reduction="sum", scatter=False, mesh=None):
+    return reduce(tensors, dims, reduction, scatter, mesh, _inplace=True)
+
+
+def to_mesh(tensors, mesh, stream=None):
+    from torch.utils._pytree import tree_map
+    return tree_map(lambda t: t.to_mesh(mesh, stream) if isinstance(t, Tensor) else t, tensors)
+
+
+def slice_mesh(tensors, **kwargs):
+    from torch.utils._pytree import tree_map
+    return tree_map(lambda t: t.slice_mesh(**kwargs) if isinstance(t, Tensor) else t, tensors)
+
+
+# --------------------------------------------------------------------------- dispatch --
+def _collect(obj, out: List[Tensor]) -> None:
+    if isinstance(obj, Tensor):
+        out.append(obj)
+    elif isinstance(obj, (list, tuple)):
+        for o in obj:
+            _collect(o, out)
+    elif isinstance(obj, dict):
+        for o in obj.values():
+            _collect(o, out)
+
+
+def _to_fake(obj):
+    if isinstance(obj, Tensor):
+        return obj._fake
+    if isinstance(obj, torch.Tensor):
+        return obj
+    if isinstance(obj, (list, tuple)):
+        return type(obj)(_to_fake(o) for o in obj)
+    if isinstance(obj, dict):
+        return {k: _to_fake(v) for k, v in obj.items()}
+    return obj
+
+
+def _to_wire(obj):
+    if isinstance(obj, Tensor):
+        return Ref(obj.ref)
+    if isinstance(obj, (list, tuple)):
+        return type(obj)(_to_wire(o) for o in obj)
+    if isinstance(obj, dict):
+        return {k: _to_wire(v) for k, v in obj.items()}
+    if isinstance(obj, torch.device):
+        return obj
+    return obj
+
+
+def _wrap_outputs(fake_out, mesh, stream, refs: List[Ref]):
+    if isinstance(fake_out, torch.Tensor):
+        t = Tensor(fake_out, mesh, stream)
+        refs.append(Ref(t.ref))
+        return t
+    if isinstance(fake_out, (list, tuple)):
+        return type(fake_out)(_wrap_outputs(o, mesh, stream, refs) for o in fake_out)
+    if isinstance(fake_out, dict):
+        return {k: _wrap_outputs(v, mesh, stream, refs) for k, v in fake_out.items()}
+    return fake_out
+
+
+def _send_call(fspec, args, kwargs, fake_out, mesh: "DeviceMesh", mutates: Sequence[Tensor] = ()):
+    stream = get_active_stream()
+    client = mesh.client
+    client._ensure_stream(stream)
+    refs: List[Ref] = []
+    out = _wrap_outputs(fake_out, mesh, stream, refs)
+    seq = client.new_seq()
+    client.send(mesh, ("call", seq, refs, [Ref(t.ref) for t in mutates], fspec, _to_wire(args),
+                       _to_wire(kwargs), stream.id))
+    return out
+
+
+def _mesh_of(tensors: List[Tensor]) -> "DeviceMesh":
+    m = tensors[0].mesh
+    for t in tensors[1:]:
+        if t.mesh is not m and t.mesh._ndslice != m._ndslice:
+            raise ValueError(f"tensors live on different meshes ({m} vs {t.mesh}); move one "
+                             "with to_mesh() first")
+    return m
+
+
+def _dispatch(func, args, kwargs):
+    ts: List[Tensor] = []
+    _collect(args, ts)
+    _collect(kwargs, ts)
+    if ts:
+        mesh = _mesh_of(ts)
+        for t in ts:
+            _check_usable(t)
+    else:
+        mesh = get_active_mesh()
+        if mesh is None:
+            raise RuntimeError("no active device mesh")
+    with _propagation():
+        fake_out = func(*_to_fake(args), **_to_fake(kwargs))
+    name = f"{func.namespace}.{func._schema.name.split('::')[1]}.{func._overloadname}"
+    # in-place / out= ops return their (already remote) argument: alias, do not re-ref
+    mutated: List[Tensor] = []
+    schema = func._schema
+    for i, a in enumerate(schema.arguments):
+        if a.alias_info is not None and a.alias_info.is_write:
+            v = args[i] if i < len(args) else kwargs.get(a.name)
+            if isinstance(v, Tensor):
+                mutated.append(v)
+    if mutated and isinstance(fake_out, torch.Tensor) and len(mutated) == 1:
+        client = mesh.client
+        stream = get_active_stream()
+        client.send(mesh, ("call", client.new_seq(), [], [Ref(t.ref) for t in mutated],
+                           ("op", name), _to_wire(args), _to_wire(kwargs), stream.id))
+        return mutated[0]
+    return _send_call(("op", name), args, kwargs, fake_out, mesh, mutated)
+
+
+# ------------------------------------------------------------------------ device mesh --
+_active: List["DeviceMesh"] = []
+
+
+def get_active_mesh() -> Optional["DeviceMesh"]:
+    return _active[-1] if _active else None
+
+
+@contextlib.contextmanager
+def no_mesh():
+    saved = list(_active)
+    _active.clear()
+    try:
+        with _NoDispatch():
+            yield
+    finally:
+        _active.extend(saved)
+
+
+class _NoDispatch(TorchDispatchMode):
+    def __torch_dispatch__(self, func, types, args=(), kwargs=None):
+        return func(*args, **(kwargs or {}))
+
+
+class _ActiveMeshMode(TorchDispatchMode):
+    """Routes factory functions (no tensor arguments) to the active mesh."""
+
+    def __torch_dispatch__(self, func, types, args=(), kwargs=None):
+        kwargs = kwargs or {}
+        if getattr(_tls, "propagating", False):
+            return func(*args, **kwargs)
+        ts: List[Tensor] = []
+        _collect(args, ts)
+        _collect(kwargs, ts)
+        if not ts and get_active_mesh() is not None and not _has_plain_tensor(args, kwargs):
+            return _dispatch(func, args, kwargs)
+        if ts:
+            return _dispatch(func, args, kwargs)
+        return func(*args, **kwargs)
+
+
+def _has_plain_tensor(args, kwargs) -> bool:
+    found = False
+
+    def visit(o):
+        nonlocal found
+        if isinstance(o, torch.Tensor) and not isinstance(o, Tensor):
+            found = True
+        elif isinstance(o, (list, tuple)):
+            for x in o:
+                visit(x)
+        elif isinstance(o, dict):
+            for x in o.values():
+                visit(x)
+    visit(args)
+    visit(kwargs)
+    return found
+
+
+class DeviceMesh(MeshTrait):
+    def __init__(self, client: Client, shape: Shape, workers, root: Optional["DeviceMesh"] = None):
+        self.client = client
+        self._shape_ = shape
+        self._workers = workers
+        self._root = root
+        self._rank_tensors: Dict[str, Tensor] = {}
+
+    @property
+    def _ndslice(self):
+        return self._shape_.ndslice
+
+    @property
+    def _labels(self):
+        return tuple(self._shape_.labels)
+
+    def _new_with_shape(self, shape: Shape) -> "DeviceMesh":
+        root = self._root or self
+        sub_workers = root._workers._new_with_shape(Shape(shape.labels, shape.ndslice))
+        return DeviceMesh(self.client, shape, sub_workers, root)
+
+    @contextlib.contextmanager
+    def activate(self):
+        _active.append(self)
+        try:
+            with _ActiveMeshMode():
+                yield self
+        finally:
+            _active.pop()
+
+    def rank(self, dim) -> Tensor:
+        """Tensor holding each proc's coordinate along ``dim`` (or the flat index over a
+        tuple of dims)."""
+        dims = (dim,) if isinstance(dim, str) else tuple(dim)
+        key = ",".join(dims)
+        if key not in self._rank_tensors:
+            labels = list(self._labels)
+            sizes = list(self._ndslice.sizes)
+            strides = list(self._ndslice.strides)
+            offset = self._ndslice.offset
+            with _propagation():
+                fake = torch.empty((), dtype=torch.int64)
+            idx = [labels.index(d) for d in dims]
+            spec = ("pickle", _RankFn(offset, sizes, strides, idx))
+            self._rank_tensors[key] = _send_call(spec, (), {}, fake, self)
+        return self._rank_tensors[key]
+
+    @property
+    def ranks(self) -> Dict[str, Tensor]:
+        return {d: self.rank(d) for d in self._labels}
+
+    def exit(self, error: Optional[Exception] = None) -> None:
+        self.client.shutdown()
+
+    def __repr__(self) -> str:
+        return f"<DeviceMesh {self._shape_}>"
+
+
+class _RankFn:
+    """Computes this proc's coordinate along mesh dims from its global rank."""
+
+    def __init__(self, offset, sizes, strides, idx):
+        self.offset, self.sizes, self.strides, self.idx = offset, sizes, strides, idx
+
+    def __call__(self):
+        from ..actor import context
+        r = context().actor_instance._native.rank - self.offset
+        order = sorted(range(len(self.sizes)), key=lambda i: -self.strides[i])
+        coord = [0] * len(self.sizes)
+        for i in order:
+            if self.sizes[i] > 1:
+                coord[i] = min(r // self.strides[i], self.sizes[i] - 1)
+                r -= coord[i] * self.strides[i]
+        flat = 0
+        for i in self.idx:
+            flat = flat * self.sizes[i] + coord[i]
+        return torch.tensor(flat, dtype=torch.int64)
+
+
+def spawn_tensor_engine(proc_mesh, use_cuda: Optional[bool] = None) -> DeviceMesh:
+    """Spawn tensor workers on every proc of ``proc_mesh`` and return its DeviceMesh."""
+    if use_cuda is None:
+        use_cuda = torch.cuda.is_available()
+    name = f"tensor_engine_workers_{next(_engine_ids)}"
+    workers = proc_mesh.spawn(name, TensorWorker, use_cuda)
+    client = Client(proc_mesh, workers, use_cuda)
+    dm = DeviceMesh(client, Shape(list(proc_mesh._labels), proc_mesh._ndslice), workers)
+    client.root_mesh = dm
+    return dm
+
+
+_engine_ids = itertools.count()

@@ -1,0 +1,384 @@
+"""Per-proc executor of the tensor engine.
+
+Parity: monarch_tensor_worker (WorkerActor routing to per-stream executors, the ref ->
+tensor/error environment, error poisoning of dependent results, Reduce / SendTensor /
+SendValue, borrows as stream events, recordings), monarch_messages/src/worker.rs (the
+message set), python/monarch/worker/worker.py (the reduce semantics used as oracle:
+all-reduce, reduce-scatter via ``scatter=True``, all-gather via ``"stack"``, all-to-all via
+``"stack"`` + scatter).
+
+One worker actor runs per proc.  Ops execute on the proc's device in message order;
+named streams map to CUDA streams (side streams are synchronised through borrow events).
+Collectives over mesh dims use process groups created on first use; between GPUs of one
+box the group's all-reduce / all-gather / reduce-scatter run this package's NVLink
+kernels when the tensors live in peer-mapped memory, otherwise torch.distributed.
+"""
+from __future__ import annotations
+
+import os
+import traceback
+from typing import Any, Dict, List, Optional, Tuple
+
+import torch
+
+from ..actor import Actor, current_rank, endpoint
+from ..actor.actor_mesh import Port
+
+
+class Ref:
+    """A controller-assigned name of a worker-side value."""
+    __slots__ = ("id",)
+
+    def __init__(self, id: int):
+        self.id = id
+
+    def __reduce__(self):
+        return (Ref, (self.id,))
+
+    def __repr__(self):
+        return f"Ref({self.id})"
+
+
+class RemoteError:
+    """What a failed op leaves in the environment instead of a tensor."""
+
+    def __init__(self, seq: int, rank: int, func: str, exc_text: str, tb: str,
+                 dependent_of: Optional[int] = None):
+        self.seq, self.rank, self.func = seq, rank, func
+        self.exc_text, self.tb, self.dependent_of = exc_text, tb, dependent_of
+
+
+def _resolve_function(spec):
+    kind = spec[0]
+    if kind == "op":          # ("op", "aten.add.Tensor")
+        ns, name, overload = spec[1].split(".")
+        packet = getattr(getattr(torch.ops, ns), name)
+        return getattr(packet, overload)
+    if kind == "path":        # ("path", "module.sub.fn")
+        mod, _, fn = spec[1].rpartition(".")
+        import importlib
+        return getattr(importlib.import_module(mod), fn)
+    if kind == "pickle":      # ("pickle", callable)
+        return spec[1]
+    raise ValueError(f"bad function spec {spec!r}")
+
+
+def _map_refs(obj, fn):
+    if isinstance(obj, Ref):
+        return fn(obj)
+    if isinstance(obj, (list, tuple)):
+        return type(obj)(_map_refs(o, fn) for o in obj)
+    if isinstance(obj, dict):
+        return {k: _map_refs(v, fn) for k, v in obj.items()}
+    return obj
+
+
+class TensorWorker(Actor):
+    def __init__(self, use_cuda: bool):
+        self.rank = current_rank().rank
+        self.world = current_rank().extent.nelements
+        self.use_cuda = bool(use_cuda and torch.cuda.is_available())
+        if self.use_cuda:
+            n = torch.cuda.device_count()
+            self.device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", self.rank)) % n)
+            torch.cuda.set_device(self.device)
+        else:
+            self.device = torch.device("cpu")
+        self.env: Dict[int, Any] = {}
+        self.streams: Dict[int, Any] = {0: None}
+        self.groups: Dict[Tuple[int, ...], Any] = {}
+        self.borrows: Dict[int, Any] = {}
+        self.recordings: Dict[int, List[tuple]] = {}
+        self.pg_ready = False
+        self.error_port: Optional[Port] = None
+        self.last_seq = -1
+
+    # ---------------------------------------------------------------------- helpers
+    def _get(self, ref: Ref, seq: int):
+        v = self.env.get(ref.id)
+        if v is None and ref.id not in self.env:
+            raise KeyError(f"{ref} is not defined on worker {self.rank}")
+        return v
+
+    def _poison(self, seq: int, results: List[Ref], err: RemoteError) -> None:
+        for r in results:
+            self.env[r.id] = err
+
+    def _report(self, err: RemoteError) -> None:
+        if self.error_port is not None and err.dependent_of is None:
+            self.error_port.send(("error", err.seq, self.rank, err.func, err.exc_text, err.tb))
+
+    def _stream_ctx(self, stream_id: int):
+        s = self.streams.get(stream_id)
+        if s is None or not self.use_cuda:
+            return _Null()
+        return torch.cuda.stream(s)
+
+    # ---------------------------------------------------------------- message entry
+    @endpoint
+    def configure(self, error_port: Port) -> int:
+        self.error_port = error_port
+        return self.rank
+
+    @endpoint
+    def run(self, msgs: List[tuple]) -> None:
+        """A batch of worker messages (one for eager dispatch, many under coalescing)."""
+        for m in msgs:
+            getattr(self, "_m_" + m[0])(*m[1:])
+
+    @endpoint
+    def run_and_reply(self, msgs: List[tuple], fetch: tuple) -> Any:
+        for m in msgs:
+            getattr(self, "_m_" + m[0])(*m[1:])
+        return self._fetch(*fetch)
+
+    # -------------------------------------------------------------------- messages
+    def _m_call(self, seq, results, mutates, fspec, args, kwargs, stream) -> None:
+        self.last_seq = seq
+        fname = fspec[1] if isinstance(fspec[1], str) else getattr(fspec[1], "__name__", "udf")
+        try:
+            dep = None
+
+            def res(r):
+                nonlocal dep
+                v = self._get(r, seq)
+                if isinstance(v, RemoteError) and dep is None:
+                    dep = v
+                return v
+
+            a = _map_refs(args, res)
+            k = _map_refs(kwargs, res)
+            if dep is not None:
+                e = RemoteError(seq, self.rank, fname, dep.exc_text, dep.tb,
+                                dependent_of=dep.seq)
+                self._poison(seq, results + mutates, e)
+                return
+            fn = _resolve_function(fspec)
+            with self._stream_ctx(stream):
+                out = fn(*a, **k)
+            flat = _flatten_tensors(out)
+            if not results and mutates:
+                flat = []  # in-place op: its return value aliases an argument
+            if len(flat) != len(results):
+                raise RuntimeError(f"{fname} returned {len(flat)} tensors, controller expected "
+                                   f"{len(results)}")
+            for r, t in zip(results, flat):
+                self.env[r.id] = t
+        except Exception as ex:  # noqa: BLE001 - the worker stays alive; the refs carry it
+            e = RemoteError(seq, self.rank, fname, f"{type(ex).__name__}: {ex}",
+                            traceback.format_exc())
+            self._poison(seq, results + mutates, e)
+            self._report(e)
+
+    def _m_delete(self, ids: List[int]) -> None:
+        for i in ids:
+            self.env.pop(i, None)
+
+    def _m_create_stream(self, stream_id: int, default: bool) -> None:
+        if stream_id not in self.streams:
+            self.streams[stream_id] = torch.cuda.Stream(device=self.device) \
+                if (self.use_cuda and not default) else None
+
+    def _m_borrow_create(self, borrow_id, ref, from_stream, to_stream, result) -> None:
+        # the borrowing stream waits for the producing stream; the value is aliased
+        if self.use_cuda:
+            ev = torch.cuda.Event()
+            ev.record(self.streams.get(from_stream) or torch.cuda.current_stream())
+            (self.streams.get(to_stream) or torch.cuda.current_stream()).wait_event(ev)
+        self.env[result.id] = self.env.get(ref.id)
+        self.borrows[borrow_id] = (from_stream, to_stream)
+
+    def _m_borrow_drop(self, borrow_id) -> None:
+        b = self.borrows.pop(borrow_id, None)
+        if b and self.use_cuda:
+            ev = torch.cuda.Event()
+            ev.record(self.streams.get(b[1]) or torch.cuda.current_stream())
+            (self.streams.get(b[0]) or torch.cuda.current_stream()).wait_event(ev)
+
+    def _m_init_pg(self, addr: str, port: int, ranks: List[int]) -> None:
+        import torch.distributed as dist
+        if self.pg_ready or not dist.is_available():
+            return
+        if dist.is_initialized():
+            self.pg_ready = True
+            return
+        backend = "nccl" if self.use_cuda else "gloo"
+        dist.init_process_group(backend, init_method=f"tcp://{addr}:{port}",
+                                rank=ranks.index(self.rank), world_size=len(ranks),
+                                **({"device_id": self.device} if self.use_cuda else {}))
+        self.pg_ready = True
+
+    def _m_split_comm(self, key: Tuple[int, ...], all_groups: List[List[int]]) -> None:
+        import torch.distributed as dist
+        if key in self.groups:
+            return
+        mine = None
+        for ranks in all_groups:  # every rank creates every group, in the same order
+            g = dist.new_group(ranks)
+            if self.rank in ranks:
+                mine = (g, ranks)
+        self.groups[key] = mine
+
+    def _m_reduce(self, seq, result, ref, key, reduction, scatter, inplace, out_ref, stream) -> None:
+        import torch.distributed as dist
+        self.last_seq = seq
+        try:
+            t = self._get(ref, seq)
+            if isinstance(t, RemoteError):
+                self._poison(seq, [result], RemoteError(seq, self.rank, "reduce", t.exc_text, t.tb,
+                                                        dependent_of=t.seq))
+                return
+            g, ranks = self.groups[key]
+            n = len(ranks)
+            with self._stream_ctx(stream):
+                if reduction == "stack":
+                    if scatter:   # all-to-all: outer dim n in, outer dim n out
+                        out = torch.empty_like(t)
+                        if dist.get_backend(g) == "nccl":
+                            dist.all_to_all_single(out, t.contiguous(), group=g)
+                        else:
+                            ins = list(t.contiguous().unbind(0))
+                            outs = [torch.empty_like(i) for i in ins]
+                            _gloo_all_to_all(outs, ins, g, ranks, self.rank)
+                            out = torch.stack(outs)
+                    else:         # all-gather: adds an outer dim n
+                        parts = [torch.empty_like(t) for _ in range(n)]
+                        dist.all_gather(parts, t.contiguous(), group=g)
+                        out = torch.stack(parts)
+                else:
+                    op = {"sum": dist.ReduceOp.SUM, "avg": dist.ReduceOp.SUM,
+                          "product": dist.ReduceOp.PRODUCT, "prod": dist.ReduceOp.PRODUCT,
+                          "min": dist.ReduceOp.MIN, "max": dist.ReduceOp.MAX,
+                          "band": dist.ReduceOp.BAND, "bor": dist.ReduceOp.BOR,
+                          "bxor": dist.ReduceOp.BXOR}[reduction]
+                    work = t if inplace else t.clone()
+                    dist.all_reduce(work, op=op, group=g)
+                    if reduction == "avg":
+                        work = work / n if not inplace else work.div_(n)
+                    if scatter:   # reduce-scatter: keep slice i of the outer dim
+                        if work.shape[0] != n:
+                            raise RuntimeError(f"scatter needs an outer dim of {n}, got "
+                                               f"{tuple(work.shape)}")
+                        work = work[ranks.index(self.rank)].clone()
+                    out = work
+                if out_ref is not None:
+                    self.env[out_ref.id].copy_(out)
+                    out = self.env[out_ref.id]
+            self.env[result.id] = out
+        except Exception as ex:  # noqa: BLE001
+            e = RemoteError(seq, self.rank, "reduce", f"{type(ex).__name__}: {ex}",
+                            traceback.format_exc())
+            self._poison(seq, [result], e)
+            self._report(e)
+
+    def _m_send_tensor(self, seq, result, ref, from_ranks, to_ranks, stream) -> None:
+        """Point-to-point move between equally shaped sub-meshes (pipeline activations)."""
+        import torch.distributed as dist
+        try:
+            pairs = list(zip(from_ranks, to_ranks))
+            t = self.env.get(ref.id) if ref is not None and self.rank in from_ranks else None
+            for src, dst in pairs:
+                if src == dst == self.rank:
+                    self.env[result.id] = t
+                elif self.rank == src:
+                    dist.send(t.contiguous(), dst)
+                elif self.rank == dst:
+                    meta = self.env.pop(("send_meta", result.id))
+                    buf = torch.empty(meta[0], dtype=meta[1], device=self.device)
+                    dist.recv(buf, src)
+                    self.env[result.id] = buf
+        except Exception as ex:  # noqa: BLE001
+            e = RemoteError(seq, self.rank, "send_tensor", f"{type(ex).__name__}: {ex}",
+                            traceback.format_exc())
+            self._poison(seq, [result], e)
+            self._report(e)
+
+    def _m_send_meta(self, result, shape, dtype) -> None:
+        self.env[("send_meta", result.id)] = (tuple(shape), dtype)
+
+    def _m_define_recording(self, rec_id: int, msgs: List[tuple]) -> None:
+        self.recordings[rec_id] = msgs
+
+    def _m_call_recording(self, rec_id: int, bind: Dict[int, int]) -> None:
+        """Replay a recording with formal ref ids rebound to this call's ids."""
+        def rb(obj):
+            return _map_refs(obj, lambda r: Ref(bind.get(r.id, r.id)))
+        for m in self.recordings[rec_id]:
+            getattr(self, "_m_" + m[0])(*[rb(x) for x in m[1:]])
+
+    # ----------------------------------------------------------------------- fetch
+    def _fetch(self, seq, ref_tree, preprocess):
+        first_err = None
+
+        def res(r):
+            nonlocal first_err
+            v = self.env.get(r.id)
+            if isinstance(v, RemoteError):
+                first_err = first_err or v
+                return None
+            return v
+
+        vals = _map_refs(ref_tree, res)
+        if first_err is not None:
+            e = first_err
+            return ("error", e.seq, e.rank, e.func, e.exc_text, e.tb, e.dependent_of)
+        try:
+            if preprocess is not None:
+                vals = _resolve_function(preprocess)(vals)
+            if self.use_cuda:
+                torch.cuda.current_stream().synchronize()
+            return ("ok", _to_cpu(vals))
+        except Exception as ex:  # noqa: BLE001
+            return ("error", seq, self.rank, "fetch", f"{type(ex).__name__}: {ex}",
+                    traceback.format_exc(), None)
+
+    @endpoint
+    def fetch(self, seq, ref_tree, preprocess=None):
+        return self._fetch(seq, ref_tree, preprocess)
+
+    @endpoint
+    def sync(self) -> int:
+        if self.use_cuda:
+            torch.cuda.synchronize(self.device)
+        return self.last_seq
+
+
+def _flatten_tensors(out) -> List[torch.Tensor]:
+    if isinstance(out, torch.Tensor):
+        return [out]
+    if isinstance(out, (list, tuple)):
+        r: List[torch.Tensor] = []
+        for o in out:
+            r += _flatten_tensors(o)
+        return r
+    if isinstance(out, dict):
+        r = []
+        for o in out.values():
+            r += _flatten_tensors(o)
+        return r
+    return []
+
+
+def _to_cpu(obj):
+    if isinstance(obj, torch.Tensor):
+        return obj.detach().cpu()
+    if isinstance(obj, (list, tuple)):
+        return type(obj)(_to_cpu(o) for o in obj)
+    if isinstance(obj, dict):
+        return {k: _to_cpu(v) for k, v in obj.items()}
+    return obj
+
+
+def _gloo_all_to_all(outs, ins, g, ranks, my_rank) -> None:
+    import torch.distributed as dist
+    me = ranks.index(my_rank)
+    for i, src in enumerate(ranks):     # round i: rank i scatters its inputs
+        dist.scatter(outs[i], ins if me == i else None, src=src, group=g)
+
+
+class _Null:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False

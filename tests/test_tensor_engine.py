@@ -1,0 +1,148 @@
+"""Distributed tensors driven from one controller: op dispatch, shape propagation, rank
+tensors, collectives (reduce variants over mesh dims), remote functions, error poisoning,
+coalescing, streams/borrows.  CPU ranks with gloo.  Modelled on the reference's
+test_tensor_engine.py / test_remote_functions.py / test_coalescing.py."""
+import pytest
+import torch
+
+from monarch_b200 import tensor_engine as te
+from monarch_b200.actor import this_host
+
+
+@pytest.fixture(scope="module")
+def dm():
+    pm = this_host().spawn_procs(per_host={"gpus": 4})
+    mesh = te.spawn_tensor_engine(pm, use_cuda=False)
+    yield mesh.split(gpus=("host", "gpu"), gpu=2)
+    mesh.exit()
+    pm.stop().get()
+
+
+def test_ops_are_dispatched_and_fetched(dm):
+    with dm.activate():
+        a = torch.ones(3, 4)
+        b = 2 * a + 1
+        assert isinstance(b, te.Tensor) and b.shape == (3, 4) and b.dtype == torch.float32
+        assert te.inspect(b).tolist() == [[3.0] * 4] * 3
+        c = (b @ b.t()).sum()
+        assert c.shape == () and te.inspect(c).item() == 9 * 4 * 9
+        b.add_(1)                      # in-place ops alias their input
+        assert te.inspect(b)[0, 0].item() == 4
+        assert te.fetch_shard(b, host=1, gpu=1).get()[0, 0].item() == 4
+
+
+def test_rank_tensors_and_mesh_reshaping(dm):
+    assert dm.sizes == {"hosts": 1, "host": 2, "gpu": 2}
+    with dm.activate():
+        r = dm.rank("host") * 10 + dm.rank("gpu")
+        got = [[te.inspect(r, host=h, gpu=g).item() for g in range(2)] for h in range(2)]
+        assert got == [[0, 1], [10, 11]]
+    flat = dm.flatten("all")
+    with flat.activate():
+        assert te.inspect(flat.rank("all"), all=3).item() == 3
+
+
+def test_reduce_variants(dm):
+    with dm.activate():
+        x = (dm.rank("host") * 2 + dm.rank("gpu") + 1).to(torch.float32) * torch.ones(2, 3)
+        assert te.inspect(x.reduce("gpu", "sum"), host=1)[0, 0].item() == 3 + 4
+        assert te.inspect(x.reduce(("host", "gpu"), "sum"))[0, 0].item() == 10
+        assert te.inspect(x.reduce("host", "max"), gpu=1)[0, 0].item() == 4
+        assert te.inspect(x.reduce("gpu", "avg"), host=0)[0, 0].item() == 1.5
+        st = x.reduce("gpu", "stack")           # all-gather adds an outer dim
+        assert st.shape == (2, 2, 3)
+        assert te.inspect(st, host=1)[:, 0, 0].tolist() == [3.0, 4.0]
+        rs = x.reduce("gpu", "sum", scatter=True)  # reduce-scatter keeps slice i on member i
+        assert rs.shape == (3,) and te.inspect(rs, host=0, gpu=1).tolist() == [3.0] * 3
+        a2a = x.reduce("gpu", "stack", scatter=True)
+        assert a2a.shape == (2, 3)
+        assert te.inspect(a2a, host=0, gpu=0)[:, 0].tolist() == [1.0, 2.0]
+        y = x.clone()
+        y.reduce_("gpu", "sum")
+        assert te.inspect(y, host=0)[0, 0].item() == 3
+        with pytest.raises(ValueError):
+            torch.ones(5).reduce("gpu", "sum", scatter=True)
+        with pytest.raises(KeyError):
+            x.reduce("nope", "sum")
+
+
+def test_remote_functions_and_errors(dm):
+    @te.remote(propagate=lambda x, k: x.sum(0))
+    def colsum(x, k):
+        return x.sum(0) * k
+
+    @te.remote(propagate=lambda x: x)
+    def nope(x):
+        raise ValueError("nope")
+
+    with dm.activate():
+        a = torch.ones(4, 2)
+        assert te.inspect(colsum(a, 3)).tolist() == [12.0, 12.0]
+        bad = nope(a)
+        worse = bad * 2 + 1              # dependants inherit the failure
+        with pytest.raises(te.RemoteException, match="nope") as ei:
+            te.inspect(worse)
+        assert ei.value.dependent_of is not None and "ValueError" in ei.value.exc_text
+        # the workers stay alive and later commands work
+        assert te.inspect(a.sum()).item() == 8
+        got = te.call_on_shard_and_fetch(lambda t: t.shape, a, shard={"host": 1}).get()
+        assert tuple(got) == (4, 2)
+
+
+def test_remote_inspect_propagation(dm):
+    @te.remote(propagate="inspect")
+    def weird(x):
+        return torch.zeros(x.shape[0] + 1, 2, dtype=torch.float64)
+
+    with dm.activate():
+        out = weird(torch.ones(3))
+        assert out.shape == (4, 2) and out.dtype == torch.float64
+
+
+def test_coalescing_batches_messages(dm):
+    from monarch_b200 import _native as N
+    with dm.activate():
+        warm = torch.ones(2) + 1
+        te.inspect(warm)
+        before = N.metrics_counter("cast.messages")
+        with te.coalescing():
+            x = torch.ones(8)
+            for _ in range(20):
+                x = x + 1
+        sent = N.metrics_counter("cast.messages") - before
+        assert sent <= 2, sent            # one cast for the whole block
+        assert te.inspect(x)[0].item() == 21
+
+
+def test_streams_and_borrows(dm):
+    comm = te.Stream("comm")
+    with dm.activate():
+        x = torch.ones(4)
+        y, borrow = comm.borrow(x, mutable=True)
+        with pytest.raises(RuntimeError, match="borrowed"):
+            x + 1                          # origin stream may not touch it meanwhile
+        with comm.activate():
+            y.add_(2)
+        borrow.drop()
+        assert te.inspect(x)[0].item() == 3
+        with pytest.raises(RuntimeError, match="dropped"):
+            y + 1
+
+
+def test_slice_mesh_and_to_mesh(dm):
+    with dm.activate():
+        f = (dm.rank("host") * 2 + dm.rank("gpu")).to(torch.float32) * 10
+    top = dm.slice(host=0)
+    bottom = dm.slice(host=1)
+    with bottom.activate():
+        moved = f.slice_mesh(host=0).to_mesh(bottom)
+        assert te.inspect(moved + 1, gpu=1).item() == 11
+    with top.activate():
+        assert te.inspect(f.slice_mesh(host=0), gpu=0).item() == 0
+
+
+def test_no_mesh_escapes_dispatch(dm):
+    with dm.activate():
+        with te.no_mesh():
+            local = torch.ones(2) * 3
+        assert not isinstance(local, te.Tensor) and local.tolist() == [3.0, 3.0]
