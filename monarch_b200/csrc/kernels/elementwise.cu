@@ -527,3 +527,72 @@ extern "C" int mb200_sumsq(const void* x, int64_t n, int is_bf16, float* out, vo
   sumsq_kernel<<<592, 256, 0, ST(stream)>>>(x, n, is_bf16, out);
   return (int)cudaGetLastError();
 }
+
+// ------------------------------------------------- allocation-free RMSNorm backward ----
+// See mb200_noalloc.h.  The partial weight-gradient sums live in this file-scope device
+// array instead of a caller-provided buffer.  In host code `g_noalloc_scratch` is only a
+// handle for the runtime, not a device address: the address the kernels receive comes
+// from cudaGetSymbolAddress, resolved once per device.
+#include <stdio.h>
+
+#include <mutex>
+
+#include "mb200_noalloc.h"
+
+static __device__ __align__(256) float g_noalloc_scratch[MB200_NOALLOC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int kNoallocMaxDevices = 64;
+std::mutex g_noalloc_mu;
+float* g_noalloc_ptr[kNoallocMaxDevices] = {nullptr};
+
+// Device address of the scratch on the current device (resolved on first use).
+int noalloc_scratch(float** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kNoallocMaxDevices) return MB200_NOALLOC_ERR_SYMBOL;
+  std::lock_guard<std::mutex> g(g_noalloc_mu);
+  if (!g_noalloc_ptr[dev]) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_scratch);
+    if (e != cudaSuccess || !p) {
+      fprintf(stderr, "mb200_rmsnorm_bwd_noalloc: cudaGetSymbolAddress failed on device %d: %s\n",
+              dev, cudaGetErrorString(e));
+      return e != cudaSuccess ? (int)e : MB200_NOALLOC_ERR_SYMBOL;
+    }
+    g_noalloc_ptr[dev] = p;
+  }
+  *out = g_noalloc_ptr[dev];
+  return 0;
+}
+}  // namespace
+
+extern "C" int mb200_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w,
+                                         const float* rstd, const void* dres, void* dx, void* dw,
+                                         int dw_accumulate, int rows, int d, void* stream) {
+  if (rows < 0) {
+    fprintf(stderr, "mb200_rmsnorm_bwd_noalloc: rows = %d is negative\n", rows);
+    return MB200_NOALLOC_ERR_BAD_ROWS;
+  }
+  if (d <= 0 || d % 8 || d > MB200_NOALLOC_MAX_D) {
+    fprintf(stderr,
+            "mb200_rmsnorm_bwd_noalloc: d = %d is not supported (multiple of 8, at most %d: the "
+            "built-in scratch holds %d floats)\n",
+            d, MB200_NOALLOC_MAX_D, MB200_NOALLOC_SCRATCH_FLOATS);
+    return MB200_NOALLOC_ERR_BAD_D;
+  }
+  if (rows == 0) return 0;
+  float* scratch = nullptr;
+  int rc = noalloc_scratch(&scratch);
+  if (rc) return rc;
+  // As many row-striding blocks as the scratch has room for ([blocks, d] floats).
+  int nb = mb200_rmsnorm_bwd_blocks(rows);
+  const int cap = MB200_NOALLOC_SCRATCH_FLOATS / d;
+  if (nb > cap) nb = cap;
+  rmsnorm_bwd_kernel<<<nb, RMS_BWD_THREADS, 0, ST(stream)>>>(CBF(dy), CBF(x), CBF(w), rstd,
+                                                              CBF(dres), BF(dx), scratch, rows, d);
+  rmsnorm_dw_reduce_kernel<<<(d + 255) / 256, 256, 0, ST(stream)>>>(scratch, nb, d, BF(dw),
+                                                                    dw_accumulate);
+  return (int)cudaGetLastError();
+}
