@@ -20,76 +20,10 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "comm.cuh"
 #include "mb200.h"
-#include "ptx.cuh"
 
 namespace mb200 {
-
-constexpr int kMaxRanks = 8;
-struct Peers {
-  void* p[kMaxRanks];
-};
-
-__device__ __forceinline__ uint32_t* flag_ptr(void* base, int slot, int src_rank) {
-  return reinterpret_cast<uint32_t*>(base) + (size_t)slot * kMaxRanks + src_rank;
-}
-
-// Publish `epoch` in slot `slot` of every rank's flag array (called by <= kMaxRanks
-// threads of one block after the data it announces has been written).
-__device__ __forceinline__ void signal_all(const Peers& flags, int world, int rank, int slot,
-                                           uint32_t epoch, int tid) {
-  if (tid < world) {
-    __threadfence_system();
-    st_release_sys(flag_ptr(flags.p[tid], slot, rank), epoch);
-  }
-}
-
-// Wait until every rank has published >= epoch in `slot` of *my* flag array.
-__device__ __forceinline__ bool wait_all(void* my_flags, int world, int slot, uint32_t epoch,
-                                         int* status) {
-  bool ok = true;
-  for (int r = 0; r < world && ok; ++r)
-    ok = flag_wait_ge<true>(flag_ptr(my_flags, slot, r), epoch, status);
-  return ok;
-}
-
-// Block-wide: thread 0 waits, everyone learns the outcome.
-__device__ __forceinline__ bool block_wait_all(void* my_flags, int world, int slot,
-                                               uint32_t epoch, int* status, int* sh_ok) {
-  if (threadIdx.x == 0) *sh_ok = wait_all(my_flags, world, slot, epoch, status) ? 1 : 0;
-  __syncthreads();
-  return *sh_ok != 0;
-}
-
-// "Last block out" notification: returns true in exactly one block (the one finishing
-// last), after all other blocks' writes are visible.
-__device__ __forceinline__ bool last_block_done(unsigned int* counter) {
-  __shared__ bool is_last;
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    unsigned int prev = atomicAdd(counter, 1u);
-    is_last = (prev == gridDim.x - 1);
-    if (is_last) *counter = 0;  // ready for the next launch
-  }
-  __syncthreads();
-  return is_last;
-}
-
-__device__ __forceinline__ void acc8(float (&a)[8], uint4 u) {
-  float2 x = unpack_bf16x2(u.x), y = unpack_bf16x2(u.y), z = unpack_bf16x2(u.z),
-         w = unpack_bf16x2(u.w);
-  a[0] += x.x; a[1] += x.y; a[2] += y.x; a[3] += y.y;
-  a[4] += z.x; a[5] += z.y; a[6] += w.x; a[7] += w.y;
-}
-__device__ __forceinline__ uint4 ld_nc_v4(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.relaxed.sys.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p)
-               : "memory");
-  return v;
-}
 
 // ------------------------------------------------------------------------ barrier --
 __global__ void barrier_kernel(Peers flags, int rank, int world, int slot, uint32_t epoch,

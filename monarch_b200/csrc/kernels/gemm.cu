@@ -120,7 +120,9 @@ extern "C" int mb200_gemm_bf16(const void* A, const void* B, void* C, const void
   p.status = status;
   p.b_ready = nullptr;
   p.b_ready_target = 0;
-  p.rows_per_flag = 1;
+  p.flag_chunk_elems = 1;
+  p.b_flag_elem0 = 0;
+  p.ldb = ldb;
   p.n_blk_rot = 0;
   const int tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + GEMM_BN - 1) / GEMM_BN);
   int grid = sm_count();

@@ -35,12 +35,15 @@ struct GemmParams {
   int ldc, ldr;
   int accumulate;  // C += result
   int* status;
-  // Optional gating of B tiles on readiness flags (fused all-gather -> GEMM):
-  // rows [f*rows_per_flag, (f+1)*rows_per_flag) of B are usable once
-  // b_ready[f] >= b_ready_target.
+  // Optional gating of B tiles on readiness flags (fused all-gather -> GEMM).  B (K-major,
+  // rows of K elements, leading dimension ldb) lives inside a buffer that is being filled
+  // chunk by chunk: elements [f*flag_chunk_elems, (f+1)*flag_chunk_elems) of that buffer
+  // are usable once b_ready[f] >= b_ready_target; B[0,0] is element b_flag_elem0 of it.
   const uint32_t* b_ready;
   uint32_t b_ready_target;
-  int rows_per_flag;
+  long long flag_chunk_elems;
+  long long b_flag_elem0;
+  int ldb;
   int n_blk_rot;  // rotate the N-block order so locally-owned blocks come first
 };
 
@@ -105,17 +108,21 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tmA, const CUte
         const int m0 = m_blk * GEMM_BM, n0 = n_blk * GEMM_BN;
         if (p.b_ready) {
           // Both ends of the block: a 256-row block may straddle two flag ranges.
-          const int f0 = n0 / p.rows_per_flag;
           int last_row = n0 + GEMM_BN - 1;
           if (last_row >= p.N) last_row = p.N - 1;
-          const int f1 = last_row / p.rows_per_flag;
+          const long long f0 = (p.b_flag_elem0 + (long long)n0 * p.ldb) / p.flag_chunk_elems;
+          const long long f1 =
+              (p.b_flag_elem0 + (long long)last_row * p.ldb + p.K - 1) / p.flag_chunk_elems;
           bool ok = true;
-          for (int f = f0; f <= f1 && ok; ++f)
+          for (long long f = f0; f <= f1 && ok; ++f)
             ok = flag_wait_ge<false>(p.b_ready + f, p.b_ready_target, p.status);
           if (!ok) {
             *abort_word = 1;
             break;
           }
+          // the chunks were written through the generic proxy by other CTAs; order those
+          // writes (observed via the acquire above) before this thread's TMA reads
+          asm volatile("fence.proxy.async;" ::: "memory");
         }
         bool failed = false;
         for (int k = 0; k < k_iters; ++k) {

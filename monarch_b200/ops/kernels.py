@@ -91,8 +91,13 @@ _OPTIONAL: dict[str, list] = {
                                    _i, _vp, _vp],
     "mb200_peer_copy": [_vp, _vp, _i64, _vp, ctypes.c_uint32, _vp, _i, _vp],
     "mb200_wait_flag": [_vp, ctypes.c_uint32, _i, _vp, _vp],
-    "mb200_ag_gemm": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp,
-                      ctypes.c_uint32, _i, _vp, _vp],
+    "mb200_ag_gemm": [_vp, _i, _i, _i, _i, _vp, ctypes.c_longlong, _i, _vp, _i, _vp, _i, _vp,
+                      ctypes.c_longlong, _i, _i, ctypes.c_longlong, ctypes.c_longlong,
+                      ctypes.c_longlong, _vp, ctypes.c_uint32, _vp, _i, ctypes.c_uint32, _i, _vp,
+                      _vp],
+    "mb200_gather_chunks": [_vp, _vp, ctypes.c_longlong, _i, _i, ctypes.c_longlong,
+                            ctypes.c_longlong, ctypes.c_longlong, _vp, ctypes.c_uint32, _vp, _i,
+                            ctypes.c_uint32, _i, _vp, _vp],
 }
 
 

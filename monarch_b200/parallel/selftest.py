@@ -148,6 +148,88 @@ def main() -> int:
     assert torch.allclose(m, mr, atol=1e-5) and torch.allclose(v, vr, atol=1e-5)
     assert torch.equal(pshard, master.to(bf16))
 
+    # ------------------------------------------- fused all-gather -> GEMM ------------------
+    # W [N, K] sits at an offset inside a flat buffer sharded over the ranks; one kernel
+    # gathers it over NVLink and multiplies as chunks land.
+    Ng, Kg, Mg = 4096, 2048, 1024
+    w_off = 4096                       # a 1-D parameter precedes the matrix
+    chunk = 1 << 18
+    unit = ((w_off + Ng * Kg + chunk * world - 1) // (chunk * world)) * (chunk * world)
+    sh = unit // world
+    shard = SymmBuffer(sh, bf16, dev, zero=False)
+    gfull = torch.Generator(device="cpu").manual_seed(77)
+    full_w = (torch.randn(unit, generator=gfull) * 0.05).to(bf16).to(dev)
+    shard.tensor.copy_(full_w[rank * sh:(rank + 1) * sh])
+    torch.cuda.synchronize()
+    dist.barrier()
+    unit_buf = torch.zeros(unit, dtype=bf16, device=dev)
+    cfl = torch.zeros(unit // chunk, dtype=torch.int32, device=dev)
+    torch.manual_seed(5)
+    xa = torch.randn(Mg, Kg, device=dev).to(bf16)
+    out = torch.empty(Mg, Ng, dtype=bf16, device=dev)
+    c0, c1 = w_off // chunk, (w_off + Ng * Kg + chunk - 1) // chunk
+
+    def run_ag_gemm(epoch, a=xa, o=out, M=Mg):
+        K.check(lib.mb200_ag_gemm(a.data_ptr(), a.stride(0), 0, M, Kg, unit_buf.data_ptr(), w_off,
+                                  Ng, o.data_ptr(), o.stride(0), None, 0, shard.ptrs_at(0), sh,
+                                  rank, world, c0, c1, chunk, cfl.data_ptr(), epoch, flags.my_ptr,
+                                  0, 0, 16, status.data_ptr(), K.stream_ptr()), "ag_gemm")
+
+    run_ag_gemm(1)
+    torch.cuda.synchronize()
+    K.check_status()
+    Wref = full_w[w_off: w_off + Ng * Kg].view(Ng, Kg)
+    ref = xa.float() @ Wref.float().t()
+    assert _rel(out, ref) < 5e-3, f"ag_gemm mismatch: {_rel(out, ref)}"
+    assert torch.equal(unit_buf[c0 * chunk: c1 * chunk], full_w[c0 * chunk: c1 * chunk])
+    results["ag_gemm_rel_err"] = _rel(out, ref)
+    if bench:
+        # FSDP-sized case: gate_up weight of Llama-3-8B (28672 x 4096) against 8192 tokens
+        Ng2, Kg2, Mg2 = 28672, 4096, 8192
+        unit2 = ((Ng2 * Kg2 + chunk * world - 1) // (chunk * world)) * (chunk * world)
+        sh2 = unit2 // world
+        shard2 = SymmBuffer(sh2, bf16, dev, zero=False)
+        shard2.tensor.normal_(0, 0.02)
+        ub2 = torch.empty(unit2, dtype=bf16, device=dev)
+        cfl2 = torch.zeros(unit2 // chunk, dtype=torch.int32, device=dev)
+        xb = torch.randn(Mg2, Kg2, device=dev).to(bf16)
+        ob = torch.empty(Mg2, Ng2, dtype=bf16, device=dev)
+        ep = [0]
+
+        def fused():
+            ep[0] += 1
+            K.check(lib.mb200_ag_gemm(xb.data_ptr(), Kg2, 0, Mg2, Kg2, ub2.data_ptr(), 0, Ng2,
+                                      ob.data_ptr(), Ng2, None, 0, shard2.ptrs_at(0), sh2, rank,
+                                      world, 0, unit2 // chunk, chunk, cfl2.data_ptr(), ep[0],
+                                      flags.my_ptr, 0, 0, 16, status.data_ptr(), K.stream_ptr()),
+                    "ag_gemm")
+
+        def separate():
+            K.check(lib.mb200_allgather_pull(ub2.data_ptr(), shard2.ptrs_at(0), sh2, rank, world,
+                                             flags.my_ptr, 0, 0, None, 0, 0, 0, status.data_ptr(),
+                                             K.stream_ptr()), "ag")
+            from .. import ops as _ops
+            _ops.gemm(xb, ub2[: Ng2 * Kg2].view(Ng2, Kg2), out=ob)
+
+        def nccl_sep():
+            dist.all_gather_into_tensor(ub2, shard2.tensor)
+            torch.matmul(xb, ub2[: Ng2 * Kg2].view(Ng2, Kg2).t(), out=ob)
+
+        def gemm_only():
+            from .. import ops as _ops
+            _ops.gemm(xb, ub2[: Ng2 * Kg2].view(Ng2, Kg2), out=ob)
+
+        t_f, t_s, t_n, t_g = (_time(f, dev) for f in (fused, separate, nccl_sep, gemm_only))
+        K.check_status()
+        flops = 2.0 * Mg2 * Ng2 * Kg2
+        link_bytes = (world - 1) / world * unit2 * 2
+        roof_ms = max(flops / 1699.4e12, link_bytes / 770e9) * 1e3
+        results["ag_gemm_bench"] = {
+            "M": Mg2, "N": Ng2, "K": Kg2, "fused_ms": t_f, "separate_ours_ms": t_s,
+            "nccl_plus_cublas_ms": t_n, "gemm_only_ms": t_g, "roofline_ms": roof_ms,
+            "fraction_of_roofline": roof_ms / t_f}
+        del shard2, ub2, xb, ob
+
     # ------------------------------------------- fused FSDP == library-collective FSDP --
     from ..models import PRESETS, LlamaEngine, ParamLayout
     from .fsdp import FSDPParamStore
