@@ -40,7 +40,11 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--out", default=None)
     ap.add_argument("--T", type=int, default=8192)
+    ap.add_argument("--impl", type=int, default=0,
+                    help="1: single-CTA tiles, 2: CTA-pair tiles, 0: the library default")
     args = ap.parse_args()
+    if args.impl:
+        K.set_gemm_impl(args.impl)
     T = args.T
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     # (name, M, N, K, a_mn, b_mn)
@@ -69,7 +73,7 @@ def main():
         o_best, o_avg = timeit(ours, flush)
         l_best, l_avg = timeit(lib, flush)
         K.check_status()
-        rows.append({"shape": name, "M": M, "N": N, "K": Kd, "ours_ms": o_best,
+        rows.append({"impl": K.gemm_impl(), "shape": name, "M": M, "N": N, "K": Kd, "ours_ms": o_best,
                      "ours_tflops": flops / o_best / 1e9, "cublas_ms": l_best,
                      "cublas_tflops": flops / l_best / 1e9, "ratio": l_best / o_best})
         print(f"{name:16s} {M:6d}x{N:6d}x{Kd:6d}  ours {o_best:7.3f} ms {flops/o_best/1e9:7.1f} TF"

@@ -17,7 +17,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
-#include "comm.cuh"
+#include "gather.cuh"
 #include "gemm_tcgen05.cuh"
 #include "mb200.h"
 
@@ -27,56 +27,6 @@ int make_gemm_tmaps(CUtensorMap* ta, CUtensorMap* tb, const void* A, const void*
                     int K, int lda, int ldb, int a_mn, int b_mn);
 int sm_count();
 
-struct GatherParams {
-  __nv_bfloat16* dst;       // local copy of the whole sharded buffer
-  Peers src;                // every rank's shard base
-  long long shard_elems;
-  int rank, world;
-  long long c_begin, c_end;  // chunk range to gather
-  long long chunk_elems;
-  long long total_elems;
-  uint32_t* chunk_flags;
-  uint32_t chunk_epoch;
-  void* my_flags;           // cross-rank epoch flags ("shard updated")
-  int wait_slot;
-  uint32_t wait_epoch;
-  int* status;
-};
-
-__device__ __forceinline__ void gather_chunks(const GatherParams& g, int cta, int n_cta) {
-  __shared__ int sh_ok;
-  if (g.wait_epoch) {
-    if (!block_wait_all(g.my_flags, g.world, g.wait_slot, g.wait_epoch, g.status, &sh_ok)) return;
-  }
-  const int nthr = blockDim.x;
-  for (long long c = g.c_begin + cta; c < g.c_end; c += n_cta) {
-    const long long e0 = c * g.chunk_elems;
-    long long e1 = e0 + g.chunk_elems;
-    if (e1 > g.total_elems) e1 = g.total_elems;
-    // 4 independent 16-byte loads in flight per thread
-    for (long long e = e0 + (long long)threadIdx.x * 8; e < e1; e += (long long)nthr * 32) {
-      uint4 v[4];
-      bool ok[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const long long ej = e + (long long)j * nthr * 8;
-        ok[j] = ej < e1;
-        if (ok[j]) {
-          const int p = (int)(ej / g.shard_elems);
-          const long long off = ej - (long long)p * g.shard_elems;
-          v[j] = ld_nc_v4(reinterpret_cast<const __nv_bfloat16*>(g.src.p[p]) + off);
-        }
-      }
-#pragma unroll
-      for (int j = 0; j < 4; ++j)
-        if (ok[j]) *reinterpret_cast<uint4*>(g.dst + e + (long long)j * nthr * 8) = v[j];
-    }
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) st_release_gpu(g.chunk_flags + c, g.chunk_epoch);
-  }
-}
-
 template <bool A_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
     ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA,
@@ -84,7 +34,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                    const GatherParams g, int n_comm) {
   extern __shared__ uint8_t smem_raw[];
   if ((int)blockIdx.x < n_comm) {
-    gather_chunks(g, blockIdx.x, n_comm);
+    gather_chunks_bulk(g, blockIdx.x, n_comm, smem_raw);
     return;
   }
   gemm_cta_body<A_MN, false>(&tmA, &tmB, p, blockIdx.x - n_comm, gridDim.x - n_comm, smem_raw);
@@ -99,30 +49,6 @@ __global__ void __launch_bounds__(GEMM_THREADS) gather_only_kernel(const GatherP
 }  // namespace mb200
 
 using namespace mb200;
-
-static GatherParams make_gather(void* unit_buf, const void* const* shard_ptrs,
-                                long long shard_elems, int rank, int world, long long c_begin,
-                                long long c_end, long long chunk_elems, uint32_t* chunk_flags,
-                                uint32_t chunk_epoch, void* my_flags, int wait_slot,
-                                uint32_t wait_epoch, int* status) {
-  GatherParams g{};
-  g.dst = reinterpret_cast<__nv_bfloat16*>(unit_buf);
-  for (int i = 0; i < world && i < kMaxRanks; ++i) g.src.p[i] = const_cast<void*>(shard_ptrs[i]);
-  g.shard_elems = shard_elems;
-  g.rank = rank;
-  g.world = world;
-  g.c_begin = c_begin;
-  g.c_end = c_end;
-  g.chunk_elems = chunk_elems;
-  g.total_elems = shard_elems * world;
-  g.chunk_flags = chunk_flags;
-  g.chunk_epoch = chunk_epoch;
-  g.my_flags = my_flags;
-  g.wait_slot = wait_slot;
-  g.wait_epoch = wait_epoch;
-  g.status = status;
-  return g;
-}
 
 // C = A * W^T (+R) where W = unit_buf[w_elem_off : w_elem_off + N*K] is gathered by the same
 // kernel.  Chunks [c_begin, c_end) of the unit are pulled and flagged with chunk_epoch.

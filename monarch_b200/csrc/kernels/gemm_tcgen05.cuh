@@ -45,7 +45,103 @@ struct GemmParams {
   long long b_flag_elem0;
   int ldb;
   int n_blk_rot;  // rotate the N-block order so locally-owned blocks come first
+  // Same gating for the A operand (K-major rows, leading dimension lda): tensor-parallel
+  // sequence-parallel all-gather of activations feeding a column-parallel GEMM.
+  const uint32_t* a_ready;
+  uint32_t a_ready_target;
+  long long a_flag_chunk_elems;
+  long long a_flag_elem0;
+  int lda;
+  // Reduce-scatter epilogue (row-parallel GEMM -> sequence-parallel output): when
+  // rs_rows_per_rank > 0 the bf16 partial tile is stored over NVLink into the staging
+  // buffer of the rank that owns the row, in the slot of the producing rank:
+  //   rs_out[row / rs_rows_per_rank][rs_src_rank][row % rs_rows_per_rank, col]
+  // (leading dimension rs_ld).  The owner sums the slots in fp32 afterwards.  C/R unused.
+  void* rs_out[8];
+  int rs_rows_per_rank;
+  int rs_ld;
+  int rs_src_rank;
 };
+
+// Shared by both bodies: write one 32-column strip of an accumulator row.
+__device__ __forceinline__ void gemm_store_strip(const GemmParams& p, const uint32_t (&v)[32],
+                                                 int row, int col, bool vec_ok) {
+  if (p.rs_rows_per_rank > 0) {
+    // reduce-scatter epilogue: bf16 partial strip into the owner rank's staging slot
+    if (row < p.M && col + 32 <= p.N) {
+      const int owner = row / p.rs_rows_per_rank;
+      __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.rs_out[owner]) +
+                          ((size_t)p.rs_src_rank * p.rs_rows_per_rank +
+                           (row - owner * p.rs_rows_per_rank)) * p.rs_ld + col;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint4 o;
+        o.x = pack_bf16x2(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]));
+        o.y = pack_bf16x2(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]));
+        o.z = pack_bf16x2(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]));
+        o.w = pack_bf16x2(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]));
+        *reinterpret_cast<uint4*>(op + q * 8) = o;
+      }
+    }
+    return;
+  }
+  if (row >= p.M || col >= p.N) return;
+  __nv_bfloat16* cp = p.C + (size_t)row * p.ldc + col;
+  const __nv_bfloat16* rp = p.R ? p.R + (size_t)row * p.ldr + col : nullptr;
+  if (vec_ok && col + 32 <= p.N) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float f[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[q * 8 + i]);
+      if (rp) {
+        uint4 r4 = *reinterpret_cast<const uint4*>(rp + q * 8);
+        float2 a = unpack_bf16x2(r4.x), b = unpack_bf16x2(r4.y), c2 = unpack_bf16x2(r4.z),
+               d = unpack_bf16x2(r4.w);
+        f[0] += a.x; f[1] += a.y; f[2] += b.x; f[3] += b.y;
+        f[4] += c2.x; f[5] += c2.y; f[6] += d.x; f[7] += d.y;
+      }
+      if (p.accumulate) {
+        uint4 r4 = *reinterpret_cast<const uint4*>(cp + q * 8);
+        float2 a = unpack_bf16x2(r4.x), b = unpack_bf16x2(r4.y), c2 = unpack_bf16x2(r4.z),
+               d = unpack_bf16x2(r4.w);
+        f[0] += a.x; f[1] += a.y; f[2] += b.x; f[3] += b.y;
+        f[4] += c2.x; f[5] += c2.y; f[6] += d.x; f[7] += d.y;
+      }
+      uint4 o;
+      o.x = pack_bf16x2(f[0], f[1]);
+      o.y = pack_bf16x2(f[2], f[3]);
+      o.z = pack_bf16x2(f[4], f[5]);
+      o.w = pack_bf16x2(f[6], f[7]);
+      *reinterpret_cast<uint4*>(cp + q * 8) = o;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      if (col + i < p.N) {
+        float f = __uint_as_float(v[i]);
+        if (rp) f += __bfloat162float(rp[i]);
+        if (p.accumulate) f += __bfloat162float(cp[i]);
+        cp[i] = __float2bfloat16(f);
+      }
+    }
+  }
+}
+
+// Bounded wait for the readiness flags that cover rows [r0, r1] (leading dimension ld,
+// K elements per row) of an operand living at element `elem0` of a chunk-flagged buffer.
+__device__ __forceinline__ bool gemm_wait_rows(const uint32_t* ready, uint32_t target,
+                                               long long chunk_elems, long long elem0, int ld,
+                                               int r0, int r1, int K, int* status) {
+  const long long f0 = (elem0 + (long long)r0 * ld) / chunk_elems;
+  const long long f1 = (elem0 + (long long)r1 * ld + K - 1) / chunk_elems;
+  bool ok = true;
+  for (long long f = f0; f <= f1 && ok; ++f) ok = flag_wait_ge<false>(ready + f, target, status);
+  // the chunks were written through the generic proxy by other CTAs; order those writes
+  // (observed via the acquire above) before this thread's TMA reads
+  asm volatile("fence.proxy.async;" ::: "memory");
+  return ok;
+}
 
 struct GemmShared {
   uint64_t full[GEMM_STAGES];
@@ -106,23 +202,23 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tmA, const CUte
         int n_blk = t / m_blocks + p.n_blk_rot;
         if (n_blk >= n_blocks) n_blk -= n_blocks;
         const int m0 = m_blk * GEMM_BM, n0 = n_blk * GEMM_BN;
+        bool ok = true;
         if (p.b_ready) {
-          // Both ends of the block: a 256-row block may straddle two flag ranges.
+          // both ends of the block: a 256-row block may straddle several flag ranges
           int last_row = n0 + GEMM_BN - 1;
           if (last_row >= p.N) last_row = p.N - 1;
-          const long long f0 = (p.b_flag_elem0 + (long long)n0 * p.ldb) / p.flag_chunk_elems;
-          const long long f1 =
-              (p.b_flag_elem0 + (long long)last_row * p.ldb + p.K - 1) / p.flag_chunk_elems;
-          bool ok = true;
-          for (long long f = f0; f <= f1 && ok; ++f)
-            ok = flag_wait_ge<false>(p.b_ready + f, p.b_ready_target, p.status);
-          if (!ok) {
-            *abort_word = 1;
-            break;
-          }
-          // the chunks were written through the generic proxy by other CTAs; order those
-          // writes (observed via the acquire above) before this thread's TMA reads
-          asm volatile("fence.proxy.async;" ::: "memory");
+          ok = gemm_wait_rows(p.b_ready, p.b_ready_target, p.flag_chunk_elems, p.b_flag_elem0,
+                              p.ldb, n0, last_row, p.K, p.status);
+        }
+        if (ok && p.a_ready) {
+          int last_row = m0 + GEMM_BM - 1;
+          if (last_row >= p.M) last_row = p.M - 1;
+          ok = gemm_wait_rows(p.a_ready, p.a_ready_target, p.a_flag_chunk_elems, p.a_flag_elem0,
+                              p.lda, m0, last_row, p.K, p.status);
+        }
+        if (!ok) {
+          *abort_word = 1;
+          break;
         }
         bool failed = false;
         for (int k = 0; k < k_iters; ++k) {
@@ -221,49 +317,7 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tmA, const CUte
         uint32_t v[32];
         tmem_ld_32x32b_x32(t_base + c * 32, v);
         tmem_ld_wait();
-        const int col = n0 + c * 32;
-        if (row < p.M && col < p.N) {
-          __nv_bfloat16* cp = p.C + (size_t)row * p.ldc + col;
-          const __nv_bfloat16* rp = p.R ? p.R + (size_t)row * p.ldr + col : nullptr;
-          if (vec_ok && col + 32 <= p.N) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              float f[8];
-#pragma unroll
-              for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[q * 8 + i]);
-              if (rp) {
-                uint4 r4 = *reinterpret_cast<const uint4*>(rp + q * 8);
-                float2 a = unpack_bf16x2(r4.x), b = unpack_bf16x2(r4.y), c2 = unpack_bf16x2(r4.z),
-                       d = unpack_bf16x2(r4.w);
-                f[0] += a.x; f[1] += a.y; f[2] += b.x; f[3] += b.y;
-                f[4] += c2.x; f[5] += c2.y; f[6] += d.x; f[7] += d.y;
-              }
-              if (p.accumulate) {
-                uint4 r4 = *reinterpret_cast<const uint4*>(cp + q * 8);
-                float2 a = unpack_bf16x2(r4.x), b = unpack_bf16x2(r4.y), c2 = unpack_bf16x2(r4.z),
-                       d = unpack_bf16x2(r4.w);
-                f[0] += a.x; f[1] += a.y; f[2] += b.x; f[3] += b.y;
-                f[4] += c2.x; f[5] += c2.y; f[6] += d.x; f[7] += d.y;
-              }
-              uint4 o;
-              o.x = pack_bf16x2(f[0], f[1]);
-              o.y = pack_bf16x2(f[2], f[3]);
-              o.z = pack_bf16x2(f[4], f[5]);
-              o.w = pack_bf16x2(f[6], f[7]);
-              *reinterpret_cast<uint4*>(cp + q * 8) = o;
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              if (col + i < p.N) {
-                float f = __uint_as_float(v[i]);
-                if (rp) f += __bfloat162float(rp[i]);
-                if (p.accumulate) f += __bfloat162float(cp[i]);
-                cp[i] = __float2bfloat16(f);
-              }
-            }
-          }
-        }
+        gemm_store_strip(p, v, row, n0 + c * 32, vec_ok);
       }
       tc_fence_before();
       __syncwarp();

@@ -37,6 +37,8 @@ def lib() -> ctypes.CDLL:
             raise KernelError(f"{_SO} is missing: run `python -m monarch_b200._build kernels`")
         _lib = ctypes.CDLL(str(_SO))
         _declare(_lib)
+        if os.environ.get("MB200_GEMM_IMPL"):
+            _lib.mb200_gemm_set_impl(int(os.environ["MB200_GEMM_IMPL"]))
     return _lib
 
 
@@ -95,10 +97,29 @@ _OPTIONAL: dict[str, list] = {
                       ctypes.c_longlong, _i, _i, ctypes.c_longlong, ctypes.c_longlong,
                       ctypes.c_longlong, _vp, ctypes.c_uint32, _vp, _i, ctypes.c_uint32, _i, _vp,
                       _vp],
+    "mb200_gemm_set_impl": [_i],
+    "mb200_gemm_get_impl": [],
+    "mb200_ag_a_gemm": [_vp, _vp, ctypes.c_longlong, _i, _i, _i, _i, _vp, _i, _i, _i, _vp, _i, _vp,
+                        _i, ctypes.c_longlong, _vp, ctypes.c_uint32, _vp, _i, ctypes.c_uint32, _i,
+                        _vp, _vp],
+    "mb200_gemm_rs": [_vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _i, _i, _i, _i, _vp, _vp],
+    "mb200_rs_finish": [_vp, _i, _i, _i, _i, _vp, _i, _vp, _i, _vp],
     "mb200_gather_chunks": [_vp, _vp, ctypes.c_longlong, _i, _i, ctypes.c_longlong,
                             ctypes.c_longlong, ctypes.c_longlong, _vp, ctypes.c_uint32, _vp, _i,
                             ctypes.c_uint32, _i, _vp, _vp],
 }
+
+
+def set_gemm_impl(impl: int) -> None:
+    """Select the GEMM kernel behind :func:`monarch_b200.ops.gemm`: 1 = single-CTA
+    128x256 tiles, 2 = CTA-pair (``cta_group::2``) 256x256 tiles."""
+    rc = lib().mb200_gemm_set_impl(int(impl))
+    if rc:
+        raise KernelError(f"unknown GEMM implementation {impl}")
+
+
+def gemm_impl() -> int:
+    return int(lib().mb200_gemm_get_impl())
 
 
 def status_word(device: torch.device | int | None = None) -> torch.Tensor:

@@ -230,6 +230,58 @@ def main() -> int:
             "fraction_of_roofline": roof_ms / t_f}
         del shard2, ub2, xb, ob
 
+    # ---------------- tensor-parallel: sequence-parallel all-gather -> GEMM, GEMM -> reduce-scatter
+    Mt, Kt, Nt = 256 * world, 1024, 1536
+    rows_l = Mt // world
+    x_shard = SymmBuffer(rows_l * Kt, bf16, dev, zero=False)
+    gx = torch.Generator(device="cpu").manual_seed(99)
+    x_all = torch.randn(Mt, Kt, generator=gx).to(bf16).to(dev)
+    x_shard.tensor.copy_(x_all[rank * rows_l:(rank + 1) * rows_l].reshape(-1))
+    w_col = (torch.randn(Nt, Kt, generator=gx) * 0.05).to(bf16).to(dev)   # this rank's column block
+    x_full = torch.zeros(Mt, Kt, dtype=bf16, device=dev)
+    tchunk = 1 << 16
+    tfl = torch.zeros((Mt * Kt + tchunk - 1) // tchunk, dtype=torch.int32, device=dev)
+    y_col = torch.empty(Mt, Nt, dtype=bf16, device=dev)
+    flags.barrier(8)   # every rank's shard is written
+    for b_mn, wmat in ((0, w_col), (1, w_col.t().contiguous())):
+        x_full.zero_()
+        K.check(lib.mb200_ag_a_gemm(x_full.data_ptr(), x_shard.ptrs_at(0), rows_l * Kt, rank, world,
+                                    Mt, Kt, wmat.data_ptr(), wmat.stride(0), b_mn, Nt,
+                                    y_col.data_ptr(), Nt, None, 0, tchunk, tfl.data_ptr(),
+                                    1 + b_mn, flags.my_ptr, 0, 0, 8, status.data_ptr(),
+                                    K.stream_ptr()), "ag_a_gemm")
+        torch.cuda.synchronize()
+        K.check_status()
+        assert torch.equal(x_full, x_all), "ag_a_gemm: gathered activation differs"
+        ref = x_all.float() @ w_col.float().t()
+        assert _rel(y_col, ref) < 5e-3, f"ag_a_gemm mismatch: {_rel(y_col, ref)}"
+    results["ag_a_gemm_rel_err"] = _rel(y_col, ref)
+
+    # row-parallel: every rank multiplies its K slice, partial tiles land in the owner's slots
+    Kr, Nr = 512, 768
+    torch.manual_seed(300 + rank)
+    a_loc = torch.randn(Mt, Kr, device=dev).to(bf16)
+    w_row = (torch.randn(Nr, Kr, device=dev) * 0.05).to(bf16)
+    staging = SymmBuffer(world * rows_l * Nr, bf16, dev)
+    res = torch.randn(rows_l, Nr, device=dev).to(bf16)
+    out_rs = torch.empty(rows_l, Nr, dtype=bf16, device=dev)
+    part = a_loc.float() @ w_row.float().t()
+    dist.all_reduce(part)
+    expect_rs = part[rank * rows_l:(rank + 1) * rows_l] + res.float()
+    for impl in (1, 2):
+        flags.barrier(9)
+        K.check(lib.mb200_gemm_rs(a_loc.data_ptr(), w_row.data_ptr(), Mt, Nr, Kr, Kr, Kr, 0, 0,
+                                  staging.ptrs_at(0), world, rows_l, Nr, rank, impl,
+                                  status.data_ptr(), K.stream_ptr()), "gemm_rs")
+        flags.barrier(9)
+        K.check(lib.mb200_rs_finish(staging.tensor.data_ptr(), world, rows_l, Nr, Nr,
+                                    res.data_ptr(), Nr, out_rs.data_ptr(), Nr, K.stream_ptr()),
+                "rs_finish")
+        torch.cuda.synchronize()
+        K.check_status()
+        assert _rel(out_rs, expect_rs) < 1e-2, f"gemm_rs impl {impl}: {_rel(out_rs, expect_rs)}"
+    results["gemm_rs_rel_err"] = _rel(out_rs, expect_rs)
+
     # ------------------------------------------- fused FSDP == library-collective FSDP --
     from ..models import PRESETS, LlamaEngine, ParamLayout
     from .fsdp import FSDPParamStore

@@ -22,10 +22,19 @@ def _status_clean():
     K.check_status()
 
 
+@pytest.fixture(params=[1, 2], ids=["cta1", "cta_pair"])
+def gemm_impl(request):
+    """Run the test under both GEMM kernels (single-CTA tiles and cta_group::2 pairs)."""
+    before = K.gemm_impl()
+    K.set_gemm_impl(request.param)
+    yield request.param
+    K.set_gemm_impl(before)
+
+
 @pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
 @pytest.mark.parametrize("M,N,K_", [(128, 256, 64), (256, 512, 256), (384, 768, 1024),
                                     (304, 520, 200), (8, 24, 72), (1024, 4096, 4096)])
-def test_gemm_matches_fp32(a_mn, b_mn, M, N, K_):
+def test_gemm_matches_fp32(gemm_impl, a_mn, b_mn, M, N, K_):
     torch.manual_seed(0)
     a = torch.randn((K_, M) if a_mn else (M, K_), device="cuda", dtype=bf16)
     b = torch.randn((K_, N) if b_mn else (N, K_), device="cuda", dtype=bf16)
@@ -35,7 +44,7 @@ def test_gemm_matches_fp32(a_mn, b_mn, M, N, K_):
     assert _rel(c, ref) < 5e-3, _rel(c, ref)
 
 
-def test_gemm_residual_and_accumulate():
+def test_gemm_residual_and_accumulate(gemm_impl):
     torch.manual_seed(1)
     M, N, K_ = 512, 1024, 512
     a = torch.randn(M, K_, device="cuda", dtype=bf16)
@@ -49,7 +58,7 @@ def test_gemm_residual_and_accumulate():
     assert _rel(c1, R.gemm(a, b, accumulate_into=c0)) < 5e-3
 
 
-def test_gemm_strided_views():
+def test_gemm_strided_views(gemm_impl):
     torch.manual_seed(2)
     big = torch.randn(512, 1024, device="cuda", dtype=bf16)
     a = big[:, 256:768]           # [512, 512], ld 1024
@@ -61,7 +70,7 @@ def test_gemm_strided_views():
     assert out_big[:, :128].abs().max() == 0 and out_big[:, 384:].abs().max() == 0
 
 
-def test_gemm_many_tiles_persistent():
+def test_gemm_many_tiles_persistent(gemm_impl):
     # more tiles than SMs: exercises the persistent loop and TMEM double buffering
     torch.manual_seed(3)
     M, N, K_ = 4096, 4096, 512
