@@ -6,6 +6,8 @@ reference so that engines and tests run without a GPU.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import kernels as K
@@ -205,7 +207,12 @@ def sumsq(x, out=None):
 
 
 def have_attention_kernel() -> bool:
-    return torch.cuda.is_available() and hasattr(K.lib(), "mb200_attn_fwd")
+    """True when the tcgen05 flash-attention kernels (forward and backward) are in the
+    loaded library and not disabled with ``MB200_ATTN=sdpa``."""
+    if not torch.cuda.is_available() or os.environ.get("MB200_ATTN", "") == "sdpa":
+        return False
+    l = K.lib()
+    return hasattr(l, "mb200_attn_fwd") and hasattr(l, "mb200_attn_bwd")
 
 
 class AttnCtx:
