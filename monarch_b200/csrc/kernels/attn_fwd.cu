@@ -235,21 +235,26 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         if (!ok) break;
         tc_fence_after();
         const bool diag = (j == qblk[s]);
-        // pass 1: row max of this block
-        float mx = -INFINITY;
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32b_x32(s_tmem + c * 32, v);
-          tmem_ld_wait();
+        // the whole S row (128 fp32) goes to registers with one wait
+        uint32_t v[128];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            float x = __uint_as_float(v[i]);
-            if (diag && (j * ATT_BN + c * 32 + i > q_row)) x = -INFINITY;
-            mx = fmaxf(mx, x);
-          }
+        for (int c = 0; c < 4; ++c)
+          tmem_ld_32x32b_x32(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[c * 32]));
+        tmem_ld_wait();
+        if (diag) {
+#pragma unroll
+          for (int i = 0; i < 128; ++i)
+            if (i > r) v[i] = 0xff800000u;  // -inf: key position after the query position
         }
-        mx *= p.scale_log2;
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int i = 0; i < 128; i += 4) {
+          mx4[0] = fmaxf(mx4[0], __uint_as_float(v[i]));
+          mx4[1] = fmaxf(mx4[1], __uint_as_float(v[i + 1]));
+          mx4[2] = fmaxf(mx4[2], __uint_as_float(v[i + 2]));
+          mx4[3] = fmaxf(mx4[3], __uint_as_float(v[i + 3]));
+        }
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
         // PV of the previous block must have retired before O may be touched, and before
         // P of this block goes on top of the S columns the tensor pipe was reading
         if (j > 0) {
@@ -268,36 +273,34 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
           l *= alpha;
 #pragma unroll 1
           for (int c = 0; c < HD / 32; ++c) {
-            uint32_t v[32];
-            tmem_ld_32x32b_x32(o_tmem + c * 32, v);
+            uint32_t ov[32];
+            tmem_ld_32x32b_x32(o_tmem + c * 32, ov);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-            tmem_st_32x32b_x32(o_tmem + c * 32, v);
+            for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+            tmem_st_32x32b_x32(o_tmem + c * 32, ov);
           }
           tmem_st_wait();
         }
-        // pass 2: P = exp2(S*c - m), packed bf16 pairs, written over the S columns
-#pragma unroll 1
+        // P = exp2(S*c - m) as packed bf16 pairs, written over the S columns
+        float l4[4] = {0.f, 0.f, 0.f, 0.f};
+        const float neg_m = -m_used;
+#pragma unroll
         for (int c = 0; c < 4; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32b_x32(s_tmem + c * 32, v);
-          tmem_ld_wait();
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            float x0 = ex2_approx(__uint_as_float(v[2 * i]) * p.scale_log2 - m_used);
-            float x1 = ex2_approx(__uint_as_float(v[2 * i + 1]) * p.scale_log2 - m_used);
-            if (diag) {
-              const int col = j * ATT_BN + c * 32 + 2 * i;
-              if (col > q_row) x0 = 0.f;
-              if (col + 1 > q_row) x1 = 0.f;
-            }
-            l += x0 + x1;
+            const float x0 =
+                ex2_approx(fmaf(__uint_as_float(v[c * 32 + 2 * i]), p.scale_log2, neg_m));
+            const float x1 =
+                ex2_approx(fmaf(__uint_as_float(v[c * 32 + 2 * i + 1]), p.scale_log2, neg_m));
+            l4[(i & 1) * 2] += x0;
+            l4[(i & 1) * 2 + 1] += x1;
             pk[i] = pack_bf16x2(x0, x1);
           }
           tmem_st_32x32b_x16(s_tmem + c * 16, pk);
         }
+        l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();

@@ -243,22 +243,38 @@ class LlamaEngine:
         dev = store.device
         self.cos, self.sin = ops.reference.rope_tables(seq_len, cfg.hd, cfg.theta, device=dev)
         self.n_units = cfg.n_layers + 2
+        # with checkpointing, keep each layer's attention output and log-sum-exp so the
+        # recompute pass skips the attention kernel (only with the hand-written kernels,
+        # whose backward needs nothing else from the forward)
+        self.keep_attention = checkpoint and ops.have_attention_kernel() and \
+            torch.device(dev).type == "cuda"
 
     # ------------------------------------------------------------------ layer forward
-    def _layer_fwd(self, w: dict, x: torch.Tensor, B: int, S: int, keep: bool):
+    def _layer_fwd(self, w: dict, x: torch.Tensor, B: int, S: int, keep: bool,
+                   attn_saved=None):
+        """One decoder layer.  ``attn_saved`` = (o, lse) kept from the first forward: the
+        recompute pass then rebuilds q/k/v but does not run the attention kernel again
+        (selective checkpointing: 2 bytes per activation element per layer)."""
         cfg = self.cfg
         h1, rstd1 = ops.rmsnorm_fwd(x, w["attn_norm"], cfg.eps)
         qkv = ops.gemm(h1, w["wqkv"])
         ops.rope_(qkv, self.cos, self.sin, S, cfg.n_heads + cfg.n_kv_heads, cfg.hd)
-        attn, actx = ops.attention_fwd(qkv, B, S, cfg.n_heads, cfg.n_kv_heads, cfg.hd,
-                                       need_bwd=keep)
+        if attn_saved is not None:
+            attn, actx = ops.attention_ctx_from_saved(qkv, attn_saved, B, S, cfg.n_heads,
+                                                      cfg.n_kv_heads, cfg.hd)
+        else:
+            attn, actx = ops.attention_fwd(qkv, B, S, cfg.n_heads, cfg.n_kv_heads, cfg.hd,
+                                           need_bwd=keep or self.keep_attention)
         x2 = ops.gemm(attn, w["wo"], residual=x)
         h2, rstd2 = ops.rmsnorm_fwd(x2, w["mlp_norm"], cfg.eps)
         gu = ops.gemm(h2, w["w_gu"])
         hmid = ops.swiglu_fwd(gu)
         y = ops.gemm(hmid, w["w_down"], residual=x2)
-        saved = (x, rstd1, h1, actx, attn, x2, rstd2, h2, gu, hmid) if keep else None
-        return y, saved
+        if keep:
+            return y, (x, rstd1, h1, actx, attn, x2, rstd2, h2, gu, hmid)
+        if self.keep_attention and actx.lse is not None:
+            return y, (actx.o, actx.lse)
+        return y, None
 
     def _layer_bwd(self, w: dict, g: dict, saved, dy: torch.Tensor):
         cfg = self.cfg
@@ -339,7 +355,9 @@ class LlamaEngine:
             w = st.unit_params(1 + i)
             g = st.unit_grads(1 + i)
             if self.checkpoint:
-                _, saved = self._layer_fwd(w, ckpt[i], B, S, keep=True)
+                _, saved = self._layer_fwd(w, ckpt[i], B, S, keep=True,
+                                           attn_saved=saved_all[i])
+                saved_all[i] = None
             else:
                 saved = saved_all[i]
                 saved_all[i] = None

@@ -259,6 +259,17 @@ def attention_fwd(qkv, B, S, Hq, Hkv, hd, scale=None, need_bwd=True):
     return ctx.o, ctx
 
 
+def attention_ctx_from_saved(qkv, saved, B, S, Hq, Hkv, hd, scale=None):
+    """Rebuild the backward context from a recomputed qkv and the (o, lse) that the first
+    forward kept, without running the attention kernel again."""
+    ctx = AttnCtx()
+    ctx.qkv, ctx.B, ctx.S, ctx.Hq, ctx.Hkv, ctx.hd = qkv, B, S, Hq, Hkv, hd
+    ctx.scale = scale if scale is not None else hd ** -0.5
+    ctx.graph = None
+    ctx.o, ctx.lse = saved
+    return ctx.o, ctx
+
+
 def attention_bwd(ctx: AttnCtx, do):
     """Gradient w.r.t. the fused (post-RoPE) qkv buffer: [B*S, (Hq+2Hkv)*hd]."""
     B, S, Hq, Hkv, hd = ctx.B, ctx.S, ctx.Hq, ctx.Hkv, ctx.hd
