@@ -35,6 +35,8 @@ def parse():
     ap.add_argument("--micro-batch", type=int, default=1)
     ap.add_argument("--parallelism", default="auto")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--microbatches", type=int, default=8,
+                    help="micro-batches per step of a pipeline-parallel run (ppPxtpT)")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
 
@@ -77,9 +79,17 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    import re
+    m_pp = re.fullmatch(r"pp(\d+)xtp(\d+)", args.parallelism)
+    n_mb = 1
     if args.impl == "aten":
         from monarch_b200.parallel.aten_baseline import AtenTrainer
         trainer = AtenTrainer(args.model, args.seq, args.micro_batch, device=dev)
+    elif m_pp:
+        from monarch_b200.parallel.pipelining import PipelineTrainer
+        n_mb = args.microbatches
+        trainer = PipelineTrainer(args.model, int(m_pp.group(1)), int(m_pp.group(2)), args.seq,
+                                  args.micro_batch, n_mb, device=dev, comm=args.comm)
     else:
         trainer = Trainer(args.model, seq_len=args.seq, micro_batch=args.micro_batch,
                           parallelism=args.parallelism, device=dev, comm=args.comm)
@@ -87,9 +97,12 @@ def main():
     B, S = args.micro_batch, args.seq
     gen = torch.Generator().manual_seed(1234 + rank)
     n_batches = 4
-    host_tok = [torch.randint(0, cfg.vocab, (B, S), generator=gen).pin_memory()
+    shape = (n_mb, B, S) if m_pp else (B, S)
+    if m_pp:
+        gen = torch.Generator().manual_seed(1234)  # one data-parallel replica: same batch
+    host_tok = [torch.randint(0, cfg.vocab, shape, generator=gen).pin_memory()
                 for _ in range(n_batches)]
-    host_tgt = [torch.randint(0, cfg.vocab, (B, S), generator=gen).pin_memory()
+    host_tgt = [torch.randint(0, cfg.vocab, shape, generator=gen).pin_memory()
                 for _ in range(n_batches)]
     dev_tok = [t.to(dev) for t in host_tok]
     dev_tgt = [t.to(dev) for t in host_tgt]
@@ -111,12 +124,14 @@ def main():
     launches = K.launch_count - l0
     K.check_status()
     ms = e0.elapsed_time(e1)
+    if m_pp and world > 1:
+        dist.all_reduce(loss, op=dist.ReduceOp.MAX)  # the last stage holds the loss
     final_loss = float(loss.item())
     t = torch.tensor([ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
-    tokens_per_step = B * S * world
+    tokens_per_step = n_mb * B * S if m_pp else B * S * world
     value = tokens_per_step * args.steps / (ms / 1e3)
 
     # ---- end-to-end through Trainer.step (pinned H2D every step, loss D2H every step)
@@ -143,7 +158,7 @@ def main():
                "d2h_bytes_per_step": trainer.d2h_bytes_per_step}
 
     if rank == 0:
-        par = trainer.parallelism if world == 1 else f"{trainer.parallelism}{world}"
+        par = trainer.parallelism if (world == 1 or m_pp) else f"{trainer.parallelism}{world}"
         flops_tok = cfg.flops_per_token(S, recompute=True)
         out = {
             "metric": "tokens/s Llama-3-8B FSDP-on-mesh" if args.model == "llama3-8b"
@@ -152,13 +167,14 @@ def main():
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "impl": args.impl,
-            "config": {"model": args.model, "global_batch": B * world, "seq_len": S,
+            "config": {"model": args.model,
+                       "global_batch": n_mb * B if m_pp else B * world, "seq_len": S,
                        "parallelism": par, "activation_checkpointing": True,
                        "optimizer": "AdamW fp32 master", "comm": args.comm,
                        "l2": "per-step working set (>100 GB of weights and optimizer state) "
                              "is far larger than the 126 MB L2"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "loss": final_loss,
-            "model_tflops_per_gpu": flops_tok * B * S * args.steps / (ms / 1e3) / 1e12,
+            "model_tflops_per_gpu": flops_tok * tokens_per_step / world * args.steps / (ms / 1e3) / 1e12,
         }
         print(json.dumps(out))
     if world > 1:

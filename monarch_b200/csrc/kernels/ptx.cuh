@@ -80,6 +80,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     for (int i = 0; i < 64; ++i)
       if (mbar_try_wait(bar, parity)) return true;
     if (*abort_word) return false;
+    // a wait that already ran out anywhere on this device (status is sticky until the host
+    // clears it) makes every later wait give up at once instead of after its own limit
+    if (status && *reinterpret_cast<volatile int*>(status) != kStatusOk) {
+      *abort_word = 1;
+      return false;
+    }
     if (clock64() - t0 > MB200_WAIT_CYCLES) {
       *abort_word = 1;
       if (status) atomicCAS(status, kStatusOk, kStatusMbarTimeout);
@@ -117,6 +123,7 @@ __device__ __forceinline__ bool flag_wait_ge(const uint32_t* flag, uint32_t targ
   while (true) {
     uint32_t v = kSys ? ld_acquire_sys(flag) : ld_acquire_gpu(flag);
     if ((int32_t)(v - target) >= 0) return true;
+    if (status && *reinterpret_cast<volatile int*>(status) != kStatusOk) return false;
     if (clock64() - t0 > limit_cycles) {
       if (status) atomicCAS(status, kStatusOk, kStatusFlagTimeout);
       return false;

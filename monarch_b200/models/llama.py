@@ -89,20 +89,31 @@ class Unit:
     offset: int  # element offset of the unit inside the flat buffer
     size: int    # padded size (multiple of ParamLayout.ALIGN)
     params: list = field(default_factory=list)
+    seed_id: int = 0  # position in the full model (embed 0, layer i -> 1+i, head L+1)
 
 
 class ParamLayout:
     """Flat layout: [embed | layer 0 | ... | layer L-1 | head]; units padded to ALIGN."""
     ALIGN = 8192  # elements: keeps every 1/8 shard 16-byte aligned with room to spare
 
-    def __init__(self, cfg: LlamaConfig):
+    def __init__(self, cfg: LlamaConfig, tp: int = 1, layers: Optional[tuple] = None,
+                 embed: bool = True, head: bool = True):
+        """``tp`` > 1: the layout of ONE tensor-parallel rank (Megatron split: wqkv and w_gu
+        by output rows -- whole heads / gate and up halves --, wo and w_down by input
+        columns; embedding, head and norm gains replicated).  ``layers=(lo, hi)`` with
+        ``embed``/``head``: the layout of one pipeline stage."""
         self.cfg = cfg
+        self.tp = tp
         self.units: list[Unit] = []
         off = 0
+        lo, hi = layers if layers is not None else (0, cfg.n_layers)
+        self.layer_range = (lo, hi)
+        if tp > 1 and (cfg.n_heads % tp or cfg.n_kv_heads % tp or cfg.ffn % tp):
+            raise ValueError(f"heads/ffn of {cfg.name} are not divisible by tp={tp}")
 
-        def add_unit(name, specs):
+        def add_unit(name, specs, seed_id):
             nonlocal off
-            u = Unit(name, off, 0)
+            u = Unit(name, off, 0, seed_id=seed_id)
             o = 0
             for n, shape in specs:
                 u.params.append(ParamSpec(n, tuple(shape), o))
@@ -115,16 +126,24 @@ class ParamLayout:
             self.units.append(u)
 
         d, F = cfg.d, cfg.ffn
-        add_unit("embed", [("embed", (cfg.vocab, d))])
-        for i in range(cfg.n_layers):
-            add_unit(f"layer{i}", [("attn_norm", (d,)), ("wqkv", (cfg.qkv_dim, d)),
-                                   ("wo", (d, d)), ("mlp_norm", (d,)),
-                                   ("w_gu", (2 * F, d)), ("w_down", (d, F))])
-        head = [("final_norm", (d,))]
-        if not cfg.tie_embeddings:
-            head.append(("lm_head", (cfg.vocab, d)))
-        add_unit("head", head)
+        if embed:
+            add_unit("embed", [("embed", (cfg.vocab, d))], 0)
+        for i in range(lo, hi):
+            add_unit(f"layer{i}", [("attn_norm", (d,)), ("wqkv", (cfg.qkv_dim // tp, d)),
+                                   ("wo", (d, cfg.n_heads * cfg.hd // tp)), ("mlp_norm", (d,)),
+                                   ("w_gu", (2 * F // tp, d)), ("w_down", (d, F // tp))], 1 + i)
+        if head:
+            hp = [("final_norm", (d,))]
+            if not cfg.tie_embeddings:
+                hp.append(("lm_head", (cfg.vocab, d)))
+            add_unit("head", hp, cfg.n_layers + 1)
         self.total = off
+
+    def unit_index(self, name: str) -> int:
+        for i, u in enumerate(self.units):
+            if u.name == name:
+                return i
+        raise KeyError(name)
 
     def views(self, unit: Unit, flat_unit: torch.Tensor) -> dict:
         out = {}
@@ -218,7 +237,7 @@ def init_params_(layout: ParamLayout, master: torch.Tensor, seed: int, std: floa
             c1 = (e - a + CH - 1) // CH
             for c in range(c0, c1):
                 g = torch.Generator(device=master.device)
-                g.manual_seed((seed * 1000003 + ui * 1009 + pi * 101 + c) & 0x7FFFFFFF)
+                g.manual_seed((seed * 1000003 + u.seed_id * 1009 + pi * 101 + c) & 0x7FFFFFFF)
                 cn = min(CH, n - c * CH)
                 vals = torch.empty(cn, dtype=torch.float32, device=master.device)
                 vals.normal_(0.0, std, generator=g)

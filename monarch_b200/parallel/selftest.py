@@ -328,6 +328,31 @@ def main() -> int:
     except ImportError:
         pass
 
+    # ------------------------------- tensor x pipeline parallel: fused == library path ----
+    from .pipelining import PipelineTrainer
+    tp_n = 2 if world < 8 else 4
+    pp_n = world // tp_n
+    if pp_n * tp_n == world:
+        Sp, Mp = 256, 4
+        gp = torch.Generator().manual_seed(4242)
+        ptok = torch.randint(0, cfg.vocab, (3, Mp, 1, Sp), generator=gp).to(dev)
+        plosses = {}
+        for mode in ("fused", "nccl"):
+            tr = PipelineTrainer(cfg, pp_n, tp_n, Sp, 1, Mp, device=dev, comm=mode, lr=1e-2,
+                                 seed=11, init_std=0.05)
+            ls = []
+            for step in range(2):
+                l = tr.step_device(ptok[step], ptok[step + 1])
+                dist.all_reduce(l, op=dist.ReduceOp.MAX)
+                ls.append(float(l))
+            torch.cuda.synchronize()
+            K.check_status()
+            plosses[mode] = ls
+            del tr
+        for a, b_ in zip(plosses["fused"], plosses["nccl"]):
+            assert abs(a - b_) < 2e-2 * abs(b_), f"TPxPP fused vs nccl: {plosses}"
+        results["tp_pp"] = {"mesh": f"pp{pp_n}xtp{tp_n}", "losses": plosses["fused"]}
+
     # ------------------------------------------------------------------ bandwidths ----
     if bench:
         sizes = [1 << 20, 1 << 24, 1 << 27]  # bf16 elements per rank buffer
