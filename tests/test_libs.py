@@ -1,0 +1,119 @@
+"""Library modules on top of the tensor engine: timers, profiler ranges, scalar logging,
+RNG state, memory stats, opaque objects/modules -- with and without a device mesh."""
+import json
+import os
+
+import pytest
+import torch
+
+from monarch_b200 import tensor_engine as te
+from monarch_b200.actor import this_host
+
+
+@pytest.fixture(scope="module")
+def dm():
+    pm = this_host().spawn_procs(per_host={"gpus": 2})
+    mesh = te.spawn_tensor_engine(pm, use_cuda=False)
+    yield mesh
+    mesh.exit()
+    pm.stop().get()
+
+
+def test_execution_timer_statistics():
+    from monarch_b200.timer import CudaTimer, ExecutionTimer
+    t = CudaTimer("t", use_cuda=False)
+    for _ in range(3):
+        with t.time():
+            sum(range(1000))
+    s = t.summary()
+    assert s["count"] == 3 and s["min_ms"] <= s["mean_ms"] <= s["max_ms"]
+    with pytest.raises(RuntimeError):
+        t.stop()
+    ExecutionTimer.reset()
+    with ExecutionTimer.time("a"):
+        pass
+    assert ExecutionTimer.summary()["a"]["count"] == 1
+    assert ExecutionTimer.get_latest_measurement("a") >= 0
+
+
+def test_profiler_and_tensorboard_local(tmp_path):
+    from monarch_b200.profiler import profile, record_function
+    from monarch_b200.tensorboard import Tensorboard
+    with profile(out_dir=str(tmp_path / "tr")):
+        with record_function("blk"):
+            torch.ones(8).sum()
+    assert any(f.startswith("trace_rank") for f in os.listdir(tmp_path / "tr"))
+    tb = Tensorboard(str(tmp_path / "tb"))
+    tb.log("loss", 1, torch.tensor(2.5))
+    tb.flush()
+    tb.close()
+    assert os.listdir(tmp_path / "tb")
+
+
+def test_remote_libs_on_mesh(dm, tmp_path):
+    from monarch_b200 import memory, random as mrandom
+    from monarch_b200.tensorboard import Tensorboard
+    from monarch_b200.timer import get_latest_timer_measurement
+    with dm.activate():
+        mrandom.manual_seed(123)
+        st = mrandom.get_state()
+        a = torch.rand(4)
+        mrandom.set_state(st)
+        b = torch.rand(4)
+        assert torch.equal(te.inspect(a), te.inspect(b))
+        assert te.inspect(memory.memory_stats()).shape == (3,)
+        te.remote("monarch_b200.timer.execution_timer_start")("k")
+        x = torch.ones(64, 64) @ torch.ones(64, 64)
+        te.remote("monarch_b200.timer.execution_timer_stop")("k")
+        ms = te.remote("monarch_b200.timer.get_latest_timer_measurement",
+                       propagate=lambda n: torch.empty((), dtype=torch.float64))("k")
+        assert te.inspect(ms).item() >= 0
+        tb = Tensorboard(str(tmp_path / "tbm"))
+        tb.log("x", 3, x.sum())
+        tb.flush()
+        te.inspect(x)  # drains the queue
+    files = os.listdir(tmp_path / "tbm")
+    assert files
+    if "scalars.jsonl" in files:
+        rec = json.loads(open(tmp_path / "tbm" / "scalars.jsonl").readline())
+        assert rec == {"tag": "x", "step": 3, "value": 64.0 * 64 * 64}
+
+
+def test_opaque_object_and_module(dm):
+    from monarch_b200.opaque_module import OpaqueModule
+    from monarch_b200.opaque_object import OpaqueObject
+    with dm.activate():
+        d = OpaqueObject("builtins.dict")
+        d.call_method("__setitem__", None, "k", 5)
+        got = d.call_method_on_shard_and_fetch("get", "k").get()
+        assert got == 5
+        torch.manual_seed(0)
+        m = OpaqueModule("torch.nn.Linear", 4, 3)
+        x = torch.ones(2, 4)
+        y = m(x)
+        assert y.shape == (2, 3)
+        gx = m.backward(torch.ones(2, 3), x)
+        assert gx.shape == (2, 4)
+        w, b = m.parameters()
+        assert torch.allclose(te.inspect(gx), te.inspect(w).sum(0).expand(2, 4))
+        gw, gb = m.grads()
+        assert te.inspect(gb).tolist() == [2.0, 2.0, 2.0]
+        w0 = te.inspect(w).clone()
+        m.sgd_step(0.5)
+        w1 = te.inspect(m.parameters()[0])
+        assert torch.allclose(w1, w0 - 0.5 * te.inspect(gw))
+
+
+def test_cached_propagation_runs_once():
+    from monarch_b200.cached_remote_function import cached_propagation
+    calls = []
+
+    def prop(x, k=1):
+        calls.append(1)
+        return x.new_empty(x.shape[0], k)
+
+    p = cached_propagation(prop)
+    assert p(torch.empty(3, 2), k=4).shape == (3, 4)
+    assert p(torch.empty(3, 2), k=4).shape == (3, 4)
+    assert p(torch.empty(5, 2), k=4).shape == (5, 4)
+    assert len(calls) == 2
