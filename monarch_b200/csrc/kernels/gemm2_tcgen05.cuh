@@ -52,9 +52,11 @@ __device__ __forceinline__ void gemm2_cta_body(const CUtensorMap* tmA, const CUt
   const uint32_t cta = cluster_ctarank();  // 0: issues the MMAs; 1: partner
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int m_blocks = (p.M + G2_BM - 1) / G2_BM;
+  const int M = gemm_dyn_m(p);
+  const int Kd = gemm_dyn_k(p);
+  const int m_blocks = (M + G2_BM - 1) / G2_BM;
   const int n_blocks = (p.N + G2_BN - 1) / G2_BN;
-  const int k_iters = (p.K + G2_BK - 1) / G2_BK;
+  const int k_iters = (Kd + G2_BK - 1) / G2_BK;
   const int num_tiles = m_blocks * n_blocks;
 
   if (threadIdx.x == 0) {
@@ -101,9 +103,9 @@ __device__ __forceinline__ void gemm2_cta_body(const CUtensorMap* tmA, const CUt
           ok = gemm_wait_rows(p.b_ready, p.b_ready_target, p.flag_chunk_elems, p.b_flag_elem0,
                               p.ldb, n0, last, p.K, p.status);
         }
-        if (ok && p.a_ready && m0 < p.M) {
+        if (ok && p.a_ready && m0 < M) {
           int last = m0 + G2_HALF - 1;
-          if (last >= p.M) last = p.M - 1;
+          if (last >= M) last = M - 1;
           ok = gemm_wait_rows(p.a_ready, p.a_ready_target, p.a_flag_chunk_elems, p.a_flag_elem0,
                               p.lda, m0, last, p.K, p.status);
         }
@@ -210,7 +212,11 @@ __device__ __forceinline__ void gemm2_cta_body(const CUtensorMap* tmA, const CUt
         uint32_t v[32];
         tmem_ld_32x32b_x32(t_base + c * 32, v);
         tmem_ld_wait();
-        gemm_store_strip(p, v, row, n0 + c * 32, vec_ok);
+        if (k_iters == 0) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0u;
+        }
+        gemm_store_strip(p, v, row, n0 + c * 32, vec_ok, M);
       }
       tc_fence_before();
       __syncwarp();

@@ -61,14 +61,56 @@ struct GemmParams {
   int rs_rows_per_rank;
   int rs_ld;
   int rs_src_rank;
+  // Row counts known only on the device (mixture-of-experts token counts): when
+  // dyn_m_nparts > 0 the number of valid rows is min(M, sum of *dyn_m_parts[i]) (the parts
+  // may live on peer GPUs); when dyn_k is set the reduction length is min(K, *dyn_k).  M and
+  // K are then capacities; operand rows beyond the dynamic K must be zero.
+  const int* dyn_m_parts[8];
+  int dyn_m_nparts;
+  const int* dyn_k;
+  // Scatter epilogue (expert output -> the token's home rank): row i of the result is
+  // stored (bf16) at sc_out[sc_rank[i]] + sc_slot[i] * sc_ld + col.  C/R unused.
+  const int* sc_rank;
+  const int* sc_slot;
+  void* sc_out[8];
+  int sc_ld;
 };
+
+__device__ __forceinline__ int gemm_dyn_m(const GemmParams& p) {
+  if (p.dyn_m_nparts <= 0) return p.M;
+  int m = 0;
+  for (int i = 0; i < p.dyn_m_nparts; ++i)
+    m += *reinterpret_cast<const volatile int*>(p.dyn_m_parts[i]);
+  return m < p.M ? m : p.M;
+}
+__device__ __forceinline__ int gemm_dyn_k(const GemmParams& p) {
+  if (!p.dyn_k) return p.K;
+  const int k = *reinterpret_cast<const volatile int*>(p.dyn_k);
+  return k < p.K ? k : p.K;
+}
 
 // Shared by both bodies: write one 32-column strip of an accumulator row.
 __device__ __forceinline__ void gemm_store_strip(const GemmParams& p, const uint32_t (&v)[32],
-                                                 int row, int col, bool vec_ok) {
+                                                 int row, int col, bool vec_ok, int M) {
+  if (p.sc_rank) {
+    if (row < M && col + 32 <= p.N) {
+      __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.sc_out[p.sc_rank[row]]) +
+                          (size_t)p.sc_slot[row] * p.sc_ld + col;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint4 o;
+        o.x = pack_bf16x2(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]));
+        o.y = pack_bf16x2(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]));
+        o.z = pack_bf16x2(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]));
+        o.w = pack_bf16x2(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]));
+        *reinterpret_cast<uint4*>(op + q * 8) = o;
+      }
+    }
+    return;
+  }
   if (p.rs_rows_per_rank > 0) {
     // reduce-scatter epilogue: bf16 partial strip into the owner rank's staging slot
-    if (row < p.M && col + 32 <= p.N) {
+    if (row < M && col + 32 <= p.N) {
       const int owner = row / p.rs_rows_per_rank;
       __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.rs_out[owner]) +
                           ((size_t)p.rs_src_rank * p.rs_rows_per_rank +
@@ -85,7 +127,7 @@ __device__ __forceinline__ void gemm_store_strip(const GemmParams& p, const uint
     }
     return;
   }
-  if (row >= p.M || col >= p.N) return;
+  if (row >= M || col >= p.N) return;
   __nv_bfloat16* cp = p.C + (size_t)row * p.ldc + col;
   const __nv_bfloat16* rp = p.R ? p.R + (size_t)row * p.ldr + col : nullptr;
   if (vec_ok && col + 32 <= p.N) {
@@ -163,9 +205,11 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tmA, const CUte
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int m_blocks = (p.M + GEMM_BM - 1) / GEMM_BM;
+  const int M = gemm_dyn_m(p);
+  const int Kd = gemm_dyn_k(p);
+  const int m_blocks = (M + GEMM_BM - 1) / GEMM_BM;
   const int n_blocks = (p.N + GEMM_BN - 1) / GEMM_BN;
-  const int k_iters = (p.K + GEMM_BK - 1) / GEMM_BK;
+  const int k_iters = (Kd + GEMM_BK - 1) / GEMM_BK;
   const int num_tiles = m_blocks * n_blocks;
 
   if (threadIdx.x == 0) {
@@ -212,7 +256,7 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tmA, const CUte
         }
         if (ok && p.a_ready) {
           int last_row = m0 + GEMM_BM - 1;
-          if (last_row >= p.M) last_row = p.M - 1;
+          if (last_row >= M) last_row = M - 1;
           ok = gemm_wait_rows(p.a_ready, p.a_ready_target, p.a_flag_chunk_elems, p.a_flag_elem0,
                               p.lda, m0, last_row, p.K, p.status);
         }
@@ -317,7 +361,11 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tmA, const CUte
         uint32_t v[32];
         tmem_ld_32x32b_x32(t_base + c * 32, v);
         tmem_ld_wait();
-        gemm_store_strip(p, v, row, n0 + c * 32, vec_ok);
+        if (k_iters == 0) {  // empty reduction (no tokens): the accumulator was never written
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0u;
+        }
+        gemm_store_strip(p, v, row, n0 + c * 32, vec_ok, M);
       }
       tc_fence_before();
       __syncwarp();

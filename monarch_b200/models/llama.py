@@ -36,6 +36,8 @@ class LlamaConfig:
     theta: float = 500000.0
     tie_embeddings: bool = False
     name: str = "llama"
+    n_experts: int = 0   # > 0: Mixtral-style mixture of SwiGLU experts in place of the MLP
+    top_k: int = 2
 
     @property
     def hd(self) -> int:
@@ -54,8 +56,11 @@ class LlamaConfig:
         return n
 
     def flops_per_token(self, seq_len: int, recompute: bool = True) -> float:
-        """Model FLOPs per token for one training step (fwd + bwd [+ recomputed fwd])."""
-        mm = self.n_layers * (self.qkv_dim * self.d + self.d * self.d + 3 * self.ffn * self.d)
+        """Model FLOPs per token for one training step (fwd + bwd [+ recomputed fwd]); with
+        experts, the ``top_k`` active ones."""
+        act = self.top_k if self.n_experts else 1
+        mm = self.n_layers * (self.qkv_dim * self.d + self.d * self.d +
+                              act * 3 * self.ffn * self.d + self.n_experts * self.d)
         mm += self.vocab * self.d
         attn = self.n_layers * 2 * seq_len * self.d / 2  # causal QK^T + PV, per token
         fwd = 2 * mm + 2 * attn
@@ -67,6 +72,12 @@ PRESETS: dict[str, LlamaConfig] = {
     "llama3.2-1b": LlamaConfig(128256, 2048, 16, 32, 8, 8192, 1e-5, 500000.0, True,
                                "llama3.2-1b"),
     "llama2-13b": LlamaConfig(32000, 5120, 40, 40, 40, 13824, 1e-5, 10000.0, False, "llama2-13b"),
+    "mixtral-8x7b": LlamaConfig(32000, 4096, 32, 32, 8, 14336, 1e-5, 1e6, False, "mixtral-8x7b",
+                                n_experts=8, top_k=2),
+    "tiny-moe": LlamaConfig(512, 256, 2, 4, 2, 512, 1e-5, 500000.0, False, "tiny-moe",
+                            n_experts=2, top_k=2),
+    "tiny-moe4": LlamaConfig(512, 256, 2, 4, 2, 512, 1e-5, 500000.0, False, "tiny-moe4",
+                             n_experts=4, top_k=2),
     "tiny": LlamaConfig(512, 256, 2, 4, 2, 512, 1e-5, 500000.0, False, "tiny"),
     "tiny-tied": LlamaConfig(512, 256, 2, 4, 2, 512, 1e-5, 500000.0, True, "tiny-tied"),
 }
@@ -97,13 +108,15 @@ class ParamLayout:
     ALIGN = 8192  # elements: keeps every 1/8 shard 16-byte aligned with room to spare
 
     def __init__(self, cfg: LlamaConfig, tp: int = 1, layers: Optional[tuple] = None,
-                 embed: bool = True, head: bool = True):
+                 embed: bool = True, head: bool = True, local_experts: Optional[int] = None):
         """``tp`` > 1: the layout of ONE tensor-parallel rank (Megatron split: wqkv and w_gu
         by output rows -- whole heads / gate and up halves --, wo and w_down by input
         columns; embedding, head and norm gains replicated).  ``layers=(lo, hi)`` with
         ``embed``/``head``: the layout of one pipeline stage."""
         self.cfg = cfg
         self.tp = tp
+        # experts held by this rank (expert parallel: n_experts / ep); all of them by default
+        self.local_experts = cfg.n_experts if local_experts is None else local_experts
         self.units: list[Unit] = []
         off = 0
         lo, hi = layers if layers is not None else (0, cfg.n_layers)
@@ -129,9 +142,16 @@ class ParamLayout:
         if embed:
             add_unit("embed", [("embed", (cfg.vocab, d))], 0)
         for i in range(lo, hi):
-            add_unit(f"layer{i}", [("attn_norm", (d,)), ("wqkv", (cfg.qkv_dim // tp, d)),
-                                   ("wo", (d, cfg.n_heads * cfg.hd // tp)), ("mlp_norm", (d,)),
-                                   ("w_gu", (2 * F // tp, d)), ("w_down", (d, F // tp))], 1 + i)
+            specs = [("attn_norm", (d,)), ("wqkv", (cfg.qkv_dim // tp, d)),
+                     ("wo", (d, cfg.n_heads * cfg.hd // tp)), ("mlp_norm", (d,))]
+            if cfg.n_experts:
+                # replicated (data-parallel) parameters first, this rank's experts last
+                specs.append(("router", (cfg.n_experts, d)))
+                for e in range(self.local_experts):
+                    specs += [(f"w_gu{e}", (2 * F, d)), (f"w_down{e}", (d, F))]
+            else:
+                specs += [("w_gu", (2 * F // tp, d)), ("w_down", (d, F // tp))]
+            add_unit(f"layer{i}", specs, 1 + i)
         if head:
             hp = [("final_norm", (d,))]
             if not cfg.tie_embeddings:
@@ -269,11 +289,10 @@ class LlamaEngine:
             torch.device(dev).type == "cuda"
 
     # ------------------------------------------------------------------ layer forward
-    def _layer_fwd(self, w: dict, x: torch.Tensor, B: int, S: int, keep: bool,
-                   attn_saved=None):
-        """One decoder layer.  ``attn_saved`` = (o, lse) kept from the first forward: the
-        recompute pass then rebuilds q/k/v but does not run the attention kernel again
-        (selective checkpointing: 2 bytes per activation element per layer)."""
+    def _attn_fwd(self, w: dict, x: torch.Tensor, B: int, S: int, keep: bool, attn_saved=None):
+        """x -> x + attention(norm(x)).  ``attn_saved`` = (o, lse) kept from the first
+        forward: the recompute pass then rebuilds q/k/v but does not run the attention kernel
+        again (selective checkpointing: 2 bytes per activation element per layer)."""
         cfg = self.cfg
         h1, rstd1 = ops.rmsnorm_fwd(x, w["attn_norm"], cfg.eps)
         qkv = ops.gemm(h1, w["wqkv"])
@@ -285,19 +304,30 @@ class LlamaEngine:
             attn, actx = ops.attention_fwd(qkv, B, S, cfg.n_heads, cfg.n_kv_heads, cfg.hd,
                                            need_bwd=keep or self.keep_attention)
         x2 = ops.gemm(attn, w["wo"], residual=x)
-        h2, rstd2 = ops.rmsnorm_fwd(x2, w["mlp_norm"], cfg.eps)
+        return x2, (x, rstd1, h1, actx, attn)
+
+    def _mlp_fwd(self, w: dict, x2: torch.Tensor, keep: bool):
+        """x2 -> x2 + mlp(norm(x2))."""
+        h2, rstd2 = ops.rmsnorm_fwd(x2, w["mlp_norm"], self.cfg.eps)
         gu = ops.gemm(h2, w["w_gu"])
         hmid = ops.swiglu_fwd(gu)
         y = ops.gemm(hmid, w["w_down"], residual=x2)
+        return y, ((x2, rstd2, h2, gu, hmid) if keep else None)
+
+    def _layer_fwd(self, w: dict, x: torch.Tensor, B: int, S: int, keep: bool,
+                   attn_saved=None):
+        x2, sa = self._attn_fwd(w, x, B, S, keep, attn_saved)
+        y, sm = self._mlp_fwd(w, x2, keep)
         if keep:
-            return y, (x, rstd1, h1, actx, attn, x2, rstd2, h2, gu, hmid)
+            return y, (sa, sm)
+        actx = sa[3]
         if self.keep_attention and actx.lse is not None:
             return y, (actx.o, actx.lse)
         return y, None
 
-    def _layer_bwd(self, w: dict, g: dict, saved, dy: torch.Tensor):
-        cfg = self.cfg
-        x, rstd1, h1, actx, attn, x2, rstd2, h2, gu, hmid = saved
+    def _mlp_bwd(self, w: dict, g: dict, sm, dy: torch.Tensor):
+        """Gradient w.r.t. x2 (residual path included)."""
+        x2, rstd2, h2, gu, hmid = sm
         d_hmid = ops.gemm(dy, w["w_down"], b_mn=True)
         ops.gemm(dy, hmid, a_mn=True, b_mn=True, out=g["w_down"])
         d_gu = ops.swiglu_bwd(gu, d_hmid)
@@ -305,7 +335,11 @@ class LlamaEngine:
         d_h2 = ops.gemm(d_gu, w["w_gu"], b_mn=True)
         ops.gemm(d_gu, h2, a_mn=True, b_mn=True, out=g["w_gu"])
         del d_gu
-        d_x2 = ops.rmsnorm_bwd(d_h2, x2, w["mlp_norm"], rstd2, g["mlp_norm"], dres=dy)
+        return ops.rmsnorm_bwd(d_h2, x2, w["mlp_norm"], rstd2, g["mlp_norm"], dres=dy)
+
+    def _attn_bwd(self, w: dict, g: dict, sa, d_x2: torch.Tensor):
+        cfg = self.cfg
+        x, rstd1, h1, actx, attn = sa
         d_attn = ops.gemm(d_x2, w["wo"], b_mn=True)
         ops.gemm(d_x2, attn, a_mn=True, b_mn=True, out=g["wo"])
         d_qkv = ops.attention_bwd(actx, d_attn)
@@ -313,8 +347,12 @@ class LlamaEngine:
                   inverse=True)
         d_h1 = ops.gemm(d_qkv, w["wqkv"], b_mn=True)
         ops.gemm(d_qkv, h1, a_mn=True, b_mn=True, out=g["wqkv"])
-        dx = ops.rmsnorm_bwd(d_h1, x, w["attn_norm"], rstd1, g["attn_norm"], dres=d_x2)
-        return dx
+        return ops.rmsnorm_bwd(d_h1, x, w["attn_norm"], rstd1, g["attn_norm"], dres=d_x2)
+
+    def _layer_bwd(self, w: dict, g: dict, saved, dy: torch.Tensor):
+        sa, sm = saved
+        d_x2 = self._mlp_bwd(w, g, sm, dy)
+        return self._attn_bwd(w, g, sa, d_x2)
 
     # ------------------------------------------------------------------------- step
     def forward_backward(self, tokens: torch.Tensor, targets: torch.Tensor,

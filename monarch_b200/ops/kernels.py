@@ -104,6 +104,14 @@ _OPTIONAL: dict[str, list] = {
                         _vp, _vp],
     "mb200_gemm_rs": [_vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _i, _i, _i, _i, _vp, _vp],
     "mb200_rs_finish": [_vp, _i, _i, _i, _i, _vp, _i, _vp, _i, _vp],
+    "mb200_moe_route": [_vp, _i, _i, _i, _vp, _vp, _vp],
+    "mb200_moe_gather_gemm": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp,
+                              _vp, ctypes.c_uint32, _vp, _i, _i, _i, _vp, _i, _i, _vp, _vp],
+    "mb200_gemm_bf16_ex": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp,
+                           _vp, _i, _i, _i, _vp, _vp],
+    "mb200_moe_swiglu_fwd": [_vp, _vp, _vp, _vp, _i, _i, _vp],
+    "mb200_moe_swiglu_bwd": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
+    "mb200_moe_combine": [_vp, _i, _i, _i, _vp, _i, _vp, _i, _vp],
     "mb200_gather_chunks": [_vp, _vp, ctypes.c_longlong, _i, _i, ctypes.c_longlong,
                             ctypes.c_longlong, ctypes.c_longlong, _vp, ctypes.c_uint32, _vp, _i,
                             ctypes.c_uint32, _i, _vp, _vp],

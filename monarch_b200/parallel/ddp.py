@@ -39,6 +39,7 @@ class DDPParamStore(LocalParamStore):
         gran = 8 * self.world
         self.bucket_elems = max(gran, (bucket_bytes // 2) // gran * gran)
         self._epoch = 0
+        self.reduce_scale = 1.0 / self.world   # gradient all-reduce computes the mean
         if comm == "fused":
             from .symm import FlagArray, SymmBuffer
             self._grads_sym = SymmBuffer(layout.total, bf16, self.device, self.group)
@@ -50,11 +51,16 @@ class DDPParamStore(LocalParamStore):
             torch.cuda.synchronize(self.device)
         dist.barrier(group=self.group)
 
+    def _reduced_extent(self, ui: int) -> int:
+        """Elements of unit ``ui`` (from its start) that are replicated across the group
+        and therefore all-reduced; the rest (none here) is rank-private."""
+        return self.layout.units[ui].size
+
     def _buckets(self, ui: int) -> List[Tuple[int, int]]:
         u = self.layout.units[ui]
         out = []
         off = u.offset
-        end = u.offset + u.size
+        end = u.offset + self._reduced_extent(ui)
         while off < end:
             n = min(self.bucket_elems, end - off)
             out.append((off, n))
@@ -74,7 +80,7 @@ class DDPParamStore(LocalParamStore):
                     self._epoch += 1
                     K.check(K.lib().mb200_allreduce_scale_cast(
                         self._grads_sym.ptrs_at(off), self._grads_sym.ptrs_at(off),
-                        self._flags.ptrs, n, 0, self.rank, self.world, 1.0 / self.world, 0,
+                        self._flags.ptrs, n, 0, self.rank, self.world, self.reduce_scale, 0,
                         self._epoch, self._flags.counter.data_ptr(), 0,
                         K.status_word(self.device).data_ptr(), K.stream_ptr()),
                         "allreduce_scale_cast", 2)
@@ -83,10 +89,11 @@ class DDPParamStore(LocalParamStore):
                     if g.dtype == bf16 and dist.get_backend(self.group) != "nccl":
                         t = g.float()
                         dist.all_reduce(t, group=self.group)
-                        g.copy_(t / self.world)
+                        g.copy_(t * self.reduce_scale)
                     else:
                         dist.all_reduce(g, group=self.group)
-                        g.div_(self.world)
+                        if self.reduce_scale != 1.0:
+                            g.mul_(self.reduce_scale)
 
     def optimizer_step(self, lr, **kw):
         if self._comm_stream is not None:

@@ -76,6 +76,12 @@ class PipelineTrainer:
         ir.validate(sched, pp, n_microbatches)
         self.actions = ir.add_communication(sched, pp)[self.stage]
         self.parallelism = f"pp{pp}xtp{tp}"
+        import os
+        # receives are posted right before they are needed unless asked otherwise: a
+        # receive posted far ahead is a kernel that sits on the GPU until its sender runs
+        self.prepost = os.environ.get("MB200_PP_PREPOST", "0") == "1"
+        self._debug = os.environ.get("MB200_PP_DEBUG", "0") == "1" and \
+            self.device.type == "cuda"
         self.Tl = self.engine.Tl
         self._tok = torch.empty(n_microbatches, micro_batch, seq_len, dtype=torch.int64,
                                 device=self.device)
@@ -116,24 +122,33 @@ class PipelineTrainer:
         dt = eng.store.params.dtype
         recv_f: Dict[int, tuple] = {}
         recv_b: Dict[int, tuple] = {}
-        # post every receive of the step up front, in schedule order per direction
-        for a in self.actions:
+
+        def post(a):
+            buf = torch.empty(self.Tl, cfg.d, dtype=dt, device=self.device)
             if a.kind == "RECV_F":
-                buf = torch.empty(self.Tl, cfg.d, dtype=dt, device=self.device)
                 recv_f[a.mb] = (buf, dist.irecv(buf, self._peer(s - 1),
                                                 group=self._fwd_groups[s - 1]))
-            elif a.kind == "RECV_B":
-                buf = torch.empty(self.Tl, cfg.d, dtype=dt, device=self.device)
+            else:
                 recv_b[a.mb] = (buf, dist.irecv(buf, self._peer(s + 1),
                                                 group=self._bwd_groups[s]))
+
+        if self.prepost:
+            # every receive of the step up front, in schedule order per direction
+            for a in self.actions:
+                if a.kind in ("RECV_F", "RECV_B"):
+                    post(a)
         outs: Dict[int, torch.Tensor] = {}
         dxs: Dict[int, torch.Tensor] = {}
         sends = []
         loss_sum = torch.zeros((), dtype=torch.float32, device=self.device)
         for a in self.actions:
             if a.kind == "RECV_F":
+                if not self.prepost:
+                    post(a)
                 recv_f[a.mb][1].wait()
             elif a.kind == "RECV_B":
+                if not self.prepost:
+                    post(a)
                 recv_b[a.mb][1].wait()
             elif a.kind == "F":
                 x_in = tokens[a.mb] if s == 0 else recv_f.pop(a.mb)[0]
@@ -156,6 +171,9 @@ class PipelineTrainer:
                                             group=self._bwd_groups[s - 1])))
             else:
                 raise NotImplementedError(f"action {a.kind} is not supported by this runtime")
+            if self._debug:
+                torch.cuda.synchronize(self.device)
+                print(f"[pp rank {self.rank}] done {a}", flush=True)
         for _, w in sends:
             w.wait()
         eng.optimizer_step(self.lr)

@@ -353,6 +353,37 @@ def main() -> int:
             assert abs(a - b_) < 2e-2 * abs(b_), f"TPxPP fused vs nccl: {plosses}"
         results["tp_pp"] = {"mesh": f"pp{pp_n}xtp{tp_n}", "losses": plosses["fused"]}
 
+    # ------------------------------- expert parallel: fused dispatch/combine == all-to-all ----
+    from .ep import EPComm
+    Te, de, Fe, ke = 512, 256, 512, 2
+    ge = torch.Generator().manual_seed(900 + rank)
+    xe = torch.randn(Te, de, generator=ge).to(dev).to(bf16)
+    dye = torch.randn(Te, de, generator=ge).to(dev).to(bf16)
+    rese = torch.randn(Te, de, generator=ge).to(dev).to(bf16)
+    lg = torch.randn(Te, world, generator=ge).to(dev)
+    tp_, ti_ = torch.topk(torch.softmax(lg, -1), min(ke, world), dim=-1)
+    if world < ke:
+        ti_ = torch.cat([ti_, ti_], 1)
+        tp_ = torch.cat([tp_, tp_], 1)
+    we = (tp_ / tp_.sum(-1, keepdim=True)).contiguous()
+    ti_ = ti_.to(torch.int32).contiguous()
+    wgu_e = (torch.randn(2 * Fe, de, generator=ge) * 0.1).to(dev).to(bf16)
+    wdn_e = (torch.randn(de, Fe, generator=ge) * 0.1).to(dev).to(bf16)
+    got = {}
+    for mode in ("fused", "nccl"):
+        epc = EPComm(dist.group.WORLD, dev, Te, de, Fe, ke, comm=mode)
+        ggu, gdn = torch.zeros_like(wgu_e), torch.zeros_like(wdn_e)
+        ye, sve = epc.forward(xe, ti_, we, wgu_e, wdn_e, residual=rese)
+        dxe, dwe = epc.backward(dye, sve, wgu_e, wdn_e, ggu, gdn, acc=False)
+        torch.cuda.synchronize()
+        K.check_status()
+        got[mode] = (ye, dxe, dwe, ggu, gdn)
+        del epc
+    names = ("y", "d_x", "d_wts", "g_gu", "g_down")
+    for nm, a_, b_ in zip(names, got["fused"], got["nccl"]):
+        assert _rel(a_, b_) < 2e-2, f"expert parallel {nm}: fused vs all-to-all {_rel(a_, b_)}"
+    results["ep_rel_err"] = {nm: _rel(a_, b_) for nm, a_, b_ in zip(names, got["fused"], got["nccl"])}
+
     # ------------------------------------------------------------------ bandwidths ----
     if bench:
         sizes = [1 << 20, 1 << 24, 1 << 27]  # bf16 elements per rank buffer
