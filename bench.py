@@ -90,6 +90,9 @@ def main():
         n_mb = args.microbatches
         trainer = PipelineTrainer(args.model, int(m_pp.group(1)), int(m_pp.group(2)), args.seq,
                                   args.micro_batch, n_mb, device=dev, comm=args.comm)
+    elif args.parallelism == "ep":
+        from monarch_b200.parallel.ep import MoETrainer
+        trainer = MoETrainer(args.model, args.seq, args.micro_batch, device=dev, comm=args.comm)
     else:
         trainer = Trainer(args.model, seq_len=args.seq, micro_batch=args.micro_batch,
                           parallelism=args.parallelism, device=dev, comm=args.comm)

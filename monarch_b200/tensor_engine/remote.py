@@ -137,3 +137,115 @@ def coalescing():
         raise RuntimeError("coalescing() needs an active device mesh")
     with mesh.client.coalescing():
         yield
+
+
+# ------------------------------------------------------------------------- recordings --
+class _Compiled:
+    """Result of :func:`compile`: traces ``fn`` once per input signature, ships the traced
+    worker messages as a *recording*, and replays it with one message per later call."""
+    _ids = iter(range(1, 1 << 30))
+
+    def __init__(self, fn, verify: bool = False):
+        self._fn = fn
+        self._verify = verify
+        self._cache = {}
+        functools.update_wrapper(self, fn)
+
+    @staticmethod
+    def _key(args, kwargs, mesh):
+        def sig(o):
+            if isinstance(o, Tensor):
+                return ("T", tuple(o.shape), o.dtype, o.requires_grad)
+            if isinstance(o, (list, tuple)):
+                return (type(o).__name__,) + tuple(sig(x) for x in o)
+            if isinstance(o, dict):
+                return tuple(sorted((k, sig(v)) for k, v in o.items()))
+            return ("V", repr(o))
+        return (sig(args), sig(kwargs), id(mesh._workers))
+
+    def __call__(self, *args, **kwargs):
+        from .device_mesh import get_active_stream
+        ins: list = []
+        _collect(args, ins)
+        _collect(kwargs, ins)
+        mesh = _mesh_of(ins) if ins else get_active_mesh()
+        if mesh is None:
+            raise RuntimeError("no active device mesh")
+        client = mesh.client
+        key = self._key(args, kwargs, mesh)
+        rec = self._cache.get(key)
+        if rec is None:
+            return self._trace(key, mesh, client, ins, args, kwargs)
+        rec_id, formals, internal, out_ids, out_meta, out_tree = rec
+        bind = {f: t.ref for f, t in zip(formals, ins)}
+        stream = get_active_stream()
+        outs = []
+        for (shape, dtype), oid in zip(out_meta, out_ids):
+            with _propagation():
+                fake = torch.empty(shape, dtype=dtype)
+            t = Tensor(fake, mesh, stream)
+            bind[oid] = t.ref
+            outs.append(t)
+        temps = []
+        for i in internal:
+            if i not in bind:
+                bind[i] = client.new_ref()
+                temps.append(bind[i])
+        client.send(mesh, ("call_recording", rec_id, bind))
+        for r in temps:
+            client.delete_ref(r)
+        it = iter(outs)
+        return torch.utils._pytree.tree_map(
+            lambda m: next(it) if m == "__tensor__" else m, out_tree)
+
+    def _trace(self, key, mesh, client, ins, args, kwargs):
+        if client._coalesce is not None:
+            raise RuntimeError("compile() cannot trace inside a coalescing block")
+        first_new = client.new_ref()      # every ref allocated from here on is internal
+        client._coalesce = []
+        try:
+            out = self._fn(*args, **kwargs)
+        finally:
+            batch, client._coalesce = client._coalesce, None
+        msgs = []
+        for m, msg in batch:
+            if m._workers is not mesh._workers:
+                raise RuntimeError("compile() supports functions that stay on one mesh")
+            msgs.append(msg)
+        outs: list = []
+        _collect(out, outs)
+        internal = set()
+
+        def visit(o):
+            if isinstance(o, Ref):
+                if o.id > first_new:
+                    internal.add(o.id)
+            elif isinstance(o, (list, tuple)):
+                for x in o:
+                    visit(x)
+            elif isinstance(o, dict):
+                for x in o.values():
+                    visit(x)
+        visit(msgs)
+        rec_id = next(self._ids)
+        client.send(mesh, ("define_recording", rec_id, msgs))
+        client.send(mesh, ("call_recording", rec_id, {}))
+        out_tree = torch.utils._pytree.tree_map(
+            lambda t: "__tensor__" if isinstance(t, Tensor) else t, out)
+        self._cache[key] = (rec_id, [t.ref for t in ins], sorted(internal),
+                            [t.ref for t in outs], [(tuple(t.shape), t.dtype) for t in outs],
+                            out_tree)
+        return out
+
+
+def compile(fn=None, *, verify: bool = False):
+    """``@compile`` -- trace a function of distributed tensors once and replay it on the
+    workers with a single message per call (the controller's per-op dispatch and shape
+    propagation disappear from the steady state).  A new trace is taken for every new
+    combination of input shapes/dtypes and non-tensor argument values.
+
+    Parity: python/monarch/common/_coalescing.py:98-298 (``compile``), worker
+    ``DefineRecording`` / ``CallRecording`` (monarch_messages/src/worker.rs:854-905)."""
+    if fn is None:
+        return lambda f: _Compiled(f, verify)
+    return _Compiled(fn, verify)

@@ -146,3 +146,32 @@ def test_no_mesh_escapes_dispatch(dm):
         with te.no_mesh():
             local = torch.ones(2) * 3
         assert not isinstance(local, te.Tensor) and local.tolist() == [3.0, 3.0]
+
+
+def test_compile_records_once_and_replays(dm):
+    calls = []
+
+    @te.compile
+    def step(w, x, scale):
+        calls.append(1)
+        h = (x @ w).relu()
+        w.add_(h.sum(0, keepdim=True).t().expand_as(w) * scale)
+        return h.sum(), h
+
+    with dm.activate():
+        w = torch.ones(3, 3)
+        x = torch.arange(6, dtype=torch.float32).reshape(2, 3)
+        with te.no_mesh():
+            ref_w = torch.ones(3, 3)
+            ref_x = torch.arange(6, dtype=torch.float32).reshape(2, 3)
+        for it in range(3):
+            s, h = step(w, x, 0.5)
+            with te.no_mesh():
+                ref_h = (ref_x @ ref_w).relu()
+                ref_w = ref_w + ref_h.sum(0, keepdim=True).t().expand_as(ref_w) * 0.5
+            assert te.inspect(s).item() == ref_h.sum().item(), it
+            assert torch.equal(te.inspect(h), ref_h)
+        assert torch.equal(te.inspect(w), ref_w)
+        assert len(calls) == 1          # traced once, replayed twice
+        step(w, torch.ones(4, 3), 0.5)  # new input shape -> new trace
+        assert len(calls) == 2
