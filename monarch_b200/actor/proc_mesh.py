@@ -332,7 +332,8 @@ def _shape_from_dims(dims: Dict[str, int]) -> Shape:
 
 def _allocate(dims: Dict[str, int], *, in_process: bool, env: Optional[Dict[str, str]] = None,
               bootstrap: Optional[Callable[[], None]] = None, gpu_env: bool = False,
-              transport: str = "unix") -> ProcMesh:
+              transport: str = "unix", remote_hosts: Optional[List[str]] = None,
+              procs_per_host: int = 1) -> ProcMesh:
     n = 1
     for v in dims.values():
         n *= int(v)
@@ -342,6 +343,13 @@ def _allocate(dims: Dict[str, int], *, in_process: bool, env: Optional[Dict[str,
     else:
         argv = [sys.executable, "-m", "monarch_b200.actor.bootstrap_main"]
         e = _child_env(env)
+        if remote_hosts:
+            # every proc is started by the allocator daemon of its host; a local stub per
+            # proc relays its output and lifetime (tools/remote_exec.py)
+            argv = [sys.executable, "-m", "monarch_b200.tools.remote_exec", "--"] + argv
+            e["MB200_REMOTE_HOSTS"] = ",".join(remote_hosts)
+            e["MB200_PROCS_PER_HOST"] = str(procs_per_host)
+            transport = "tcp"
         if bootstrap is not None:
             import base64
             import cloudpickle
@@ -356,9 +364,12 @@ class HostMesh(MeshTrait):
     """A mesh of hosts on which procs are spawned.  One box = one host; ``in_process``
     hosts create procs inside the client (fast API tests)."""
 
-    def __init__(self, shape: Shape, in_process: bool = False):
+    def __init__(self, shape: Shape, in_process: bool = False,
+                 allocators: Optional[List[str]] = None):
         self._shape_ = shape
         self._in_process = in_process
+        # addresses (``tcp!host:port``) of the process-allocator daemons, one per host
+        self._allocators = list(allocators) if allocators else None
 
     @property
     def _ndslice(self):
@@ -369,7 +380,10 @@ class HostMesh(MeshTrait):
         return tuple(self._shape_.labels)
 
     def _new_with_shape(self, shape: Shape) -> "HostMesh":
-        return HostMesh(shape, self._in_process)
+        al = None
+        if self._allocators:
+            al = [self._allocators[r] for r in shape.ndslice.ranks()]
+        return HostMesh(shape, self._in_process, al)
 
     def spawn_procs(self, per_host: Optional[Dict[str, int]] = None,
                     bootstrap: Optional[Callable[[], None]] = None,
@@ -378,12 +392,26 @@ class HostMesh(MeshTrait):
         clash = set(per_host) & set(self._labels)
         if clash:
             raise ValueError(f"host mesh already has dims {sorted(clash)}")
-        if len(self._shape_.ndslice) != 1:
-            raise NotImplementedError("multi-host allocation needs a remote allocator; this "
-                                      "build drives one box")
         dims = {**dict(zip(self._labels, self._shape_.ndslice.sizes)), **per_host}
+        if self._allocators:
+            n_per = 1
+            for v in per_host.values():
+                n_per *= int(v)
+            hosts = list(self._allocators)
+            return _allocate(dims, in_process=False, env=env, bootstrap=bootstrap,
+                             remote_hosts=hosts, procs_per_host=n_per)
+        if len(self._shape_.ndslice) != 1 and not self._in_process:
+            raise NotImplementedError("a multi-host mesh needs process-allocator daemons: build "
+                                      "it with hosts_from_config() or HostMesh.from_allocators()")
         return _allocate(dims, in_process=self._in_process, env=env, bootstrap=bootstrap,
                          gpu_env="gpus" in per_host or "gpu" in per_host)
+
+    @staticmethod
+    def from_allocators(addresses: List[str], dim: str = "hosts") -> "HostMesh":
+        """A host mesh whose procs are started by the process-allocator daemons listening at
+        ``addresses`` (``tcp!host:port``, see ``monarch_b200.tools.process_allocator``)."""
+        return HostMesh(Shape([dim], N.Slice.new_row_major([len(addresses)])),
+                        allocators=list(addresses))
 
 
 def this_host() -> HostMesh:
@@ -397,7 +425,16 @@ def fake_in_process_host() -> HostMesh:
 
 
 def hosts_from_config(name: str) -> HostMesh:
-    raise NotImplementedError("named host configurations need a scheduler integration")
+    """Host mesh named ``name`` in the job file written by ``monarch_b200.tools.cli create``
+    (``$MB200_JOBS_DIR`` or ``~/.monarch_b200/jobs``): a JSON list of allocator addresses."""
+    import json
+    d = os.environ.get("MB200_JOBS_DIR", os.path.expanduser("~/.monarch_b200/jobs"))
+    path = os.path.join(d, f"{name}.json")
+    if not os.path.exists(path):
+        raise KeyError(f"no host configuration {name!r} in {d}")
+    with open(path) as f:
+        job = json.load(f)
+    return HostMesh.from_allocators(job["allocators"])
 
 
 _this_proc: Optional[ProcMesh] = None

@@ -1,0 +1,70 @@
+"""Remote process allocation: procs started by process-allocator daemons ("hosts" here are
+daemons on localhost ports, as in the reference's allocator tests), driven through the job
+CLI and ``hosts_from_config``; a vanished client leaves no orphan procs."""
+import os
+import subprocess
+import sys
+import time
+
+import pytest
+
+from monarch_b200.actor import Actor, endpoint, hosts_from_config
+from monarch_b200.tools import cli
+
+
+class Where(Actor):
+    @endpoint
+    def pid(self) -> int:
+        return os.getpid()
+
+    @endpoint
+    def env(self, k: str):
+        return os.environ.get(k)
+
+
+@pytest.fixture()
+def job(tmp_path, monkeypatch):
+    monkeypatch.setenv("MB200_JOBS_DIR", str(tmp_path))
+    j = cli.create("t", hosts=2)
+    yield j
+    try:
+        cli.stop("t")
+    except SystemExit:
+        pass
+
+
+def test_procs_run_under_the_daemons(job):
+    assert cli.info("t")["running"]
+    hosts = hosts_from_config("t")
+    assert hosts.sizes == {"hosts": 2}
+    pm = hosts.spawn_procs(per_host={"gpus": 2})
+    assert pm.sizes == {"hosts": 2, "gpus": 2}
+    a = pm.spawn("w", Where)
+    pids = [v for _, v in a.pid.call().get(timeout=60).items()]
+    assert len(set(pids)) == 4 and os.getpid() not in pids
+    idx = [v for _, v in a.env.call("MB200_LOCAL_INDEX").get(timeout=30).items()]
+    assert idx == ["0", "1", "0", "1"]
+    # each proc is a child of a daemon, not of this client
+    daemon_pids = set(job["pids"])
+    for p in pids:
+        ppid = int(open(f"/proc/{p}/stat").read().split(")")[1].split()[1])
+        assert ppid in daemon_pids, (p, ppid, daemon_pids)
+    pm.stop().get()
+    deadline = time.time() + 15
+    while time.time() < deadline and any(os.path.exists(f"/proc/{p}") for p in pids):
+        time.sleep(0.2)
+    assert not any(os.path.exists(f"/proc/{p}") for p in pids)
+
+
+def test_cli_roundtrip(tmp_path, monkeypatch):
+    monkeypatch.setenv("MB200_JOBS_DIR", str(tmp_path))
+    env = dict(os.environ, MB200_JOBS_DIR=str(tmp_path))
+    run = lambda *a: subprocess.run([sys.executable, "-m", "monarch_b200.tools.cli", *a],
+                                    env=env, capture_output=True, text=True, timeout=60)
+    r = run("create", "--name", "x", "--hosts", "1")
+    assert r.returncode == 0, r.stderr
+    assert "x" in run("list").stdout
+    assert '"running": true' in run("info", "x").stdout
+    assert run("bounce", "x").returncode == 0
+    assert run("stop", "x").returncode == 0
+    assert "x" not in run("list").stdout
