@@ -342,7 +342,11 @@ def _allocate(dims: Dict[str, int], *, in_process: bool, env: Optional[Dict[str,
         native = N.ProcMesh.allocate_local(world, n)
     else:
         argv = [sys.executable, "-m", "monarch_b200.actor.bootstrap_main"]
+        # the job-wide controller registry must exist before children are started: they
+        # find it through MB200_CONTROLLER_REF in their environment
+        _controller_controller()
         e = _child_env(env)
+        e.setdefault("MB200_CONTROLLER_REF", os.environ.get("MB200_CONTROLLER_REF", ""))
         if remote_hosts:
             # every proc is started by the allocator daemon of its host; a local stub per
             # proc relays its output and lifetime (tools/remote_exec.py)
