@@ -8,8 +8,9 @@ without installation and are the files a process actually maps):
 * ``monarch_b200/_native.so`` -- the C++ runtime (ndslice, channels, mailboxes,
   procs, mesh layer, telemetry) with pybind11 bindings.
 * ``monarch_b200/_gradgen.so`` -- the incremental autograd executor (torch extension).
+* ``monarch_b200/_tensor_worker.so`` -- the tensor worker's executor core (torch extension).
 
-Usage: ``python -m monarch_b200._build [kernels|native|gradgen|all] [--force]``
+Usage: ``python -m monarch_b200._build [kernels|native|gradgen|tensor_worker|all] [--force]``
 """
 from __future__ import annotations
 
@@ -159,10 +160,39 @@ def build_gradgen(force: bool = False) -> Path:
     return target
 
 
+def _build_torch_ext(name: str, src: Path, force: bool) -> Path:
+    """One-file torch extension (links libtorch + torch_python), built in-tree."""
+    target = ROOT / f"{name}.so"
+    if not src.exists():
+        return target
+    import torch
+    from torch.utils import cpp_extension as ce
+    flags = ["-O2", "-std=c++17", "-fPIC", f"-DTORCH_EXTENSION_NAME={name}",
+             "-D_GLIBCXX_USE_CXX11_ABI=" + str(int(torch._C._GLIBCXX_USE_CXX11_ABI))]
+    stamp = _stamp([src], flags + [torch.__version__])
+    if not force and _up_to_date(target, stamp):
+        return target
+    incs = []
+    for i in ce.include_paths():
+        incs += ["-isystem", i]
+    libdir = os.path.join(os.path.dirname(torch.__file__), "lib")
+    _run([CXX, *flags, *incs, *_py_includes(), "-shared", str(src), "-o", str(target),
+          "-L", libdir, "-Wl,-rpath," + libdir, "-ltorch", "-ltorch_cpu", "-lc10",
+          "-ltorch_python"])
+    _write_stamp(target, stamp)
+    return target
+
+
+def build_tensor_worker(force: bool = False) -> Path:
+    """The tensor worker's native executor core (ATen dispatcher calls, recordings)."""
+    return _build_torch_ext("_tensor_worker", CSRC / "tensor_worker" / "worker_core.cpp", force)
+
+
 def build_all(force: bool = False) -> None:
     build_kernels(force)
     build_native(force)
     build_gradgen(force)
+    build_tensor_worker(force)
 
 
 if __name__ == "__main__":
@@ -170,5 +200,5 @@ if __name__ == "__main__":
     force = "--force" in sys.argv
     for w in what:
         {"kernels": build_kernels, "native": build_native, "gradgen": build_gradgen,
-         "all": build_all}[w](force)
+         "tensor_worker": build_tensor_worker, "all": build_all}[w](force)
         print("built", w)

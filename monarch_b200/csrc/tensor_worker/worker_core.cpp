@@ -1,0 +1,405 @@
+// Native executor core of the tensor worker.
+//
+// Holds the worker's environment (controller-assigned ref id -> tensor | error | other
+// Python value) and executes ATen operator calls against it without returning to Python:
+// refs in the arguments are resolved from the environment, a poisoned input poisons the
+// results (dependent error), the operator is looked up once in the c10 dispatcher and
+// called boxed on the requested CUDA stream, outputs are stored under the result refs.
+// Recordings (the worker half of compile()) are parsed once into native call lists and
+// replayed with ref rebinding in one call; messages that are not operator calls (UDFs,
+// collectives, borrows) are handed back to a Python callback in order.
+//
+// Parity: monarch_tensor_worker/src/stream.rs:701-784 (try_define, call_torch_op),
+// :1771-2026 (recordings), borrow.rs:27-68 (borrow state machine, here CUDA events),
+// torch-sys/src/call_op.rs:169 (boxed dispatcher call), torch-sys/src/cell.rs (alias
+// tracking is left to ATen: results that alias inputs share storage as usual).
+#include <torch/csrc/jit/python/pybind_utils.h>
+#include <torch/extension.h>
+
+#include <ATen/core/dispatch/Dispatcher.h>
+#include <c10/core/Stream.h>
+#include <c10/core/impl/VirtualGuardImpl.h>
+
+#include <memory>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <variant>
+#include <vector>
+
+namespace py = pybind11;
+
+namespace {
+
+struct RemoteErr {
+  int64_t seq, rank;
+  std::string func, text, tb;
+  int64_t dependent_of;  // -1: original failure
+};
+using ErrPtr = std::shared_ptr<RemoteErr>;
+using Value = std::variant<std::monostate, at::Tensor, ErrPtr, py::object>;
+
+struct Arg {           // one positional or keyword argument of a recorded call
+  enum Kind { Const, RefOne, RefList } kind = Const;
+  c10::IValue constant;
+  std::vector<int64_t> refs;
+  std::string name;    // keyword name ("" = positional)
+};
+
+struct OpCall {
+  int64_t seq = 0;
+  std::vector<int64_t> results, mutates;
+  std::string name;
+  c10::OperatorHandle op;
+  std::vector<Arg> args;
+  int64_t stream = 0;
+  explicit OpCall(c10::OperatorHandle h) : op(std::move(h)) {}
+};
+
+struct RecItem {
+  std::unique_ptr<OpCall> call;  // null: not an operator call -> Python fallback
+  size_t index = 0;
+};
+
+class WorkerCore {
+ public:
+  WorkerCore(int64_t rank, py::object ref_type) : rank_(rank), ref_type_(std::move(ref_type)) {}
+
+  // ------------------------------------------------------------------ environment
+  void set(int64_t id, py::object v) {
+    if (v.is_none()) {
+      env_[id] = std::monostate{};
+    } else if (THPVariable_Check(v.ptr())) {
+      env_[id] = THPVariable_Unpack(v.ptr());
+    } else {
+      env_[id] = std::move(v);
+    }
+  }
+  void set_error(int64_t id, int64_t seq, int64_t rank, std::string func, std::string text,
+                 std::string tb, int64_t dep) {
+    env_[id] = std::make_shared<RemoteErr>(RemoteErr{seq, rank, std::move(func), std::move(text),
+                                                     std::move(tb), dep});
+  }
+  bool contains(int64_t id) const { return env_.count(id) != 0; }
+  py::object get(int64_t id) const {
+    auto it = env_.find(id);
+    if (it == env_.end()) throw py::key_error("Ref(" + std::to_string(id) + ")");
+    return to_py(it->second);
+  }
+  py::object pop(int64_t id) {
+    auto it = env_.find(id);
+    if (it == env_.end()) return py::none();
+    py::object v = to_py(it->second);
+    env_.erase(it);
+    return v;
+  }
+  void erase(const std::vector<int64_t>& ids) {
+    for (auto i : ids) env_.erase(i);
+  }
+  size_t size() const { return env_.size(); }
+  int64_t live_bytes() const {
+    int64_t n = 0;
+    for (auto& kv : env_)
+      if (auto* t = std::get_if<at::Tensor>(&kv.second))
+        if (t->defined()) n += (int64_t)t->numel() * t->element_size();
+    return n;
+  }
+
+  // ------------------------------------------------------------------ operator calls
+  // Returns None on success, or (seq, rank, func, text, tb, dependent_of) of the error that
+  // now poisons the result refs (dependent_of >= 0: inherited, nothing new to report).
+  py::object call_op(int64_t seq, std::vector<int64_t> results, std::vector<int64_t> mutates,
+                     const std::string& qualname, py::tuple args, py::dict kwargs,
+                     int64_t stream) {
+    auto call = parse_call(seq, std::move(results), std::move(mutates), qualname, args, kwargs,
+                           stream);
+    return run(*call, nullptr);
+  }
+
+  // ---------------------------------------------------------------------- recordings
+  // msgs: the recorded worker messages.  ("call", seq, results, mutates, ("op", name), args,
+  // kwargs, stream) items become native calls; everything else stays with Python.
+  void define_recording(int64_t rec_id, py::list msgs) {
+    std::vector<RecItem> items;
+    size_t idx = 0;
+    for (auto h : msgs) {
+      py::tuple m = py::reinterpret_borrow<py::tuple>(h);
+      RecItem it;
+      it.index = idx++;
+      if (py::str(m[0]).cast<std::string>() == "call") {
+        py::tuple spec = m[4];
+        if (py::str(spec[0]).cast<std::string>() == "op") {
+          try {
+            it.call = parse_call(m[1].cast<int64_t>(), refs_of(m[2]), refs_of(m[3]),
+                                 spec[1].cast<std::string>(), m[5], m[6],
+                                 m[7].cast<int64_t>());
+          } catch (const std::exception&) {
+            it.call.reset();  // unusual argument structure: let Python run this one
+          }
+        }
+      }
+      items.push_back(std::move(it));
+    }
+    recordings_[rec_id] = std::move(items);
+  }
+
+  // Replays recording `rec_id` with ref ids rebound through `bind`.  `fallback(index, bind)`
+  // runs the non-native messages; `report(err_tuple)` is called for each new failure.
+  int64_t call_recording(int64_t rec_id, const std::unordered_map<int64_t, int64_t>& bind,
+                         py::object fallback, py::object report) {
+    auto rit = recordings_.find(rec_id);
+    if (rit == recordings_.end()) throw py::key_error("recording " + std::to_string(rec_id));
+    int64_t native = 0;
+    for (auto& it : rit->second) {
+      if (it.call) {
+        py::object err = run(*it.call, &bind);
+        ++native;
+        if (!err.is_none() && !report.is_none() &&
+            err.cast<py::tuple>()[5].cast<int64_t>() < 0)
+          report(err);
+      } else {
+        fallback(it.index, bind);
+      }
+    }
+    return native;
+  }
+  bool has_recording(int64_t id) const { return recordings_.count(id) != 0; }
+
+  // ------------------------------------------------------------------------- streams
+  void create_stream(int64_t id, py::object torch_stream) { streams_[id] = std::move(torch_stream); }
+
+ private:
+  int64_t rank_;
+  py::object ref_type_;
+  std::unordered_map<int64_t, Value> env_;
+  std::unordered_map<int64_t, std::vector<RecItem>> recordings_;
+  std::unordered_map<int64_t, py::object> streams_;
+
+  static py::object to_py(const Value& v) {
+    if (std::holds_alternative<std::monostate>(v)) return py::none();
+    if (auto* t = std::get_if<at::Tensor>(&v))
+      return py::reinterpret_steal<py::object>(THPVariable_Wrap(*t));
+    if (auto* e = std::get_if<ErrPtr>(&v)) return err_tuple(**e, true);
+    return std::get<py::object>(v);
+  }
+  static py::object err_tuple(const RemoteErr& e, bool tagged) {
+    py::object dep = e.dependent_of >= 0 ? py::cast(e.dependent_of) : py::cast(int64_t(-1));
+    if (tagged)
+      return py::make_tuple("__remote_error__", e.seq, e.rank, e.func, e.text, e.tb, dep);
+    return py::make_tuple(e.seq, e.rank, e.func, e.text, e.tb, dep);
+  }
+
+  bool is_ref(py::handle h) const { return py::isinstance(h, ref_type_); }
+  std::vector<int64_t> refs_of(py::handle seq) const {
+    std::vector<int64_t> out;
+    for (auto h : seq) out.push_back(h.attr("id").cast<int64_t>());
+    return out;
+  }
+
+  std::unique_ptr<OpCall> parse_call(int64_t seq, std::vector<int64_t> results,
+                                     std::vector<int64_t> mutates, const std::string& qualname,
+                                     py::handle args, py::handle kwargs, int64_t stream) {
+    // "aten.add.Tensor" -> ("aten::add", "Tensor")
+    auto p1 = qualname.find('.');
+    auto p2 = qualname.rfind('.');
+    if (p1 == std::string::npos || p2 == p1) throw std::runtime_error("bad op name " + qualname);
+    std::string name = qualname.substr(0, p1) + "::" + qualname.substr(p1 + 1, p2 - p1 - 1);
+    std::string overload = qualname.substr(p2 + 1);
+    if (overload == "default") overload = "";
+    auto call = std::make_unique<OpCall>(
+        c10::Dispatcher::singleton().findSchemaOrThrow(name.c_str(), overload.c_str()));
+    call->seq = seq;
+    call->results = std::move(results);
+    call->mutates = std::move(mutates);
+    call->name = qualname;
+    call->stream = stream;
+    const auto& schema = call->op.schema();
+    const auto& sargs = schema.arguments();
+    size_t pos = 0;
+    for (auto h : args) {
+      if (pos >= sargs.size()) throw std::runtime_error("too many arguments for " + qualname);
+      call->args.push_back(parse_arg(h, sargs[pos].type(), ""));
+      ++pos;
+    }
+    if (kwargs && !kwargs.is_none()) {
+      for (auto kv : py::reinterpret_borrow<py::dict>(kwargs)) {
+        std::string k = py::str(kv.first).cast<std::string>();
+        auto idx = schema.argumentIndexWithName(k);
+        if (!idx) throw std::runtime_error("unknown keyword " + k + " for " + qualname);
+        call->args.push_back(parse_arg(kv.second, sargs[*idx].type(), k));
+      }
+    }
+    return call;
+  }
+
+  Arg parse_arg(py::handle h, const c10::TypePtr& type, std::string name) const {
+    Arg a;
+    a.name = std::move(name);
+    if (is_ref(h)) {
+      a.kind = Arg::RefOne;
+      a.refs.push_back(h.attr("id").cast<int64_t>());
+      return a;
+    }
+    if ((py::isinstance<py::list>(h) || py::isinstance<py::tuple>(h)) && py::len(h) > 0) {
+      bool all_refs = true, any_ref = false;
+      for (auto x : h) {
+        bool r = is_ref(x);
+        all_refs = all_refs && r;
+        any_ref = any_ref || r;
+      }
+      if (all_refs) {
+        a.kind = Arg::RefList;
+        for (auto x : h) a.refs.push_back(x.attr("id").cast<int64_t>());
+        return a;
+      }
+      if (any_ref) throw std::runtime_error("mixed ref/value list");
+    }
+    a.kind = Arg::Const;
+    a.constant = torch::jit::toIValue(h, type);
+    return a;
+  }
+
+  // Resolve one ref; records the first poisoned input in `dep`.
+  bool resolve(int64_t id, const std::unordered_map<int64_t, int64_t>* bind, at::Tensor& out,
+               ErrPtr& dep, bool& is_none) const {
+    if (bind) {
+      auto b = bind->find(id);
+      if (b != bind->end()) id = b->second;
+    }
+    auto it = env_.find(id);
+    if (it == env_.end()) throw std::runtime_error("Ref(" + std::to_string(id) + ") is not defined");
+    is_none = false;
+    if (auto* t = std::get_if<at::Tensor>(&it->second)) {
+      out = *t;
+      return true;
+    }
+    if (auto* e = std::get_if<ErrPtr>(&it->second)) {
+      if (!dep) dep = *e;
+      return false;
+    }
+    if (std::holds_alternative<std::monostate>(it->second)) {
+      is_none = true;
+      return true;
+    }
+    throw std::runtime_error("Ref(" + std::to_string(id) + ") does not hold a tensor");
+  }
+
+  static int64_t rebound(int64_t id, const std::unordered_map<int64_t, int64_t>* bind) {
+    if (!bind) return id;
+    auto b = bind->find(id);
+    return b == bind->end() ? id : b->second;
+  }
+
+  py::object poison(const OpCall& c, const std::unordered_map<int64_t, int64_t>* bind,
+                    ErrPtr e) {
+    for (auto r : c.results) env_[rebound(r, bind)] = e;
+    for (auto r : c.mutates) env_[rebound(r, bind)] = e;
+    return err_tuple(*e, false);
+  }
+
+  py::object run(const OpCall& c, const std::unordered_map<int64_t, int64_t>* bind) {
+    ErrPtr dep;
+    try {
+      const auto& schema = c.op.schema();
+      const auto& sargs = schema.arguments();
+      std::vector<c10::IValue> slots(sargs.size());
+      std::vector<bool> filled(sargs.size(), false);
+      size_t pos = 0;
+      for (const auto& a : c.args) {
+        size_t idx = pos;
+        if (!a.name.empty()) {
+          idx = *schema.argumentIndexWithName(a.name);
+        } else {
+          ++pos;
+        }
+        if (a.kind == Arg::Const) {
+          slots[idx] = a.constant;
+        } else if (a.kind == Arg::RefOne) {
+          at::Tensor t;
+          bool none = false;
+          if (resolve(a.refs[0], bind, t, dep, none)) slots[idx] = none ? c10::IValue() : c10::IValue(t);
+        } else {
+          c10::List<at::Tensor> l;
+          for (auto id : a.refs) {
+            at::Tensor t;
+            bool none = false;
+            if (resolve(id, bind, t, dep, none)) l.push_back(t);
+          }
+          slots[idx] = c10::IValue(l);
+        }
+        filled[idx] = true;
+      }
+      if (dep) {
+        auto e = std::make_shared<RemoteErr>(
+            RemoteErr{c.seq, rank_, c.name, dep->text, dep->tb, dep->seq});
+        return poison(c, bind, e);
+      }
+      for (size_t i = 0; i < sargs.size(); ++i) {
+        if (filled[i]) continue;
+        if (!sargs[i].default_value())
+          throw std::runtime_error("missing argument " + sargs[i].name() + " of " + c.name);
+        slots[i] = *sargs[i].default_value();
+      }
+      torch::jit::Stack stack(slots.begin(), slots.end());
+      {
+        py::object guard;
+        auto sit = streams_.find(c.stream);
+        bool has_stream = sit != streams_.end() && !sit->second.is_none();
+        if (has_stream) {
+          // torch.cuda.stream(s) context: enter/exit around the launch (GIL is held)
+          guard = py::module_::import("torch").attr("cuda").attr("stream")(sit->second);
+          guard.attr("__enter__")();
+        }
+        try {
+          py::gil_scoped_release nogil;
+          c.op.callBoxed(stack);
+        } catch (...) {
+          if (has_stream) guard.attr("__exit__")(py::none(), py::none(), py::none());
+          throw;
+        }
+        if (has_stream) guard.attr("__exit__")(py::none(), py::none(), py::none());
+      }
+      // flatten tensor outputs (tensors and tensor lists) in return order
+      std::vector<at::Tensor> flat;
+      for (auto& v : stack) {
+        if (v.isTensor()) {
+          flat.push_back(v.toTensor());
+        } else if (v.isTensorList()) {
+          for (const at::Tensor& t : v.toTensorList()) flat.push_back(t);
+        }
+      }
+      if (c.results.empty() && !c.mutates.empty()) flat.clear();  // in-place: aliases an arg
+      if (flat.size() != c.results.size())
+        throw std::runtime_error(c.name + " returned " + std::to_string(flat.size()) +
+                                 " tensors, controller expected " +
+                                 std::to_string(c.results.size()));
+      for (size_t i = 0; i < flat.size(); ++i) env_[rebound(c.results[i], bind)] = flat[i];
+      return py::none();
+    } catch (const std::exception& ex) {
+      auto e = std::make_shared<RemoteErr>(
+          RemoteErr{c.seq, rank_, c.name, std::string("RuntimeError: ") + ex.what(), "", -1});
+      return poison(c, bind, e);
+    }
+  }
+};
+
+}  // namespace
+
+PYBIND11_MODULE(_tensor_worker, m) {
+  m.doc() = "native executor core of the tensor worker";
+  py::class_<WorkerCore>(m, "WorkerCore")
+      .def(py::init<int64_t, py::object>(), py::arg("rank"), py::arg("ref_type"))
+      .def("set", &WorkerCore::set)
+      .def("set_error", &WorkerCore::set_error)
+      .def("get", &WorkerCore::get)
+      .def("pop", &WorkerCore::pop)
+      .def("contains", &WorkerCore::contains)
+      .def("erase", &WorkerCore::erase)
+      .def("__len__", &WorkerCore::size)
+      .def("live_bytes", &WorkerCore::live_bytes)
+      .def("call_op", &WorkerCore::call_op)
+      .def("define_recording", &WorkerCore::define_recording)
+      .def("call_recording", &WorkerCore::call_recording)
+      .def("has_recording", &WorkerCore::has_recording)
+      .def("create_stream", &WorkerCore::create_stream);
+}

@@ -73,6 +73,71 @@ def _map_refs(obj, fn):
     return obj
 
 
+def _load_core():
+    """The native executor core (built in-tree by ``monarch_b200._build``); None when the
+    extension is absent or disabled with ``MB200_PY_WORKER=1`` (pure-Python execution)."""
+    if os.environ.get("MB200_PY_WORKER") == "1":
+        return None
+    try:
+        from .. import _tensor_worker
+        return _tensor_worker
+    except ImportError:
+        try:
+            from .. import _build
+            _build.build_tensor_worker()
+            from .. import _tensor_worker
+            return _tensor_worker
+        except Exception:  # noqa: BLE001 - no compiler here: stay on the Python path
+            return None
+
+
+class _Env:
+    """dict view of the worker environment.  Integer keys (refs) live in the native core
+    when there is one, so operator calls and recordings never leave C++; everything else
+    (bookkeeping entries keyed by tuples) stays in a Python dict."""
+
+    def __init__(self, core):
+        self._core = core
+        self._py: Dict[Any, Any] = {}
+
+    @staticmethod
+    def _wrap(v):
+        if isinstance(v, tuple) and len(v) == 7 and v[0] == "__remote_error__":
+            return RemoteError(v[1], v[2], v[3], v[4], v[5], None if v[6] < 0 else v[6])
+        return v
+
+    def __contains__(self, k) -> bool:
+        if self._core is not None and isinstance(k, int):
+            return self._core.contains(k)
+        return k in self._py
+
+    def __getitem__(self, k):
+        if self._core is not None and isinstance(k, int):
+            return self._wrap(self._core.get(k))
+        return self._py[k]
+
+    def get(self, k, default=None):
+        return self[k] if k in self else default
+
+    def __setitem__(self, k, v) -> None:
+        if self._core is not None and isinstance(k, int):
+            if isinstance(v, RemoteError):
+                self._core.set_error(k, v.seq, v.rank, v.func, v.exc_text, v.tb,
+                                     -1 if v.dependent_of is None else v.dependent_of)
+            else:
+                self._core.set(k, v)
+        else:
+            self._py[k] = v
+
+    def pop(self, k, default=None):
+        if self._core is not None and isinstance(k, int):
+            return self._wrap(self._core.pop(k)) if self._core.contains(k) else default
+        return self._py.pop(k, default)
+
+    def __len__(self) -> int:
+        return (len(self._core) if self._core is not None else 0) + len(self._py)
+
+
 class TensorWorker(Actor):
     def __init__(self, use_cuda: bool):
         self.rank = current_rank().rank
@@ -84,7 +149,9 @@ class TensorWorker(Actor):
             torch.cuda.set_device(self.device)
         else:
             self.device = torch.device("cpu")
-        self.env: Dict[int, Any] = {}
+        mod = _load_core()
+        self.core = mod.WorkerCore(self.rank, Ref) if mod is not None else None
+        self.env = _Env(self.core)
         self.streams: Dict[int, Any] = {0: None}
         self.groups: Dict[Tuple[int, ...], Any] = {}
         self.borrows: Dict[int, Any] = {}
@@ -136,6 +203,20 @@ class TensorWorker(Actor):
     def _m_call(self, seq, results, mutates, fspec, args, kwargs, stream) -> None:
         self.last_seq = seq
         fname = fspec[1] if isinstance(fspec[1], str) else getattr(fspec[1], "__name__", "udf")
+        if self.core is not None and fspec[0] == "op":
+            # ATen operator: resolved, checked for poisoned inputs, dispatched and stored
+            # by the native core
+            try:
+                err = self.core.call_op(seq, [r.id for r in results], [r.id for r in mutates],
+                                        fspec[1], tuple(args), dict(kwargs), stream)
+            except Exception:  # noqa: BLE001 - argument shapes the core does not take
+                err = "python"
+            if err is None:
+                return
+            if err != "python":
+                if err[5] < 0:
+                    self._report(RemoteError(*err[:5]))
+                return
         try:
             dep = None
 
@@ -178,6 +259,8 @@ class TensorWorker(Actor):
         if stream_id not in self.streams:
             self.streams[stream_id] = torch.cuda.Stream(device=self.device) \
                 if (self.use_cuda and not default) else None
+            if self.core is not None:
+                self.core.create_stream(stream_id, self.streams[stream_id])
 
     def _m_borrow_create(self, borrow_id, ref, from_stream, to_stream, result) -> None:
         # the borrowing stream waits for the producing stream; the value is aliased
@@ -298,13 +381,26 @@ class TensorWorker(Actor):
 
     def _m_define_recording(self, rec_id: int, msgs: List[tuple]) -> None:
         self.recordings[rec_id] = msgs
+        if self.core is not None:
+            self.core.define_recording(rec_id, list(msgs))
 
     def _m_call_recording(self, rec_id: int, bind: Dict[int, int]) -> None:
-        """Replay a recording with formal ref ids rebound to this call's ids."""
-        def rb(obj):
-            return _map_refs(obj, lambda r: Ref(bind.get(r.id, r.id)))
-        for m in self.recordings[rec_id]:
+        """Replay a recording with formal ref ids rebound to this call's ids.  Operator calls
+        are replayed by the native core in one go; the other messages of the recording come
+        back through ``fallback`` in their recorded position."""
+        msgs = self.recordings[rec_id]
+
+        def run_py(index: int, b: Dict[int, int]) -> None:
+            m = msgs[index]
+            rb = lambda obj: _map_refs(obj, lambda r: Ref(b.get(r.id, r.id)))  # noqa: E731
             getattr(self, "_m_" + m[0])(*[rb(x) for x in m[1:]])
+
+        if self.core is not None:
+            self.core.call_recording(rec_id, dict(bind), run_py,
+                                     lambda e: self._report(RemoteError(*e[:5])))
+            return
+        for i in range(len(msgs)):
+            run_py(i, bind)
 
     # ----------------------------------------------------------------------- fetch
     def _fetch(self, seq, ref_tree, preprocess):
