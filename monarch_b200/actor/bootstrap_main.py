@@ -11,6 +11,11 @@ import sys
 
 
 def main() -> int:
+    for mod in filter(None, os.environ.get("MB200_PREIMPORT", "").split(",")):
+        try:
+            __import__(mod)     # on the main thread, before any actor thread exists
+        except ImportError:
+            pass
     fn = os.environ.get("MB200_BOOTSTRAP_FN")
     if fn:
         import cloudpickle

@@ -66,7 +66,12 @@ class _Unpickler(pickle.Unpickler):
             if len(raw) == 0:
                 t = torch.empty(shape, dtype=dt)
             else:
-                t = torch.frombuffer(bytearray(raw), dtype=torch.uint8).view(dt).reshape(shape)
+                # one copy into storage that torch owns (no Python buffer kept alive by a
+                # tensor that may outlive this interpreter thread)
+                t = torch.empty(len(raw), dtype=torch.uint8)
+                import ctypes
+                ctypes.memmove(t.data_ptr(), raw, len(raw))
+                t = t.view(dt).reshape(shape)
             return t.requires_grad_(req) if req else t
         raise pickle.UnpicklingError(f"unknown persistent id {pid!r}")
 

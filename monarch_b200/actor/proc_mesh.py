@@ -319,6 +319,12 @@ def _child_env(extra: Optional[Dict[str, str]]) -> Dict[str, str]:
     if root not in paths:
         paths.insert(0, root)
     env.setdefault("PYTHONPATH", os.pathsep.join(paths))
+    # A proc whose first ``import torch`` happens on one of the runtime's actor threads (while
+    # a message carrying tensors is being unpickled) crashed on its next tensor allocation;
+    # importing it on the proc's main thread before any actor runs does not.  So when this
+    # process uses torch, tell the children to import it at start-up.
+    if "torch" in sys.modules:
+        env.setdefault("MB200_PREIMPORT", "torch")
     main = sys.modules.get("__main__")
     main_file = getattr(main, "__file__", None)
     if main_file:

@@ -14,7 +14,8 @@ import torch
 # ---- worker-side (called by path) ---------------------------------------------------
 def _manual_seed(seed: int, per_rank: bool = False) -> None:
     import os
-    s = int(seed) + (int(os.environ.get("RANK", 0)) if per_rank else 0)
+    rank = os.environ.get("RANK", os.environ.get("HYPERACTOR_MESH_INDEX", "0"))
+    s = int(seed) + (int(rank) if per_rank else 0)
     torch.manual_seed(s)
 
 

@@ -1,0 +1,37 @@
+"""The example programs double as acceptance tests."""
+import importlib.util
+import os
+
+
+def _load(name):
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples",
+                        name + ".py")
+    spec = importlib.util.spec_from_file_location(name, path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def test_ping_pong_and_dining_philosophers():
+    out = _load("ping_pong").run(in_process=False)
+    assert out["ping_hits"] == [4, 4]           # 6 bounces + the serve end on the ping side
+    assert out["meals"] == [3] * 5
+    assert 1 <= out["max_eating_at_once"] <= 2  # never two neighbours at once
+
+
+def test_grpo_weight_refresh_learns():
+    out = _load("grpo_weight_refresh").run(iters=40)
+    assert out["versions"] == 40
+    assert out["reward_last"] > out["reward_first"] + 0.1, out
+
+
+def test_distributed_tensor_ddp():
+    out = _load("distributed_tensors_ddp").run()
+    assert out["replicas_in_sync"]
+    assert out["loss_last"] < out["loss_first"]
+
+
+def test_lazy_top_level_api():
+    import monarch_b200 as m
+    assert m.DeviceMesh is m.tensor_engine.DeviceMesh and callable(m.remote)
+    assert "fetch_shard" in dir(m) and m.timer.CudaTimer
