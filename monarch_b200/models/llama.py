@@ -227,6 +227,19 @@ class LocalParamStore:
         self.params.copy_(flat)
         self.master.copy_(flat)
 
+    def state_dict_shard(self) -> dict:
+        """Everything a resumed run needs from this store (fp32 master weights and moments,
+        optimizer step)."""
+        return {"master": self.master, "m": self.m, "v": self.v, "step": self.step_count,
+                "rank": 0, "world": 1}
+
+    def load_state_dict_shard(self, sd: dict) -> None:
+        self.master.copy_(sd["master"])
+        self.m.copy_(sd["m"])
+        self.v.copy_(sd["v"])
+        self.step_count = int(sd["step"])
+        self.params.copy_(self.master)
+
 
 def init_params_(layout: ParamLayout, master: torch.Tensor, seed: int, std: float,
                  lo: int = 0, hi: Optional[int] = None) -> None:

@@ -90,6 +90,7 @@ class FSDPParamStore:
         self._buf_age = [0] * n_buffers
         self._clock = 0
         self.step_count = 0
+        self._adam_offset = 0
         self._phase = "fwd"
         self._hyper = dict(lr=1e-4, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1, grad_scale=1.0)
         self._pending_updates: List[int] = []
@@ -249,7 +250,8 @@ class FSDPParamStore:
                     self._shard(self.v, ui).data_ptr(),
                     self._shard(self.param_shards, ui).data_ptr(), s, self.rank, self.world, ui,
                     n_units + ui, self.step_count, h["lr"], h["beta1"], h["beta2"], h["eps"],
-                    h["wd"], self.step_count, scale, self._flags.counter.data_ptr(), 0,
+                    h["wd"], self.step_count + self._adam_offset, scale,
+                    self._flags.counter.data_ptr(), 0,
                     K.status_word(self.device).data_ptr(), K.stream_ptr()), "rs_adamw")
             return
         # library path
@@ -263,8 +265,8 @@ class FSDPParamStore:
             g_shard.copy_(tmp[self.rank * s: (self.rank + 1) * s])
         ops.adamw_(self._shard(self.master, ui), self._shard(self.m, ui), self._shard(self.v, ui),
                    g_shard, self._shard(self.param_shards, ui), lr=h["lr"], beta1=h["beta1"],
-                   beta2=h["beta2"], eps=h["eps"], wd=h["wd"], step=self.step_count,
-                   grad_scale=scale)
+                   beta2=h["beta2"], eps=h["eps"], wd=h["wd"],
+                   step=self.step_count + self._adam_offset, grad_scale=scale)
 
     def optimizer_step(self, lr, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1, grad_scale=1.0) -> None:
         """The per-unit updates were issued during backward with the hyper-parameters set
@@ -300,13 +302,19 @@ class FSDPParamStore:
 
     def state_dict_shard(self) -> dict:
         """This rank's optimizer/parameter shard for resumable checkpoints."""
-        return {"master": self.master, "m": self.m, "v": self.v, "step": self.step_count,
-                "rank": self.rank, "world": self.world}
+        return {"master": self.master, "m": self.m, "v": self.v,
+                "step": self.step_count + self._adam_offset, "rank": self.rank,
+                "world": self.world}
 
     def load_state_dict_shard(self, sd: dict) -> None:
         assert sd["world"] == self.world and sd["rank"] == self.rank
         self.master.copy_(sd["master"])
         self.m.copy_(sd["m"])
         self.v.copy_(sd["v"])
-        self.step_count = sd["step"]
+        # step_count doubles as the epoch of the cross-rank flags of this process group and
+        # must keep counting from where this process is; only the optimizer's step moves
+        self._adam_offset = int(sd["step"]) - self.step_count
         self.param_shards.copy_(self.master)
+        if self._cuda:
+            torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)

@@ -90,6 +90,45 @@ class Trainer:
         from ..models.llama import to_hf_state_dict
         return to_hf_state_dict(self.cfg, self.layout, self.store.full_params())
 
+    def save_checkpoint(self, path: str) -> None:
+        """Resumable checkpoint: every rank writes ``<path>/shard_<rank>.pt`` (its fp32 master
+        weights, AdamW moments, optimizer step, RNG states) and rank 0 writes
+        ``<path>/manifest.json`` (model, parallelism, world size, step).  The model-only,
+        Hugging Face-named view of the same weights is :meth:`state_dict`."""
+        import json
+        from ..random import get_rng_state_all
+        os.makedirs(path, exist_ok=True)
+        sd = {k: (v.detach().cpu() if isinstance(v, torch.Tensor) else v)
+              for k, v in self.store.state_dict_shard().items()}
+        sd["rng"] = get_rng_state_all()
+        torch.save(sd, os.path.join(path, f"shard_{self.rank}.pt"))
+        if self.rank == 0:
+            with open(os.path.join(path, "manifest.json"), "w") as f:
+                json.dump({"model": self.cfg.name, "parallelism": self.parallelism,
+                           "world": self.world, "step": int(sd["step"]),
+                           "seq_len": self.seq_len, "format": 1}, f)
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+
+    def load_checkpoint(self, path: str) -> int:
+        """Restore what :meth:`save_checkpoint` wrote (same parallelism and world size);
+        returns the optimizer step to continue from."""
+        import json
+        from ..random import set_rng_state_all
+        with open(os.path.join(path, "manifest.json")) as f:
+            man = json.load(f)
+        if man["world"] != self.world or man["parallelism"] != self.parallelism or \
+                man["model"] != self.cfg.name:
+            raise ValueError(f"checkpoint is for {man['model']} {man['parallelism']} x "
+                             f"{man['world']}, this trainer is {self.cfg.name} "
+                             f"{self.parallelism} x {self.world}; re-shard through state_dict()")
+        sd = torch.load(os.path.join(path, f"shard_{self.rank}.pt"), map_location="cpu",
+                        weights_only=False)
+        self.store.load_state_dict_shard(sd)
+        set_rng_state_all(sd["rng"])
+        return int(sd["step"])
+
     def load_state_dict(self, sd: dict) -> None:
         from ..models.llama import load_hf_state_dict
         flat = torch.empty(self.layout.total, dtype=torch.bfloat16, device=self.device)
