@@ -3,6 +3,7 @@
 
     python benchmarks/profile_case.py gemm            # 3 launches of one 8192x4096x4096 GEMM
     python benchmarks/profile_case.py elementwise     # one launch of each memory-bound kernel
+    python benchmarks/profile_case.py attn            # attention forward + backward, S=4096, 16q/4kv
     python benchmarks/profile_case.py step            # 2-layer Llama-3-8B-shaped training steps
 
 Inputs are larger than the 126 MB L2 but only a few hundred MB, so a multi-pass capture
@@ -58,8 +59,8 @@ def elementwise_case():
     torch.cuda.synchronize()
 
 
-def attn_case():
-    B, S, Hq, Hkv, hd = 1, 8192, 32, 8, 128
+def attn_case(S=4096, Hq=16, Hkv=4):
+    B, hd = 1, 128   # qkv + o + do + dqkv = 56 MB at the default size: a short capture
     qkv = torch.randn(B * S, (Hq + 2 * Hkv) * hd, device="cuda", dtype=bf16)
     o, ctx = ops.attention_fwd(qkv, B, S, Hq, Hkv, hd)
     do = torch.randn_like(o)
