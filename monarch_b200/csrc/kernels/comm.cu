@@ -17,7 +17,9 @@
 // status word instead of hanging.  No TMA, no multicast loads: peer data moves with
 // per-thread 16-byte loads and stores.
 #include <cuda_bf16.h>
+#include <cuda.h>
 #include <cuda_runtime.h>
+#include <string.h>
 #include <stdint.h>
 
 #include "comm.cuh"
@@ -214,7 +216,20 @@ __global__ void __launch_bounds__(256)
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   const bool aligned = ((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src)) & 15) == 0;
   if (aligned) {
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride)
+    // four independent 16-byte loads in flight per thread: a pull over NVLink is bound by
+    // the number of outstanding loads, not by issue rate
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; i + 3 * stride < nvec; i += 4 * stride) {
+      uint4 v0 = ld_nc_v4(reinterpret_cast<const uint4*>(src) + i);
+      uint4 v1 = ld_nc_v4(reinterpret_cast<const uint4*>(src) + i + stride);
+      uint4 v2 = ld_nc_v4(reinterpret_cast<const uint4*>(src) + i + 2 * stride);
+      uint4 v3 = ld_nc_v4(reinterpret_cast<const uint4*>(src) + i + 3 * stride);
+      reinterpret_cast<uint4*>(dst)[i] = v0;
+      reinterpret_cast<uint4*>(dst)[i + stride] = v1;
+      reinterpret_cast<uint4*>(dst)[i + 2 * stride] = v2;
+      reinterpret_cast<uint4*>(dst)[i + 3 * stride] = v3;
+    }
+    for (; i < nvec; i += stride)
       reinterpret_cast<uint4*>(dst)[i] = ld_nc_v4(reinterpret_cast<const uint4*>(src) + i);
     for (int64_t b = (nvec << 4) + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; b < nbytes;
          b += stride)
@@ -335,6 +350,89 @@ extern "C" int mb200_peer_copy(void* dst, const void* src, int64_t nbytes, uint3
                                                  done_flag, done_value, counter);
   return (int)cudaGetLastError();
 }
+
+// Let kernels running on device `dev` dereference memory that lives on device `peer` (memory
+// opened through CUDA IPC or allocated by this process).  Idempotent.  Returns 0, or 1003 when
+// the two devices have no peer path.
+extern "C" int mb200_enable_peer_access(int dev, int peer) {
+  if (dev == peer) return 0;
+  int can = 0;
+  cudaError_t e = cudaDeviceCanAccessPeer(&can, dev, peer);
+  if (e != cudaSuccess) return (int)e;
+  if (!can) return 1003;
+  int cur = 0;
+  cudaGetDevice(&cur);
+  cudaSetDevice(dev);
+  e = cudaDeviceEnablePeerAccess(peer, 0);
+  if (e == cudaErrorPeerAccessAlreadyEnabled) {
+    cudaGetLastError();
+    e = cudaSuccess;
+  }
+  cudaSetDevice(cur);
+  return (int)e;
+}
+
+// ---- CUDA IPC export / import of a device buffer (RDMABuffer between processes) -----------
+// Export: the handle names the whole allocation that contains `ptr`; `offset` is ptr's
+// distance from its base.  Import: must run with the READER's device current and with lazy
+// peer access, so that the mapping is usable by kernels of that device even when the memory
+// lives on another GPU (a mapping opened in the owner device's context is not reachable
+// through peer access from a different device of the importing process).
+extern "C" int mb200_ipc_export(const void* ptr, void* handle_out64, int64_t* offset_out,
+                                int64_t* alloc_size_out) {
+  using GetRange = CUresult (*)(CUdeviceptr*, size_t*, CUdeviceptr);
+  static GetRange get_range = nullptr;
+  if (!get_range) {
+    void* fp = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &fp, cudaEnableDefault, &q) !=
+            cudaSuccess || q != cudaDriverEntryPointSuccess)
+      return 1004;
+    get_range = reinterpret_cast<GetRange>(fp);
+  }
+  // the driver call needs the owning device's context current on this thread (the caller may
+  // be a runtime thread that has never touched CUDA)
+  cudaPointerAttributes attr;
+  cudaError_t e = cudaPointerGetAttributes(&attr, ptr);
+  if (e != cudaSuccess) return (int)e;
+  if (attr.type != cudaMemoryTypeDevice) return 1006;
+  int cur = 0;
+  cudaGetDevice(&cur);
+  cudaSetDevice(attr.device);
+  cudaFree(nullptr);
+  CUdeviceptr base = 0;
+  size_t size = 0;
+  const CUresult cr = get_range(&base, &size, reinterpret_cast<CUdeviceptr>(ptr));
+  cudaIpcMemHandle_t h;
+  if (cr == CUDA_SUCCESS) e = cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(base));
+  cudaSetDevice(cur);
+  if (cr != CUDA_SUCCESS) return 1005;
+  if (e != cudaSuccess) return (int)e;
+  static_assert(sizeof(h) == 64, "cudaIpcMemHandle_t is 64 bytes");
+  memcpy(handle_out64, &h, 64);
+  *offset_out = (int64_t)(reinterpret_cast<CUdeviceptr>(ptr) - base);
+  *alloc_size_out = (int64_t)size;
+  return 0;
+}
+
+extern "C" int mb200_ipc_open(const void* handle64, int reader_device, void** base_out) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  int cur = 0;
+  cudaGetDevice(&cur);
+  cudaSetDevice(reader_device);
+  void* p = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  cudaSetDevice(cur);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return (int)e;
+  }
+  *base_out = p;
+  return 0;
+}
+
+extern "C" int mb200_ipc_close(void* base) { return (int)cudaIpcCloseMemHandle(base); }
 
 extern "C" int mb200_wait_flag(const uint32_t* flag, uint32_t value, int limit_ms, int* status,
                                void* stream) {

@@ -75,9 +75,16 @@ class _Manager:
                 raw[off: off + data.numel()].copy_(data)
                 body, parts = flatten(("ok", None))
             elif op == "cuda_handle":
-                from torch.multiprocessing.reductions import reduce_tensor
-                fn, args = reduce_tensor(raw)
-                body, parts = flatten(("ok", (fn, args)))
+                import ctypes
+                from ..ops import kernels as K
+                h = ctypes.create_string_buffer(64)
+                off, size = ctypes.c_int64(0), ctypes.c_int64(0)
+                K.check(K.lib().mb200_ipc_export(raw.data_ptr(), h, ctypes.byref(off),
+                                                 ctypes.byref(size)), "ipc_export", 0)
+                # the owner must not free or reuse the allocation while peers map it: the
+                # registry keeps the tensor alive until drop()
+                body, parts = flatten(("ok", (bytes(h.raw), int(off.value), raw.numel(),
+                                              raw.device.index or 0)))
             elif op == "drop":
                 self.buffers.pop(bid, None)
                 body, parts = flatten(("ok", None))
@@ -109,29 +116,75 @@ def _manager_for_current_proc() -> _Manager:
         return m
 
 
-_peer_cache: Dict[Tuple[str, int], torch.Tensor] = {}
+_peer_cache: Dict[tuple, int] = {}
 _copy_state: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
+_peer_enabled: set = set()
 
 
-def _device_copy(dst: torch.Tensor, src: torch.Tensor) -> None:
-    """dst <- src with the peer-copy kernel (either side may be a peer mapping)."""
+def _ensure_peer_access(dev: int, other: int) -> None:
+    """A kernel on ``dev`` is about to dereference memory of device ``other`` (an IPC mapping
+    of another process's buffer is opened on the owner's device): peer access must be on in
+    that direction, or the first access faults."""
+    if dev == other or (dev, other) in _peer_enabled:
+        return
     from ..ops import kernels as K
-    dev = dst.device if dst.is_cuda else src.device
-    idx = dev.index or 0
-    st = _copy_state.get(idx)
+    rc = K.lib().mb200_enable_peer_access(dev, other)
+    if rc == 1003:
+        raise RDMAError(f"GPU {dev} has no peer path to GPU {other}")
+    K.check(rc, "enable_peer_access", 0)
+    _peer_enabled.add((dev, other))
+
+
+def _device_copy_ptr(dst_ptr: int, src_ptr: int, nbytes: int, dev_index: int) -> None:
+    """nbytes from src_ptr to dst_ptr with the peer-copy kernel running on ``dev_index``
+    (either pointer may be a mapping of another process's / GPU's memory)."""
+    from ..ops import kernels as K
+    dev = torch.device("cuda", dev_index)
+    st = _copy_state.get(dev_index)
     if st is None:
         st = (torch.zeros(4, dtype=torch.int32, device=dev),
               torch.zeros(4, dtype=torch.int32, device=dev))
-        _copy_state[idx] = st
+        _copy_state[dev_index] = st
     done, counter = st
     with torch.cuda.device(dev):
         done.zero_()
-        K.check(K.lib().mb200_peer_copy(dst.data_ptr(), src.data_ptr(), dst.numel(),
-                                        done.data_ptr(), 1, counter.data_ptr(), 0,
-                                        K.stream_ptr()), "peer_copy")
+        K.check(K.lib().mb200_peer_copy(dst_ptr, src_ptr, nbytes, done.data_ptr(), 1,
+                                        counter.data_ptr(), 0, K.stream_ptr()), "peer_copy")
         torch.cuda.current_stream().synchronize()
         if int(done[0].item()) != 1:
             raise RDMAError("peer copy did not publish its completion flag")
+
+
+def _device_copy(dst: torch.Tensor, src: torch.Tensor) -> None:
+    """dst <- src between tensors of this process (same or different GPUs)."""
+    dev = dst.device if dst.is_cuda else src.device
+    idx = dev.index or 0
+    for t in (dst, src):
+        if t.is_cuda and (t.device.index or 0) != idx:
+            _ensure_peer_access(idx, t.device.index or 0)
+    _device_copy_ptr(dst.data_ptr(), src.data_ptr(), dst.numel(), idx)
+
+
+_ipc_open: Dict[Tuple[bytes, int], int] = {}   # (handle, reader device) -> mapped base address
+
+
+def _open_ipc(handle: bytes, reader_device: int) -> int:
+    """Map another process's allocation for kernels of ``reader_device`` (once per handle and
+    device; CUDA refuses to open the same handle twice in one process)."""
+    import ctypes
+    from ..ops import kernels as K
+    key = (handle, reader_device)
+    base = _ipc_open.get(key)
+    if base is None:
+        torch.cuda.init()
+        with torch.cuda.device(reader_device):
+            torch.cuda.current_stream()          # makes sure the device's context exists
+            out = ctypes.c_void_p(0)
+            K.check(K.lib().mb200_ipc_open(handle, reader_device, ctypes.byref(out)),
+                    "ipc_open", 0)
+        base = int(out.value)
+        _ipc_open[key] = base
+    return base
 
 
 class RDMABuffer:
@@ -180,14 +233,18 @@ class RDMABuffer:
             raise RDMAError(payload)
         return payload
 
-    def _peer_mapping(self, timeout: float) -> torch.Tensor:
-        key = (self._owner, self._id)
-        t = _peer_cache.get(key)
-        if t is None:
-            fn, args = self._request(("cuda_handle", self._id), timeout)
-            t = fn(*args)
-            _peer_cache[key] = t
-        return t
+    def _peer_pointer(self, reader_device: int, timeout: float) -> int:
+        """Address, valid for kernels of ``reader_device`` in this process, of byte 0 of the
+        owner's buffer."""
+        key = (self._owner, self._id, reader_device)
+        p = _peer_cache.get(key)
+        if p is None:
+            handle, off, nbytes, _owner_dev = self._request(("cuda_handle", self._id), timeout)
+            if nbytes != self._nbytes:
+                raise RDMAError("the owner's buffer changed size")
+            p = _open_ipc(handle, reader_device) + off
+            _peer_cache[key] = p
+        return p
 
     def read_into(self, dst: torch.Tensor, offset: int = 0, timeout: float = 3) -> Future[None]:
         """Copy ``dst.nbytes`` bytes starting at ``offset`` of the remote buffer into ``dst``."""
@@ -210,7 +267,8 @@ class RDMABuffer:
                     d.copy_(src)
                 return None
             if self._cuda and d.is_cuda:
-                _device_copy(d, self._peer_mapping(timeout)[offset: offset + n])
+                idx = d.device.index or 0
+                _device_copy_ptr(d.data_ptr(), self._peer_pointer(idx, timeout) + offset, n, idx)
                 return None
             data = self._request(("read", self._id, offset, n), timeout)
             d.copy_(data)
@@ -236,7 +294,8 @@ class RDMABuffer:
                     dst.copy_(s)
                 return None
             if self._cuda and s.is_cuda:
-                _device_copy(self._peer_mapping(timeout)[offset: offset + n], s)
+                idx = s.device.index or 0
+                _device_copy_ptr(self._peer_pointer(idx, timeout) + offset, s.data_ptr(), n, idx)
                 return None
             self._request(("write", self._id, offset, s.cpu()), timeout)
             return None
@@ -250,7 +309,8 @@ class RDMABuffer:
                 m.buffers.pop(self._id, None)
             else:
                 self._request(("drop", self._id), 3)
-            _peer_cache.pop((self._owner, self._id), None)
+            for k in [k for k in _peer_cache if k[:2] == (self._owner, self._id)]:
+                _peer_cache.pop(k, None)
             return None
         return Future(run)
 
