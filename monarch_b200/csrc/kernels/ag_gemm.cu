@@ -18,6 +18,7 @@
 #include <cuda_runtime.h>
 
 #include "gather.cuh"
+#include "gemm2_tcgen05.cuh"
 #include "gemm_tcgen05.cuh"
 #include "mb200.h"
 
@@ -25,6 +26,8 @@ namespace mb200 {
 
 int make_gemm_tmaps(CUtensorMap* ta, CUtensorMap* tb, const void* A, const void* B, int M, int N,
                     int K, int lda, int ldb, int a_mn, int b_mn);
+int make_gemm2_tmaps(CUtensorMap* ta, CUtensorMap* tb, const void* A, const void* B, int M, int N,
+                     int K, int lda, int ldb, int a_mn, int b_mn);
 int sm_count();
 
 template <bool A_MN>
@@ -38,6 +41,22 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     return;
   }
   gemm_cta_body<A_MN, false>(&tmA, &tmB, p, blockIdx.x - n_comm, gridDim.x - n_comm, smem_raw);
+}
+
+// CTA-pair variant: the copy CTAs are the first n_comm/2 clusters, every other cluster is one
+// 256x256-tile GEMM pair (cta_group::2).  n_comm is even, so no cluster mixes the two roles.
+template <bool A_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+    ag_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA,
+                        const __grid_constant__ CUtensorMap tmB, const GemmParams p,
+                        const GatherParams g, int n_comm) {
+  extern __shared__ uint8_t smem_raw[];
+  if ((int)blockIdx.x < n_comm) {
+    gather_chunks_bulk(g, blockIdx.x, n_comm, smem_raw);
+    return;
+  }
+  gemm2_cta_body<A_MN, false>(&tmA, &tmB, p, ((int)blockIdx.x - n_comm) >> 1,
+                              ((int)gridDim.x - n_comm) >> 1, smem_raw);
 }
 
 // Gather-only launch of the same copy loop (used for the chunks that hold 1-D parameters,
@@ -84,11 +103,38 @@ extern "C" int mb200_ag_gemm(const void* A, int lda, int a_mn, int M, int K, voi
   const int sms = sm_count();
   if (n_comm <= 0) n_comm = 16;
   if (n_comm > sms / 2) n_comm = sms / 2;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (mb200_gemm_get_impl() == 2) {
+    n_comm &= ~1;
+    if (n_comm < 2) n_comm = 2;
+    CUtensorMap ta2, tb2;
+    r = make_gemm2_tmaps(&ta2, &tb2, A, W, M, N, K, lda, K, a_mn, 0);
+    if (r) return 1000 - r;
+    const int tiles = ((M + G2_BM - 1) / G2_BM) * ((N + G2_BN - 1) / G2_BN);
+    int pairs = sms / 2 - n_comm / 2;
+    if (tiles < pairs) pairs = tiles;
+    const int grid = n_comm + 2 * pairs;
+    static bool configured2[2] = {false, false};
+    if (!configured2[a_mn ? 1 : 0]) {
+      cudaError_t e = a_mn ? cudaFuncSetAttribute(ag_gemm_pair_kernel<true>,
+                                                  cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                  G2_SMEM_BYTES)
+                           : cudaFuncSetAttribute(ag_gemm_pair_kernel<false>,
+                                                  cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                  G2_SMEM_BYTES);
+      if (e != cudaSuccess) return (int)e;
+      configured2[a_mn ? 1 : 0] = true;
+    }
+    if (a_mn)
+      ag_gemm_pair_kernel<true><<<grid, GEMM_THREADS, G2_SMEM_BYTES, st>>>(ta2, tb2, p, g, n_comm);
+    else
+      ag_gemm_pair_kernel<false><<<grid, GEMM_THREADS, G2_SMEM_BYTES, st>>>(ta2, tb2, p, g, n_comm);
+    return (int)cudaGetLastError();
+  }
   const int tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + GEMM_BN - 1) / GEMM_BN);
   int gemm_ctas = sms - n_comm;
   if (tiles < gemm_ctas) gemm_ctas = tiles;
   const int grid = n_comm + gemm_ctas;
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   static bool configured[2] = {false, false};
   if (!configured[a_mn ? 1 : 0]) {
     cudaError_t e = a_mn ? cudaFuncSetAttribute(ag_gemm_kernel<true>,

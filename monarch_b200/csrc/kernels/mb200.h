@@ -14,6 +14,11 @@ int mb200_gemm_bf16(const void* A, const void* B, void* C, const void* R, int M,
                     int lda, int ldb, int ldc, int ldr, int a_mn, int b_mn, int accumulate,
                     int* status, void* stream);
 
+// Which GEMM kernel the library uses: 1 = single-CTA 128x256 tiles, 2 = CTA-pair 256x256
+// tiles (default).  The fused collective+GEMM kernels follow the same setting.
+int mb200_gemm_set_impl(int impl);
+int mb200_gemm_get_impl(void);
+
 // RMSNorm over the last dimension. x,y: [rows, d] bf16 (row stride = d); w: [d] bf16;
 // rstd: [rows] fp32 (saved for backward).
 int mb200_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int d,

@@ -133,6 +133,20 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   gemm_cta_body<false, B_MN>(&tmA, &tmB, p, blockIdx.x - n_comm, gridDim.x - n_comm, smem_raw);
 }
 
+template <bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+    moe_gather_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA,
+                                const __grid_constant__ CUtensorMap tmB, const GemmParams p,
+                                const MoeGather g, int n_comm) {
+  extern __shared__ uint8_t smem_raw[];
+  if ((int)blockIdx.x < n_comm) {   // n_comm is even: whole clusters gather
+    moe_gather_rows(g, blockIdx.x, n_comm);
+    return;
+  }
+  gemm2_cta_body<false, B_MN>(&tmA, &tmB, p, ((int)blockIdx.x - n_comm) >> 1,
+                              ((int)gridDim.x - n_comm) >> 1, smem_raw);
+}
+
 // ------------------------------------------------------------------- expert SwiGLU
 // h[i] = w[i] * silu(gate[i]) * up[i] for rows i < *m; rows up to the next multiple of 64
 // (bounded by cap) are zeroed.
@@ -309,10 +323,39 @@ extern "C" int mb200_moe_gather_gemm(const void* const* counts_ptrs, const void*
   const int sms = sm_count();
   if (n_comm <= 0) n_comm = 24;
   if (n_comm > sms / 2) n_comm = sms / 2;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (mb200_gemm_get_impl() == 2) {
+    n_comm &= ~1;
+    if (n_comm < 2) n_comm = 2;
+    CUtensorMap ta2, tb2;
+    r = make_gemm2_tmaps(&ta2, &tb2, gathered, W, cap, N, d, d, ldw, 0, b_mn);
+    if (r) return 1000 - r;
+    const int tiles = ((cap + G2_BM - 1) / G2_BM) * ((N + G2_BN - 1) / G2_BN);
+    int pairs = sms / 2 - n_comm / 2;
+    if (tiles < pairs) pairs = tiles;
+    const int grid = n_comm + 2 * pairs;
+    static bool configured2[2] = {false, false};
+    if (!configured2[b_mn ? 1 : 0]) {
+      cudaError_t e = b_mn ? cudaFuncSetAttribute(moe_gather_gemm_pair_kernel<true>,
+                                                  cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                  G2_SMEM_BYTES)
+                           : cudaFuncSetAttribute(moe_gather_gemm_pair_kernel<false>,
+                                                  cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                  G2_SMEM_BYTES);
+      if (e != cudaSuccess) return (int)e;
+      configured2[b_mn ? 1 : 0] = true;
+    }
+    if (b_mn)
+      moe_gather_gemm_pair_kernel<true><<<grid, GEMM_THREADS, G2_SMEM_BYTES, st>>>(ta2, tb2, p, g,
+                                                                                  n_comm);
+    else
+      moe_gather_gemm_pair_kernel<false><<<grid, GEMM_THREADS, G2_SMEM_BYTES, st>>>(ta2, tb2, p, g,
+                                                                                   n_comm);
+    return (int)cudaGetLastError();
+  }
   const int tiles = ((cap + GEMM_BM - 1) / GEMM_BM) * ((N + GEMM_BN - 1) / GEMM_BN);
   int gemm_ctas = sms - n_comm;
   if (tiles < gemm_ctas) gemm_ctas = tiles;
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   static bool configured[2] = {false, false};
   if (!configured[b_mn ? 1 : 0]) {
     cudaError_t e = b_mn ? cudaFuncSetAttribute(moe_gather_gemm_kernel<true>,

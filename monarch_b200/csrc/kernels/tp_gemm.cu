@@ -44,6 +44,20 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   gemm_cta_body<false, B_MN>(&tmA, &tmB, p, blockIdx.x - n_comm, gridDim.x - n_comm, smem_raw);
 }
 
+template <bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+    ag_a_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA,
+                          const __grid_constant__ CUtensorMap tmB, const GemmParams p,
+                          const GatherParams g, int n_comm) {
+  extern __shared__ uint8_t smem_raw[];
+  if ((int)blockIdx.x < n_comm) {   // n_comm is even: whole clusters copy
+    gather_chunks_bulk(g, blockIdx.x, n_comm, smem_raw);
+    return;
+  }
+  gemm2_cta_body<false, B_MN>(&tmA, &tmB, p, ((int)blockIdx.x - n_comm) >> 1,
+                              ((int)gridDim.x - n_comm) >> 1, smem_raw);
+}
+
 // out[r, c] = sum_s staging[s][r][c] (+ residual[r, c]); fp32 accumulation, bf16 out.
 __global__ void __launch_bounds__(256)
     rs_finish_kernel(const __nv_bfloat16* __restrict__ staging, int world, int rows, int N, int ld,
@@ -107,11 +121,38 @@ extern "C" int mb200_ag_a_gemm(void* a_full, const void* const* shard_ptrs, long
   const int sms = sm_count();
   if (n_comm <= 0) n_comm = 16;
   if (n_comm > sms / 2) n_comm = sms / 2;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (mb200_gemm_get_impl() == 2) {
+    n_comm &= ~1;
+    if (n_comm < 2) n_comm = 2;
+    CUtensorMap ta2, tb2;
+    r = make_gemm2_tmaps(&ta2, &tb2, a_full, B, M, N, K, K, ldb, 0, b_mn);
+    if (r) return 1000 - r;
+    const int tiles = ((M + G2_BM - 1) / G2_BM) * ((N + G2_BN - 1) / G2_BN);
+    int pairs = sms / 2 - n_comm / 2;
+    if (tiles < pairs) pairs = tiles;
+    const int grid = n_comm + 2 * pairs;
+    static bool configured2[2] = {false, false};
+    if (!configured2[b_mn ? 1 : 0]) {
+      cudaError_t e = b_mn ? cudaFuncSetAttribute(ag_a_gemm_pair_kernel<true>,
+                                                  cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                  G2_SMEM_BYTES)
+                           : cudaFuncSetAttribute(ag_a_gemm_pair_kernel<false>,
+                                                  cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                  G2_SMEM_BYTES);
+      if (e != cudaSuccess) return (int)e;
+      configured2[b_mn ? 1 : 0] = true;
+    }
+    if (b_mn)
+      ag_a_gemm_pair_kernel<true><<<grid, GEMM_THREADS, G2_SMEM_BYTES, st>>>(ta2, tb2, p, g, n_comm);
+    else
+      ag_a_gemm_pair_kernel<false><<<grid, GEMM_THREADS, G2_SMEM_BYTES, st>>>(ta2, tb2, p, g, n_comm);
+    return (int)cudaGetLastError();
+  }
   const int tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + GEMM_BN - 1) / GEMM_BN);
   int gemm_ctas = sms - n_comm;
   if (tiles < gemm_ctas) gemm_ctas = tiles;
   const int grid = n_comm + gemm_ctas;
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   static bool configured[2] = {false, false};
   if (!configured[b_mn ? 1 : 0]) {
     cudaError_t e = b_mn ? cudaFuncSetAttribute(ag_a_gemm_kernel<true>,
