@@ -174,6 +174,8 @@ def main():
                        "global_batch": n_mb * B if m_pp else B * world, "seq_len": S,
                        "parallelism": par, "activation_checkpointing": True,
                        "optimizer": "AdamW fp32 master", "comm": args.comm,
+                       **({"fsdp_gather": os.environ.get("MB200_FSDP_GATHER", "prefetch")}
+                          if par.startswith("fsdp") else {}),
                        "l2": "per-step working set (>100 GB of weights and optimizer state) "
                              "is far larger than the 126 MB L2"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "loss": final_loss,

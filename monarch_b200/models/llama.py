@@ -279,6 +279,14 @@ def init_params_(layout: ParamLayout, master: torch.Tensor, seed: int, std: floa
                 master[ss - lo: ee - lo].copy_(vals[ss - ca: ee - ca])
 
 
+def _unit_gemm(w, a: torch.Tensor, name: str) -> torch.Tensor:
+    """``a @ w[name]^T``.  A parameter store may hand out a unit whose weights are still
+    sharded across ranks and offer ``gemm(a, name)`` to fetch them inside the GEMM kernel
+    (FSDP with in-GEMM gathering); a plain dict of views takes the ordinary kernel."""
+    f = getattr(w, "gemm", None)
+    return f(a, name) if f is not None else ops.gemm(a, w[name])
+
+
 class LlamaEngine:
     """Explicit training engine: ``loss = engine.forward_backward(tokens, targets)``
     then ``engine.optimizer_step(lr)``.
@@ -308,7 +316,7 @@ class LlamaEngine:
         again (selective checkpointing: 2 bytes per activation element per layer)."""
         cfg = self.cfg
         h1, rstd1 = ops.rmsnorm_fwd(x, w["attn_norm"], cfg.eps)
-        qkv = ops.gemm(h1, w["wqkv"])
+        qkv = _unit_gemm(w, h1, "wqkv")
         ops.rope_(qkv, self.cos, self.sin, S, cfg.n_heads + cfg.n_kv_heads, cfg.hd)
         if attn_saved is not None:
             attn, actx = ops.attention_ctx_from_saved(qkv, attn_saved, B, S, cfg.n_heads,
@@ -322,7 +330,7 @@ class LlamaEngine:
     def _mlp_fwd(self, w: dict, x2: torch.Tensor, keep: bool):
         """x2 -> x2 + mlp(norm(x2))."""
         h2, rstd2 = ops.rmsnorm_fwd(x2, w["mlp_norm"], self.cfg.eps)
-        gu = ops.gemm(h2, w["w_gu"])
+        gu = _unit_gemm(w, h2, "w_gu")
         hmid = ops.swiglu_fwd(gu)
         y = ops.gemm(hmid, w["w_down"], residual=x2)
         return y, ((x2, rstd2, h2, gu, hmid) if keep else None)

@@ -22,6 +22,7 @@ The reference has no FSDP; the primitives it offers are ``reduce(scatter=True)``
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Optional
 
 import torch
@@ -34,10 +35,49 @@ from ..ops import kernels as K
 bf16 = torch.bfloat16
 
 
+class _DeferredUnit(dict):
+    """Parameter views of a unit whose gather rides on its GEMMs.  ``gemm(a, name)`` runs
+    the fused gather+GEMM kernel when ``name`` lies beyond the gather frontier; plain item
+    access pulls whatever the item still lacks with the copy-only kernel first, so code
+    that knows nothing of the deferral stays correct."""
+
+    def __init__(self, views, store, ui, b):
+        super().__init__(views)
+        self._store, self._ui, self._b = store, ui, b
+
+    def _live(self) -> bool:
+        st = self._store
+        return st._buf_unit[self._b] == self._ui and st._frontier[self._b] is not None
+
+    def __getitem__(self, name):
+        if self._live():
+            st = self._store
+            _, c1, _ = st._chunk_span(self._ui, name)
+            if c1 > st._frontier[self._b]:
+                st._gather_plain(self._ui, self._b, c1)
+        return dict.__getitem__(self, name)
+
+    def gemm(self, a, name):
+        st = self._store
+        if self._live() and name in st._FUSE_AT:
+            _, c1, _ = st._chunk_span(self._ui, name)
+            if c1 > st._frontier[self._b]:
+                return st._gemm_gathering(self._ui, self._b, a, name)
+        return ops.gemm(a, self[name])
+
+
 class FSDPParamStore:
     def __init__(self, layout: ParamLayout, device, seed: int = 0, init_std: float = 0.02,
                  comm: str = "fused", group: Optional[dist.ProcessGroup] = None,
-                 n_buffers: int = 3):
+                 n_buffers: int = 3, gather: Optional[str] = None,
+                 gather_chunk: int = 1 << 18):
+        """``gather``: how the layer units reach the compute stream when ``comm`` is
+        "fused".  "prefetch" (default) pulls unit i+1 on a side stream while unit i
+        computes.  "gemm" issues no separate gather for a layer: the layer's QKV GEMM
+        launch also pulls the attention half of the unit and its gate/up GEMM launch the
+        MLP half (``mb200_ag_gemm``: copy CTAs pull chunks over NVLink, the tensor-core
+        CTAs of the same kernel start on a weight tile as soon as its chunks are flagged),
+        so nothing is held ahead of use and no second stream competes for SMs."""
         self.layout = layout
         self.device = torch.device(device)
         self.group = group or dist.group.WORLD
@@ -46,6 +86,10 @@ class FSDPParamStore:
         if self.device.type != "cuda" and comm == "fused":
             comm = "nccl"
         self.comm = comm
+        gather = gather or os.environ.get("MB200_FSDP_GATHER", "prefetch")
+        if gather not in ("prefetch", "gemm"):
+            raise ValueError(f"unknown gather mode {gather!r}")
+        self.gather = gather if comm == "fused" else "prefetch"
         W = self.world
         for u in layout.units:
             if u.size % (W * 8):
@@ -94,6 +138,17 @@ class FSDPParamStore:
         self._phase = "fwd"
         self._hyper = dict(lr=1e-4, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1, grad_scale=1.0)
         self._pending_updates: List[int] = []
+        # in-GEMM gather: per buffer, one ready flag per chunk and the gather frontier
+        if gather_chunk <= 0 or gather_chunk % 8192:
+            raise ValueError("gather_chunk must be a positive multiple of 8192 elements")
+        self._chunk = gather_chunk
+        self._n_chunks_max = (self.max_unit + self._chunk - 1) // self._chunk
+        self._frontier: List[Optional[int]] = [None] * n_buffers   # None: gathered elsewhere
+        self._chunk_epoch = [0] * n_buffers
+        if self.gather == "gemm":
+            self._cflags = [torch.zeros(self._n_chunks_max, dtype=torch.int32, device=dev)
+                            for _ in range(n_buffers)]
+        self.fused_gemm_launches = 0
         if dev.type == "cuda":
             torch.cuda.synchronize(dev)
         dist.barrier(group=self.group)
@@ -128,6 +183,7 @@ class FSDPParamStore:
         u = self.layout.units[ui]
         s = self.shard_sizes[ui]
         dst = self._bufs[b][: u.size]
+        self._frontier[b] = None
         if self._cuda:
             cs = self._comm_stream
             if self._buf_free[b] is not None:
@@ -162,13 +218,27 @@ class FSDPParamStore:
                 dist.all_gather(parts, src, group=self.group)
                 torch.cat(parts, out=dst)
 
+    def _gathers_in_gemm(self, ui: int) -> bool:
+        return self.gather == "gemm" and self.layout.units[ui].name.startswith("layer")
+
     def _acquire(self, ui: int) -> int:
         b = self._find(ui)
         if b is None:
             b = self._free_buffer()
             if b is None:
                 raise RuntimeError("no free gather buffer (raise n_buffers)")
-            self._gather_into(ui, b)
+            if self._gathers_in_gemm(ui):
+                # nothing is launched here: the unit's first GEMMs pull it (_DeferredUnit)
+                if self._buf_free[b] is not None:
+                    torch.cuda.current_stream().wait_event(self._buf_free[b])
+                self._buf_unit[b] = ui
+                self._buf_ready[b] = None
+                self._frontier[b] = 0
+                self._chunk_epoch[b] += 1
+                self._clock += 1
+                self._buf_age[b] = self._clock
+            else:
+                self._gather_into(ui, b)
         if self._cuda and self._buf_ready[b] is not None:
             torch.cuda.current_stream().wait_event(self._buf_ready[b])
         self._buf_refs[b] += 1
@@ -176,6 +246,8 @@ class FSDPParamStore:
 
     def _prefetch(self, ui: int) -> None:
         if ui < 0 or ui >= len(self.layout.units) or self._find(ui) is not None:
+            return
+        if self._gathers_in_gemm(ui):
             return
         b = self._free_buffer()
         if b is not None:
@@ -207,7 +279,70 @@ class FSDPParamStore:
         if b is None:
             raise RuntimeError(f"unit {ui} is not gathered; hooks out of order")
         u = self.layout.units[ui]
-        return self.layout.views(u, self._bufs[b][: u.size])
+        views = self.layout.views(u, self._bufs[b][: u.size])
+        if self._frontier[b] is not None:
+            return _DeferredUnit(views, self, ui, b)
+        return views
+
+    # ---------------------------------------------------------------- in-GEMM gathering
+    _FUSE_AT = ("wqkv", "w_gu")   # the GEMMs that carry a gather, in layout order
+
+    def _chunk_span(self, ui: int, name: str):
+        u = self.layout.units[ui]
+        for p in u.params:
+            if p.name == name:
+                n = 1
+                for d in p.shape:
+                    n *= d
+                return p.offset // self._chunk, (p.offset + n + self._chunk - 1) // self._chunk, p
+        raise KeyError(name)
+
+    def _n_chunks(self, ui: int) -> int:
+        return (self.layout.units[ui].size + self._chunk - 1) // self._chunk
+
+    def _wait_epoch(self) -> int:
+        return self.step_count - 1 if self.step_count > 1 else 0
+
+    def _gather_plain(self, ui: int, b: int, c_end: int) -> None:
+        """Pull chunks [frontier, c_end) with the copy-only kernel on the compute stream
+        (the chunk that holds a norm gain, read before the layer's first GEMM)."""
+        c0 = self._frontier[b]
+        if c0 is None or c_end <= c0:
+            return
+        n_units = len(self.layout.units)
+        K.check(K.lib().mb200_gather_chunks(
+            self._bufs[b].data_ptr(), self._shards_sym.ptrs_at(self.shard_offsets[ui]),
+            self.shard_sizes[ui], self.rank, self.world, c0, c_end, self._chunk,
+            self._cflags[b].data_ptr(), self._chunk_epoch[b], self._flags.my_ptr, n_units + ui,
+            self._wait_epoch(), 0, K.status_word(self.device).data_ptr(), K.stream_ptr()),
+            "gather_chunks")
+        self._frontier[b] = c_end
+
+    def _gemm_gathering(self, ui: int, b: int, a: torch.Tensor, name: str) -> torch.Tensor:
+        """``a @ W[name]^T`` in the kernel that also pulls the unit's chunks from the
+        frontier up to the next gather-carrying weight."""
+        c0, c1, spec = self._chunk_span(ui, name)
+        u = self.layout.units[ui]
+        later = [q for q in u.params if q.name in self._FUSE_AT and q.offset > spec.offset]
+        target = (later[0].offset + self._chunk - 1) // self._chunk if later else self._n_chunks(ui)
+        target = max(target, c1)
+        N, Kd = spec.shape
+        a2 = a.reshape(-1, Kd)
+        if not a2.is_contiguous():
+            a2 = a2.contiguous()
+        M = a2.shape[0]
+        out = torch.empty(M, N, dtype=bf16, device=a.device)
+        n_units = len(self.layout.units)
+        K.check(K.lib().mb200_ag_gemm(
+            a2.data_ptr(), Kd, 0, M, Kd, self._bufs[b].data_ptr(), spec.offset, N,
+            out.data_ptr(), N, None, 0, self._shards_sym.ptrs_at(self.shard_offsets[ui]),
+            self.shard_sizes[ui], self.rank, self.world, self._frontier[b], target, self._chunk,
+            self._cflags[b].data_ptr(), self._chunk_epoch[b], self._flags.my_ptr, n_units + ui,
+            self._wait_epoch(), 16, K.status_word(self.device).data_ptr(), K.stream_ptr()),
+            "ag_gemm")
+        self._frontier[b] = target
+        self.fused_gemm_launches += 1
+        return out.view(*a.shape[:-1], N)
 
     def unit_grads(self, ui: int) -> Dict[str, torch.Tensor]:
         u = self.layout.units[ui]

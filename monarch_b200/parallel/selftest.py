@@ -291,8 +291,10 @@ def main() -> int:
     gen = torch.Generator().manual_seed(1000 + rank)
     toks = torch.randint(0, cfg.vocab, (4, 2, S), generator=gen).to(dev)
     outs = {}
-    for mode in ("fused", "nccl"):
-        st = FSDPParamStore(layout, dev, seed=3, init_std=0.05, comm=mode)
+    for mode in ("fused", "fused-gemm", "nccl"):
+        st = FSDPParamStore(layout, dev, seed=3, init_std=0.05, comm=mode.split("-")[0],
+                            gather="gemm" if mode.endswith("-gemm") else "prefetch",
+                            gather_chunk=1 << 15)
         eng = LlamaEngine(cfg, st, S)
         losses = []
         for step in range(3):
@@ -304,9 +306,19 @@ def main() -> int:
         torch.cuda.synchronize()
         K.check_status()
         outs[mode] = (st.full_params().float(), [float(l) for l in losses])
+        if mode == "fused-gemm":
+            results["fsdp_gemm_gather_launches"] = st.fused_gemm_launches
+            assert st.fused_gemm_launches > 0, "in-GEMM gathering never ran"
     rel = _rel(outs["fused"][0], outs["nccl"][0])
     assert rel < 2e-2, f"fused FSDP diverges from the NCCL path: {rel}"
     results["fsdp_rel_diff"] = rel
+    # the same math; run-to-run differences come from the atomics of the embedding backward
+    rel_g = _rel(outs["fused-gemm"][0], outs["fused"][0])
+    assert rel_g < 2e-2, f"in-GEMM gathering diverges from prefetch gathering: {rel_g}"
+    for la, lb in zip(outs["fused-gemm"][1], outs["fused"][1]):
+        assert abs(la - lb) < 2e-2 * abs(lb), (outs["fused-gemm"][1], outs["fused"][1])
+    results["fsdp_gemm_gather_rel_diff"] = rel_g
+    results["fsdp_gemm_gather_losses"] = outs["fused-gemm"][1]
     results["fsdp_losses"] = outs["fused"][1]
 
     # --------------------------------------------------------- DDP fused == library ----
