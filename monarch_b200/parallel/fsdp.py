@@ -6,7 +6,9 @@ head) of the flat parameter layout.
 
 ``comm="fused"`` (GPU): this package's own kernels over peer-mapped memory --
   * the bf16 shards of a unit are pulled from all ranks into a local buffer by
-    ``allgather_pull`` on a side stream, one unit ahead of compute;
+    ``allgather_pull`` on a side stream, one unit ahead of compute (``gather="prefetch"``),
+    or, with ``gather="gemm"``, by the layer's own QKV and gate/up GEMM launches: the fused
+    all-gather->GEMM kernel pulls the chunks while its tensor-core CTAs multiply;
   * after a unit's backward, ``rs_adamw`` reads that unit's gradient slice from every
     rank, reduces it in fp32, applies AdamW to the rank's fp32 master/moment shard and
     writes the updated bf16 shard -- reduce-scatter, cast and optimizer in one kernel,
