@@ -22,6 +22,8 @@ _LAZY = {
     "no_mesh": ("tensor_engine", "no_mesh"), "reduce": ("tensor_engine", "reduce"),
     "reduce_": ("tensor_engine", "reduce_"), "to_mesh": ("tensor_engine", "to_mesh"),
     "slice_mesh": ("tensor_engine", "slice_mesh"), "remote": ("tensor_engine", "remote"),
+    "Pipe": ("tensor_engine", "Pipe"), "create_pipe": ("tensor_engine", "create_pipe"),
+    "remote_generator": ("tensor_engine", "remote_generator"),
     "coalescing": ("tensor_engine", "coalescing"), "compile": ("tensor_engine", "compile"),
     "call_on_shard_and_fetch": ("tensor_engine", "call_on_shard_and_fetch"),
     "fetch_shard": ("tensor_engine", "fetch_shard"), "inspect": ("tensor_engine", "inspect"),

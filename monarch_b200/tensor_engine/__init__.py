@@ -15,3 +15,7 @@ __all__ += ["Borrow", "DeviceMesh", "RemoteException", "Stream", "Tensor", "get_
             "get_active_stream", "no_mesh", "reduce", "reduce_", "slice_mesh",
             "spawn_tensor_engine", "to_mesh", "Remote", "call_on_shard_and_fetch", "coalescing",
             "compile", "fetch_shard", "inspect", "remote", "show"]
+
+from .pipe import Pipe, create_pipe, remote_generator  # noqa: E402
+
+__all__ += ["Pipe", "create_pipe", "remote_generator"]

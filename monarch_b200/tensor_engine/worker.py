@@ -16,6 +16,8 @@ kernels when the tensors live in peer-mapped memory, otherwise torch.distributed
 from __future__ import annotations
 
 import os
+import queue
+import threading
 import traceback
 from typing import Any, Dict, List, Optional, Tuple
 
@@ -138,6 +140,89 @@ class _Env:
         return (len(self._core) if self._core is not None else 0) + len(self._py)
 
 
+class _PipeClosed(Exception):
+    pass
+
+
+class WorkerPipe:
+    """Worker end of a pipe: the generator runs on its own thread; its ``send`` blocks while
+    ``max_messages`` are waiting (python/monarch/worker/worker.py:573-595, 1158-1191)."""
+
+    def __init__(self, max_messages: int, ranks: Dict[str, int], sizes: Dict[str, int]):
+        self._out: "queue.Queue" = queue.Queue(maxsize=max(1, max_messages))
+        self._in: "queue.Queue" = queue.Queue(maxsize=max(1, max_messages))
+        self.ranks = ranks
+        self.sizes = sizes
+        self._closed = threading.Event()
+        self._thread: Optional[threading.Thread] = None
+
+    # ---- the generator's side
+    def _put_out(self, item) -> None:
+        while not self._closed.is_set():
+            try:
+                self._out.put(item, timeout=0.2)
+                return
+            except queue.Full:
+                continue
+        raise _PipeClosed()
+
+    def send(self, obj: Any) -> None:
+        self._put_out(("value", obj))
+
+    def recv(self) -> Any:
+        while not self._closed.is_set():
+            try:
+                return self._in.get(timeout=0.2)
+            except queue.Empty:
+                continue
+        raise _PipeClosed()
+
+    # ---- the worker's side
+    def start(self, fn, args, kwargs) -> None:
+        def main():
+            try:
+                r = fn(self, *args, **kwargs)
+                if hasattr(r, "__next__"):
+                    for item in r:
+                        self.send(item)
+                self._put_out(("end", None))
+            except _PipeClosed:
+                pass
+            except Exception as ex:  # noqa: BLE001 - surfaces at the next recv
+                self.fail(ex, traceback.format_exc())
+
+        self._thread = threading.Thread(target=main, name="pipe", daemon=True)
+        self._thread.start()
+
+    def fail(self, ex, tb: str) -> None:
+        try:
+            self._put_out(("error", f"{type(ex).__name__}: {ex}\n{tb}"))
+        except _PipeClosed:
+            pass
+
+    def next_message(self, timeout: float = 600.0) -> Any:
+        if getattr(self, "_terminal", None) is not None:
+            return self._raise_terminal()
+        kind, v = self._out.get(timeout=timeout)
+        if kind == "value":
+            return v
+        self._closed.set()   # terminal: later recvs report the same state
+        self._terminal = (kind, v)
+        return self._raise_terminal()
+
+    def _raise_terminal(self):
+        kind, v = self._terminal
+        if kind == "end":
+            raise RuntimeError("the remote generator is exhausted")
+        raise RuntimeError(f"remote generator failed: {v}")
+
+    def put_inbound(self, v: Any) -> None:
+        self._in.put(v, timeout=600.0)
+
+    def close(self) -> None:
+        self._closed.set()
+
+
 class TensorWorker(Actor):
     def __init__(self, use_cuda: bool):
         self.rank = current_rank().rank
@@ -156,6 +241,7 @@ class TensorWorker(Actor):
         self.groups: Dict[Tuple[int, ...], Any] = {}
         self.borrows: Dict[int, Any] = {}
         self.recordings: Dict[int, List[tuple]] = {}
+        self.pipes: Dict[int, WorkerPipe] = {}
         self.pg_ready = False
         self.error_port: Optional[Port] = None
         self.last_seq = -1
@@ -401,6 +487,64 @@ class TensorWorker(Actor):
             return
         for i in range(len(msgs)):
             run_py(i, bind)
+
+    # ----------------------------------------------------------------------- pipes
+    def _m_create_pipe(self, pipe_id, fspec, max_messages, args, kwargs, labels, offset, sizes,
+                       strides) -> None:
+        rem = self.rank - offset
+        ranks = {l: ((rem // st) % n if st else 0) for l, n, st in zip(labels, sizes, strides)}
+        pipe = WorkerPipe(max_messages, ranks, dict(zip(labels, sizes)))
+        self.pipes[pipe_id] = pipe
+        try:
+            fn = _resolve_function(fspec)
+        except Exception as ex:  # noqa: BLE001 - surfaces at the first recv
+            pipe.fail(ex, traceback.format_exc())
+            return
+        pipe.start(fn, args, kwargs)
+
+    def _m_pipe_recv(self, seq, results, pipe_id, stream) -> None:
+        self.last_seq = seq
+        try:
+            out = self.pipes[pipe_id].next_message()
+            flat = _flatten_tensors(out)
+            if len(flat) != len(results):
+                raise RuntimeError(f"pipe produced {len(flat)} tensors, controller expected "
+                                   f"{len(results)}")
+            with self._stream_ctx(stream):
+                for r, t in zip(results, flat):
+                    self.env[r.id] = t.to(self.device, non_blocking=True)
+        except Exception as ex:  # noqa: BLE001 - the refs carry the failure
+            e = RemoteError(seq, self.rank, "pipe.recv", f"{type(ex).__name__}: {ex}",
+                            traceback.format_exc())
+            self._poison(seq, list(results), e)
+            self._report(e)
+
+    def _m_pipe_send(self, seq, pipe_id, obj, stream) -> None:
+        self.last_seq = seq
+        try:
+            dep = None
+
+            def res(r):
+                nonlocal dep
+                v = self._get(r, seq)
+                if isinstance(v, RemoteError) and dep is None:
+                    dep = v
+                return v
+
+            val = _map_refs(obj, res)
+            if dep is not None:
+                raise RuntimeError(f"input failed at seq {dep.seq}: {dep.exc_text}")
+            if self.use_cuda:
+                torch.cuda.synchronize(self.device)   # the generator thread reads the values
+            self.pipes[pipe_id].put_inbound(val)
+        except Exception as ex:  # noqa: BLE001
+            self._report(RemoteError(seq, self.rank, "pipe.send", f"{type(ex).__name__}: {ex}",
+                                     traceback.format_exc()))
+
+    def _m_drop_pipe(self, pipe_id) -> None:
+        p = self.pipes.pop(pipe_id, None)
+        if p is not None:
+            p.close()
 
     # ----------------------------------------------------------------------- fetch
     def _fetch(self, seq, ref_tree, preprocess):

@@ -175,3 +175,78 @@ def test_compile_records_once_and_replays(dm):
         assert len(calls) == 1          # traced once, replayed twice
         step(w, torch.ones(4, 3), 0.5)  # new input shape -> new trace
         assert len(calls) == 2
+
+
+# ------------------------------------------------------------------------------- pipes --
+def _counting_loader(pipe, n, width):
+    """Worker side of a pipe: a generator; each worker yields batches marked with its
+    coordinates."""
+    tag = pipe.ranks["host"] * 10 + pipe.ranks["gpu"]
+    for i in range(n):
+        yield {"x": torch.full((2, width), float(tag + 100 * i)), "i": torch.tensor(i)}
+
+
+def _echo_loader(pipe):
+    """Worker side that talks back: doubles whatever the controller sends."""
+    while True:
+        v = pipe.recv()
+        pipe.send(v["t"] * 2 + v["k"])
+
+
+def _broken_loader(pipe):
+    yield torch.zeros(1)
+    raise ValueError("loader broke")
+
+
+def test_pipe_generator_feeds_distributed_tensors(dm):
+    @te.remote_generator(_counting_loader, max_messages=2)
+    def loader(pipe, n, width):
+        for _ in range(n):
+            yield {"x": torch.zeros(2, width), "i": torch.tensor(0)}
+
+    with dm.activate():
+        p = loader(3, 5)
+        b0 = p.recv()
+        b1 = p.recv()
+        assert isinstance(b0["x"], te.Tensor) and b0["x"].shape == (2, 5)
+        assert te.inspect(b0["x"], host=1, gpu=1)[0, 0].item() == 11
+        assert te.inspect(b1["x"], host=0, gpu=1)[1, 4].item() == 101
+        assert te.inspect(b1["i"]).item() == 1
+        s = (b0["x"] + b1["x"]).reduce(("host", "gpu"), "sum")   # usable like any tensor
+        assert te.inspect(s)[0, 0].item() == (0 + 1 + 10 + 11) * 2 + 400
+        p.recv()
+        with pytest.raises(StopIteration):
+            p.recv()          # the propagation generator ends with the worker's
+
+
+def test_pipe_send_reaches_the_generator(dm):
+    @te.remote_generator(_echo_loader)
+    def echo(pipe):
+        while True:
+            v = pipe.recv()
+            yield v["t"] * 2 + v["k"]
+
+    with dm.activate():
+        p = echo()
+        t = dm.rank("gpu").to(torch.float32) * torch.ones(3)
+        p.send({"t": t, "k": 5})
+        out = p.recv()
+        assert out.shape == (3,)
+        assert te.inspect(out, host=0, gpu=1).tolist() == [7.0] * 3
+        p.drop()
+
+
+def test_pipe_failure_poisons_the_received_tensors(dm):
+    @te.remote_generator(_broken_loader)
+    def broken(pipe):
+        while True:
+            yield torch.zeros(1)
+
+    with dm.activate():
+        p = broken()
+        ok = p.recv()
+        assert te.inspect(ok).item() == 0
+        bad = p.recv()
+        with pytest.raises(te.RemoteException, match="loader broke"):
+            te.inspect(bad)
+        assert te.inspect(ok + 1).item() == 1     # workers stay alive
