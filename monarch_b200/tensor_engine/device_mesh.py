@@ -17,8 +17,10 @@ from __future__ import annotations
 
 import contextlib
 import itertools
+import os
 import socket
 import threading
+import time
 import warnings
 from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
 
@@ -46,6 +48,14 @@ class RemoteException(Exception):
 
 
 # ---------------------------------------------------------------------------- streams --
+class WorkerTimeoutError(RuntimeError):
+    """Some workers made no progress within the operation timeout."""
+
+    def __init__(self, msg: str, ranks: List[int]):
+        super().__init__(msg)
+        self.ranks = ranks
+
+
 class Stream:
     _ids = itertools.count(1)
 
@@ -146,6 +156,16 @@ class Client:
         port, self._err_rx = Channel.open()
         workers.configure.call(port).get(timeout=60)
         self._closed = False
+        # progress watchdog (controller/src/lib.rs:263-336 CheckWorkerProgress): a ping
+        # rides the command stream; ranks that have not answered it within
+        # ``operation_timeout`` seconds are stuck behind a command
+        self.operation_timeout = float(os.environ.get("MB200_OPERATION_TIMEOUT", "120"))
+        self.fail_on_worker_timeout = os.environ.get("MB200_FAIL_ON_WORKER_TIMEOUT", "0") == "1"
+        self.progress_interval = 5.0
+        self.stalls: List[dict] = []
+        self._ping: Optional[dict] = None
+        self._last_ping = time.monotonic()
+        self._failed: Optional[Exception] = None
 
     def new_seq(self) -> int:
         return next(self._seq)
@@ -178,8 +198,52 @@ class Client:
         if self._coalesce is not None:
             self._coalesce.append((mesh, msg))
             return
+        self._watch()
         self._send_deletes()
         mesh._workers.run.broadcast([msg])
+
+    def _watch(self) -> None:
+        """Progress watchdog step; called from the command path and from waits, so it needs
+        no thread of its own.  Raises :class:`WorkerTimeoutError` once a stall was seen and
+        ``fail_on_worker_timeout`` is set."""
+        if self._failed is not None:
+            raise self._failed
+        if self.operation_timeout <= 0 or self._closed:
+            return
+        now = time.monotonic()
+        p = self._ping
+        if p is not None:
+            while True:
+                env = p["rx"]._rx.try_recv()
+                if env is None:
+                    break
+                from ..actor.pickle import unflatten
+                _, rank, last_seq = unflatten(env.data, env.parts)
+                p["seen"][rank] = last_seq
+            if len(p["seen"]) == p["n"]:
+                p["rx"].close()
+                self._ping = None
+            elif now - p["t"] > self.operation_timeout and not p["reported"]:
+                p["reported"] = True
+                missing = sorted(set(range(p["n"])) - set(p["seen"]))
+                stall = {"ranks": missing, "waited_s": now - p["t"], "controller_seq": p["seq"],
+                         "last_seq_of_responders": dict(p["seen"])}
+                self.stalls.append(stall)
+                msg = (f"tensor workers {missing} made no progress for {now - p['t']:.1f} s "
+                       f"(operation timeout {self.operation_timeout:.1f} s, controller at seq "
+                       f"{p['seq']})")
+                import logging
+                logging.getLogger("monarch_b200.tensor_engine").warning(msg)
+                if self.fail_on_worker_timeout:
+                    self._failed = WorkerTimeoutError(msg, missing)
+                    raise self._failed
+        if self._ping is None and now - self._last_ping >= self.progress_interval:
+            ep = self.root_mesh._workers.progress
+            port, rx = ep._open()
+            ep._send((), {}, port)
+            self._last_ping = now
+            self._ping = {"rx": rx, "t": now, "n": len(self.root_mesh._workers), "seen": {},
+                          "seq": next(self._seq), "reported": False}
 
     def _ensure_stream(self, s: Stream) -> None:
         if s.id not in self._streams_made:
@@ -251,20 +315,40 @@ class Client:
 
     def fetch(self, mesh: "DeviceMesh", ref_tree, preprocess=None, timeout: Optional[float] = None):
         seq = self.new_seq()
+        self._watch()
         self._send_deletes()
-        fut = mesh._workers.run_and_reply.call([], (seq, ref_tree, preprocess))
+        ep = mesh._workers.run_and_reply
+        mesh._workers._raise_if_unhealthy()
+        port, rx = ep._open()
+        ep._send(([], (seq, ref_tree, preprocess)), {}, port)
+        n = len(mesh._workers)
 
         def wait(t):
             # replies are unpickled into ordinary local tensors: keep the active-mesh
             # dispatch mode out of the way while that happens
+            t = t if t is not None else timeout
+            deadline = None if t is None else time.monotonic() + t
             prev = getattr(_tls, "propagating", False)
             _tls.propagating = True
+            replies: List[Any] = [None] * n
+            got = 0
             try:
-                vm = fut.get(t if t is not None else timeout)
+                while got < n:
+                    left = 1.0 if deadline is None else min(1.0, max(deadline - time.monotonic(), 0.0))
+                    try:
+                        rank, v = rx._next(left)
+                    except TimeoutError:
+                        self._watch()      # the wait doubles as the watchdog's clock
+                        if deadline is not None and time.monotonic() >= deadline:
+                            raise
+                        continue
+                    replies[rank] = v
+                    got += 1
             finally:
                 _tls.propagating = prev
+                rx.close()
             out = []
-            for _, r in vm.items():
+            for r in replies:
                 if r[0] == "error":
                     raise RemoteException(*r[1:])
                 out.append(r[1])

@@ -577,6 +577,12 @@ class TensorWorker(Actor):
         return self._fetch(seq, ref_tree, preprocess)
 
     @endpoint
+    def progress(self) -> int:
+        """Watchdog ping: answered in command order, so a reply means that everything sent
+        before it has been executed (not necessarily finished on the GPU)."""
+        return self.last_seq
+
+    @endpoint
     def sync(self) -> int:
         if self.use_cuda:
             torch.cuda.synchronize(self.device)

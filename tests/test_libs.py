@@ -117,3 +117,46 @@ def test_cached_propagation_runs_once():
     assert p(torch.empty(3, 2), k=4).shape == (3, 4)
     assert p(torch.empty(5, 2), k=4).shape == (5, 4)
     assert len(calls) == 2
+
+
+# ----------------------------------------------------------------------- remote classes --
+from monarch_b200.remote_class import ControllerRemoteClass, WorkerRemoteClass  # noqa: E402
+
+
+class _WorkerAccumulator(WorkerRemoteClass):
+    def __init__(self, start):
+        self.total = torch.tensor(float(start))
+
+    def add(self, t, scale=1.0):
+        self.total = self.total + t.sum() * scale
+
+    def store_into(self, out):
+        out.copy_(self.total)
+
+
+class _Accumulator(ControllerRemoteClass):
+    def __init__(self, start):
+        super().__init__(_WorkerAccumulator, start)
+
+    @ControllerRemoteClass.remote_method
+    def add(self, t, scale=1.0):
+        pass
+
+    @ControllerRemoteClass.remote_method
+    def store_into(self, out):
+        pass
+
+
+def test_remote_class_runs_methods_on_every_worker(dm):
+    with dm.activate():
+        acc = _Accumulator(10)
+        x = (dm.rank("gpus") + 1).to(torch.float32) * torch.ones(4)
+        acc.add(x)
+        acc.add(x, scale=0.5)
+        out = torch.zeros(())
+        acc.store_into(out)
+        assert te.inspect(out, gpus=0).item() == 10 + 4 * 1.5
+        assert te.inspect(out, gpus=1).item() == 10 + 8 * 1.5
+        acc.drop()
+        with pytest.raises(Exception):
+            _Accumulator.add(acc, x)     # dropped: no mesh to run on

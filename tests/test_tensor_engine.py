@@ -250,3 +250,40 @@ def test_pipe_failure_poisons_the_received_tensors(dm):
         with pytest.raises(te.RemoteException, match="loader broke"):
             te.inspect(bad)
         assert te.inspect(ok + 1).item() == 1     # workers stay alive
+
+
+# ---------------------------------------------------------------------------- watchdog --
+def _sleep_on(rank_t, which, seconds):
+    import time
+    if int(rank_t.item()) == which:
+        time.sleep(seconds)
+    return rank_t + 0
+
+
+def test_progress_watchdog_names_the_stuck_ranks(dm):
+    client = dm.client
+    saved = (client.operation_timeout, client.progress_interval, client.fail_on_worker_timeout)
+    client.operation_timeout, client.progress_interval = 0.8, 0.1
+    sleepy = te.remote(_sleep_on, propagate=lambda t, w, s: t)
+    flat = dm.flatten("all")
+    try:
+        with flat.activate():
+            r = flat.rank("all")
+            n0 = len(client.stalls)
+            out = sleepy(r, 2, 3.0)
+            assert te.inspect(out, all=2).item() == 2          # waits through the stall
+            assert len(client.stalls) == n0 + 1
+            assert client.stalls[-1]["ranks"] == [2]
+            # with fail_on_worker_timeout the wait itself raises, naming the ranks
+            client.fail_on_worker_timeout = True
+            out = sleepy(r, 1, 3.0)
+            with pytest.raises(te.WorkerTimeoutError) as ei:
+                te.inspect(out, all=1)
+            assert ei.value.ranks == [1]
+    finally:
+        client._failed = None
+        client.operation_timeout, client.progress_interval, client.fail_on_worker_timeout = saved
+    import time
+    time.sleep(3.0)     # let the sleeper finish before the fixture tears the mesh down
+    with flat.activate():
+        assert te.inspect(flat.rank("all") + 1, all=3).item() == 4
