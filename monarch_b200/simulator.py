@@ -301,6 +301,7 @@ def mock_mesh(hosts: int = 1, gpus: int = 1, cost: Optional[CostModel] = None,
     client.errors = []
     client._closed = False
     client._err_rx = None
+    client._init_watchdog(0.0)   # simulated workers cannot stall
     dm = DeviceMesh(client, shape, workers)
     client.root_mesh = dm
     return dm, Simulator(workers)
