@@ -225,6 +225,30 @@ class ProcMesh(MeshTrait):
             rows.append(f"{r}\t" + "\t".join(str(c) for c in sl.coordinates(r)))
         return "\n".join(rows)
 
+    def ledger(self, timeout: float = 5.0) -> Dict[int, List[dict]]:
+        """Actor-tree snapshot of every proc of the mesh (hyperactor/src/proc.rs:139-315
+        ``ledger_snapshot``): rank -> list of ``{actor_id, status, messages_handled, failure,
+        children, last_event}``.  Procs that do not answer in time are absent."""
+        out: Dict[int, List[dict]] = {}
+        for rank, text in self._owner._native.ledger(int(timeout * 1000)):
+            rows = []
+            for line in text.splitlines():
+                f = (line.split("\t") + [""] * 6)[:6]
+                rows.append({"actor_id": f[0], "status": f[1], "messages_handled": int(f[2] or 0),
+                             "failure": f[3], "children": [c for c in f[4].split(",") if c],
+                             "last_event": f[5]})
+            out[int(rank)] = rows
+        return out
+
+    def serve_admin(self, address: Optional[str] = None) -> str:
+        """Start the admin endpoint of this job (``python -m monarch_b200.tools.admin`` talks
+        to it) and return its address."""
+        from ..tools.admin import AdminServer
+        owner = self._owner
+        if getattr(owner, "_admin", None) is None:
+            owner._admin = AdminServer(owner, address)
+        return owner._admin.address
+
     # ops --------------------------------------------------------------------------------
     def logging_option(self, stream_to_client: bool = True, aggregate_window_sec: Optional[float] = 5,
                        level: int = 20) -> Future[None]:

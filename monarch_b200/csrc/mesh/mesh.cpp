@@ -587,9 +587,23 @@ ActorHooks make_mesh_agent(const std::shared_ptr<Proc>& proc_sp, std::shared_ptr
     } else if (kind == "ledger") {
       PortId reply = read_port(r);
       std::ostringstream os;
-      for (auto& s : proc->ledger_snapshot())
-        os << s.actor_id << "\t" << s.status << "\t" << s.messages_handled << "\t" << s.failure
-           << "\n";
+      // one line per actor: id, status, messages handled, failure, children (comma
+      // separated), newest recorded event
+      auto flat = [](std::string v) {
+        for (auto& c : v)
+          if (c == '\t' || c == '\n') c = ' ';
+        return v;
+      };
+      for (auto& s : proc->ledger_snapshot()) {
+        os << s.actor_id << "\t" << s.status << "\t" << s.messages_handled << "\t"
+           << flat(s.failure) << "\t";
+        for (size_t i = 0; i < s.children.size(); ++i) os << (i ? "," : "") << s.children[i];
+        os << "\t";
+        if (!s.events.empty())
+          os << s.events.back().t_us << " " << flat(s.events.back().name) << " "
+             << flat(s.events.back().detail);
+        os << "\n";
+      }
       self.send(reply, os.str(), {{kHdrKind, "ledger"}});
     }
   };
@@ -979,6 +993,29 @@ void ProcMesh::stop_actor(const std::string& name, int64_t timeout_ms) {
     if (replies->recv(std::min<int64_t>(left, 200))) ++got;
   }
   client_inst_->unbind(reply_port.port);
+}
+
+std::vector<std::pair<int64_t, std::string>> ProcMesh::ledger(int64_t timeout_ms) {
+  auto replies = std::make_shared<QueueSink>();
+  PortId reply_port = client_inst_->bind(replies);
+  for (size_t rank = 0; rank < n_; ++rank) {
+    Writer w;
+    write_port(w, reply_port);
+    client_inst_->send(PortId{ActorId{proc_id((int64_t)rank), "mesh_agent", 0}, kPortMessage},
+                       std::move(w.buf), {{kHdrKind, "ledger"}});
+  }
+  std::vector<std::pair<int64_t, std::string>> out;
+  auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms);
+  while (out.size() < n_) {
+    int64_t left = std::chrono::duration_cast<std::chrono::milliseconds>(
+                       deadline - std::chrono::steady_clock::now()).count();
+    if (left <= 0) break;
+    auto env = replies->recv(std::min<int64_t>(left, 200));
+    if (env) out.emplace_back(env->sender.proc.rank, env->data);
+  }
+  client_inst_->unbind(reply_port.port);
+  std::sort(out.begin(), out.end());
+  return out;
 }
 
 void ProcMesh::stop() {

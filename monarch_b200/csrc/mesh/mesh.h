@@ -153,6 +153,9 @@ class ProcMesh : public std::enable_shared_from_this<ProcMesh> {
             const ActorId& sender, std::string data, std::map<std::string, std::string> headers,
             std::vector<std::string> parts, const Slice& cast_shape);
   void stop_actor(const std::string& name, int64_t timeout_ms);
+  // Actor-tree snapshot of every proc (rank, tab-separated lines as written by the mesh
+  // agent); procs that do not answer within the timeout are missing from the result.
+  std::vector<std::pair<int64_t, std::string>> ledger(int64_t timeout_ms);
 
   // Supervision / lifecycle events for Python monitors: blocks up to timeout.
   struct Event {

@@ -648,6 +648,8 @@ PYBIND11_MODULE(_native, m) {
            py::arg("parts") = std::vector<py::bytes>{}, py::arg("cast_shape") = Slice())
       .def("stop_actor", &ProcMesh::stop_actor, py::arg("name"), py::arg("timeout_ms") = 5000,
            py::call_guard<py::gil_scoped_release>())
+      .def("ledger", &ProcMesh::ledger, py::arg("timeout_ms") = 5000,
+           py::call_guard<py::gil_scoped_release>())
       .def("next_event",
            [](ProcMesh& pm, int64_t timeout_ms) -> py::object {
              std::optional<ProcMesh::Event> e;
