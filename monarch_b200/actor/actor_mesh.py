@@ -303,10 +303,12 @@ class ValueMesh(MeshTrait, Generic[R]):
                                                    shape.ndslice.ranks()])
 
     def item(self, **kwargs) -> R:
-        coords = [kwargs[l] for l in self._labels]
-        if len(kwargs) != len(self._labels):
-            raise KeyError(f"expected coordinates for {self._labels}, got {tuple(kwargs)}")
         sl = self._shape_.ndslice
+        unknown = [k for k in kwargs if k not in self._labels]
+        missing = [l for l, n in zip(self._labels, sl.sizes) if l not in kwargs and n != 1]
+        if unknown or missing:
+            raise KeyError(f"expected coordinates for {self._labels}, got {tuple(kwargs)}")
+        coords = [kwargs.get(l, 0) for l in self._labels]   # dims of size 1 may be left out
         return self._values[sl.index(sl.nditem(coords))]
 
     def items(self) -> Iterator[Tuple[Point, R]]:

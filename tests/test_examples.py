@@ -35,3 +35,26 @@ def test_lazy_top_level_api():
     import monarch_b200 as m
     assert m.DeviceMesh is m.tensor_engine.DeviceMesh and callable(m.remote)
     assert "fetch_shard" in dir(m) and m.timer.CudaTimer
+
+
+def test_sieve_of_dynamically_spawned_actors():
+    out = _load("sieve").run(15)
+    assert out["primes"] == [2, 3, 5, 7, 11, 13, 17, 19, 23, 29, 31, 37, 41, 43, 47]
+
+
+def test_rdma_parameter_server_converges():
+    out = _load("rdma_parameter_server").run(n_workers=2, steps=60)
+    assert out["loss_last"] < 1e-3 * out["loss_first"], out
+    assert out["weight_error"] < 0.05
+
+
+def test_spmd_ddp_inside_actors():
+    out = _load("spmd_ddp").run(world_size=2, steps=30)
+    assert out["replicas_in_sync"], out
+    assert out["loss_last"] < 0.5 * out["loss_first"], out
+
+
+def test_getting_started_tour():
+    out = _load("getting_started").run()
+    assert out["values"] == [2, 2, 1, 1] and out["registered"] == 2
+    assert out["supervision_event"] == "actor_failed" and out["caller_error"]
