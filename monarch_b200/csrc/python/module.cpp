@@ -276,6 +276,29 @@ PYBIND11_MODULE(_native, m) {
   });
   m.def("trace_json", [] { return TraceWriter::global().to_json(); });
   m.def("trace_clear", [] { TraceWriter::global().clear(); });
+  m.def("span_enter", [](const std::string& n, const std::string& a) { return span_enter(n, a); },
+        py::arg("name"), py::arg("actor_id") = "");
+  m.def("span_exit", &span_exit);
+  m.def("current_span_id", &current_span_id);
+  m.def("use_sim_clock", &use_sim_clock);
+  m.def("use_real_clock", &use_real_clock);
+  m.def("sim_clock_advance_us", &sim_clock_advance_us);
+  m.def("telemetry_now_us", &telemetry_now_us);
+  m.def("execution_id", [] { return execution_id(); });
+  m.def("events_enable", [](bool on) { EventCollector::global().enable(on); });
+  m.def("events_dropped", [] { return EventCollector::global().dropped(); });
+  m.def("events_drain", [] {
+    py::list out;
+    for (auto& e : EventCollector::global().drain())
+      out.append(py::make_tuple(e.kind, e.t_us, e.level, e.file, e.line, e.message, e.actor_id,
+                                e.span_id, e.parent_id, e.thread));
+    return out;
+  });
+  m.def("log_event", [](int level, const std::string& file, int line, const std::string& msg) {
+    LogLevel l = level < 0 ? LogLevel::Trace : level > 4 ? LogLevel::Error : (LogLevel)level;
+    // captured for readers even when below the file/stderr thresholds
+    if (log_enabled(l) || EventCollector::global().enabled()) log_write(l, file.c_str(), line, msg);
+  });
   m.def("now_us", &now_us);
   m.def("channel_stats", [] {
     auto& s = channel_stats();

@@ -165,7 +165,8 @@ void log_init() {
 bool log_enabled(LogLevel lvl) {
   LogState& s = ls();
   if (!s.inited) log_init();
-  return lvl >= s.file_level || lvl >= s.stderr_level;
+  return lvl >= s.file_level || lvl >= s.stderr_level ||
+         (lvl >= LogLevel::Debug && EventCollector::global().enabled());
 }
 std::string log_file_path() {
   log_init();
@@ -186,6 +187,17 @@ void log_write(LogLevel lvl, const char* file, int line, const std::string& msg)
   std::snprintf(head, sizeof(head), "%c%02d%02d %02d:%02d:%02d.%06ld %d %s:%d] ", tag[(int)lvl],
                 tmv.tm_mon + 1, tmv.tm_mday, tmv.tm_hour, tmv.tm_min, tmv.tm_sec, (long)us,
                 (int)getpid(), base ? base + 1 : file, line);
+  if (EventCollector::global().enabled()) {
+    CollectedEvent ev;
+    ev.kind = "event";
+    ev.t_us = telemetry_now_us();
+    ev.level = (int)lvl;
+    ev.file = base ? base + 1 : file;
+    ev.line = line;
+    ev.message = msg;
+    ev.span_id = current_span_id();
+    EventCollector::global().push(std::move(ev));
+  }
   std::lock_guard<std::mutex> g(s.mu);
   if (s.file && lvl >= s.file_level) {
     std::fputs(head, s.file);
@@ -332,5 +344,119 @@ void TraceWriter::clear() {
   std::lock_guard<std::mutex> g(mu_);
   events_.clear();
 }
+
+// ------------------------------------------------------------ spans + event capture --
+namespace {
+struct SimClock {
+  std::atomic<bool> on{false};
+  std::mutex mu;
+  double t_us = 0;
+};
+SimClock& sim_clock() {
+  static SimClock c;
+  return c;
+}
+struct OpenSpan {
+  uint64_t id;
+  std::string name;
+  double t0_us;      // telemetry clock
+  double t0_mono_us;  // steady clock, for the trace writer
+};
+thread_local std::vector<OpenSpan> tl_spans;
+std::atomic<uint64_t> g_next_span{1};
+uint64_t thread_tag() {
+  static std::atomic<uint64_t> next{1};
+  thread_local uint64_t mine = next.fetch_add(1);
+  return mine;
+}
+}  // namespace
+
+void use_sim_clock() { sim_clock().on = true; }
+void use_real_clock() { sim_clock().on = false; }
+void sim_clock_advance_us(double us) {
+  std::lock_guard<std::mutex> g(sim_clock().mu);
+  sim_clock().t_us += us;
+}
+double telemetry_now_us() {
+  SimClock& c = sim_clock();
+  if (c.on) {
+    std::lock_guard<std::mutex> g(c.mu);
+    return c.t_us;
+  }
+  return std::chrono::duration<double, std::micro>(
+             std::chrono::system_clock::now().time_since_epoch())
+      .count();
+}
+
+const std::string& execution_id() {
+  static const std::string id = [] {
+    for (const char* k : {"HYPERACTOR_EXECUTION_ID", "MONARCH_EXECUTION_ID"})
+      if (const char* e = std::getenv(k))
+        if (*e) return std::string(e);
+    char buf[64];
+    std::snprintf(buf, sizeof(buf), "exec_%ld_%d", (long)std::time(nullptr), (int)getpid());
+    return std::string(buf);
+  }();
+  return id;
+}
+
+EventCollector& EventCollector::global() {
+  static EventCollector c;
+  return c;
+}
+void EventCollector::enable(bool on) { enabled_ = on; }
+void EventCollector::push(CollectedEvent&& e) {
+  e.thread = thread_tag();
+  std::lock_guard<std::mutex> g(mu_);
+  if (q_.size() >= kMax) {
+    ++dropped_;
+    return;
+  }
+  q_.push_back(std::move(e));
+}
+std::vector<CollectedEvent> EventCollector::drain() {
+  std::lock_guard<std::mutex> g(mu_);
+  std::vector<CollectedEvent> out;
+  out.swap(q_);
+  return out;
+}
+
+uint64_t span_enter(const std::string& name, const std::string& actor_id) {
+  const uint64_t id = g_next_span.fetch_add(1);
+  const uint64_t parent = tl_spans.empty() ? 0 : tl_spans.back().id;
+  const double t = telemetry_now_us();
+  tl_spans.push_back(OpenSpan{id, name, t, now_us()});
+  if (EventCollector::global().enabled()) {
+    CollectedEvent ev;
+    ev.kind = "span_enter";
+    ev.t_us = t;
+    ev.message = name;
+    ev.actor_id = actor_id;
+    ev.span_id = id;
+    ev.parent_id = parent;
+    EventCollector::global().push(std::move(ev));
+  }
+  return id;
+}
+void span_exit(uint64_t id) {
+  // spans close innermost-first; closing an outer span closes what is still open inside it
+  while (!tl_spans.empty()) {
+    OpenSpan s = tl_spans.back();
+    tl_spans.pop_back();
+    if (EventCollector::global().enabled()) {
+      CollectedEvent ev;
+      ev.kind = "span_exit";
+      ev.t_us = telemetry_now_us();
+      ev.message = s.name;
+      ev.span_id = s.id;
+      EventCollector::global().push(std::move(ev));
+    }
+    if (TraceWriter::global().enabled())
+      TraceWriter::global().complete(s.name, "span", s.t0_mono_us, now_us() - s.t0_mono_us,
+                                     (int64_t)getpid(), (int64_t)thread_tag());
+    if (s.id == id) break;
+  }
+}
+uint64_t current_span_id() { return tl_spans.empty() ? 0 : tl_spans.back().id; }
 
 }  // namespace mb

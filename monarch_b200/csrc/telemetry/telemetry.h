@@ -133,4 +133,47 @@ class TraceWriter {
 
 double now_us();
 
+// ------------------------------------------------------------ spans + event capture --
+// Parity: hyperactor_telemetry spans (PySpan, get_current_span_id), the sqlite layer's
+// event capture (sqlite.rs: log events and span lifecycles as rows) and the real/sim clock
+// switch.  Capture is off until a reader turns it on; a reader drains the rows and stores
+// them where it likes (the Python side writes them into a sqlite database).
+struct CollectedEvent {
+  std::string kind;      // "event" | "span_enter" | "span_exit"
+  double t_us = 0;       // telemetry clock (wall time since the epoch, or the sim clock)
+  int level = 2;         // LogLevel of an event
+  std::string file;
+  int line = 0;
+  std::string message;   // event text, or span name
+  std::string actor_id;
+  uint64_t span_id = 0;  // the span itself, or the span an event happened in
+  uint64_t parent_id = 0;
+  uint64_t thread = 0;
+};
+class EventCollector {
+ public:
+  static EventCollector& global();
+  void enable(bool on);
+  bool enabled() const { return enabled_; }
+  void push(CollectedEvent&& e);
+  std::vector<CollectedEvent> drain();
+  uint64_t dropped() const { return dropped_; }
+
+ private:
+  std::atomic<bool> enabled_{false};
+  std::atomic<uint64_t> dropped_{0};
+  std::mutex mu_;
+  std::vector<CollectedEvent> q_;
+  static constexpr size_t kMax = 1 << 18;
+};
+uint64_t span_enter(const std::string& name, const std::string& actor_id = "");
+void span_exit(uint64_t id);
+uint64_t current_span_id();
+// Telemetry timestamps: wall clock by default, a manually advanced clock in simulations.
+void use_sim_clock();
+void use_real_clock();
+void sim_clock_advance_us(double us);
+double telemetry_now_us();
+const std::string& execution_id();
+
 }  // namespace mb
