@@ -10,6 +10,7 @@
 
 #include "actor/runtime.h"
 #include "channel/channel.h"
+#include "actor/durable.h"
 #include "mesh/mesh.h"
 #include "ndslice/ndslice.h"
 #include "telemetry/telemetry.h"
@@ -589,6 +590,131 @@ PYBIND11_MODULE(_native, m) {
     Metrics::global().counter_add("cast.messages");
     proc->post(std::move(e));
   });
+  // ---- durable sender, checkpoints, preemptible lock --------------------------------
+  py::class_<MessageLog, std::shared_ptr<MessageLog>>(m, "MessageLog")
+      .def(py::init<const std::string&>())
+      .def("append",
+           [](MessageLog& l, const std::string& sender, const std::string& dest, py::bytes data,
+              std::map<std::string, std::string> headers, std::vector<py::bytes> parts) {
+             Envelope e;
+             e.sender = ActorId::parse(sender);
+             e.dest = PortId::parse(dest);
+             e.data = data;
+             e.headers = std::move(headers);
+             e.parts = to_strings(parts);
+             return l.append(e);
+           },
+           py::arg("sender"), py::arg("dest"), py::arg("data"),
+           py::arg("headers") = std::map<std::string, std::string>{},
+           py::arg("parts") = std::vector<py::bytes>{})
+      .def("flush", &MessageLog::flush, py::call_guard<py::gil_scoped_release>())
+      .def_property_readonly("next_seq", &MessageLog::next_seq)
+      .def_property_readonly("path", &MessageLog::path)
+      .def("read",
+           [](MessageLog& l, uint64_t from) {
+             py::list out;
+             for (auto& r : l.read(from)) out.append(py::make_tuple(r.first, to_py(r.second)));
+             return out;
+           },
+           py::arg("from_seq") = 0);
+  py::class_<DurableMailboxSender, std::shared_ptr<DurableMailboxSender>>(m, "DurableSender")
+      .def(py::init([](std::shared_ptr<MessageLog> log, std::shared_ptr<Proc> proc) {
+             return std::make_shared<DurableMailboxSender>(
+                 std::move(log), std::make_shared<ProcSender>(proc),
+                 [](Envelope env, const std::string& why) {
+                   MB_LOG(Error, "message to " + env.dest.to_string() + " dropped: " + why);
+                 });
+           }),
+           py::arg("log"), py::arg("proc"))
+      .def("post",
+           [](DurableMailboxSender& d, const std::string& sender, const std::string& dest,
+              py::bytes data, std::map<std::string, std::string> headers,
+              std::vector<py::bytes> parts) {
+             Envelope e;
+             e.sender = ActorId::parse(sender);
+             e.dest = PortId::parse(dest);
+             e.data = data;
+             e.headers = std::move(headers);
+             e.parts = to_strings(parts);
+             py::gil_scoped_release rel;
+             d.post(std::move(e));
+           },
+           py::arg("sender"), py::arg("dest"), py::arg("data"),
+           py::arg("headers") = std::map<std::string, std::string>{},
+           py::arg("parts") = std::vector<py::bytes>{})
+      .def("replay", &DurableMailboxSender::replay, py::arg("from_seq") = 0,
+           py::call_guard<py::gil_scoped_release>());
+  m.def("write_checkpoint", [](const std::string& path, py::bytes blob) {
+    std::string b = blob;
+    py::gil_scoped_release rel;
+    write_checkpoint(path, b);
+  });
+  m.def("read_checkpoint", [](const std::string& path) -> py::object {
+    std::string b;
+    if (!read_checkpoint(path, &b)) return py::none();
+    return py::bytes(b);
+  });
+  struct PyRwLock {
+    PreemptibleRwLock lock;
+    std::mutex mu;
+    std::map<uint64_t, std::unique_ptr<PreemptibleRwLock::ReadGuard>> reads;
+    std::unique_ptr<PreemptibleRwLock::WriteGuard> write;
+    uint64_t next = 1;
+  };
+  py::class_<PyRwLock, std::shared_ptr<PyRwLock>>(m, "PreemptibleRwLock")
+      .def(py::init<>())
+      .def("read_acquire",
+           [](PyRwLock& l, int64_t timeout_ms) -> py::object {
+             std::unique_ptr<PreemptibleRwLock::ReadGuard> g;
+             bool ok;
+             {
+               py::gil_scoped_release rel;
+               ok = l.lock.try_read_for(timeout_ms, &g);
+             }
+             if (!ok) return py::none();
+             std::lock_guard<std::mutex> lk(l.mu);
+             uint64_t id = l.next++;
+             l.reads[id] = std::move(g);
+             return py::int_(id);
+           },
+           py::arg("timeout_ms") = -1)
+      .def("preempted",
+           [](PyRwLock& l, uint64_t id) {
+             std::lock_guard<std::mutex> lk(l.mu);
+             auto it = l.reads.find(id);
+             return it != l.reads.end() && it->second->preempted();
+           })
+      .def("read_release",
+           [](PyRwLock& l, uint64_t id) {
+             std::unique_ptr<PreemptibleRwLock::ReadGuard> g;
+             {
+               std::lock_guard<std::mutex> lk(l.mu);
+               auto it = l.reads.find(id);
+               if (it == l.reads.end()) return;
+               g = std::move(it->second);
+               l.reads.erase(it);
+             }
+             g->release();
+           })
+      .def("write_acquire",
+           [](PyRwLock& l) {
+             py::gil_scoped_release rel;
+             auto g = std::make_unique<PreemptibleRwLock::WriteGuard>(l.lock.write());
+             std::lock_guard<std::mutex> lk(l.mu);
+             l.write = std::move(g);
+           })
+      .def("write_release",
+           [](PyRwLock& l) {
+             std::unique_ptr<PreemptibleRwLock::WriteGuard> g;
+             {
+               std::lock_guard<std::mutex> lk(l.mu);
+               g = std::move(l.write);
+             }
+             if (g) g->release();
+           })
+      .def_property_readonly("readers", [](PyRwLock& l) { return l.lock.readers(); })
+      .def_property_readonly("writers_waiting",
+                             [](PyRwLock& l) { return l.lock.writers_waiting(); });
   m.def("client_proc", [] { return client_ctx().proc; });
   m.def("bootstrap_main", [] {
     py::gil_scoped_release rel;
