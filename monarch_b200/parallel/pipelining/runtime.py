@@ -160,11 +160,13 @@ class PipelineTrainer:
             elif a.kind == "SEND_F":
                 t = outs.pop(a.mb)
                 sends.append((t, dist.isend(t, self._peer(s + 1), group=self._fwd_groups[s])))
-            elif a.kind == "B":
+            elif a.kind in ("B", "BI"):
                 dy = None if s == self.pp - 1 else recv_b.pop(a.mb)[0]
-                dx = eng.backward(a.mb, dy)
+                dx = eng.backward(a.mb, dy, split=a.kind == "BI")
                 if dx is not None:
                     dxs[a.mb] = dx
+            elif a.kind == "W":
+                eng.backward_weight(a.mb)
             elif a.kind == "SEND_B":
                 t = dxs.pop(a.mb)
                 sends.append((t, dist.isend(t, self._peer(s - 1),

@@ -205,25 +205,37 @@ class TPStageEngine:
     def _swiglu_fwd(self, gu):
         return ops.swiglu_fwd(gu)
 
-    def _layer_bwd(self, w, g, saved, dy, acc):
+    def _layer_bwd(self, w, g, saved, dy, acc, acc_w=None, defer=None):
+        """Backward of one layer.  ``acc``: accumulate into the norm-gain gradients,
+        ``acc_w`` (default ``acc``): into the matrix gradients.  With ``defer`` (a list) the
+        weight-gradient GEMMs are not run: their operands are appended for
+        :meth:`backward_weight` (zero-bubble schedules split B into BI and W)."""
         cfg, c = self.cfg, self.comm
+        acc_w = acc if acc_w is None else acc_w
+
+        def wgrad(d_out, inp, name):
+            if defer is not None:
+                defer.append((d_out, inp, g[name]))
+            else:
+                ops.gemm(d_out, inp, a_mn=True, b_mn=True, out=g[name], accumulate=acc_w)
+
         x, rstd1, h1f, actx, attn, x2, rstd2, h2f, gu, hmid = saved
         d_hmid, dyf = c.ag_gemm(dy, w["w_down"], b_mn=True)
-        ops.gemm(dyf, hmid, a_mn=True, b_mn=True, out=g["w_down"], accumulate=acc)
+        wgrad(dyf, hmid, "w_down")
         d_gu = ops.swiglu_bwd(gu, d_hmid)
         del d_hmid, dyf
         d_h2 = c.gemm_rs(d_gu, w["w_gu"], b_mn=True)
-        ops.gemm(d_gu, h2f, a_mn=True, b_mn=True, out=g["w_gu"], accumulate=acc)
+        wgrad(d_gu, h2f, "w_gu")
         del d_gu
         d_x2 = ops.rmsnorm_bwd(d_h2, x2, w["mlp_norm"], rstd2, g["mlp_norm"], accumulate=acc,
                                dres=dy)
         d_attn, dx2f = c.ag_gemm(d_x2, w["wo"], b_mn=True)
-        ops.gemm(dx2f, attn, a_mn=True, b_mn=True, out=g["wo"], accumulate=acc)
+        wgrad(dx2f, attn, "wo")
         del dx2f
         d_qkv = ops.attention_bwd(actx, d_attn)
         ops.rope_(d_qkv, self.cos, self.sin, self.S, self.Hq + self.Hkv, cfg.hd, inverse=True)
         d_h1 = c.gemm_rs(d_qkv, w["wqkv"], b_mn=True)
-        ops.gemm(d_qkv, h1f, a_mn=True, b_mn=True, out=g["wqkv"], accumulate=acc)
+        wgrad(d_qkv, h1f, "wqkv")
         return ops.rmsnorm_bwd(d_h1, x, w["attn_norm"], rstd1, g["attn_norm"], accumulate=acc,
                                dres=d_x2)
 
@@ -237,6 +249,8 @@ class TPStageEngine:
         self._inputs.clear()
         self._dys.clear()
         self._seen_bwd = 0
+        self._seen_w = 0
+        self._wstash = {}
         if self.has_embed:
             self.store.unit_grads(0)["embed"].zero_()
 
@@ -277,24 +291,43 @@ class TPStageEngine:
                                         accumulate=mb > 0)
         return loss_rows.sum()
 
-    def backward(self, mb: int, dy: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    def backward(self, mb: int, dy: Optional[torch.Tensor] = None,
+                 split: bool = False) -> Optional[torch.Tensor]:
+        """Backward of micro-batch ``mb`` through this stage; returns the gradient for the
+        previous stage (None on the first).  ``split=True`` is the BI action of a
+        zero-bubble schedule: only input gradients (and the cheap norm-gain gradients) are
+        computed now, the weight-gradient GEMMs wait for :meth:`backward_weight`."""
         st = self.store
         if self.has_head:
             dy = self._dys.pop(mb)
         first, ckpt = self._inputs.pop(mb)
         acc = self._seen_bwd > 0
         self._seen_bwd += 1
+        defer = [] if split else None
+        acc_w = self._seen_w > 0
+        if not split:
+            self._seen_w += 1
         units = self._layer_units()
         for k in reversed(range(len(units))):
             ui = units[k]
             w, g = st.unit_params(ui), st.unit_grads(ui)
             _, saved = self._layer_fwd(w, ckpt[k], keep=True)
-            dy = self._layer_bwd(w, g, saved, dy, acc)
+            dy = self._layer_bwd(w, g, saved, dy, acc, acc_w, defer)
             ckpt[k] = None
+        if split:
+            self._wstash[mb] = defer
         if self.has_embed:
             ops.embedding_bwd_(dy, first, st.unit_grads(0)["embed"])
             return None
         return dy
+
+    def backward_weight(self, mb: int) -> None:
+        """The W action: weight gradients of micro-batch ``mb`` from the operands that its
+        BI action kept."""
+        acc_w = self._seen_w > 0
+        self._seen_w += 1
+        for d_out, inp, g_out in self._wstash.pop(mb):
+            ops.gemm(d_out, inp, a_mn=True, b_mn=True, out=g_out, accumulate=acc_w)
 
     def optimizer_step(self, lr: float, **kw):
         # gradients of replicated parameters: every rank saw only its own rows

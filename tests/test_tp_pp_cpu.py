@@ -21,7 +21,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, pp, tp, out):
+def _worker(rank, world, port, pp, tp, out, schedule="1f1b"):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     torch.set_num_threads(1)
@@ -42,7 +42,8 @@ def _worker(rank, world, port, pp, tp, out):
     ref.optimizer_step(1e-2, eps=1e-3)
     sd_ref = to_hf_state_dict(cfg, layout, ref_store.params)
 
-    tr = PipelineTrainer(cfg, pp, tp, S, B, M, device="cpu", lr=1e-2, comm="nccl")
+    tr = PipelineTrainer(cfg, pp, tp, S, B, M, device="cpu", lr=1e-2, comm="nccl",
+                         schedule=schedule)
     tr.load_state_dict(sd0)
     orig = tr.engine.store.optimizer_step
     tr.engine.store.optimizer_step = lambda lr, **kw: orig(lr, eps=1e-3, **kw)
@@ -56,13 +57,14 @@ def _worker(rank, world, port, pp, tp, out):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("pp,tp", [(2, 2), (1, 2), (2, 1)])
-def test_tp_pp_matches_single_process(pp, tp):
+@pytest.mark.parametrize("pp,tp,schedule", [(2, 2, "1f1b"), (1, 2, "1f1b"), (2, 1, "1f1b"),
+                                            (2, 1, "zb-h1"), (2, 2, "zb-h1"), (2, 1, "gpipe")])
+def test_tp_pp_matches_single_process(pp, tp, schedule):
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
     world = pp * tp
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, pp, tp, out)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, pp, tp, out, schedule)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:
