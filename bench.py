@@ -35,6 +35,8 @@ def parse():
     ap.add_argument("--micro-batch", type=int, default=1)
     ap.add_argument("--parallelism", default="auto")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--schedule", default="1f1b", choices=["gpipe", "1f1b", "zb-h1"],
+                    help="pipeline schedule (ppPxtpT only)")
     ap.add_argument("--microbatches", type=int, default=8,
                     help="micro-batches per step of a pipeline-parallel run (ppPxtpT)")
     ap.add_argument("--no-e2e", action="store_true")
@@ -89,7 +91,8 @@ def main():
         from monarch_b200.parallel.pipelining import PipelineTrainer
         n_mb = args.microbatches
         trainer = PipelineTrainer(args.model, int(m_pp.group(1)), int(m_pp.group(2)), args.seq,
-                                  args.micro_batch, n_mb, device=dev, comm=args.comm)
+                                  args.micro_batch, n_mb, device=dev, comm=args.comm,
+                                  schedule=args.schedule)
     elif args.parallelism == "ep":
         from monarch_b200.parallel.ep import MoETrainer
         trainer = MoETrainer(args.model, args.seq, args.micro_batch, device=dev, comm=args.comm)
