@@ -14,6 +14,7 @@ from typing import Any, Callable, List, Optional, Tuple
 import cloudpickle
 
 _OOB_MIN_BYTES = 4096
+_OOB_MIN_RAW_BYTES = 65536   # bytes / bytearray payloads of this size travel as parts too
 
 
 def _torch():
@@ -40,10 +41,15 @@ class _Pickler(cloudpickle.Pickler):
             t = t.contiguous()
             nbytes = t.numel() * t.element_size()
             if nbytes >= _OOB_MIN_BYTES:
-                raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if nbytes else b""
-                self._parts.append(raw)
+                # a view of the tensor's memory: the native send copies it once, straight
+                # into the buffer that goes on the wire
+                self._parts.append(memoryview(t.reshape(-1).view(torch.uint8).numpy()))
                 return ("t", len(self._parts) - 1, str(t.dtype).split(".")[-1], tuple(t.shape),
                         bool(obj.requires_grad))
+        tp = type(obj)
+        if (tp is bytes or tp is bytearray) and len(obj) >= _OOB_MIN_RAW_BYTES:
+            self._parts.append(obj)
+            return ("b" if tp is bytes else "ba", len(self._parts) - 1)
         return None
 
 
@@ -62,6 +68,8 @@ class _Unpickler(pickle.Unpickler):
             import torch
             _, idx, dtype, shape, req = pid
             raw = self._parts[idx]
+            if type(raw) is not bytes:
+                raw = bytes(raw)      # same-process delivery hands the sender's view over
             dt = getattr(torch, dtype)
             if len(raw) == 0:
                 t = torch.empty(shape, dtype=dt)
@@ -73,6 +81,11 @@ class _Unpickler(pickle.Unpickler):
                 ctypes.memmove(t.data_ptr(), raw, len(raw))
                 t = t.view(dt).reshape(shape)
             return t.requires_grad_(req) if req else t
+        if pid[0] == "b":
+            raw = self._parts[pid[1]]
+            return raw if type(raw) is bytes else bytes(raw)
+        if pid[0] == "ba":
+            return bytearray(self._parts[pid[1]])
         raise pickle.UnpicklingError(f"unknown persistent id {pid!r}")
 
 

@@ -382,31 +382,81 @@ class NetRx : public Rx, public std::enable_shared_from_this<NetRx> {
       channel_stats().acks_sent++;
       return ::send(fd, b, 8, MSG_NOSIGNAL) == 8;
     };
-    std::string payload;
+    constexpr uint64_t kSmallFrame = 64 * 1024;
+    std::string small;
     while (!stop_) {
+      // frame = len(8) type(1) ...; a message frame continues with seq(8) nparts(8)
+      // head_len(8) part_len(8)* head parts*.  Head and parts of a large frame are read
+      // straight into the strings that are handed on, so a large part is written once by
+      // the kernel and never copied again on this side.
       char lenb[8];
       if (!read_exact(fd, lenb, 8)) break;
       uint64_t len = get_be64(lenb);
       if (len == 0 || len > max_frame) break;
-      payload.resize(len);
-      if (!read_exact(fd, payload.data(), len)) break;
-      uint8_t type = (uint8_t)payload[0];
-      if (type == kFrameInit && len >= 9) {
-        session = get_be64(payload.data() + 1);
-        continue;
-      }
-      if (type != kFrameMsg || len < 1 + 8 + 4 + 8) break;
-      const char* p = payload.data() + 1;
-      uint64_t seq = get_be64(p);
-      p += 8;
-      uint32_t nparts = (uint32_t)get_be64(p) >> 0;  // stored as be64 for simplicity
-      p += 8;
-      uint64_t head_len = get_be64(p);
-      p += 8;
-      std::vector<uint64_t> plens(nparts);
-      for (auto& l : plens) {
-        l = get_be64(p);
-        p += 8;
+      Frame f;
+      uint64_t seq = 0;
+      if (len <= kSmallFrame) {
+        // small frame: one read, then split
+        small.resize(len);
+        if (!read_exact(fd, small.data(), len)) break;
+        uint8_t type = (uint8_t)small[0];
+        if (type == kFrameInit && len >= 9) {
+          session = get_be64(small.data() + 1);
+          continue;
+        }
+        if (type != kFrameMsg || len < 25) break;
+        const char* p = small.data() + 1;
+        seq = get_be64(p);
+        uint64_t nparts = get_be64(p + 8);
+        uint64_t head_len = get_be64(p + 16);
+        p += 24;
+        if (25 + 8 * nparts > len) break;
+        uint64_t total = 25 + 8 * nparts + head_len;
+        std::vector<uint64_t> plens(nparts);
+        for (auto& l : plens) {
+          l = get_be64(p);
+          p += 8;
+          total += l;
+        }
+        if (head_len > len || total != len) break;
+        f.head.assign(p, head_len);
+        p += head_len;
+        for (uint64_t l : plens) {
+          f.parts.emplace_back(p, l);
+          p += l;
+        }
+      } else {
+        char type_b;
+        if (!read_exact(fd, &type_b, 1)) break;
+        if ((uint8_t)type_b != kFrameMsg) break;
+        char fixed[24];
+        if (!read_exact(fd, fixed, 24)) break;
+        seq = get_be64(fixed);
+        uint64_t nparts = get_be64(fixed + 8);
+        uint64_t head_len = get_be64(fixed + 16);
+        if (nparts > (1u << 20) || 25 + 8 * nparts > len) break;
+        std::vector<uint64_t> plens(nparts);
+        {
+          std::string lens(8 * nparts, '\0');
+          if (nparts && !read_exact(fd, lens.data(), lens.size())) break;
+          for (uint64_t i = 0; i < nparts; ++i) plens[i] = get_be64(lens.data() + 8 * i);
+        }
+        uint64_t total = 25 + 8 * nparts + head_len;
+        bool sane = head_len <= len;
+        for (uint64_t l : plens) {
+          if (l > len) sane = false;
+          total += l;
+        }
+        if (!sane || total != len) break;
+        f.head.resize(head_len);
+        if (head_len && !read_exact(fd, f.head.data(), head_len)) break;
+        bool ok = true;
+        f.parts.resize(nparts);
+        for (uint64_t i = 0; i < nparts && ok; ++i) {
+          f.parts[i].resize(plens[i]);
+          if (plens[i] && !read_exact(fd, f.parts[i].data(), plens[i])) ok = false;
+        }
+        if (!ok) break;
       }
       bool deliver;
       {
@@ -421,13 +471,6 @@ class NetRx : public Rx, public std::enable_shared_from_this<NetRx> {
         }
       }
       if (deliver) {
-        Frame f;
-        f.head.assign(p, head_len);
-        p += head_len;
-        for (uint64_t l : plens) {
-          f.parts.emplace_back(p, l);
-          p += l;
-        }
         channel_stats().frames_received++;
         q_->push(std::move(f));
       }

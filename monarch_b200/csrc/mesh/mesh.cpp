@@ -622,6 +622,7 @@ struct CastWire {
   std::map<std::string, std::string> headers;
   std::vector<RoutingFrame> frames;
   std::string body;
+  bool body_in_parts = false;  // the body is the last part of the carrying envelope
 };
 
 std::string encode_cast(const CastWire& c) {
@@ -643,7 +644,8 @@ std::string encode_cast(const CastWire& c) {
     w.u64(f.dim);
     encode_selection(w, f.sel);
   }
-  w.str(c.body);
+  w.u8(c.body_in_parts ? 1 : 0);
+  if (!c.body_in_parts) w.str(c.body);
   return std::move(w.buf);
 }
 
@@ -669,12 +671,13 @@ CastWire decode_cast(std::string_view b) {
     f.dim = r.u64();
     f.sel = decode_selection(r);
   }
-  c.body = r.str();
+  c.body_in_parts = r.u8() != 0;
+  if (!c.body_in_parts) c.body = r.str();
   return c;
 }
 }  // namespace
 
-std::string encode_cast_root(const CastRequest& c) {
+std::string encode_cast_root(CastRequest& c, std::vector<std::string>& parts) {
   CastWire w;
   w.mesh_id = c.mesh_id;
   w.slice = c.slice;
@@ -683,7 +686,12 @@ std::string encode_cast_root(const CastRequest& c) {
   w.seq = c.seq;
   w.headers = c.headers;
   w.frames.push_back(RoutingFrame::root(c.selection, c.slice));
-  w.body = c.data;
+  if (c.data.size() >= kCastBodyAsPartBytes) {
+    w.body_in_parts = true;
+    parts.push_back(std::move(c.data));
+  } else {
+    w.body = c.data;
+  }
   return encode_cast(w);
 }
 
@@ -697,7 +705,10 @@ ActorHooks make_comm_actor(const std::shared_ptr<Proc>& proc_sp) {
     CastWire c = decode_cast(env.data);
     const size_t my_rank = (size_t)proc->id().rank;
     Resolved res = resolve_routing(my_rank, c.slice, std::move(c.frames), /*seed=*/4 + c.seq);
-    // Forward first so the subtree makes progress while we deliver locally.
+    // Forward first so the subtree makes progress while we deliver locally.  The parts
+    // (with a large body among them) are copied for every consumer but the last, which
+    // takes them over.
+    size_t consumers = res.next.size() + (res.deliver_here ? 1 : 0);
     for (auto& kv : res.next) {
       CastWire fwd;
       fwd.mesh_id = c.mesh_id;
@@ -707,12 +718,16 @@ ActorHooks make_comm_actor(const std::shared_ptr<Proc>& proc_sp) {
       fwd.seq = c.seq;
       fwd.headers = c.headers;
       fwd.frames = std::move(kv.second);
-      fwd.body = c.body;
+      fwd.body_in_parts = c.body_in_parts;
+      if (!c.body_in_parts) fwd.body = c.body;
       Envelope e;
       e.sender = self.id();
       e.dest = PortId{ActorId{ProcId{proc->id().world, (int64_t)kv.first}, "comm", 0}, kPortMessage};
       e.data = encode_cast(fwd);
-      e.parts = env.parts;
+      if (--consumers == 0)
+        e.parts = std::move(env.parts);
+      else
+        e.parts = env.parts;
       proc->post(std::move(e));
     }
     if (res.deliver_here) {
@@ -729,8 +744,13 @@ ActorHooks make_comm_actor(const std::shared_ptr<Proc>& proc_sp) {
       e.headers[kHdrCastRank] = std::to_string(cast_rank);
       e.headers[kHdrCastSender] = c.sender.to_string();
       e.headers[kHdrCastMesh] = c.mesh_id;
-      e.data = std::move(c.body);
       e.parts = std::move(env.parts);
+      if (c.body_in_parts && !e.parts.empty()) {
+        e.data = std::move(e.parts.back());
+        e.parts.pop_back();
+      } else {
+        e.data = std::move(c.body);
+      }
       proc->post(std::move(e));
     }
     Metrics::global().histogram_record("comm.cast_hop_us", now_us() - t0);
@@ -970,7 +990,7 @@ void ProcMesh::cast(const std::string& name, const Slice& slice, const Sel& sele
   Envelope e;
   e.sender = sender;
   e.dest = PortId{ActorId{proc_id(root), "comm", 0}, kPortMessage};
-  e.data = encode_cast_root(c);
+  e.data = encode_cast_root(c, parts);
   e.parts = std::move(parts);
   client_->post(std::move(e));
 }

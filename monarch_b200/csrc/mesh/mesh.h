@@ -119,7 +119,12 @@ struct CastRequest {
   uint64_t seq = 0;        // per (sender, mesh) sequence number
   Slice cast_shape;        // shape reported to receivers (CAST_SHAPE); cast_rank = index in it
 };
-std::string encode_cast_root(const CastRequest& c);
+// Bodies of this size or more travel as the last part of the envelope instead of inside the
+// routing header, so that the hops of the cast tree never re-encode (copy) them.
+constexpr size_t kCastBodyAsPartBytes = 4096;
+// Encodes the routing header.  A large body is moved out of `c.data` and appended to
+// `parts` (the envelope's parts).
+std::string encode_cast_root(CastRequest& c, std::vector<std::string>& parts);
 
 // ----------------------------------------------------------------------- proc mesh ----
 struct SpawnResult {

@@ -134,6 +134,27 @@ std::vector<std::string> to_strings(const std::vector<py::bytes>& parts) {
   return out;
 }
 
+// Parts given as bytes or as any C-contiguous buffer (memoryview of a tensor's storage, numpy
+// array, bytearray): one copy, from the object's memory into the string that travels.
+std::vector<std::string> to_strings(const std::vector<py::object>& parts) {
+  std::vector<std::string> out;
+  out.reserve(parts.size());
+  for (auto& p : parts) {
+    if (PyBytes_Check(p.ptr())) {
+      char* buf = nullptr;
+      Py_ssize_t len = 0;
+      PyBytes_AsStringAndSize(p.ptr(), &buf, &len);
+      out.emplace_back(buf, (size_t)len);
+      continue;
+    }
+    Py_buffer view;
+    if (PyObject_GetBuffer(p.ptr(), &view, PyBUF_C_CONTIGUOUS) != 0) throw py::error_already_set();
+    out.emplace_back(static_cast<const char*>(view.buf), (size_t)view.len);
+    PyBuffer_Release(&view);
+  }
+  return out;
+}
+
 }  // namespace
 
 PYBIND11_MODULE(_native, m) {
@@ -440,7 +461,7 @@ PYBIND11_MODULE(_native, m) {
       .def_property_readonly("proc", &Instance::proc)
       .def("send",
            [](Instance& i, const std::string& dest, py::bytes data,
-              std::map<std::string, std::string> headers, std::vector<py::bytes> parts) {
+              std::map<std::string, std::string> headers, std::vector<py::object> parts) {
              PortId d = PortId::parse(dest);
              std::string body = data;
              auto ps = to_strings(parts);
@@ -448,7 +469,7 @@ PYBIND11_MODULE(_native, m) {
              i.send(d, std::move(body), std::move(headers), std::move(ps));
            },
            py::arg("dest"), py::arg("data"), py::arg("headers") = std::map<std::string, std::string>{},
-           py::arg("parts") = std::vector<py::bytes>{})
+           py::arg("parts") = std::vector<py::object>{})
       .def("open_port",
            [](Instance& i, bool once) {
              auto q = std::make_shared<QueueSink>(once);
@@ -565,7 +586,7 @@ PYBIND11_MODULE(_native, m) {
   m.def("cast", [](std::shared_ptr<Instance> inst, const std::string& world,
                    const std::string& name, const Slice& slice, std::shared_ptr<Selection> sel,
                    py::bytes data, std::map<std::string, std::string> headers,
-                   std::vector<py::bytes> parts, const Slice& cast_shape) {
+                   std::vector<py::object> parts, const Slice& cast_shape) {
     static std::atomic<uint64_t> seq{0};
     CastRequest c;
     c.mesh_id = name;
@@ -585,7 +606,7 @@ PYBIND11_MODULE(_native, m) {
     Envelope e;
     e.sender = inst->id();
     e.dest = PortId{ActorId{ProcId{world, root}, "comm", 0}, kPortMessage};
-    e.data = encode_cast_root(c);
+    e.data = encode_cast_root(c, ps);
     e.parts = std::move(ps);
     Metrics::global().counter_add("cast.messages");
     proc->post(std::move(e));
@@ -783,7 +804,7 @@ PYBIND11_MODULE(_native, m) {
       .def("cast",
            [](ProcMesh& pm, const std::string& name, const Slice& slice,
               std::shared_ptr<Selection> sel, const std::string& sender, py::bytes data,
-              std::map<std::string, std::string> headers, std::vector<py::bytes> parts,
+              std::map<std::string, std::string> headers, std::vector<py::object> parts,
               const Slice& cast_shape) {
              ActorId s = ActorId::parse(sender);
              std::string body = data;
@@ -794,7 +815,7 @@ PYBIND11_MODULE(_native, m) {
            },
            py::arg("name"), py::arg("slice"), py::arg("selection"), py::arg("sender"),
            py::arg("data"), py::arg("headers") = std::map<std::string, std::string>{},
-           py::arg("parts") = std::vector<py::bytes>{}, py::arg("cast_shape") = Slice())
+           py::arg("parts") = std::vector<py::object>{}, py::arg("cast_shape") = Slice())
       .def("stop_actor", &ProcMesh::stop_actor, py::arg("name"), py::arg("timeout_ms") = 5000,
            py::call_guard<py::gil_scoped_release>())
       .def("ledger", &ProcMesh::ledger, py::arg("timeout_ms") = 5000,
