@@ -335,6 +335,17 @@ def shape_normalised(shape: Shape) -> Shape:
 
 
 # -------------------------------------------------------------------------- endpoints --
+_signatures: Dict[Any, inspect.Signature] = {}
+
+
+def _signature_of(fn) -> inspect.Signature:
+    """``inspect.signature`` costs tens of microseconds; endpoints are called in loops."""
+    sig = _signatures.get(fn)
+    if sig is None:
+        sig = _signatures[fn] = inspect.signature(fn)
+    return sig
+
+
 class EndpointProperty:
     """What ``@endpoint`` leaves on the class: resolved to an :class:`Endpoint` when read
     from an :class:`ActorMesh`, to the plain bound method when read from the actor."""
@@ -379,7 +390,7 @@ class Endpoint(Generic[R]):
     def _check_signature(self, args, kwargs) -> None:
         if self._fn is None:
             return
-        sig = inspect.signature(self._fn)
+        sig = _signature_of(self._fn)
         extra = [None] * (2 if self._explicit else 1)  # self (+ port)
         try:
             sig.bind(*extra, *args, **kwargs)
@@ -612,7 +623,10 @@ class ActorMesh(MeshTrait, Generic[T]):
             sel = N.Selection.all()
         else:
             sel = N.Selection.of_ranks(root, sl.ranks() if ranks is None else ranks)
-        headers = {"cast_shape": json.dumps([self._shape_.labels, list(sl.sizes)])}
+        headers = self.__dict__.get("_cast_headers")
+        if headers is None:
+            headers = self._cast_headers = {
+                "cast_shape": json.dumps([self._shape_.labels, list(sl.sizes)])}
         inst = context().actor_instance._native
         N.cast(inst, self._world, self._name, root, sel, body, headers, parts, sl)
 

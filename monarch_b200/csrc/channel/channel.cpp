@@ -527,6 +527,36 @@ class NetTx : public Tx {
       }
   }
   void post(Frame f, std::function<void(Frame&&)> on_fail) override {
+    // Fast path: a small frame on an idle, connected, writable link is written by the
+    // caller itself, which saves waking the writer thread (one thread hop per message).
+    // io_mu_ serialises everything that writes to or closes the socket and is always taken
+    // before mu_; the writer thread moves frames from the outbox to the unacked queue only
+    // while holding it, so the wire order equals the sequence order.
+    if (f.size() <= kInlineSendBytes) {
+      std::unique_lock<std::mutex> io(io_mu_, std::try_to_lock);
+      if (io.owns_lock()) {
+        Item* it = nullptr;
+        int fd = -1;
+        {
+          std::lock_guard<std::mutex> g(mu_);
+          if (!closed_ && !stop_ && fd_ >= 0 && outbox_.empty()) {
+            pollfd pf{fd_, POLLOUT, 0};
+            if (::poll(&pf, 1, 0) == 1 && (pf.revents & POLLOUT) &&
+                !(pf.revents & (POLLERR | POLLHUP))) {
+              unacked_.push_back(Item{next_seq_++, std::move(f), std::move(on_fail),
+                                      std::chrono::steady_clock::now()});
+              it = &unacked_.back();
+              fd = fd_;
+            }
+          }
+        }
+        if (it) {
+          channel_stats().frames_sent++;
+          if (!send_item(fd, *it)) ::shutdown(fd, SHUT_RDWR);  // the writer thread reconnects
+          return;                                               // and resends what is unacked
+        }
+      }
+    }
     {
       std::lock_guard<std::mutex> g(mu_);
       if (closed_) {
@@ -600,6 +630,7 @@ class NetTx : public Tx {
   void fail_all() {
     std::deque<Item> items;
     {
+      std::lock_guard<std::mutex> io(io_mu_);  // no caller-side send is using an item
       std::lock_guard<std::mutex> g(mu_);
       closed_ = true;
       for (auto& i : unacked_) items.push_back(std::move(i));
@@ -671,6 +702,7 @@ class NetTx : public Tx {
         bool ok = ::send(fd, init, sizeof(init), MSG_NOSIGNAL) == (ssize_t)sizeof(init);
         // Resend everything not yet acknowledged, in order.
         if (ok) {
+          std::lock_guard<std::mutex> io(io_mu_);
           std::lock_guard<std::mutex> g(mu_);
           for (auto& it : unacked_) {
             channel_stats().frames_resent++;
@@ -684,12 +716,14 @@ class NetTx : public Tx {
           ::close(fd);
           continue;
         }
+        std::lock_guard<std::mutex> io(io_mu_);
         std::lock_guard<std::mutex> g(mu_);
         fd_ = fd;
       }
       // Send new items.
       bool io_ok = true;
       while (io_ok) {
+        std::lock_guard<std::mutex> io(io_mu_);
         Item* it = nullptr;
         {
           std::lock_guard<std::mutex> g(mu_);
@@ -726,6 +760,7 @@ class NetTx : public Tx {
         }
       }
       if (!io_ok) {
+        std::lock_guard<std::mutex> io(io_mu_);
         std::lock_guard<std::mutex> g(mu_);
         ::close(fd_);
         fd_ = -1;
@@ -733,6 +768,7 @@ class NetTx : public Tx {
       }
     }
     {
+      std::lock_guard<std::mutex> io(io_mu_);
       std::lock_guard<std::mutex> g(mu_);
       if (fd_ >= 0) {
         ::close(fd_);
@@ -746,6 +782,8 @@ class NetTx : public Tx {
   uint64_t session_;
   int wake_fd_ = -1;
   int fd_ = -1;
+  static constexpr size_t kInlineSendBytes = 16 * 1024;
+  std::mutex io_mu_;  // writers to / closers of fd_; taken before mu_
   std::mutex mu_;
   std::deque<Item> outbox_, unacked_;
   uint64_t next_seq_ = 0;
