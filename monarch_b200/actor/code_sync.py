@@ -11,7 +11,7 @@ the file mover, auto_reload.rs + python/monarch/_src/actor/code_sync/auto_reload
 ``AutoReloader`` that snapshots module sources by hash and reloads the changed ones),
 python/monarch/_src/actor/proc_mesh.py ``sync_workspace``.  Files travel as message parts
 over the actor channels (content-hash manifest, only changed files), not through an rsync
-daemon.  conda environment sync is not provided.
+daemon.  Environment (conda / virtualenv) sync lives in ``env_sync.py``.
 """
 from __future__ import annotations
 

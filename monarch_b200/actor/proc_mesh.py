@@ -264,10 +264,20 @@ class ProcMesh(MeshTrait):
 
     def sync_workspace(self, workspace: Optional[str] = None, conda: bool = False,
                        auto_reload: bool = False) -> Future[None]:
-        if conda:
-            raise NotImplementedError("conda environment sync is not supported")
         from .code_sync import sync_workspace
-        return sync_workspace(self, workspace, auto_reload)
+        fut = sync_workspace(self, workspace, auto_reload)
+        if not conda:
+            return fut
+        # also bring the procs' Python environment (conda prefix or virtualenv) in line with
+        # the client's; procs that share the client's directory need nothing
+        from .env_sync import sync_env
+
+        def both(timeout):
+            out = fut.get(timeout)
+            sync_env(self, timeout=timeout)
+            return out
+
+        return Future(both)
 
     def stop(self) -> Future[None]:
         owner = self._owner
