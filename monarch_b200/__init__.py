@@ -40,6 +40,13 @@ _LAZY = {
     "local_proc_mesh": ("actor", "local_proc_mesh"), "proc_mesh": ("actor", "proc_mesh"),
     "sim_proc_mesh": ("actor", "sim_proc_mesh"),
     "mock_mesh": ("simulator", "mock_mesh"), "Simulator": ("simulator", "Simulator"),
+    "python_local_mesh": ("mesh_constructors", "python_local_mesh"),
+    "local_mesh": ("mesh_constructors", "local_mesh"),
+    "local_meshes": ("mesh_constructors", "local_meshes"),
+    "sim_mesh": ("mesh_constructors", "sim_mesh"),
+    "world_mesh": ("mesh_constructors", "world_mesh"),
+    "ControllerRemoteClass": ("remote_class", "ControllerRemoteClass"),
+    "WorkerRemoteClass": ("remote_class", "WorkerRemoteClass"),
     # opaque objects
     "OpaqueRef": ("opaque_object", "OpaqueRef"), "OpaqueObject": ("opaque_object", "OpaqueObject"),
     "OpaqueModule": ("opaque_module", "OpaqueModule"),
@@ -49,7 +56,8 @@ _LAZY = {
 def __getattr__(name):
     ent = _LAZY.get(name)
     if ent is None:
-        if name in ("timer", "profiler", "random", "memory", "tensorboard", "builtins"):
+        if name in ("timer", "profiler", "random", "memory", "tensorboard", "builtins", "telemetry",
+                    "remote_class", "mesh_constructors"):
             import importlib
             return importlib.import_module(f"{__name__}.{name}")
         raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

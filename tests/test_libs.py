@@ -160,3 +160,18 @@ def test_remote_class_runs_methods_on_every_worker(dm):
         acc.drop()
         with pytest.raises(Exception):
             _Accumulator.add(acc, x)     # dropped: no mesh to run on
+
+
+def test_mesh_constructors():
+    import monarch_b200 as m
+    with m.local_mesh(gpus_per_host=2, use_cuda=False) as mesh:
+        assert mesh.sizes == {"hosts": 1, "gpus": 2}
+        with mesh.activate():
+            x = mesh.rank("gpus").to(torch.float32) + torch.ones(2)
+            assert te.inspect(x.reduce("gpus", "sum")).tolist() == [3.0, 3.0]
+    sims = m.sim_mesh(n_meshes=2, hosts=1, gpus_per_host=4)
+    assert len(sims) == 2 and sims[0].sizes == {"hosts": 1, "gpus": 4}
+    with sims[1].activate():
+        y = torch.ones(8, 8) @ torch.ones(8, 8)
+        assert y.shape == (8, 8)
+    assert sims[1].simulator is not None
