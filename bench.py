@@ -35,6 +35,9 @@ def parse():
     ap.add_argument("--micro-batch", type=int, default=1)
     ap.add_argument("--parallelism", default="auto")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--recompute-layers", type=int, default=None,
+                    help="activation checkpointing: recompute only the first N layers and keep "
+                         "the activations of the rest (default: recompute every layer)")
     ap.add_argument("--schedule", default="1f1b", choices=["gpipe", "1f1b", "zb-h1"],
                     help="pipeline schedule (ppPxtpT only)")
     ap.add_argument("--microbatches", type=int, default=8,
@@ -98,6 +101,7 @@ def main():
         trainer = MoETrainer(args.model, args.seq, args.micro_batch, device=dev, comm=args.comm)
     else:
         trainer = Trainer(args.model, seq_len=args.seq, micro_batch=args.micro_batch,
+                          recompute_layers=args.recompute_layers,
                           parallelism=args.parallelism, device=dev, comm=args.comm)
     cfg = trainer.cfg
     B, S = args.micro_batch, args.seq
@@ -175,13 +179,16 @@ def main():
             "impl": args.impl,
             "config": {"model": args.model,
                        "global_batch": n_mb * B if m_pp else B * world, "seq_len": S,
-                       "parallelism": par, "activation_checkpointing": True,
+                       "parallelism": par,
+                       "activation_checkpointing": True if args.recompute_layers is None else
+                       f"first {args.recompute_layers} layers recomputed, the rest kept",
                        "optimizer": "AdamW fp32 master", "comm": args.comm,
                        **({"fsdp_gather": os.environ.get("MB200_FSDP_GATHER", "prefetch")}
                           if par.startswith("fsdp") else {}),
                        "l2": "per-step working set (>100 GB of weights and optimizer state) "
                              "is far larger than the 126 MB L2"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "loss": final_loss,
+            "max_mem_gb": torch.cuda.max_memory_allocated() / 1e9,
             "model_tflops_per_gpu": flops_tok * tokens_per_step / world * args.steps / (ms / 1e3) / 1e12,
         }
         print(json.dumps(out))

@@ -295,11 +295,21 @@ class LlamaEngine:
     unit's forward and backward so that FSDP / DDP / TP variants only swap the store.
     """
 
-    def __init__(self, cfg: LlamaConfig, store, seq_len: int, checkpoint: bool = True):
+    def __init__(self, cfg: LlamaConfig, store, seq_len: int, checkpoint: bool = True,
+                 recompute_layers: Optional[int] = None):
+        """``checkpoint``: keep only each layer's input (and attention output) in the forward
+        and recompute the rest in the backward.  ``recompute_layers`` (with ``checkpoint``):
+        how many of the layers, counted from the first, are treated that way; the remaining
+        last layers keep all their activations (about 17 bytes per token per model-dim
+        element each), trading spare HBM for one skipped forward per kept layer.  Default:
+        all layers are recomputed."""
         self.cfg = cfg
         self.store = store
         self.seq_len = seq_len
         self.checkpoint = checkpoint
+        if recompute_layers is None:
+            recompute_layers = cfg.n_layers if checkpoint else 0
+        self.recompute_layers = max(0, min(cfg.n_layers, recompute_layers)) if checkpoint else 0
         dev = store.device
         self.cos, self.sin = ops.reference.rope_tables(seq_len, cfg.hd, cfg.theta, device=dev)
         self.n_units = cfg.n_layers + 2
@@ -398,7 +408,7 @@ class LlamaEngine:
             st.pre_forward(1 + i)
             w = st.unit_params(1 + i)
             ckpt.append(x)
-            x, saved = self._layer_fwd(w, x, B, S, keep=not self.checkpoint)
+            x, saved = self._layer_fwd(w, x, B, S, keep=i >= self.recompute_layers)
             saved_all.append(saved)
             st.post_forward(1 + i)
 
@@ -432,7 +442,7 @@ class LlamaEngine:
             st.pre_backward(1 + i)
             w = st.unit_params(1 + i)
             g = st.unit_grads(1 + i)
-            if self.checkpoint:
+            if i < self.recompute_layers:
                 _, saved = self._layer_fwd(w, ckpt[i], B, S, keep=True,
                                            attn_saved=saved_all[i])
                 saved_all[i] = None

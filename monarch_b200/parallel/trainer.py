@@ -26,7 +26,7 @@ class Trainer:
     def __init__(self, model: str | LlamaConfig = "llama3-8b", seq_len: int = 8192,
                  micro_batch: int = 1, parallelism: str = "auto", device=None,
                  checkpoint: bool = True, lr: float = 3e-4, seed: int = 0,
-                 comm: str = "fused"):
+                 comm: str = "fused", recompute_layers: Optional[int] = None):
         self.cfg = PRESETS[model] if isinstance(model, str) else model
         self.seq_len = seq_len
         self.micro_batch = micro_batch
@@ -54,7 +54,8 @@ class Trainer:
             self.store = DDPParamStore(self.layout, self.device, seed=seed, comm=comm)
         else:
             raise ValueError(f"unknown parallelism {parallelism!r}")
-        self.engine = LlamaEngine(self.cfg, self.store, seq_len, checkpoint=checkpoint)
+        self.engine = LlamaEngine(self.cfg, self.store, seq_len, checkpoint=checkpoint,
+                                  recompute_layers=recompute_layers)
         shape = (micro_batch, seq_len)
         self._tok_dev = torch.empty(shape, dtype=torch.int64, device=self.device)
         self._tgt_dev = torch.empty(shape, dtype=torch.int64, device=self.device)

@@ -15,12 +15,17 @@ def _fp32_store(cfg, layout):
     return st
 
 
-@pytest.mark.parametrize("preset,ckpt", [("tiny", True), ("tiny", False), ("tiny-tied", True)])
+@pytest.mark.parametrize("preset,ckpt", [("tiny", True), ("tiny", False), ("tiny-tied", True),
+                                         ("tiny", 1)])
 def test_engine_matches_autograd(preset, ckpt):
     cfg = PRESETS[preset]
     layout = ParamLayout(cfg)
     st = _fp32_store(cfg, layout)
-    eng = LlamaEngine(cfg, st, seq_len=16, checkpoint=ckpt)
+    if ckpt is True or ckpt is False:
+        eng = LlamaEngine(cfg, st, seq_len=16, checkpoint=ckpt)
+    else:   # recompute only the first `ckpt` layers, keep the activations of the rest
+        eng = LlamaEngine(cfg, st, seq_len=16, checkpoint=True, recompute_layers=ckpt)
+        assert eng.recompute_layers == ckpt < cfg.n_layers
     torch.manual_seed(0)
     tokens = torch.randint(0, cfg.vocab, (2, 16))
     targets = torch.randint(0, cfg.vocab, (2, 16))
