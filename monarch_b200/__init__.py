@@ -47,6 +47,13 @@ _LAZY = {
     "world_mesh": ("mesh_constructors", "world_mesh"),
     "ControllerRemoteClass": ("remote_class", "ControllerRemoteClass"),
     "WorkerRemoteClass": ("remote_class", "WorkerRemoteClass"),
+    "ProcessAllocator": ("actor.allocator", "ProcessAllocator"),
+    "LocalAllocator": ("actor.allocator", "LocalAllocator"),
+    "SimAllocator": ("actor.allocator", "SimAllocator"),
+    "RemoteAllocator": ("actor.allocator", "RemoteAllocator"),
+    "AllocSpec": ("actor.allocator", "AllocSpec"),
+    "NDSlice": ("actor.shape", "NDSlice"),
+    "ActorFuture": ("actor", "Future"),
     # opaque objects
     "OpaqueRef": ("opaque_object", "OpaqueRef"), "OpaqueObject": ("opaque_object", "OpaqueObject"),
     "OpaqueModule": ("opaque_module", "OpaqueModule"),

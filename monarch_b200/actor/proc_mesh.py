@@ -225,6 +225,12 @@ class ProcMesh(MeshTrait):
             rows.append(f"{r}\t" + "\t".join(str(c) for c in sl.coordinates(r)))
         return "\n".join(rows)
 
+    @staticmethod
+    def from_alloc(alloc) -> "ProcMesh":
+        """The proc mesh described by an :class:`~monarch_b200.actor.allocator.Alloc`."""
+        from .allocator import proc_mesh_from_alloc
+        return proc_mesh_from_alloc(alloc)
+
     def ledger(self, timeout: float = 5.0) -> Dict[int, List[dict]]:
         """Actor-tree snapshot of every proc of the mesh (hyperactor/src/proc.rs:139-315
         ``ledger_snapshot``): rank -> list of ``{actor_id, status, messages_handled, failure,
@@ -373,7 +379,7 @@ def _shape_from_dims(dims: Dict[str, int]) -> Shape:
 def _allocate(dims: Dict[str, int], *, in_process: bool, env: Optional[Dict[str, str]] = None,
               bootstrap: Optional[Callable[[], None]] = None, gpu_env: bool = False,
               transport: str = "unix", remote_hosts: Optional[List[str]] = None,
-              procs_per_host: int = 1) -> ProcMesh:
+              procs_per_host: int = 1, argv: Optional[List[str]] = None) -> ProcMesh:
     n = 1
     for v in dims.values():
         n *= int(v)
@@ -381,7 +387,7 @@ def _allocate(dims: Dict[str, int], *, in_process: bool, env: Optional[Dict[str,
     if in_process:
         native = N.ProcMesh.allocate_local(world, n)
     else:
-        argv = [sys.executable, "-m", "monarch_b200.actor.bootstrap_main"]
+        argv = list(argv) if argv else [sys.executable, "-m", "monarch_b200.actor.bootstrap_main"]
         # the job-wide controller registry must exist before children are started: they
         # find it through MB200_CONTROLLER_REF in their environment
         _controller_controller()

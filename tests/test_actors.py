@@ -252,3 +252,41 @@ def test_subprocess_mesh_end_to_end():
         assert len(set(pids)) == 2 and os.getpid() not in pids
     finally:
         m.stop().get()
+
+
+def test_allocators_and_from_alloc():
+    from monarch_b200.actor import ProcMesh
+    from monarch_b200.actor.allocator import (AllocConstraints, AllocSpec, LocalAllocator,
+                                              ProcessAllocator, RemoteAllocator,
+                                              StaticRemoteAllocInitializer)
+
+    class Who(Actor):
+        @endpoint
+        def pid(self) -> int:
+            import os
+            return os.getpid()
+
+    import os
+    spec = AllocSpec(AllocConstraints(), hosts=1, gpus=2)
+    with pytest.raises(ValueError):
+        AllocSpec(gpus=0)
+    alloc = LocalAllocator().allocate(spec)
+    pm = ProcMesh.from_alloc(alloc)
+    try:
+        assert pm.sizes == {"hosts": 1, "gpus": 2}
+        assert set(pm.spawn("who", Who).pid.call().get().values()) == {os.getpid()}
+        with pytest.raises(RuntimeError):
+            ProcMesh.from_alloc(alloc)             # an alloc is used once
+    finally:
+        pm.stop().get()
+    pm = ProcMesh.from_alloc(ProcessAllocator(env={"MB200_TEST_MARK": "1"}).allocate(spec))
+    try:
+        pids = pm.spawn("who", Who).pid.call().get(timeout=60).values()
+        assert len(set(pids)) == 2 and os.getpid() not in pids
+    finally:
+        pm.stop().get()
+    ra = RemoteAllocator("w", StaticRemoteAllocInitializer("tcp!127.0.0.1:1", "127.0.0.1:2"))
+    a = ra.allocate(AllocSpec(hosts=2, gpus=4))
+    assert a.params == {"hosts": ["127.0.0.1:1", "127.0.0.1:2"], "procs_per_host": 4}
+    with pytest.raises(ValueError):
+        ra.allocate(AllocSpec(hosts=3, gpus=1))
