@@ -51,7 +51,7 @@ def reference_unavailable():
         "impl": "reference",
         "unavailable": "pytorch-labs/monarch needs cargo + Rust nightly + crates.io and "
                        "setuptools_rust to build; none is installed offline here (pip install "
-                       "of /root/reference fails at metadata: No module named 'setuptools_rust')",
+                       "of the reference tree fails at metadata: No module named 'setuptools_rust')",
     }))
     return 0
 
