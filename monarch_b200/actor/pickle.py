@@ -13,6 +13,8 @@ from typing import Any, Callable, List, Optional, Tuple
 
 import cloudpickle
 
+_PLAIN_TYPES = frozenset({str, int, float, bool, type(None), tuple, list, dict, set, frozenset,
+                          complex, range, slice})
 _OOB_MIN_BYTES = 4096
 _OOB_MIN_RAW_BYTES = 65536   # bytes / bytearray payloads of this size travel as parts too
 
@@ -28,6 +30,10 @@ class _Pickler(cloudpickle.Pickler):
         self._extra = extra_pid
 
     def persistent_id(self, obj):
+        # called for every object of the message: the common plain types leave at once
+        tp = type(obj)
+        if tp in _PLAIN_TYPES:
+            return None
         if self._extra is not None:
             r = self._extra(obj)
             if r is not None:

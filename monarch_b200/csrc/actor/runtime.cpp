@@ -269,6 +269,22 @@ bool Instance::deliver(Envelope&& env) {
     std::lock_guard<std::mutex> g(mu_);
     if (!accepting_) return false;
   }
+  if (port == kPortMessage && hooks_.inline_messages && hooks_.on_message) {
+    std::lock_guard<std::mutex> one_at_a_time(inline_mu_);
+    try {
+      status_ = ActorStatus::Processing;
+      hooks_.on_message(*this, env);
+      handled_++;
+      status_ = ActorStatus::Idle;
+    } catch (const std::exception& e) {
+      // fail on the actor's own thread, through the same path as a throwing loop handler
+      ActorSupervisionEvent ev;
+      ev.mesh = "__self__";
+      ev.message = e.what();
+      post_supervision(ev);
+    }
+    return true;
+  }
   Work w;
   switch (port) {
     case kPortMessage:

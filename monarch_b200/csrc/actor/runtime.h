@@ -118,6 +118,12 @@ struct ActorHooks {
   // Return true if handled; false fails this actor (the default for returned messages).
   std::function<bool(Instance&, Envelope& returned, const std::string& reason)> on_undeliverable;
   std::function<void(Instance&)> on_stop;
+  // Run on_message on the thread that delivers the message (one at a time, under a lock)
+  // instead of waking the actor's own thread.  For stateless relays such as the comm actors
+  // of the cast tree, where the hand-over to another thread is most of the hop's cost.  The
+  // handler must not block and must only deliver "downstream" (no cycles between inline
+  // actors), since deliveries nest.
+  bool inline_messages = false;
 };
 
 class Instance : public std::enable_shared_from_this<Instance> {
@@ -179,6 +185,7 @@ class Instance : public std::enable_shared_from_this<Instance> {
   std::weak_ptr<Instance> parent_;
   bool has_loop_;
 
+  std::mutex inline_mu_;  // serialises inline_messages handlers
   mutable std::mutex mu_;
   std::condition_variable cv_;
   std::deque<Work> work_;

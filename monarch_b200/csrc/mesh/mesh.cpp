@@ -698,6 +698,9 @@ std::string encode_cast_root(CastRequest& c, std::vector<std::string>& parts) {
 ActorHooks make_comm_actor(const std::shared_ptr<Proc>& proc_sp) {
   std::weak_ptr<Proc> wproc = proc_sp;
   ActorHooks h;
+  // a relay without state: routed on the delivering thread (forwards go down the tree of
+  // the mesh's spawn-time slice, so nested deliveries cannot form a cycle)
+  h.inline_messages = Config::global().get_bool("COMM_ACTOR_INLINE");
   h.on_message = [wproc](Instance& self, Envelope& env) {
     auto proc = wproc.lock();
     if (!proc) return;

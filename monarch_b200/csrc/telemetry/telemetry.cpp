@@ -40,6 +40,7 @@ Config::Config() {
       {"KERNEL_SPIN_BUDGET_MS", "1500"},
       {"DDP_BUCKET_BYTES", "26214400"},
       {"NVLS_ENABLE", "true"},
+      {"COMM_ACTOR_INLINE", "true"},
   };
 }
 Config& Config::global() {
