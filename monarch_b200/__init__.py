@@ -17,6 +17,7 @@ _LAZY = {
     "Tensor": ("tensor_engine", "Tensor"), "DeviceMesh": ("tensor_engine", "DeviceMesh"),
     "Stream": ("tensor_engine", "Stream"), "Borrow": ("tensor_engine", "Borrow"),
     "RemoteException": ("tensor_engine", "RemoteException"),
+    "RemoteProcessGroup": ("tensor_engine", "RemoteProcessGroup"),
     "get_active_mesh": ("tensor_engine", "get_active_mesh"),
     "get_active_stream": ("tensor_engine", "get_active_stream"),
     "no_mesh": ("tensor_engine", "no_mesh"), "reduce": ("tensor_engine", "reduce"),

@@ -30,7 +30,7 @@ from torch.utils._python_dispatch import TorchDispatchMode
 
 from ..actor import Channel, Future
 from ..actor.shape import MeshTrait, Shape
-from .worker import Ref, TensorWorker, _map_refs
+from .worker import PGRef, Ref, TensorWorker, _map_refs
 
 _fake_mode = FakeTensorMode(allow_non_fake_inputs=True)
 
@@ -584,6 +584,8 @@ def _to_fake(obj):
 def _to_wire(obj):
     if isinstance(obj, Tensor):
         return Ref(obj.ref)
+    if isinstance(obj, RemoteProcessGroup):
+        return PGRef(obj.key)
     if isinstance(obj, (list, tuple)):
         return type(obj)(_to_wire(o) for o in obj)
     if isinstance(obj, dict):
@@ -717,6 +719,27 @@ def _has_plain_tensor(args, kwargs) -> bool:
     return found
 
 
+class RemoteProcessGroup:
+    """The controller's handle of the process groups over some dims of a device mesh (one
+    group per combination of the other dims' coordinates).  Passed to a remote function it
+    arrives as the worker's own ``torch.distributed`` group, for collectives written by hand
+    inside the function (python/monarch/common/device_mesh.py:50-95 in the reference)."""
+
+    def __init__(self, dims: Tuple[str, ...], mesh: "DeviceMesh"):
+        self.dims = tuple(dims)
+        self.device_mesh = mesh
+        self.key = mesh.client.ensure_comm(mesh, self.dims)
+
+    def size(self) -> int:
+        n = 1
+        for d in self.dims:
+            n *= self.device_mesh.sizes[d]
+        return n
+
+    def __repr__(self) -> str:
+        return f"RemoteProcessGroup({self.dims})"
+
+
 class DeviceMesh(MeshTrait):
     def __init__(self, client: Client, shape: Shape, workers, root: Optional["DeviceMesh"] = None):
         self.client = client
@@ -746,6 +769,16 @@ class DeviceMesh(MeshTrait):
                 yield self
         finally:
             _active.pop()
+
+    def process_group(self, dims) -> RemoteProcessGroup:
+        """Process groups over ``dims`` (a name or a tuple of names) for use inside remote
+        functions."""
+        if isinstance(dims, str):
+            dims = (dims,)
+        for d in dims:
+            if d not in self._labels:
+                raise KeyError(f"mesh has no dim {d!r} (dims: {self._labels})")
+        return RemoteProcessGroup(tuple(dims), self)
 
     def rank(self, dim) -> Tensor:
         """Tensor holding each proc's coordinate along ``dim`` (or the flat index over a

@@ -41,6 +41,21 @@ class Ref:
         return f"Ref({self.id})"
 
 
+class PGRef(Ref):
+    """Names a process group of the worker (created by ``split_comm``) in the arguments of a
+    remote function; the worker passes its ``torch.distributed`` group in its place."""
+
+    def __init__(self, key):
+        super().__init__(-1)
+        self.key = tuple(key)
+
+    def __reduce__(self):
+        return (PGRef, (self.key,))
+
+    def __repr__(self):
+        return f"PGRef({self.key})"
+
+
 class RemoteError:
     """What a failed op leaves in the environment instead of a tensor."""
 
@@ -248,6 +263,11 @@ class TensorWorker(Actor):
 
     # ---------------------------------------------------------------------- helpers
     def _get(self, ref: Ref, seq: int):
+        if isinstance(ref, PGRef):
+            ent = self.groups.get(ref.key)
+            if ent is None:
+                raise KeyError(f"process group {ref.key} does not include worker {self.rank}")
+            return ent[0]
         v = self.env.get(ref.id)
         if v is None and ref.id not in self.env:
             raise KeyError(f"{ref} is not defined on worker {self.rank}")

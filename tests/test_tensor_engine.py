@@ -287,3 +287,25 @@ def test_progress_watchdog_names_the_stuck_ranks(dm):
     time.sleep(3.0)     # let the sleeper finish before the fixture tears the mesh down
     with flat.activate():
         assert te.inspect(flat.rank("all") + 1, all=3).item() == 4
+
+
+# ------------------------------------------------------------------- process groups ----
+def _hand_written_allreduce(t, pg):
+    import torch.distributed as dist
+    out = t.clone()
+    dist.all_reduce(out, group=pg)
+    return out * dist.get_world_size(pg)
+
+
+def test_remote_process_group_in_a_remote_function(dm):
+    fn = te.remote(_hand_written_allreduce, propagate=lambda t, pg: t)
+    with dm.activate():
+        pg = dm.process_group("gpu")
+        assert pg.size() == 2 and isinstance(pg, te.RemoteProcessGroup)
+        x = (dm.rank("host") * 2 + dm.rank("gpu") + 1).to(torch.float32) * torch.ones(3)
+        y = fn(x, pg)
+        # host 0 holds 1 and 2, host 1 holds 3 and 4; summed over "gpu", times group size 2
+        assert te.inspect(y, host=0, gpu=1).tolist() == [6.0] * 3
+        assert te.inspect(y, host=1, gpu=0).tolist() == [14.0] * 3
+        with pytest.raises(KeyError):
+            dm.process_group("nope")
