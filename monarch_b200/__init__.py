@@ -18,6 +18,7 @@ _LAZY = {
     "Stream": ("tensor_engine", "Stream"), "Borrow": ("tensor_engine", "Borrow"),
     "RemoteException": ("tensor_engine", "RemoteException"),
     "RemoteProcessGroup": ("tensor_engine", "RemoteProcessGroup"),
+    "function_resolvers": ("tensor_engine", "function_resolvers"),
     "get_active_mesh": ("tensor_engine", "get_active_mesh"),
     "get_active_stream": ("tensor_engine", "get_active_stream"),
     "no_mesh": ("tensor_engine", "no_mesh"), "reduce": ("tensor_engine", "reduce"),

@@ -10,12 +10,12 @@ from .device_mesh import (Borrow, DeviceMesh, RemoteException, Stream, Tensor,  
                           get_active_mesh, get_active_stream, no_mesh, reduce, reduce_,
                           slice_mesh, spawn_tensor_engine, to_mesh)
 from .remote import (Remote, call_on_shard_and_fetch, coalescing, compile, fetch_shard,  # noqa: E402
-                     inspect, remote, show)
+                     inspect, remote, show, function_resolvers)
 
 __all__ += ["WorkerTimeoutError", "RemoteProcessGroup", "Borrow", "DeviceMesh", "RemoteException", "Stream", "Tensor", "get_active_mesh",
             "get_active_stream", "no_mesh", "reduce", "reduce_", "slice_mesh",
             "spawn_tensor_engine", "to_mesh", "Remote", "call_on_shard_and_fetch", "coalescing",
-            "compile", "fetch_shard", "inspect", "remote", "show"]
+            "compile", "fetch_shard", "inspect", "remote", "show", "function_resolvers"]
 
 from .pipe import Pipe, create_pipe, remote_generator  # noqa: E402
 

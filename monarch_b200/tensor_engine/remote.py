@@ -19,10 +19,53 @@ from .device_mesh import (DeviceMesh, Tensor, _collect, _mesh_of, _propagation, 
 from .worker import Ref
 
 
-def _resolve_spec(fn) -> tuple:
-    if isinstance(fn, str):
+def _string_resolver(fn) -> Optional[tuple]:
+    if isinstance(fn, str) and "." in fn:
         return ("path", fn)
-    return ("pickle", fn)
+    return None
+
+
+def _torch_op_resolver(fn) -> Optional[tuple]:
+    if isinstance(fn, torch._ops.OpOverload):
+        return ("op", str(fn))          # e.g. "aten.add.Tensor"
+    return None
+
+
+def _import_path_resolver(fn) -> Optional[tuple]:
+    """A module-level function that the workers can import travels as its dotted path (a
+    few bytes) instead of a pickle.  Functions of the launching script and of modules loaded
+    by a test runner's own import machinery do not qualify: the workers could not find them."""
+    mod, name = getattr(fn, "__module__", None), getattr(fn, "__qualname__", "")
+    if not callable(fn) or not mod or mod in ("__main__", "__mp_main__") or "<" in name \
+            or "." in name:
+        return None
+    import sys
+    m = sys.modules.get(mod)
+    if m is None or getattr(m, name, None) is not fn:
+        return None
+    loader = type(getattr(m, "__loader__", None)).__module__ or ""
+    if "pytest" in loader or getattr(m, "__file__", None) is None:
+        return None
+    return ("path", f"{mod}.{name}")
+
+
+def _pickle_resolver(fn) -> Optional[tuple]:
+    return ("pickle", fn) if callable(fn) else None
+
+
+# Tried in order; the first that answers decides how a function reaches the workers
+# (python/monarch/common/function.py ``resolvers`` in the reference).  Programs may insert
+# their own, e.g. to map handles of a registry to paths.
+function_resolvers = [_string_resolver, _torch_op_resolver, _import_path_resolver,
+                      _pickle_resolver]
+
+
+def _resolve_spec(fn) -> tuple:
+    for r in function_resolvers:
+        spec = r(fn)
+        if spec is not None:
+            return spec
+    raise ValueError(f"{fn!r} cannot be sent to the workers as a function")
 
 
 class Remote:
