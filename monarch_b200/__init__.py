@@ -54,7 +54,7 @@ _LAZY = {
     "SimAllocator": ("actor.allocator", "SimAllocator"),
     "RemoteAllocator": ("actor.allocator", "RemoteAllocator"),
     "AllocSpec": ("actor.allocator", "AllocSpec"),
-    "NDSlice": ("actor.shape", "NDSlice"),
+    "NDSlice": ("actor.shape", "NDSlice"), "Selection": ("_native", "Selection"),
     "ActorFuture": ("actor", "Future"),
     # opaque objects
     "OpaqueRef": ("opaque_object", "OpaqueRef"), "OpaqueObject": ("opaque_object", "OpaqueObject"),
