@@ -111,6 +111,35 @@ NATIVE_FLAGS = ["-O2", "-std=c++20", "-fPIC", "-fvisibility=hidden", "-pthread",
                 "-Wno-unused-function"]
 
 
+def build_runtime_stress(sanitizer: str = "thread") -> Path:
+    """The native runtime's concurrency stress program (``csrc/tests/runtime_stress.cpp``)
+    linked with the host runtime sources under ``-fsanitize=<sanitizer>`` ("thread" or
+    "address"); no Python, no GPU.  Returns the executable."""
+    if sanitizer not in ("thread", "address", "none"):
+        raise ValueError(f"unknown sanitizer {sanitizer!r}")
+    dirs = [CSRC / d for d in ("ndslice", "actor", "channel", "mesh", "telemetry")]
+    srcs = sorted(p for d in dirs for p in d.rglob("*.cpp")) + [CSRC / "tests" / "runtime_stress.cpp"]
+    flags = ["-O1", "-g", "-std=c++20", "-pthread", "-fno-omit-frame-pointer"]
+    if sanitizer != "none":
+        flags.append(f"-fsanitize={sanitizer}")
+    odir = OBJ / f"stress_{sanitizer}"
+    odir.mkdir(parents=True, exist_ok=True)
+    target = odir / "runtime_stress"
+    stamp = _stamp(_deps(dirs + [CSRC / "tests"]), flags)
+    if _up_to_date(target, stamp):
+        return target
+    jobs, objs = [], []
+    for s in srcs:
+        o = odir / (s.parent.name + "_" + s.stem + ".o")
+        objs.append(str(o))
+        jobs.append(([CXX, *flags, "-I", str(CSRC), "-c", str(s), "-o", str(o)],
+                     odir / (s.parent.name + "_" + s.stem + ".log")))
+    _compile_many(jobs)
+    _run([CXX, *flags, *objs, "-o", str(target), "-lrt"])
+    _write_stamp(target, stamp)
+    return target
+
+
 def build_native(force: bool = False) -> Path:
     target = ROOT / "_native.so"
     dirs = [CSRC / d for d in ("ndslice", "actor", "channel", "mesh", "telemetry", "python",

@@ -6,6 +6,7 @@
 // hyperactor/src/checkpoint.rs (Checkpointable: save/load of actor state),
 // preempt_rwlock/src/lib.rs (PreemptibleRwLock used by SharedCell).
 #pragma once
+#include <atomic>
 #include <condition_variable>
 #include <cstdint>
 #include <cstdio>
@@ -116,7 +117,7 @@ class PreemptibleRwLock {
   std::condition_variable cv_;
   int readers_ = 0;
   bool writer_ = false;
-  int writers_waiting_ = 0;
+  std::atomic<int> writers_waiting_{0};  // read without the mutex by ReadGuard::preempted
 };
 
 }  // namespace mb

@@ -190,7 +190,12 @@ bool write_all_iov(int fd, std::vector<iovec>& iov) {
   size_t idx = 0;
   while (idx < iov.size()) {
     int cnt = (int)std::min<size_t>(iov.size() - idx, 64);
-    ssize_t n = ::writev(fd, &iov[idx], cnt);
+    // sendmsg rather than writev: MSG_NOSIGNAL keeps a peer that went away from raising
+    // SIGPIPE in hosts that have not ignored it (a plain C++ embedder, unlike Python)
+    msghdr mh{};
+    mh.msg_iov = &iov[idx];
+    mh.msg_iovlen = (size_t)cnt;
+    ssize_t n = ::sendmsg(fd, &mh, MSG_NOSIGNAL);
     if (n < 0) {
       if (errno == EINTR) continue;
       return false;
