@@ -335,6 +335,10 @@ def shape_normalised(shape: Shape) -> Shape:
 
 
 # -------------------------------------------------------------------------- endpoints --
+def _tracing_on() -> bool:
+    return N.events_enabled() or N.trace_enabled()
+
+
 _signatures: Dict[Any, inspect.Signature] = {}
 
 
@@ -707,6 +711,10 @@ class _ActorState:
             prop = getattr(self.cls, method, None)
             explicit = isinstance(prop, EndpointProperty) and prop._explicit_response_port
             fn = prop._fn if isinstance(prop, EndpointProperty) else getattr(self.cls, method)
+            # every endpoint call runs inside a span when somebody is listening (event
+            # capture or the chrome trace); otherwise the call pays nothing for it
+            span_id = N.span_enter(f"{self.cls.__name__}.{method}", instance.actor_id) \
+                if _tracing_on() else 0
             try:
                 if explicit:
                     self._run(fn, (self.obj, response, *args), kwargs)
@@ -714,6 +722,9 @@ class _ActorState:
                     response.send(self._run(fn, (self.obj, *args), kwargs))
             except Exception as e:  # noqa: BLE001
                 response.exception(ActorError(e))
+            finally:
+                if span_id:
+                    N.span_exit(span_id)
             N.metrics_counter_add("py_messages_handled", 1)
         finally:
             _tls.ctx = None

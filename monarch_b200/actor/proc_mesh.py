@@ -369,6 +369,10 @@ def _child_env(extra: Optional[Dict[str, str]]) -> Dict[str, str]:
     main_file = getattr(main, "__file__", None)
     if main_file:
         env.setdefault("MB200_MAIN_FILE", os.path.abspath(main_file))
+    # one execution id for the whole job: logs, spans and traces of every proc carry it
+    # (hyperactor_mesh/src/bootstrap.rs MONARCH_CLIENT_TRACE_ID in the reference)
+    env.setdefault("HYPERACTOR_EXECUTION_ID", N.execution_id())
+    env.setdefault("MONARCH_CLIENT_TRACE_ID", N.execution_id())
     return env
 
 

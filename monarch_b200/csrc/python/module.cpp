@@ -308,6 +308,8 @@ PYBIND11_MODULE(_native, m) {
   m.def("telemetry_now_us", &telemetry_now_us);
   m.def("execution_id", [] { return execution_id(); });
   m.def("events_enable", [](bool on) { EventCollector::global().enable(on); });
+  m.def("events_enabled", [] { return EventCollector::global().enabled(); });
+  m.def("trace_enabled", [] { return TraceWriter::global().enabled(); });
   m.def("events_dropped", [] { return EventCollector::global().dropped(); });
   m.def("events_drain", [] {
     py::list out;

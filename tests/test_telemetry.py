@@ -107,3 +107,37 @@ def test_spans_reach_the_chrome_trace():
     ev = json.loads(N.trace_json())
     ev = ev["traceEvents"] if isinstance(ev, dict) else ev
     assert any(e.get("name") == "traced" and e.get("ph") == "X" for e in ev)
+
+
+def test_endpoint_calls_run_in_spans_and_children_share_the_execution_id():
+    import os
+    from monarch_b200.actor import this_host
+
+    class B(Actor):
+        @endpoint
+        def exec_id(self) -> str:
+            return T.get_execution_id()
+
+        @endpoint
+        def work(self) -> int:
+            return T.get_current_span_id()
+
+    with T.SqliteTracing(in_memory=True) as t:
+        pm = local_proc_mesh(gpus=2)
+        b = pm.spawn("b", B)
+        ids = b.work.call().get().values()
+        assert all(i != 0 for i in ids)          # the handler ran inside its endpoint span
+        pm.stop().get()
+        rows = t.query("select name, actor_id from spans where name = 'B.work'")
+        assert len(rows) == 2 and all(".b[" in r[1] for r in rows)
+    # outside a capture no span is opened
+    pm = local_proc_mesh(gpus=1)
+    b = pm.spawn("b", B)
+    assert b.work.call().get().values() == [0]
+    pm.stop().get()
+    # subprocess children inherit the client's execution id
+    pm = this_host().spawn_procs(per_host={"gpus": 1})
+    try:
+        assert pm.spawn("b", B).exec_id.call().get(timeout=60).values() == [T.get_execution_id()]
+    finally:
+        pm.stop().get()
