@@ -59,6 +59,7 @@ struct OpCall {
 struct RecItem {
   std::unique_ptr<OpCall> call;  // null: not an operator call -> Python fallback
   size_t index = 0;
+  std::vector<int64_t> drop;     // refs of the recording that are dead after this item
 };
 
 class WorkerCore {
@@ -119,7 +120,8 @@ class WorkerCore {
   // ---------------------------------------------------------------------- recordings
   // msgs: the recorded worker messages.  ("call", seq, results, mutates, ("op", name), args,
   // kwargs, stream) items become native calls; everything else stays with Python.
-  void define_recording(int64_t rec_id, py::list msgs) {
+  void define_recording(int64_t rec_id, py::list msgs,
+                        const std::unordered_map<int64_t, std::vector<int64_t>>& drop_after) {
     std::vector<RecItem> items;
     size_t idx = 0;
     for (auto h : msgs) {
@@ -138,6 +140,8 @@ class WorkerCore {
           }
         }
       }
+      auto d = drop_after.find((int64_t)it.index);
+      if (d != drop_after.end()) it.drop = d->second;
       items.push_back(std::move(it));
     }
     recordings_[rec_id] = std::move(items);
@@ -160,6 +164,8 @@ class WorkerCore {
       } else {
         fallback(it.index, bind);
       }
+      // temporaries of the recording die after their last use
+      for (int64_t id : it.drop) env_.erase(id);
     }
     return native;
   }
@@ -255,6 +261,26 @@ class WorkerCore {
       if (any_ref) throw std::runtime_error("mixed ref/value list");
     }
     a.kind = Arg::Const;
+    // A Python number in a Tensor slot (`x + 1.0` reaches the dispatcher as
+    // add.Tensor(x, 1.0)): a 0-dim "wrapped number" tensor, which takes part in type
+    // promotion like the scalar it stands for.
+    const bool tensor_slot =
+        type->kind() == c10::TypeKind::TensorType ||
+        (type->kind() == c10::TypeKind::OptionalType &&
+         type->expectRef<c10::OptionalType>().getElementType()->kind() == c10::TypeKind::TensorType);
+    if (tensor_slot && (py::isinstance<py::float_>(h) || py::isinstance<py::int_>(h) ||
+                        py::isinstance<py::bool_>(h))) {
+      at::Tensor t;
+      if (py::isinstance<py::bool_>(h))
+        t = at::scalar_to_tensor(c10::Scalar(h.cast<bool>()));
+      else if (py::isinstance<py::int_>(h))
+        t = at::scalar_to_tensor(c10::Scalar(h.cast<int64_t>()));
+      else
+        t = at::scalar_to_tensor(c10::Scalar(h.cast<double>()));
+      t.unsafeGetTensorImpl()->set_wrapped_number(true);
+      a.constant = c10::IValue(t);
+      return a;
+    }
     a.constant = torch::jit::toIValue(h, type);
     return a;
   }
@@ -398,7 +424,8 @@ PYBIND11_MODULE(_tensor_worker, m) {
       .def("__len__", &WorkerCore::size)
       .def("live_bytes", &WorkerCore::live_bytes)
       .def("call_op", &WorkerCore::call_op)
-      .def("define_recording", &WorkerCore::define_recording)
+      .def("define_recording", &WorkerCore::define_recording, py::arg("rec_id"), py::arg("msgs"),
+           py::arg("drop_after") = std::unordered_map<int64_t, std::vector<int64_t>>{})
       .def("call_recording", &WorkerCore::call_recording)
       .def("has_recording", &WorkerCore::has_recording)
       .def("create_stream", &WorkerCore::create_stream);

@@ -175,7 +175,7 @@ class SimWorker:
                 self._advance(stream, "send_tensor",
                               self.cost.collective(t.numel() * t.element_size(), 2, "p2p"))
 
-    def _m_define_recording(self, rec_id, msgs) -> None:
+    def _m_define_recording(self, rec_id, msgs, temps=()) -> None:
         self.recordings[rec_id] = msgs
 
     def _m_call_recording(self, rec_id, bind) -> None:

@@ -25,6 +25,7 @@ import warnings
 from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
 
 import torch
+from torch._subclasses.fake_tensor import FakeTensor as _FakeTensor
 from torch._subclasses.fake_tensor import FakeTensorMode
 from torch.utils._python_dispatch import TorchDispatchMode
 
@@ -628,6 +629,100 @@ def _mesh_of(tensors: List[Tensor]) -> "DeviceMesh":
     return m
 
 
+# ---- cached shape propagation -------------------------------------------------------------
+# Running an operator on FakeTensors costs 100-300 us in this torch (meta kernels and
+# decompositions written in Python); the answer depends only on the operator and on the
+# metadata of its arguments.  Functional operators (no aliasing or mutation in the schema) are
+# therefore propagated once per distinct signature; later calls rebuild the output fakes from
+# the remembered shapes, strides and dtypes (python/monarch/common/function_caching.py plays
+# this role for remote functions in the reference).
+class _Uncacheable(Exception):
+    pass
+
+
+_PLAIN_ARG_TYPES = (int, float, bool, str, type(None), torch.dtype, torch.device, torch.layout,
+                    torch.memory_format, complex)
+_prop_cache: Dict[tuple, Any] = {}
+_cacheable_op: Dict[Any, bool] = {}
+_PROP_CACHE_MAX = 4096
+
+
+def _op_is_functional(func) -> bool:
+    r = _cacheable_op.get(func)
+    if r is None:
+        sch = func._schema
+        r = not any(a.alias_info is not None for a in sch.arguments) and \
+            not any(x.alias_info is not None for x in sch.returns)
+        _cacheable_op[func] = r
+    return r
+
+
+def _arg_sig(o):
+    tp = type(o)
+    if tp is Tensor:
+        f = o._fake
+        return ("T", tuple(f.shape), f.stride(), f.dtype, f.device, f.requires_grad)
+    if tp in _PLAIN_ARG_TYPES:
+        return (tp, o)
+    if tp is list or tp is tuple:
+        return (tp, tuple(_arg_sig(x) for x in o))
+    if tp is dict:
+        return (tp, tuple((k, _arg_sig(v)) for k, v in o.items()))
+    if tp is torch.Size:
+        return (tp, tuple(o))
+    raise _Uncacheable()
+
+
+def _out_template(o):
+    if isinstance(o, torch.Tensor):
+        return ("T", tuple(o.shape), tuple(o.stride()), o.dtype, o.device, o.requires_grad)
+    if isinstance(o, (list, tuple)):
+        return ("S", type(o), [_out_template(x) for x in o])
+    if type(o) in _PLAIN_ARG_TYPES:
+        return ("V", o)
+    raise _Uncacheable()
+
+
+def _from_template(t):
+    if t[0] == "T":
+        _, shape, stride, dtype, device, req = t
+        meta = torch.empty_strided(shape, stride, dtype=dtype, device="meta")
+        f = _FakeTensor(_fake_mode, meta, device)
+        return f.requires_grad_(True) if req else f
+    if t[0] == "S":
+        return t[1](_from_template(x) for x in t[2])
+    return t[1]
+
+
+def _propagate(func, args, kwargs):
+    """Output fakes of ``func(*args, **kwargs)`` (``Tensor`` arguments stand for their fakes)."""
+    key = None
+    if _op_is_functional(func):
+        try:
+            key = (func, _arg_sig(args), _arg_sig(kwargs) if kwargs else None,
+                   torch.is_grad_enabled())
+            tmpl = _prop_cache.get(key)
+            if tmpl is not None:
+                prev = getattr(_tls, "propagating", False)
+                _tls.propagating = True
+                try:
+                    return _from_template(tmpl)
+                finally:
+                    _tls.propagating = prev
+        except (_Uncacheable, TypeError):     # TypeError: an unhashable argument
+            key = None
+    with _propagation():
+        fake_out = func(*_to_fake(args), **_to_fake(kwargs))
+    if key is not None:
+        try:
+            if len(_prop_cache) >= _PROP_CACHE_MAX:
+                _prop_cache.clear()
+            _prop_cache[key] = _out_template(fake_out)
+        except _Uncacheable:
+            pass
+    return fake_out
+
+
 def _dispatch(func, args, kwargs):
     ts: List[Tensor] = []
     _collect(args, ts)
@@ -640,8 +735,7 @@ def _dispatch(func, args, kwargs):
         mesh = get_active_mesh()
         if mesh is None:
             raise RuntimeError("no active device mesh")
-    with _propagation():
-        fake_out = func(*_to_fake(args), **_to_fake(kwargs))
+    fake_out = _propagate(func, args, kwargs)
     name = f"{func.namespace}.{func._schema.name.split('::')[1]}.{func._overloadname}"
     # in-place / out= ops return their (already remote) argument: alias, do not re-ref
     mutated: List[Tensor] = []

@@ -219,24 +219,22 @@ class _Compiled:
         rec = self._cache.get(key)
         if rec is None:
             return self._trace(key, mesh, client, ins, args, kwargs)
-        rec_id, formals, internal, out_ids, out_meta, out_tree = rec
+        rec_id, formals, out_ids, out_meta, out_tree = rec
         bind = {f: t.ref for f, t in zip(formals, ins)}
+        by_formal = dict(zip(formals, ins))
         stream = get_active_stream()
         outs = []
         for (shape, dtype), oid in zip(out_meta, out_ids):
+            if oid in by_formal:          # the function handed one of its inputs back
+                outs.append(by_formal[oid])
+                continue
             with _propagation():
                 fake = torch.empty(shape, dtype=dtype)
             t = Tensor(fake, mesh, stream)
             bind[oid] = t.ref
             outs.append(t)
-        temps = []
-        for i in internal:
-            if i not in bind:
-                bind[i] = client.new_ref()
-                temps.append(bind[i])
+        # the recording's temporaries live and die on the workers: nothing to bind or delete
         client.send(mesh, ("call_recording", rec_id, bind))
-        for r in temps:
-            client.delete_ref(r)
         it = iter(outs)
         return torch.utils._pytree.tree_map(
             lambda m: next(it) if m == "__tensor__" else m, out_tree)
@@ -271,13 +269,14 @@ class _Compiled:
                     visit(x)
         visit(msgs)
         rec_id = next(self._ids)
-        client.send(mesh, ("define_recording", rec_id, msgs))
+        out_refs = {t.ref for t in outs}
+        temps = sorted(i for i in internal if i not in out_refs)
+        client.send(mesh, ("define_recording", rec_id, msgs, temps))
         client.send(mesh, ("call_recording", rec_id, {}))
         out_tree = torch.utils._pytree.tree_map(
             lambda t: "__tensor__" if isinstance(t, Tensor) else t, out)
-        self._cache[key] = (rec_id, [t.ref for t in ins], sorted(internal),
-                            [t.ref for t in outs], [(tuple(t.shape), t.dtype) for t in outs],
-                            out_tree)
+        self._cache[key] = (rec_id, [t.ref for t in ins], [t.ref for t in outs],
+                            [(tuple(t.shape), t.dtype) for t in outs], out_tree)
         return out
 
 

@@ -485,16 +485,31 @@ class TensorWorker(Actor):
     def _m_send_meta(self, result, shape, dtype) -> None:
         self.env[("send_meta", result.id)] = (tuple(shape), dtype)
 
-    def _m_define_recording(self, rec_id: int, msgs: List[tuple]) -> None:
-        self.recordings[rec_id] = msgs
+    def _m_define_recording(self, rec_id: int, msgs: List[tuple], temps=()) -> None:
+        """``temps``: refs that exist only inside the recording.  Each is dropped right after
+        the last message that mentions it, so a replay reuses memory the way eager
+        execution does instead of holding every intermediate until the end."""
+        last_use: Dict[int, int] = {}
+        temp_set = set(temps)
+        if temp_set:
+            for i, m in enumerate(msgs):
+                def note(r, i=i):
+                    if r.id in temp_set:
+                        last_use[r.id] = i
+                    return r
+                _map_refs(m, note)
+        drop_after: Dict[int, List[int]] = {}
+        for rid, i in last_use.items():
+            drop_after.setdefault(i, []).append(rid)
+        self.recordings[rec_id] = (msgs, drop_after)
         if self.core is not None:
-            self.core.define_recording(rec_id, list(msgs))
+            self.core.define_recording(rec_id, list(msgs), drop_after)
 
     def _m_call_recording(self, rec_id: int, bind: Dict[int, int]) -> None:
         """Replay a recording with formal ref ids rebound to this call's ids.  Operator calls
         are replayed by the native core in one go; the other messages of the recording come
         back through ``fallback`` in their recorded position."""
-        msgs = self.recordings[rec_id]
+        msgs, drop_after = self.recordings[rec_id]
 
         def run_py(index: int, b: Dict[int, int]) -> None:
             m = msgs[index]
@@ -507,6 +522,8 @@ class TensorWorker(Actor):
             return
         for i in range(len(msgs)):
             run_py(i, bind)
+            for rid in drop_after.get(i, ()):
+                self.env.pop(rid, None)
 
     # ----------------------------------------------------------------------- pipes
     def _m_create_pipe(self, pipe_id, fspec, max_messages, args, kwargs, labels, offset, sizes,
