@@ -439,3 +439,62 @@ extern "C" int mb200_wait_flag(const uint32_t* flag, uint32_t value, int limit_m
   wait_flag_kernel<<<1, 32, 0, ST(stream)>>>(flag, value, limit_ms, status);
   return (int)cudaGetLastError();
 }
+
+// ------------------------------------------------------------------ GPU-driven ping-pong --
+// Two GPUs bounce a payload with no host in the loop: the leader stores `n_vec` 16-byte words
+// into the follower's buffer over NVLink and raises the follower's flag; the follower waits for
+// the flag, stores the payload back and raises the leader's flag.  One launch per rank does
+// `iters` round trips.  Every wait is bounded: a peer that never launches costs the waiting
+// side its time limit and an error status, not a hang.  (The reference's counterpart drives
+// a NIC from the GPU and spins without a limit: monarch_rdma/examples/cuda_ping_pong.)
+__global__ void __launch_bounds__(256)
+    pingpong_kernel(uint4* __restrict__ my_buf, uint4* __restrict__ peer_buf, uint32_t* my_flag,
+                    uint32_t* peer_flag, long long n_vec, int iters, uint32_t base, int leader,
+                    int* status, unsigned long long* elapsed_ns) {
+  __shared__ int sh_ok;
+  unsigned long long t0 = 0;
+  if (threadIdx.x == 0) {
+    sh_ok = 1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  }
+  __syncthreads();
+  for (int i = 0; i < iters; ++i) {
+    const uint32_t epoch = base + (uint32_t)i + 1;
+    if (!leader) {
+      // follower: wait for the ball first
+      if (threadIdx.x == 0) sh_ok = flag_wait_ge<true>(my_flag, epoch, status) ? 1 : 0;
+      __syncthreads();
+      if (!sh_ok) return;
+    }
+    // send what is in my buffer to the peer (the follower sends back what it received)
+    for (long long v = threadIdx.x; v < n_vec; v += blockDim.x) peer_buf[v] = my_buf[v];
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) st_release_sys(peer_flag, epoch);
+    if (leader) {
+      if (threadIdx.x == 0) sh_ok = flag_wait_ge<true>(my_flag, epoch, status) ? 1 : 0;
+      __syncthreads();
+      if (!sh_ok) return;
+    }
+  }
+  if (threadIdx.x == 0 && elapsed_ns) {
+    unsigned long long t1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+    *elapsed_ns = t1 - t0;
+  }
+}
+
+// my_buf / peer_buf: nbytes each (multiple of 16), in peer-mapped memory; my_flag / peer_flag:
+// one u32 each on the respective GPU; `base`: flag value before this call (both ranks pass
+// the same).  elapsed_ns (device memory, may be null) receives the leader's or follower's
+// device time for all `iters` trips.
+extern "C" int mb200_pingpong(void* my_buf, void* peer_buf, uint32_t* my_flag, uint32_t* peer_flag,
+                              long long nbytes, int iters, uint32_t base, int leader, int* status,
+                              unsigned long long* elapsed_ns, void* stream) {
+  if (nbytes < 0 || (nbytes & 15) || iters <= 0) return 1001;
+  pingpong_kernel<<<1, 256, 0, ST(stream)>>>(reinterpret_cast<uint4*>(my_buf),
+                                              reinterpret_cast<uint4*>(peer_buf), my_flag,
+                                              peer_flag, nbytes / 16, iters, base, leader, status,
+                                              elapsed_ns);
+  return (int)cudaGetLastError();
+}

@@ -64,6 +64,9 @@ int mb200_sumsq(const void* x, int64_t n, int is_bf16, float* out, void* stream)
 
 // Causal grouped-query attention (flash style, tcgen05). q: [B,S,Hq,hd], k/v: [B,S,Hkv,hd]
 // inside a fused qkv buffer with row stride `ld`; o: [B,S,Hq,hd] dense; lse: [B,Hq,S] fp32.
+int mb200_pingpong(void* my_buf, void* peer_buf, uint32_t* my_flag, uint32_t* peer_flag,
+                   long long nbytes, int iters, uint32_t base, int leader, int* status,
+                   unsigned long long* elapsed_ns, void* stream);
 int mb200_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int S,
                    int Hq, int Hkv, int hd, int ld_qkv, int ld_o, float scale, int* status,
                    void* stream);

@@ -116,6 +116,8 @@ _OPTIONAL: dict[str, list] = {
     "mb200_moe_swiglu_fwd": [_vp, _vp, _vp, _vp, _i, _i, _vp],
     "mb200_moe_swiglu_bwd": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "mb200_moe_combine": [_vp, _i, _i, _i, _vp, _i, _vp, _i, _vp],
+    "mb200_pingpong": [_vp, _vp, _vp, _vp, ctypes.c_longlong, _i, ctypes.c_uint32, _i, _vp, _vp,
+                       _vp],
     "mb200_gather_chunks": [_vp, _vp, ctypes.c_longlong, _i, _i, ctypes.c_longlong,
                             ctypes.c_longlong, ctypes.c_longlong, _vp, ctypes.c_uint32, _vp, _i,
                             ctypes.c_uint32, _i, _vp, _vp],

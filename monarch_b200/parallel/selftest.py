@@ -396,6 +396,41 @@ def main() -> int:
         assert _rel(a_, b_) < 2e-2, f"expert parallel {nm}: fused vs all-to-all {_rel(a_, b_)}"
     results["ep_rel_err"] = {nm: _rel(a_, b_) for nm, a_, b_ in zip(names, got["fused"], got["nccl"])}
 
+    # ------------------------------------------------- GPU-driven ping-pong (ranks 0, 1) ----
+    # No host in the loop: each side's kernel stores into the other's memory over NVLink and
+    # polls its own flag (bounded).  Rank 0 leads; the other ranks sit this one out.
+    from .symm import MAX_RANKS
+    pp_slot = 15
+    pp_rows = []
+    pp_base = 0
+    pp_buf = SymmBuffer(1 << 20, torch.uint8, dev, zero=True)
+    pp_ns = torch.zeros(1, dtype=torch.int64, device=dev)
+    for nbytes, iters in ((16, 200), (4096, 200), (1 << 20, 50)):
+        if rank < 2:
+            peer = 1 - rank
+            pattern = (torch.arange(nbytes, device=dev) % 251).to(torch.uint8)
+            pp_buf.tensor[:nbytes].copy_(pattern if rank == 0 else torch.zeros_like(pattern))
+        torch.cuda.synchronize()
+        dist.barrier()
+        if rank < 2:
+            my_flag = flags.buf.ptrs[rank] + 4 * (pp_slot * MAX_RANKS + peer)
+            peer_flag = flags.buf.ptrs[peer] + 4 * (pp_slot * MAX_RANKS + rank)
+            K.check(lib.mb200_pingpong(pp_buf.ptrs[rank], pp_buf.ptrs[peer], my_flag, peer_flag,
+                                       nbytes, iters, pp_base, 1 if rank == 0 else 0,
+                                       status.data_ptr(), pp_ns.data_ptr(), K.stream_ptr()),
+                    "pingpong")
+        torch.cuda.synchronize()
+        K.check_status()
+        pp_base += iters
+        if rank == 1:
+            assert torch.equal(pp_buf.tensor[:nbytes], pattern), "ping-pong payload mismatch"
+        if rank == 0:
+            assert torch.equal(pp_buf.tensor[:nbytes], pattern)
+            pp_rows.append({"bytes": nbytes, "round_trip_us": pp_ns.item() / iters / 1e3})
+        dist.barrier()
+    if rank == 0:
+        results["gpu_pingpong"] = pp_rows
+
     # ------------------------------------------------------------------ bandwidths ----
     if bench:
         sizes = [1 << 20, 1 << 24, 1 << 27]  # bf16 elements per rank buffer
