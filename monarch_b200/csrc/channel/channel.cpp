@@ -463,21 +463,20 @@ class NetRx : public Rx, public std::enable_shared_from_this<NetRx> {
         }
         if (!ok) break;
       }
-      bool deliver;
       {
+        // The sequence check and the hand-over to the queue are one critical section: after
+        // a reconnect the reader of the old connection may still hold frames it had already
+        // read while the reader of the new connection delivers the resent tail; checked and
+        // queued separately, an older frame could land behind a newer one.
         std::lock_guard<std::mutex> g(mu_);
         uint64_t& next = next_seq_[session];
         if (seq < next) {
-          deliver = false;
           channel_stats().duplicates_dropped++;
         } else {
-          deliver = true;
           next = seq + 1;
+          channel_stats().frames_received++;
+          q_->push(std::move(f));
         }
-      }
-      if (deliver) {
-        channel_stats().frames_received++;
-        q_->push(std::move(f));
       }
       last_seq = seq;
       have_seq = true;
@@ -758,6 +757,9 @@ class NetTx : public Tx {
             while (ack_buf_.size() >= 8) {
               uint64_t acked = get_be64(ack_buf_.data());
               ack_buf_.erase(0, 8);
+              // io_mu_ first: a caller-side send may still be inside sendmsg with pointers
+              // into the item whose acknowledgement has just arrived
+              std::lock_guard<std::mutex> io(io_mu_);
               std::lock_guard<std::mutex> g(mu_);
               while (!unacked_.empty() && unacked_.front().seq <= acked) unacked_.pop_front();
             }

@@ -468,7 +468,8 @@ __global__ void __launch_bounds__(256)
     }
     // send what is in my buffer to the peer (the follower sends back what it received)
     for (long long v = threadIdx.x; v < n_vec; v += blockDim.x) peer_buf[v] = my_buf[v];
-    __threadfence_system();
+    // the CTA barrier orders every thread's payload stores before thread 0's release store
+    // (system scope, cumulative), so one release publishes the whole payload
     __syncthreads();
     if (threadIdx.x == 0) st_release_sys(peer_flag, epoch);
     if (leader) {
