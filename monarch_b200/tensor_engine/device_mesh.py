@@ -264,17 +264,16 @@ class Client:
             yield
         finally:
             batch, self._coalesce = self._coalesce, None
-            # one cast per distinct mesh, preserving order within each
-            by_mesh: Dict[int, Tuple[Any, List[tuple]]] = {}
-            order: List[int] = []
+            # one cast per run of consecutive messages to the same workers: program order is
+            # kept across meshes too (a message to a sub-mesh may read what an earlier
+            # message to the whole mesh wrote, and the other way round)
+            runs: List[Tuple[Any, List[tuple]]] = []
             for mesh, msg in batch:
-                k = id(mesh._workers)
-                if k not in by_mesh:
-                    by_mesh[k] = (mesh, [])
-                    order.append(k)
-                by_mesh[k][1].append(msg)
-            for i, k in enumerate(order):
-                mesh, msgs = by_mesh[k]
+                if runs and runs[-1][0]._workers is mesh._workers:
+                    runs[-1][1].append(msg)
+                else:
+                    runs.append((mesh, [msg]))
+            for i, (mesh, msgs) in enumerate(runs):
                 if i == 0:
                     self._send_deletes()
                 mesh._workers.run.broadcast(msgs)

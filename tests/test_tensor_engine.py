@@ -309,3 +309,20 @@ def test_remote_process_group_in_a_remote_function(dm):
         assert te.inspect(y, host=1, gpu=0).tolist() == [14.0] * 3
         with pytest.raises(KeyError):
             dm.process_group("nope")
+
+
+def test_coalescing_keeps_program_order_across_meshes(dm):
+    """A block that alternates between the whole mesh and a sub-mesh is sent as runs of
+    consecutive messages, so a sub-mesh read sits between the two whole-mesh writes it was
+    written between."""
+    sub = dm.slice(host=0)
+    with dm.activate():
+        a = torch.ones(3)
+        with te.coalescing():
+            a.add_(10)                      # whole mesh
+            b = a.slice_mesh(host=0)        # same data, seen from the sub-mesh
+            with sub.activate():
+                c = b + 0                   # sub-mesh read: must see 11
+            a.add_(10)                      # whole mesh again
+        assert te.inspect(c, gpu=1).tolist() == [11.0] * 3
+        assert te.inspect(a, host=0, gpu=0).tolist() == [21.0] * 3
