@@ -340,6 +340,23 @@ def _tracing_on() -> bool:
 
 
 _signatures: Dict[Any, inspect.Signature] = {}
+_bound_ok: set = set()
+_cast_points: Dict[Tuple[str, int], "Point"] = {}
+
+
+def _cast_point(shape_hdr: Optional[str], cast_rank: int) -> "Point":
+    """The ``Point`` a cast message is addressed to, from its headers (cached: the same few
+    (shape, rank) pairs recur for the life of a mesh)."""
+    if not shape_hdr:
+        return Point(0, Extent([], []))
+    key = (shape_hdr, cast_rank)
+    p = _cast_points.get(key)
+    if p is None:
+        labels, sizes = json.loads(shape_hdr)
+        p = Point(cast_rank, Extent(labels, sizes))
+        if len(_cast_points) < 65536:
+            _cast_points[key] = p
+    return p
 
 
 def _signature_of(fn) -> inspect.Signature:
@@ -394,12 +411,19 @@ class Endpoint(Generic[R]):
     def _check_signature(self, args, kwargs) -> None:
         if self._fn is None:
             return
+        # the outcome depends only on how many positional arguments and which keywords are
+        # passed: remember the shapes of calls that bound successfully
+        shape = (self._fn, self._explicit, len(args), tuple(kwargs) if kwargs else ())
+        if shape in _bound_ok:
+            return
         sig = _signature_of(self._fn)
         extra = [None] * (2 if self._explicit else 1)  # self (+ port)
         try:
             sig.bind(*extra, *args, **kwargs)
         except TypeError as e:
             raise TypeError(f"{self._mesh._class_name}.{self._name}: {e}") from None
+        if len(_bound_ok) < 4096:
+            _bound_ok.add(shape)
 
     def _send(self, args, kwargs, port: Optional[Port], ranks: Optional[List[int]] = None) -> None:
         self._check_signature(args, kwargs)
@@ -687,12 +711,7 @@ class _ActorState:
         msg = unflatten(env.data, env.parts, getattr(self, "_extra_load", None))
         kind = msg[0]
         cast_rank = int(env.headers.get("cast_rank", "0"))
-        shape_hdr = env.headers.get("cast_shape")
-        if shape_hdr:
-            labels, sizes = json.loads(shape_hdr)
-            point = Point(cast_rank, Extent(labels, sizes))
-        else:
-            point = Point(0, Extent([], []))
+        point = _cast_point(env.headers.get("cast_shape"), cast_rank)
         try:
             self._ensure(instance)
         except BaseException:
