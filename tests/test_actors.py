@@ -290,3 +290,41 @@ def test_allocators_and_from_alloc():
     assert a.params == {"hosts": ["127.0.0.1:1", "127.0.0.1:2"], "procs_per_host": 4}
     with pytest.raises(ValueError):
         ra.allocate(AllocSpec(hosts=3, gpus=1))
+
+
+def test_many_client_threads_call_concurrently():
+    """Calls issued from several threads of the client at once (they share the channel to
+    every proc: the caller-side send path and the writer thread interleave) all get their
+    own answers back."""
+    import threading
+
+    class Adder(Actor):
+        @endpoint
+        def add(self, a: int, b: int) -> int:
+            return a + b + current_rank().rank
+
+    pm = this_host().spawn_procs(per_host={"gpus": 4})
+    try:
+        m = pm.spawn("adders", Adder)
+        m.add.call(0, 0).get(timeout=60)
+        errors = []
+
+        def worker(t):
+            try:
+                for i in range(150):
+                    got = m.add.call(t * 1000, i).get(timeout=60).values()
+                    assert got == [t * 1000 + i + r for r in range(4)], got
+                    one = m.slice(gpus=i % 4).add.call_one(t, i).get(timeout=60)
+                    assert one == t + i, one    # a slice of one: the rank inside the cast is 0
+            except Exception as e:  # noqa: BLE001 - reported by the main thread
+                errors.append(repr(e))
+
+        threads = [threading.Thread(target=worker, args=(t,)) for t in range(6)]
+        for th in threads:
+            th.start()
+        for th in threads:
+            th.join(120)
+        assert not errors, errors[:3]
+        assert not any(th.is_alive() for th in threads)
+    finally:
+        pm.stop().get()
