@@ -174,16 +174,25 @@ class ReducePort(Port):
     by the C++ reducer of the receiving mailbox (no unpickling on the reduce path);
     exceptions go to a separate ordinary port."""
 
-    def __init__(self, port_id: str, error_port_id: str, rank: Optional[int] = None):
+    def __init__(self, port_id: str, error_port_id: str, rank: Optional[int] = None,
+                 via: Optional[str] = None, key: Optional[str] = None):
         super().__init__(port_id, rank)
         self._error_port_id = error_port_id
+        # when the cast asked for a reduction along its tree: the comm actor of this proc,
+        # which folds the subtree's updates before passing one message up
+        self._via, self._key = via, key
 
     def send(self, obj) -> None:
         import numpy as np
         arr = obj.detach().cpu().contiguous().numpy() if hasattr(obj, "detach") else \
             np.ascontiguousarray(obj)
-        context().actor_instance._native.send(self._port_id, arr.tobytes(),
-                                              {"kind": "reduce", "no_return": "1"}, [])
+        inst = context().actor_instance._native
+        if self._via is not None:
+            inst.send(self._via, arr.tobytes(),
+                      {"kind": "reduce_part", "no_return": "1", "reduce_key": self._key,
+                       "reduce_port": self._port_id, "n": "1"}, [])
+            return
+        inst.send(self._port_id, arr.tobytes(), {"kind": "reduce", "no_return": "1"}, [])
 
     def exception(self, obj: BaseException) -> None:
         if not isinstance(obj, ActorError):
@@ -425,9 +434,10 @@ class Endpoint(Generic[R]):
         if len(_bound_ok) < 4096:
             _bound_ok.add(shape)
 
-    def _send(self, args, kwargs, port: Optional[Port], ranks: Optional[List[int]] = None) -> None:
+    def _send(self, args, kwargs, port: Optional[Port], ranks: Optional[List[int]] = None,
+              headers: Optional[Dict[str, str]] = None) -> None:
         self._check_signature(args, kwargs)
-        self._mesh._cast(("call", self._name, args, kwargs, port), ranks)
+        self._mesh._cast(("call", self._name, args, kwargs, port), ranks, headers)
 
     def _open(self, once: bool = False) -> Tuple[Port, PortReceiver]:
         return Channel.open(once, _health=self._mesh._health, _actor_name=self._mesh._name)
@@ -488,7 +498,10 @@ class Endpoint(Generic[R]):
         port_id, acc = inst.open_accum_port(reducer, b"")
         err_port, err_rx = self._open()
         n = len(self._mesh)
-        self._send(args, kwargs, ReducePort(port_id, err_port._port_id))
+        # the updates are folded along the cast tree: every comm actor passes one partial
+        # result up, so the caller receives one message per child of the root, not one per actor
+        self._send(args, kwargs, ReducePort(port_id, err_port._port_id),
+                   headers={"reduce_tree": reducer, "reduce_port": port_id})
         mesh = self._mesh
 
         def wait(timeout: Optional[float]):
@@ -643,7 +656,8 @@ class ActorMesh(MeshTrait, Generic[T]):
             if err is not None:
                 raise SupervisionError(f"actor mesh '{self._name}' is unhealthy: {err}")
 
-    def _cast(self, message: Tuple, ranks: Optional[List[int]] = None) -> None:
+    def _cast(self, message: Tuple, ranks: Optional[List[int]] = None,
+              extra_headers: Optional[Dict[str, str]] = None) -> None:
         body, parts = flatten(message)
         sl = self._shape_.ndslice
         root = self._root_slice
@@ -655,6 +669,8 @@ class ActorMesh(MeshTrait, Generic[T]):
         if headers is None:
             headers = self._cast_headers = {
                 "cast_shape": json.dumps([self._shape_.labels, list(sl.sizes)])}
+        if extra_headers:
+            headers = {**headers, **extra_headers}
         inst = context().actor_instance._native
         N.cast(inst, self._world, self._name, root, sel, body, headers, parts, sl)
 
@@ -723,7 +739,9 @@ class _ActorState:
                 return
             _, method, args, kwargs, port = msg
             if isinstance(port, ReducePort):
-                port = ReducePort(port._port_id, port._error_port_id, cast_rank)
+                port = ReducePort(port._port_id, port._error_port_id, cast_rank,
+                                  via=env.headers.get("reduce_via"),
+                                  key=env.headers.get("reduce_key"))
             elif port is not None:
                 port = Port(port._port_id, cast_rank)
             response = port if port is not None else DroppingPort()

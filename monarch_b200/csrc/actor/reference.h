@@ -180,5 +180,13 @@ constexpr const char* kHdrCastShape = "cast_shape";
 constexpr const char* kHdrCastSender = "cast_originating_sender";
 constexpr const char* kHdrCastMesh = "cast_actor_mesh_id";
 constexpr const char* kHdrKind = "kind";
+// Tree reduction of replies to a cast (the reference's split ports with a reducer): the cast
+// names a built-in reducer and the final accumulating port; every comm actor folds the
+// partial results of its subtree and passes one message up.
+constexpr const char* kHdrReduceTree = "reduce_tree";    // reducer name, on the cast
+constexpr const char* kHdrReducePort = "reduce_port";    // final port, on the cast
+constexpr const char* kHdrReduceVia = "reduce_via";      // local comm actor, on the delivery
+constexpr const char* kHdrReduceKey = "reduce_key";      // identifies the cast
+constexpr const char* kHdrReduceCount = "n";             // contributions folded into a part
 
 }  // namespace mb

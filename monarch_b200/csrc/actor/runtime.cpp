@@ -160,11 +160,21 @@ ReduceFn builtin_reducer(const std::string& name) {
 }
 
 void AccumSink::deliver(Envelope&& env) {
+  // an update folded along a reduction tree stands for several senders
+  uint64_t n = 1;
+  if (auto it = env.headers.find(kHdrReduceCount); it != env.headers.end()) {
+    try {
+      n = std::stoull(it->second);
+    } catch (const std::exception&) {
+      n = 1;
+    }
+  }
   {
     std::lock_guard<std::mutex> g(mu_);
     state_ = fn_(state_, env.data);
-    ++count_;
+    count_ += n;
   }
+  Metrics::global().counter_add("accum.messages");
   cv_.notify_all();
 }
 std::string AccumSink::state() const {

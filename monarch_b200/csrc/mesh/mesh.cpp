@@ -695,16 +695,70 @@ std::string encode_cast_root(CastRequest& c, std::vector<std::string>& parts) {
   return encode_cast(w);
 }
 
+namespace {
+// Partial results of the casts whose replies are reduced along the tree.
+struct PendingReduce {
+  PortId parent;            // where the folded result of this subtree goes
+  bool parent_is_comm = false;
+  std::string final_port;   // the caller's accumulating port
+  ReduceFn fn;
+  size_t expected = 0;      // local actor (if any) + one part per child hop
+  size_t received = 0;
+  uint64_t contributions = 0;
+  std::string state;
+  double t_us = 0;
+};
+struct ReduceTable {
+  std::map<std::string, PendingReduce> pending;
+};
+}  // namespace
+
 ActorHooks make_comm_actor(const std::shared_ptr<Proc>& proc_sp) {
   std::weak_ptr<Proc> wproc = proc_sp;
+  auto reduces = std::make_shared<ReduceTable>();  // touched only by this actor's handler
   ActorHooks h;
   // a relay without state: routed on the delivering thread (forwards go down the tree of
   // the mesh's spawn-time slice, so nested deliveries cannot form a cycle)
   h.inline_messages = Config::global().get_bool("COMM_ACTOR_INLINE");
-  h.on_message = [wproc](Instance& self, Envelope& env) {
+  h.on_message = [wproc, reduces](Instance& self, Envelope& env) {
     auto proc = wproc.lock();
     if (!proc) return;
     double t0 = now_us();
+    auto kind_it = env.headers.find(kHdrKind);
+    if (kind_it != env.headers.end() && kind_it->second == "reduce_part") {
+      // a partial result from the local actor or from a child hop
+      const std::string key = env.headers[kHdrReduceKey];
+      uint64_t n = 1;
+      if (auto it = env.headers.find(kHdrReduceCount); it != env.headers.end())
+        n = std::stoull(it->second);
+      auto pit = reduces->pending.find(key);
+      if (pit == reduces->pending.end()) {
+        // no record (expired, or the cast never passed here): hand it to the caller as is
+        Envelope e;
+        e.sender = self.id();
+        e.dest = PortId::parse(env.headers[kHdrReducePort]);
+        e.headers = {{kHdrKind, "reduce"}, {"no_return", "1"}, {kHdrReduceCount, std::to_string(n)}};
+        e.data = std::move(env.data);
+        proc->post(std::move(e));
+        return;
+      }
+      PendingReduce& pr = pit->second;
+      pr.state = pr.fn(pr.state, env.data);
+      pr.contributions += n;
+      if (++pr.received < pr.expected) return;
+      Envelope e;
+      e.sender = self.id();
+      e.dest = pr.parent;
+      e.headers = {{kHdrKind, pr.parent_is_comm ? "reduce_part" : "reduce"},
+                   {"no_return", "1"},
+                   {kHdrReduceKey, key},
+                   {kHdrReducePort, pr.final_port},
+                   {kHdrReduceCount, std::to_string(pr.contributions)}};
+      e.data = std::move(pr.state);
+      reduces->pending.erase(pit);
+      proc->post(std::move(e));
+      return;
+    }
     CastWire c = decode_cast(env.data);
     const size_t my_rank = (size_t)proc->id().rank;
     Resolved res = resolve_routing(my_rank, c.slice, std::move(c.frames), /*seed=*/4 + c.seq);
@@ -712,6 +766,24 @@ ActorHooks make_comm_actor(const std::shared_ptr<Proc>& proc_sp) {
     // (with a large body among them) are copied for every consumer but the last, which
     // takes them over.
     size_t consumers = res.next.size() + (res.deliver_here ? 1 : 0);
+    std::string reduce_key;
+    if (auto rt = c.headers.find(kHdrReduceTree); rt != c.headers.end() && consumers > 0) {
+      reduce_key = c.sender.to_string() + "/" + c.mesh_id + "/" + std::to_string(c.seq);
+      PendingReduce pr;
+      pr.fn = builtin_reducer(rt->second);
+      pr.final_port = c.headers[kHdrReducePort];
+      pr.expected = consumers;
+      pr.t_us = t0;
+      // the previous hop is a comm actor unless this is the root of the tree
+      pr.parent_is_comm = env.sender.name == "comm" && env.sender.proc.world == proc->id().world;
+      pr.parent = pr.parent_is_comm ? PortId{env.sender, kPortMessage}
+                                    : PortId::parse(pr.final_port);
+      if (reduces->pending.size() > 256) {  // forget what was abandoned long ago
+        for (auto it = reduces->pending.begin(); it != reduces->pending.end();)
+          it = (t0 - it->second.t_us > 600e6) ? reduces->pending.erase(it) : std::next(it);
+      }
+      reduces->pending[reduce_key] = std::move(pr);
+    }
     for (auto& kv : res.next) {
       CastWire fwd;
       fwd.mesh_id = c.mesh_id;
@@ -747,6 +819,10 @@ ActorHooks make_comm_actor(const std::shared_ptr<Proc>& proc_sp) {
       e.headers[kHdrCastRank] = std::to_string(cast_rank);
       e.headers[kHdrCastSender] = c.sender.to_string();
       e.headers[kHdrCastMesh] = c.mesh_id;
+      if (!reduce_key.empty()) {
+        e.headers[kHdrReduceKey] = reduce_key;
+        e.headers[kHdrReduceVia] = PortId{self.id(), kPortMessage}.to_string();
+      }
       e.parts = std::move(env.parts);
       if (c.body_in_parts && !e.parts.empty()) {
         e.data = std::move(e.parts.back());
