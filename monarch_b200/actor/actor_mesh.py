@@ -13,11 +13,14 @@ Replies go straight to the caller's port.
 from __future__ import annotations
 
 import asyncio
+import collections
 import contextvars
 import functools
 import inspect
 import json
+import os
 import random
+import struct
 import threading
 import time
 import traceback
@@ -148,14 +151,24 @@ _KIND_EXCEPTION = "exception"
 class Port(Generic[R]):
     """Send side of a port; picklable and usable from any actor."""
 
-    def __init__(self, port_id: str, rank: Optional[int] = None):
+    def __init__(self, port_id: str, rank: Optional[int] = None, via: Optional[str] = None,
+                 key: Optional[str] = None):
         self._port_id = port_id
         self._rank = rank
+        # set on the response port of a cast whose replies are gathered along its tree: the
+        # reply goes to the comm actor of this proc, which hands one batch per subtree up
+        self._via, self._key = via, key
 
     def _post(self, kind: str, obj: Any) -> None:
         body, parts = flatten((kind, self._rank, obj))
-        context().actor_instance._native.send(self._port_id, body,
-                                              {"kind": kind, "no_return": "1"}, parts)
+        inst = context().actor_instance._native
+        if self._via is not None:
+            via, self._via = self._via, None     # exactly one reply travels by the tree
+            inst.send(via, body, {"kind": "reduce_part", "no_return": "1", "gather": "1",
+                                  "gather_item": "1", "reduce_key": self._key,
+                                  "reduce_port": self._port_id, "n": "1"}, parts)
+            return
+        inst.send(self._port_id, body, {"kind": kind, "no_return": "1"}, parts)
 
     def send(self, obj: R) -> None:
         self._post(_KIND_RESULT, obj)
@@ -247,6 +260,22 @@ def _recv_checked(receiver, health: Optional[_Health], actor_name: str,
             raise TimeoutError("timed out waiting for a reply")
 
 
+def _unpack_batch(data: bytes, parts: List[bytes]) -> "collections.deque":
+    """Replies gathered along a cast tree arrive as one envelope: ``data`` is a sequence of
+    records (u32 part count, u64 body length, body), ``parts`` the replies' parts in order."""
+    out: "collections.deque" = collections.deque()
+    mv = memoryview(data)
+    pos, p = 0, 0
+    n = len(mv)
+    while pos < n:
+        n_parts, body_len = struct.unpack_from("<IQ", mv, pos)
+        pos += 12
+        out.append((bytes(mv[pos:pos + body_len]), parts[p:p + n_parts]))
+        pos += body_len
+        p += n_parts
+    return out
+
+
 class PortReceiver(Generic[R]):
     def __init__(self, native_receiver, port_id: str, instance, health: Optional[_Health] = None,
                  actor_name: str = ""):
@@ -257,9 +286,18 @@ class PortReceiver(Generic[R]):
         self._actor_name = actor_name
 
     def _next(self, timeout: Optional[float]) -> Tuple[Optional[int], Any]:
-        deadline = None if timeout is None else time.monotonic() + timeout
-        env = _recv_checked(self._rx, self._health, self._actor_name, deadline)
-        kind, rank, obj = unflatten(env.data, env.parts)
+        batch = self.__dict__.get("_batch")
+        if not batch:
+            deadline = None if timeout is None else time.monotonic() + timeout
+            env = _recv_checked(self._rx, self._health, self._actor_name, deadline)
+            if env.headers.get("kind") != "batch":
+                kind, rank, obj = unflatten(env.data, env.parts)
+                if kind == _KIND_EXCEPTION:
+                    raise obj
+                return rank, obj
+            batch = self._batch = _unpack_batch(env.data, env.parts)
+        data, parts = batch.popleft()
+        kind, rank, obj = unflatten(data, parts)
         if kind == _KIND_EXCEPTION:
             raise obj
         return rank, obj
@@ -348,6 +386,11 @@ def _tracing_on() -> bool:
     return N.events_enabled() or N.trace_enabled()
 
 
+# Gathering replies along the tree trades one extra (in-process) hop per level for far fewer
+# messages at the caller.  Measured on one 8-core box it loses up to 16 procs (call p50
+# 1.2 ms against 0.88 ms), so it only switches on for meshes large enough that the caller's
+# per-reply cost dominates.
+_GATHER_MIN = int(os.environ.get("MB200_GATHER_MIN", "512"))
 _signatures: Dict[Any, inspect.Signature] = {}
 _bound_ok: set = set()
 _cast_points: Dict[Tuple[str, int], "Point"] = {}
@@ -447,7 +490,7 @@ class Endpoint(Generic[R]):
         self._mesh._raise_if_unhealthy()
         port, rx = self._open()
         n = len(self._mesh)
-        self._send(args, kwargs, port)
+        self._send(args, kwargs, port, headers=self._gather_headers(port, n))
         shape = shape_normalised(self._mesh._shape)
 
         def wait(timeout: Optional[float]) -> ValueMesh[R]:
@@ -463,6 +506,14 @@ class Endpoint(Generic[R]):
             return ValueMesh(shape, out)
 
         return Future(wait)
+
+    def _gather_headers(self, port: Port, n: int) -> Optional[Dict[str, str]]:
+        """Replies of a cast to more than a few actors come back gathered along the cast
+        tree: one batch per child of the root instead of one message per actor.  Endpoints
+        with an explicit response port answer as often as they like and are left alone."""
+        if n <= _GATHER_MIN or self._explicit:
+            return None
+        return {"reduce_tree": "gather", "reduce_port": port._port_id}
 
     def call_one(self, *args, **kwargs) -> Future[R]:
         if len(self._mesh) != 1:
@@ -742,11 +793,12 @@ class _ActorState:
                 port = ReducePort(port._port_id, port._error_port_id, cast_rank,
                                   via=env.headers.get("reduce_via"),
                                   key=env.headers.get("reduce_key"))
-            elif port is not None:
-                port = Port(port._port_id, cast_rank)
-            response = port if port is not None else DroppingPort()
             prop = getattr(self.cls, method, None)
             explicit = isinstance(prop, EndpointProperty) and prop._explicit_response_port
+            if port is not None and not isinstance(port, ReducePort):
+                via = None if explicit else env.headers.get("reduce_via")
+                port = Port(port._port_id, cast_rank, via=via, key=env.headers.get("reduce_key"))
+            response = port if port is not None else DroppingPort()
             fn = prop._fn if isinstance(prop, EndpointProperty) else getattr(self.cls, method)
             # every endpoint call runs inside a span when somebody is listening (event
             # capture or the chrome trace); otherwise the call pays nothing for it

@@ -706,8 +706,15 @@ struct PendingReduce {
   size_t received = 0;
   uint64_t contributions = 0;
   std::string state;
+  // "gather": replies are not folded but collected -- `state` holds one record per reply
+  // (u32 part count, u64 body length, body) and `parts` every reply's parts in order
+  bool gather = false;
+  std::vector<std::string> parts;
   double t_us = 0;
 };
+
+void append_u32(std::string& s, uint32_t v) { s.append(reinterpret_cast<const char*>(&v), 4); }
+void append_u64(std::string& s, uint64_t v) { s.append(reinterpret_cast<const char*>(&v), 8); }
 struct ReduceTable {
   std::map<std::string, PendingReduce> pending;
 };
@@ -737,24 +744,41 @@ ActorHooks make_comm_actor(const std::shared_ptr<Proc>& proc_sp) {
         Envelope e;
         e.sender = self.id();
         e.dest = PortId::parse(env.headers[kHdrReducePort]);
-        e.headers = {{kHdrKind, "reduce"}, {"no_return", "1"}, {kHdrReduceCount, std::to_string(n)}};
+        const bool item = env.headers.count("gather_item") != 0;
+        e.headers = {{kHdrKind, item ? "reply" : (env.headers.count("gather") ? "batch" : "reduce")},
+                     {"no_return", "1"},
+                     {kHdrReduceCount, std::to_string(n)}};
         e.data = std::move(env.data);
+        e.parts = std::move(env.parts);
         proc->post(std::move(e));
         return;
       }
       PendingReduce& pr = pit->second;
-      pr.state = pr.fn(pr.state, env.data);
+      if (pr.gather) {
+        if (env.headers.count("gather_item")) {  // one reply of the local actor: make a record
+          append_u32(pr.state, (uint32_t)env.parts.size());
+          append_u64(pr.state, (uint64_t)env.data.size());
+          pr.state += env.data;
+        } else {                                 // records collected by a child hop
+          pr.state += env.data;
+        }
+        for (auto& p : env.parts) pr.parts.push_back(std::move(p));
+      } else {
+        pr.state = pr.fn(pr.state, env.data);
+      }
       pr.contributions += n;
       if (++pr.received < pr.expected) return;
       Envelope e;
       e.sender = self.id();
       e.dest = pr.parent;
-      e.headers = {{kHdrKind, pr.parent_is_comm ? "reduce_part" : "reduce"},
+      e.headers = {{kHdrKind, pr.parent_is_comm ? "reduce_part" : (pr.gather ? "batch" : "reduce")},
                    {"no_return", "1"},
                    {kHdrReduceKey, key},
                    {kHdrReducePort, pr.final_port},
                    {kHdrReduceCount, std::to_string(pr.contributions)}};
+      if (pr.gather) e.headers["gather"] = "1";
       e.data = std::move(pr.state);
+      e.parts = std::move(pr.parts);
       reduces->pending.erase(pit);
       proc->post(std::move(e));
       return;
@@ -770,7 +794,8 @@ ActorHooks make_comm_actor(const std::shared_ptr<Proc>& proc_sp) {
     if (auto rt = c.headers.find(kHdrReduceTree); rt != c.headers.end() && consumers > 0) {
       reduce_key = c.sender.to_string() + "/" + c.mesh_id + "/" + std::to_string(c.seq);
       PendingReduce pr;
-      pr.fn = builtin_reducer(rt->second);
+      pr.gather = rt->second == "gather";
+      if (!pr.gather) pr.fn = builtin_reducer(rt->second);
       pr.final_port = c.headers[kHdrReducePort];
       pr.expected = consumers;
       pr.t_us = t0;

@@ -328,3 +328,44 @@ def test_many_client_threads_call_concurrently():
         assert not any(th.is_alive() for th in threads)
     finally:
         pm.stop().get()
+
+
+def test_replies_gathered_along_the_cast_tree(monkeypatch):
+    """Forced on for a small mesh: results, exceptions and tensor payloads come back through
+    the comm actors in batches and look exactly like direct replies."""
+    import torch
+    from monarch_b200.actor import actor_mesh as am
+
+    class G(Actor):
+        @endpoint
+        def val(self, k: int):
+            r = current_rank().rank
+            return {"r": r, "t": torch.full((2000,), float(r + k))}    # 8 KB: travels as a part
+
+        @endpoint
+        def flaky(self) -> int:
+            if current_rank().rank == 5:
+                raise ValueError("rank five says no")
+            return 1
+
+        @endpoint(explicit_response_port=True)
+        def twice(self, port, x):
+            port.send(x)           # explicit ports stay direct: any number of sends is fine
+
+    monkeypatch.setattr(am, "_GATHER_MIN", 2)
+    pm = local_proc_mesh(gpus=20)
+    try:
+        g = pm.spawn("g", G)
+        out = g.val.call(3).get(timeout=60)
+        vals = out.values()
+        assert [v["r"] for v in vals] == list(range(20))
+        assert all(v["t"].shape == (2000,) and v["t"][0].item() == v["r"] + 3 for v in vals)
+        # a slice: gathered too, ranks renumbered inside the cast
+        sub = g.slice(gpus=slice(4, 12)).val.call(0).get(timeout=60).values()
+        assert [v["r"] for v in sub] == list(range(8))
+        with pytest.raises(ActorError, match="rank five says no"):
+            g.flaky.call().get(timeout=60)
+        assert g.twice.call(7).get(timeout=60).values() == [7] * 20
+        assert g.val.call(1).get(timeout=60).item(gpus=19)["r"] == 19   # still healthy
+    finally:
+        pm.stop().get()
