@@ -58,3 +58,11 @@ def test_getting_started_tour():
     out = _load("getting_started").run()
     assert out["values"] == [2, 2, 1, 1] and out["registered"] == 2
     assert out["supervision_event"] == "actor_failed" and out["caller_error"]
+
+
+def test_fsdp_training_driven_over_an_actor_mesh():
+    out = _load("fsdp_on_mesh").run(model="tiny", gpus=2, seq=32, steps=4, use_cuda=False)
+    assert len(out["losses_first"]) == 2
+    first = sum(out["losses_first"]) / 2
+    last = sum(out["losses_last"]) / 2
+    assert last < first, out          # the sharded optimizer step learns
