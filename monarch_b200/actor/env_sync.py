@@ -21,12 +21,14 @@ destination prefix no longer than the source one (the conda-pack rule).
 from __future__ import annotations
 
 import hashlib
+import itertools
 import os
 import stat
 from typing import Any, Callable, Dict, List, Optional, Tuple
 
 from .actor_mesh import Actor, endpoint
 
+_ids = itertools.count()
 _SKIP = {"__pycache__", ".git", "pkgs"}
 # kept by the receiver in its prefix: files whose content was rewritten have another size
 # than their source; the index remembers the source size so that the next comparison is
@@ -397,7 +399,3 @@ def sync_env(proc_mesh, src_prefix: Optional[str] = None, dst_prefix: Optional[s
         out[rank] = final.get("stats", {})
     return out
 
-
-import itertools as _it  # noqa: E402
-
-_ids = _it.count()
