@@ -294,6 +294,7 @@ def mock_mesh(hosts: int = 1, gpus: int = 1, cost: Optional[CostModel] = None,
     client._lock = threading.RLock()
     client._pending_deletes = []
     client._coalesce = None
+    client._init_batching(1)     # simulated workers answer synchronously: nothing to batch
     client._recording = None
     client._pg_init = True      # there are no process groups to create
     client._comms = set()

@@ -149,6 +149,7 @@ class Client:
         self._lock = threading.RLock()
         self._pending_deletes: List[int] = []
         self._coalesce: Optional[List[Tuple[Any, tuple]]] = None
+        self._init_batching(int(os.environ.get("MB200_EAGER_BATCH", "16")))
         self._recording: Optional[List[tuple]] = None
         self._pg_init = False
         self._comms: set = set()
@@ -158,6 +159,15 @@ class Client:
         workers.configure.call(port).get(timeout=60)
         self._closed = False
         self._init_watchdog(float(os.environ.get("MB200_OPERATION_TIMEOUT", "120")))
+
+    def _init_batching(self, eager_batch: int) -> None:
+        """``eager_batch``: how many eager commands may wait for one cast (1 sends each on
+        its own)."""
+        self.eager_batch = eager_batch
+        self._pending: List[Tuple[Any, tuple]] = []
+        self._plock = threading.RLock()
+        self._flusher: Optional[threading.Thread] = None
+        self._flush_event = threading.Event()
 
     def _init_watchdog(self, operation_timeout: float) -> None:
         """Progress watchdog (controller/src/lib.rs:263-336 CheckWorkerProgress): a ping
@@ -202,9 +212,65 @@ class Client:
         if self._coalesce is not None:
             self._coalesce.append((mesh, msg))
             return
-        self._watch()
+        if self.eager_batch <= 1:
+            self._watch()
+            self._send_deletes()
+            mesh._workers.run.broadcast([msg])
+            return
+        # eager commands are handed to the workers a few at a time: every cast costs the
+        # controller a pickle and a trip through the native runtime, and the workers execute
+        # asynchronously anyway.  Whatever needs an answer flushes first; a background thread
+        # flushes what is left within a millisecond.
+        with self._plock:
+            self._pending.append((mesh, msg))
+            if len(self._pending) >= self.eager_batch:
+                self._flush_locked()
+            else:
+                self._kick_flusher()
+
+    def flush(self) -> None:
+        """Hand every buffered command to the workers now."""
+        with self._plock:
+            self._flush_locked()
+
+    def _flush_locked(self) -> None:
+        if not self._pending:
+            return
+        batch, self._pending = self._pending, []
+        self._send_runs(batch)
+
+    def _send_runs(self, batch: List[Tuple[Any, tuple]]) -> None:
+        """One cast per run of consecutive messages to the same workers: program order is
+        kept across meshes too (a message to a sub-mesh may read what an earlier message to
+        the whole mesh wrote, and the other way round)."""
+        runs: List[Tuple[Any, List[tuple]]] = []
+        for mesh, msg in batch:
+            if runs and runs[-1][0]._workers is mesh._workers:
+                runs[-1][1].append(msg)
+            else:
+                runs.append((mesh, [msg]))
+        for mesh, msgs in runs:
+            mesh._workers.run.broadcast(msgs)
+        # refs dropped by the controller go last: a buffered command may still name them
+        # (a ref that is already dropped cannot appear in any later command)
         self._send_deletes()
-        mesh._workers.run.broadcast([msg])
+
+    def _kick_flusher(self) -> None:
+        if self._flusher is None:
+            self._flusher = threading.Thread(target=self._flusher_loop, daemon=True,
+                                             name="tensor-engine-flush")
+            self._flusher.start()
+        self._flush_event.set()
+
+    def _flusher_loop(self) -> None:
+        while not self._closed:
+            self._flush_event.wait()
+            self._flush_event.clear()
+            time.sleep(0.001)           # let a burst of commands accumulate
+            try:
+                self.flush()
+            except Exception as e:  # noqa: BLE001 - surfaces at the caller's next command
+                self._failed = e
 
     def _watch(self) -> None:
         """Progress watchdog step; called from the command path and from waits, so it needs
@@ -242,6 +308,7 @@ class Client:
                     self._failed = WorkerTimeoutError(msg, missing)
                     raise self._failed
         if self._ping is None and now - self._last_ping >= self.progress_interval:
+            self.flush()     # the ping stands behind everything issued so far
             ep = self.root_mesh._workers.progress
             port, rx = ep._open()
             ep._send((), {}, port)
@@ -259,24 +326,15 @@ class Client:
         if self._coalesce is not None:
             yield
             return
+        self.flush()
         self._coalesce = []
         try:
             yield
         finally:
             batch, self._coalesce = self._coalesce, None
-            # one cast per run of consecutive messages to the same workers: program order is
-            # kept across meshes too (a message to a sub-mesh may read what an earlier
-            # message to the whole mesh wrote, and the other way round)
-            runs: List[Tuple[Any, List[tuple]]] = []
-            for mesh, msg in batch:
-                if runs and runs[-1][0]._workers is mesh._workers:
-                    runs[-1][1].append(msg)
-                else:
-                    runs.append((mesh, [msg]))
-            for i, (mesh, msgs) in enumerate(runs):
-                if i == 0:
-                    self._send_deletes()
-                mesh._workers.run.broadcast(msgs)
+            with self._plock:
+                self._flush_locked()
+                self._send_runs(batch)
 
     def ensure_process_group(self) -> None:
         if self._pg_init:
@@ -319,6 +377,7 @@ class Client:
     def fetch(self, mesh: "DeviceMesh", ref_tree, preprocess=None, timeout: Optional[float] = None):
         seq = self.new_seq()
         self._watch()
+        self.flush()
         self._send_deletes()
         ep = mesh._workers.run_and_reply
         if not hasattr(ep, "_open"):      # simulated workers answer synchronously
@@ -374,7 +433,12 @@ class Client:
         return self.errors
 
     def shutdown(self) -> None:
+        try:
+            self.flush()
+        except Exception:  # noqa: BLE001 - the workers may be gone already
+            pass
         self._closed = True
+        self._flush_event.set()
 
 
 # ----------------------------------------------------------------------------- tensor --
