@@ -786,7 +786,18 @@ def _propagate(func, args, kwargs):
     return fake_out
 
 
+# operators whose result is a Python value computed from tensor data: the controller holds no
+# data, so these cannot be answered here
+_DATA_DEPENDENT = {"_local_scalar_dense", "item", "is_nonzero", "equal", "nonzero", "unique",
+                   "_unique2", "masked_select"}
+
+
 def _dispatch(func, args, kwargs):
+    if func._schema.name.split("::")[1] in _DATA_DEPENDENT:
+        raise RuntimeError(
+            f"{func._schema.name} needs the values of a distributed tensor, which live on the "
+            "workers.  Bring them to the controller with fetch_shard(t).get() or inspect(t), "
+            "or compute on the workers inside a remote function.")
     ts: List[Tensor] = []
     _collect(args, ts)
     _collect(kwargs, ts)

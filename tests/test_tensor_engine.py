@@ -326,3 +326,13 @@ def test_coalescing_keeps_program_order_across_meshes(dm):
             a.add_(10)                      # whole mesh again
         assert te.inspect(c, gpu=1).tolist() == [11.0] * 3
         assert te.inspect(a, host=0, gpu=0).tolist() == [21.0] * 3
+
+
+def test_reading_values_on_the_controller_is_a_clear_error(dm):
+    with dm.activate():
+        t = torch.ones(3)
+        with pytest.raises(RuntimeError, match="fetch_shard"):
+            t.sum().item()
+        with pytest.raises(RuntimeError, match="fetch_shard"):
+            bool(t.sum() > 2)
+        assert te.inspect(t.sum()).item() == 3.0      # the way to do it
