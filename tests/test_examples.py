@@ -66,3 +66,9 @@ def test_fsdp_training_driven_over_an_actor_mesh():
     first = sum(out["losses_first"]) / 2
     last = sum(out["losses_last"]) / 2
     assert last < first, out          # the sharded optimizer step learns
+
+
+def test_distributed_tensors_tour():
+    out = _load("distributed_tensors").run()
+    assert out["error_caught"] and out["pipeline_out"] == 16.0
+    assert out["coords"] == [[0, 1], [10, 11]] and out["compiled"] == (189.0, 189.0)
