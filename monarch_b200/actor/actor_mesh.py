@@ -750,6 +750,8 @@ class _ActorState:
         (self.cls, self.args, self.kwargs, self.meta) = unflatten(params, [])
         self.obj: Any = None
         self.loop: Optional[asyncio.AbstractEventLoop] = None
+        self._loop_thread: Optional[threading.Thread] = None
+        self._has_async: Optional[bool] = None
         self.instance_info: Optional[ActorInstance] = None
 
     def _ensure(self, instance) -> None:
@@ -773,12 +775,42 @@ class _ActorState:
             r = self.loop.run_until_complete(r)
         return r
 
-    def on_message(self, instance, env) -> None:
-        t0 = time.perf_counter()
+    def _parse(self, env):
+        """(kind, method, fn, args, kwargs, response port, explicit, point) of a message."""
         msg = unflatten(env.data, env.parts, getattr(self, "_extra_load", None))
         kind = msg[0]
         cast_rank = int(env.headers.get("cast_rank", "0"))
         point = _cast_point(env.headers.get("cast_shape"), cast_rank)
+        if kind == "init":
+            return kind, None, None, (), {}, None, False, point
+        _, method, args, kwargs, port = msg
+        if isinstance(port, ReducePort):
+            port = ReducePort(port._port_id, port._error_port_id, cast_rank,
+                              via=env.headers.get("reduce_via"),
+                              key=env.headers.get("reduce_key"))
+        prop = getattr(self.cls, method, None)
+        explicit = isinstance(prop, EndpointProperty) and prop._explicit_response_port
+        if port is not None and not isinstance(port, ReducePort):
+            via = None if explicit else env.headers.get("reduce_via")
+            port = Port(port._port_id, cast_rank, via=via, key=env.headers.get("reduce_key"))
+        response = port if port is not None else DroppingPort()
+        fn = prop._fn if isinstance(prop, EndpointProperty) else getattr(self.cls, method)
+        return kind, method, fn, args, kwargs, response, explicit, point
+
+    def on_message(self, instance, env) -> None:
+        if self._has_async is None:
+            self._has_async = any(
+                isinstance(v, EndpointProperty) and inspect.iscoroutinefunction(v._fn)
+                for klass in self.cls.__mro__ for v in vars(klass).values())
+        if self._has_async:
+            # an actor with async endpoints lives on its own event-loop thread: constructor,
+            # sync and async endpoints all run there (one at a time, except that async
+            # endpoints give way to each other and to later messages wherever they await)
+            self._start_loop()
+            self.loop.call_soon_threadsafe(self._handle_on_loop, instance, env)
+            return
+        t0 = time.perf_counter()
+        kind, method, fn, args, kwargs, response, explicit, point = self._parse(env)
         try:
             self._ensure(instance)
         except BaseException:
@@ -788,18 +820,6 @@ class _ActorState:
         try:
             if kind == "init":
                 return
-            _, method, args, kwargs, port = msg
-            if isinstance(port, ReducePort):
-                port = ReducePort(port._port_id, port._error_port_id, cast_rank,
-                                  via=env.headers.get("reduce_via"),
-                                  key=env.headers.get("reduce_key"))
-            prop = getattr(self.cls, method, None)
-            explicit = isinstance(prop, EndpointProperty) and prop._explicit_response_port
-            if port is not None and not isinstance(port, ReducePort):
-                via = None if explicit else env.headers.get("reduce_via")
-                port = Port(port._port_id, cast_rank, via=via, key=env.headers.get("reduce_key"))
-            response = port if port is not None else DroppingPort()
-            fn = prop._fn if isinstance(prop, EndpointProperty) else getattr(self.cls, method)
             # every endpoint call runs inside a span when somebody is listening (event
             # capture or the chrome trace); otherwise the call pays nothing for it
             span_id = N.span_enter(f"{self.cls.__name__}.{method}", instance.actor_id) \
@@ -819,6 +839,61 @@ class _ActorState:
             _tls.ctx = None
             N.metrics_histogram_record("py_endpoint_us", (time.perf_counter() - t0) * 1e6)
 
+    # ---- actors with async endpoints ---------------------------------------------------
+    def _start_loop(self) -> None:
+        if self.loop is None:
+            self.loop = asyncio.new_event_loop()
+
+            def main(loop=self.loop):
+                asyncio.set_event_loop(loop)
+                loop.run_forever()
+
+            self._loop_thread = threading.Thread(target=main, daemon=True,
+                                                 name=f"actor-loop-{self.name}")
+            self._loop_thread.start()
+
+    def _handle_on_loop(self, instance, env) -> None:
+        """Runs on the actor's loop thread, in message order."""
+        try:
+            kind, method, fn, args, kwargs, response, explicit, point = self._parse(env)
+            try:
+                self._ensure(instance)
+                ctx = Context(self.instance_info, point)
+                if kind == "init":
+                    return
+                if inspect.iscoroutinefunction(fn):
+                    _tls.ctx = None
+                    self.loop.create_task(self._run_async(instance, fn, args, kwargs, response,
+                                                          explicit, ctx))
+                    return
+                _tls.ctx = ctx
+                try:
+                    if explicit:
+                        fn(self.obj, response, *args, **kwargs)
+                    else:
+                        response.send(fn(self.obj, *args, **kwargs))
+                except Exception as e:  # noqa: BLE001
+                    response.exception(ActorError(e))
+                N.metrics_counter_add("py_messages_handled", 1)
+            finally:
+                _tls.ctx = None
+        except BaseException as e:  # noqa: BLE001 - nobody to answer to: the actor fails
+            instance.fail(f"{type(e).__name__}: {e}\n{traceback.format_exc()}")
+
+    async def _run_async(self, instance, fn, args, kwargs, response, explicit, ctx) -> None:
+        _context.set(ctx)       # a task has its own copy of the context variables
+        try:
+            try:
+                if explicit:
+                    await fn(self.obj, response, *args, **kwargs)
+                else:
+                    response.send(await fn(self.obj, *args, **kwargs))
+            except Exception as e:  # noqa: BLE001
+                response.exception(ActorError(e))
+            N.metrics_counter_add("py_messages_handled", 1)
+        except BaseException as e:  # noqa: BLE001 - e.g. a broadcast endpoint that raised
+            instance.fail(f"{type(e).__name__}: {e}\n{traceback.format_exc()}")
+
     def on_undeliverable(self, instance, env, reason: str) -> bool:
         if self.obj is None:
             return False
@@ -827,7 +902,11 @@ class _ActorState:
     def on_stop(self, instance) -> None:
         if self.loop is not None:
             try:
-                self.loop.close()
+                if self._loop_thread is not None:
+                    self.loop.call_soon_threadsafe(self.loop.stop)
+                    self._loop_thread.join(2.0)
+                if not self.loop.is_running():
+                    self.loop.close()
             except Exception:  # noqa: BLE001
                 pass
 

@@ -369,3 +369,83 @@ def test_replies_gathered_along_the_cast_tree(monkeypatch):
         assert g.val.call(1).get(timeout=60).item(gpus=19)["r"] == 19   # still healthy
     finally:
         pm.stop().get()
+
+
+def test_async_endpoints_give_way_to_later_messages():
+    """An async endpoint that is waiting does not block the actor: a later message is
+    handled meanwhile (and can end the wait)."""
+    class Waiter(Actor):
+        def __init__(self):
+            self.stop = False
+            self.spins = 0
+
+        @endpoint
+        async def wait_until_told(self) -> int:
+            while not self.stop:
+                self.spins += 1
+                await asyncio.sleep(0.01)
+            return self.spins
+
+        @endpoint
+        async def tell(self) -> None:
+            self.stop = True
+
+    pm = this_host().spawn_procs(per_host={"gpus": 1})
+    try:
+        w = pm.spawn("waiter", Waiter)
+        pending = w.wait_until_told.call()
+        time.sleep(0.1)
+        w.tell.call().get(timeout=20)          # goes through while the first call is waiting
+        assert pending.get(timeout=20).values()[0] >= 1
+    finally:
+        pm.stop().get()
+
+
+def test_sync_and_async_endpoints_share_one_thread():
+    """Constructor, sync and async endpoints of an actor see the same thread-local state."""
+    import threading
+
+    class TLS(Actor):
+        def __init__(self):
+            self.local = threading.local()
+            self.local.value = 0
+
+        @endpoint
+        def increment(self) -> None:
+            self.local.value += 1
+
+        @endpoint
+        async def increment_async(self) -> None:
+            self.local.value += 1
+
+        @endpoint
+        def get_value(self) -> int:
+            return self.local.value
+
+        @endpoint
+        async def get_async(self) -> int:
+            return self.local.value
+
+        @endpoint
+        async def boom(self) -> None:
+            raise ValueError("async boom")
+
+    pm = local_proc_mesh(gpus=1)
+    try:
+        a = pm.spawn("tls", TLS)
+        a.increment.call_one().get(timeout=20)
+        a.increment_async.call_one().get(timeout=20)
+        a.increment.call_one().get(timeout=20)
+        a.increment_async.call_one().get(timeout=20)
+        assert a.get_value.call_one().get(timeout=20) == 4
+        assert a.get_async.call_one().get(timeout=20) == 4
+        with pytest.raises(ActorError, match="async boom"):
+            a.boom.call_one().get(timeout=20)
+        assert a.get_value.call_one().get(timeout=20) == 4     # still alive
+        # without anybody to answer to, an async failure goes up the supervision tree
+        mon = pm.monitor()
+        a.boom.broadcast()
+        ev = mon.get(timeout=20)
+        assert ev.kind == "actor_failed" and "async boom" in ev.message
+    finally:
+        pm.stop().get()
