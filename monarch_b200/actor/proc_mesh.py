@@ -186,6 +186,9 @@ class ProcMesh(MeshTrait):
         if parts:
             raise ValueError("large tensors cannot be passed as spawn arguments; send them "
                              "through an endpoint after spawning")
+        if name in self._actor_names:
+            raise RuntimeError(f"gspawn failed: an actor with name '{name}' has already been "
+                               "spawned on this proc mesh")
         results = self._native.spawn(name, "python", params)
         bad = [r for r in results if not r[1]]
         if bad:
@@ -443,6 +446,11 @@ class HostMesh(MeshTrait):
                     bootstrap: Optional[Callable[[], None]] = None,
                     env: Optional[Dict[str, str]] = None) -> ProcMesh:
         per_host = dict(per_host or {})
+        have = dict(zip(self._labels, self._shape_.ndslice.sizes))
+        # naming a host dim again is only accepted when it says what is already true
+        # (``per_host={"hosts": 1, "gpus": 2}`` on a one-host mesh)
+        for k in [k for k in per_host if k in have and int(per_host[k]) == have[k]]:
+            del per_host[k]
         clash = set(per_host) & set(self._labels)
         if clash:
             raise ValueError(f"host mesh already has dims {sorted(clash)}")

@@ -449,3 +449,41 @@ def test_sync_and_async_endpoints_share_one_thread():
         assert ev.kind == "actor_failed" and "async boom" in ev.message
     finally:
         pm.stop().get()
+
+
+def test_reference_behaviours_rank_strings_duplicates_and_lost_references():
+    """Scenarios of the reference's actor test-suite (python/tests/test_python_actors.py:
+    rank_size, rank_string, mesh_len, same_actor_twice, this_and_that,
+    things_survive_losing_python_reference) on this package's API."""
+    import gc
+    import operator
+
+    class RunIt(Actor):
+        @endpoint
+        def run(self, fn):
+            return fn()
+
+        @endpoint
+        def rank_str(self) -> str:
+            return str(current_rank())
+
+    proc = fake_in_process_host().spawn_procs(per_host={"hosts": 1, "gpus": 2})
+    r = proc.spawn("runit", RunIt)
+    acc = Accumulator(r.run, 0, operator.add)
+    assert acc.accumulate(lambda: current_rank()["gpus"]).get() == 1
+    assert acc.accumulate(lambda: current_size()["gpus"]).get() == 4
+    vm = r.rank_str.call().get().flatten("r")
+    assert vm.slice(r=0).item() == "{'hosts': 0/1, 'gpus': 0/2}"
+    assert vm.slice(r=1).item() == "{'hosts': 0/1, 'gpus': 1/2}"
+    with pytest.raises(ValueError):
+        fake_in_process_host().spawn_procs(per_host={"hosts": 2})      # a real conflict
+    assert len(fake_in_process_host().spawn_procs(per_host={"gpus": 12}).spawn("s", RunIt)) == 12
+
+    with pytest.raises(RuntimeError, match="an actor with name 'runit' has already been spawned"):
+        proc.spawn("runit", RunIt)
+
+    assert this_proc().spawn("counter7", Counter, 7).value.call_one().get() == 7
+
+    kept = this_host().spawn_procs(per_host={"gpus": 1}).spawn("kept", Counter, 3).slice(gpus=0)
+    gc.collect()             # the proc mesh object is gone; the actors are not
+    assert kept.value.call_one().get(timeout=30) == 3
