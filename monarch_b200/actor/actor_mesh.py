@@ -722,6 +722,11 @@ class ActorMesh(MeshTrait, Generic[T]):
                 "cast_shape": json.dumps([self._shape_.labels, list(sl.sizes)])}
         if extra_headers:
             headers = {**headers, **extra_headers}
+        port = message[4] if len(message) > 4 else None
+        if type(port) is Port:
+            # outside the pickle too: a message that cannot be unpickled on the far side can
+            # still be answered (with the error) instead of failing the actor
+            headers = {**headers, "reply_port": port._port_id}
         inst = context().actor_instance._native
         N.cast(inst, self._world, self._name, root, sel, body, headers, parts, sl)
 
@@ -775,9 +780,19 @@ class _ActorState:
             r = self.loop.run_until_complete(r)
         return r
 
-    def _parse(self, env):
+    def _parse(self, env, instance=None):
         """(kind, method, fn, args, kwargs, response port, explicit, point) of a message."""
-        msg = unflatten(env.data, env.parts, getattr(self, "_extra_load", None))
+        try:
+            msg = unflatten(env.data, env.parts, getattr(self, "_extra_load", None))
+        except Exception as e:  # noqa: BLE001 - e.g. an argument whose __setstate__ raises
+            reply = env.headers.get("reply_port")
+            if reply is None or instance is None:
+                raise
+            body, parts = flatten((_KIND_EXCEPTION, int(env.headers.get("cast_rank", "0")),
+                                   ActorError(e)))
+            instance.send(reply, body, {"kind": _KIND_EXCEPTION, "no_return": "1"}, parts)
+            return "undecodable", None, None, (), {}, None, False, \
+                _cast_point(env.headers.get("cast_shape"), int(env.headers.get("cast_rank", "0")))
         kind = msg[0]
         cast_rank = int(env.headers.get("cast_rank", "0"))
         point = _cast_point(env.headers.get("cast_shape"), cast_rank)
@@ -810,7 +825,7 @@ class _ActorState:
             self.loop.call_soon_threadsafe(self._handle_on_loop, instance, env)
             return
         t0 = time.perf_counter()
-        kind, method, fn, args, kwargs, response, explicit, point = self._parse(env)
+        kind, method, fn, args, kwargs, response, explicit, point = self._parse(env, instance)
         try:
             self._ensure(instance)
         except BaseException:
@@ -818,7 +833,7 @@ class _ActorState:
             raise
         _tls.ctx = Context(self.instance_info, point)
         try:
-            if kind == "init":
+            if kind == "init" or kind == "undecodable":
                 return
             # every endpoint call runs inside a span when somebody is listening (event
             # capture or the chrome trace); otherwise the call pays nothing for it
@@ -855,11 +870,11 @@ class _ActorState:
     def _handle_on_loop(self, instance, env) -> None:
         """Runs on the actor's loop thread, in message order."""
         try:
-            kind, method, fn, args, kwargs, response, explicit, point = self._parse(env)
+            kind, method, fn, args, kwargs, response, explicit, point = self._parse(env, instance)
             try:
                 self._ensure(instance)
                 ctx = Context(self.instance_info, point)
-                if kind == "init":
+                if kind == "init" or kind == "undecodable":
                     return
                 if inspect.iscoroutinefunction(fn):
                     _tls.ctx = None

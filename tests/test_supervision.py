@@ -33,6 +33,10 @@ class Worker(Actor):
         time.sleep(s)
         return "woke"
 
+    @endpoint
+    def echo(self, x):
+        return repr(type(x))
+
 
 class BadInit(Actor):
     def __init__(self):
@@ -181,3 +185,62 @@ def test_supervision_bubbles_to_parent_unless_handled():
     assert snap[child2.actor_id]["status"] == "failed"
     assert child2.actor_id in snap[parent2.actor_id]["children"]
     proc.stop_all(500)
+
+
+class _BrokenPickle:
+    def __init__(self, on_get: bool, on_set: bool):
+        self.on_get, self.on_set = on_get, on_set
+
+    def __getstate__(self):
+        if self.on_get:
+            raise RuntimeError("__getstate__ error")
+        return {"on_get": self.on_get, "on_set": self.on_set}
+
+    def __setstate__(self, state):
+        if state["on_set"]:
+            raise RuntimeError("__setstate__ error")
+        self.__dict__.update(state)
+
+
+def test_arguments_that_break_pickling():
+    """An argument that cannot be pickled fails the call locally; one that cannot be
+    unpickled on the far side comes back as an ActorError, and the actor lives on
+    (python/tests/test_actor_error.py test_broken_pickle_class in the reference)."""
+    pm = this_host().spawn_procs(per_host={"gpus": 2})
+    try:
+        w = pm.spawn("w", Worker)
+        with pytest.raises(RuntimeError, match="__getstate__ error"):
+            w.echo.call(_BrokenPickle(True, False))
+        with pytest.raises(ActorError, match="__setstate__ error"):
+            w.echo.call(_BrokenPickle(False, True)).get(timeout=30)
+        with pytest.raises(ActorError, match="__setstate__ error"):
+            w.slice(gpus=1).echo.call_one(_BrokenPickle(False, True)).get(timeout=30)
+        assert w.ok.call().get(timeout=30).values() == [1, 1]      # nobody died
+    finally:
+        pm.stop().get()
+
+
+def test_base_exceptions_take_the_actor_down():
+    """A BaseException (not an Exception) in an endpoint is not an answer: the actor fails
+    and the caller sees a supervision error (test_base_exception_handling in the reference)."""
+    class Fatal(BaseException):
+        pass
+
+    class E(Actor):
+        @endpoint
+        def die(self):
+            raise Fatal("beyond repair")
+
+        @endpoint
+        def check(self) -> int:
+            return 1
+
+    pm = local_proc_mesh(gpus=1)
+    try:
+        e = pm.spawn("e", E)
+        with pytest.raises(SupervisionError):
+            e.die.call_one().get(timeout=30)
+        with pytest.raises(SupervisionError):
+            e.check.call().get(timeout=30)
+    finally:
+        pm.stop().get()
