@@ -70,6 +70,18 @@ class Extent:
         return (Extent, (self._labels, self._sizes))
 
 
+class DimIndexError(IndexError, ValueError):
+    """An index outside a dimension (an ``IndexError``; also a ``ValueError``, which is what
+    the reference's bindings raise for it)."""
+
+
+class DimLabelError(KeyError, ValueError):
+    """A dimension name the shape does not have (a ``KeyError``; also a ``ValueError``)."""
+
+    def __str__(self) -> str:        # KeyError would show the repr of the message
+        return str(self.args[0]) if self.args else ""
+
+
 class Point(Mapping):
     """A position in an extent: a mapping label -> coordinate with a flat ``rank``."""
 
@@ -172,7 +184,8 @@ class Shape:
         if index < 0:
             index += size
         if not 0 <= index < size:
-            raise IndexError(f"index {index} out of range for dimension '{label}' of size {size}")
+            raise DimIndexError(f"index {index} out of range for dimension '{label}' of size "
+                                f"{size}")
         labels = self._labels[:d] + self._labels[d + 1:]
         return Shape(labels, self._slice.at(d, index))
 
@@ -193,7 +206,7 @@ class Shape:
         try:
             return self._labels.index(label)
         except ValueError:
-            raise KeyError(f"{self} does not have dimension {label!r}") from None
+            raise DimLabelError(f"{self} does not have dimension {label!r}") from None
 
     def __len__(self) -> int:
         return len(self._slice)

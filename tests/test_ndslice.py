@@ -175,3 +175,36 @@ def test_point_and_extent():
     assert pickle.loads(pickle.dumps(p)) == p
     with pytest.raises(ValueError):
         Point(2, ext)
+
+
+def test_shape_at_and_select_follow_the_reference_vectors():
+    """Golden values of the reference's shape tests (python/tests/test_actor_shape.py)."""
+    from monarch_b200.actor.shape import Shape
+    sh = Shape(["batch", "height", "width"], N.Slice(0, [2, 3, 4], [12, 4, 1]))
+    r = sh.at("batch", 1)
+    assert (r.labels, list(r.ndslice.sizes), list(r.ndslice.strides), r.ndslice.offset) == \
+        (["height", "width"], [3, 4], [4, 1], 12)
+    r = sh.at("height", 2)
+    assert (r.labels, list(r.ndslice.sizes), list(r.ndslice.strides), r.ndslice.offset) == \
+        (["batch", "width"], [2, 4], [12, 1], 8)
+    r = sh.at("width", 3)
+    assert (list(r.ndslice.sizes), list(r.ndslice.strides), r.ndslice.offset) == ([2, 3], [12, 4], 3)
+    rc = Shape(["rows", "cols"], N.Slice.new_row_major([4, 6]))
+    r = rc.select("rows", slice(1, 3))
+    assert (r.labels, list(r.ndslice.sizes), r.ndslice.offset) == (["rows", "cols"], [2, 6], 6)
+    r = rc.select("cols", slice(0, 6, 2))
+    assert (list(r.ndslice.sizes), list(r.ndslice.strides)) == ([4, 3], [6, 2])
+    r = sh.select("width", slice(1, 4)).at("batch", 0)
+    assert (r.labels, list(r.ndslice.sizes)) == (["height", "width"], [3, 3])
+    r = sh.at("height", 1).select("width", slice(2, 4))
+    assert (r.labels, list(r.ndslice.sizes)) == (["batch", "width"], [2, 2])
+    # errors are ValueErrors (as in the reference) and the usual Python lookup errors
+    with pytest.raises(ValueError):
+        rc.at("nonexistent", 0)
+    with pytest.raises(KeyError):
+        rc.at("nonexistent", 0)
+    with pytest.raises(ValueError):
+        rc.at("rows", 5)
+    with pytest.raises(IndexError):
+        rc.at("rows", 5)
+    assert rc.at("rows", -1).ndslice.offset == 18        # Python-style negative indices
