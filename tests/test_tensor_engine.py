@@ -336,3 +336,77 @@ def test_reading_values_on_the_controller_is_a_clear_error(dm):
         with pytest.raises(RuntimeError, match="fetch_shard"):
             bool(t.sum() > 2)
         assert te.inspect(t.sum()).item() == 3.0      # the way to do it
+
+
+# ------------------------------------------- compile scenarios of the reference's tests --
+def _bogus_matmul(x, y):
+    return x @ y
+
+
+def test_compiled_blocks_with_closures_formals_errors_and_borrows(dm):
+    """python/tests/test_coalescing.py of the reference: repeat_simple, repeat_formals,
+    repeat_error_inside, repeat_inner_borrow, nested_coalescing."""
+    with dm.activate():
+        a = torch.zeros(())
+
+        @te.compile
+        def bump():
+            nonlocal a
+            z = torch.ones(())
+            a += z                       # a tensor of the enclosing scope, mutated in place
+            return z
+
+        z = None
+        for _ in range(3):
+            z = bump()
+        assert te.inspect(a).item() == 3 and te.inspect(z).item() == 1
+
+        w = torch.rand(3, 4)
+
+        @te.compile
+        def affine(p, q):
+            return 2 * p + q
+
+        @te.compile
+        def affine_closed(q):
+            return 2 * w + q
+
+        for fn, args in ((affine, (w,)), (affine_closed, ())):
+            for _ in range(3):
+                q = torch.rand(3, 4)
+                lz, lw, lq = te.inspect((fn(*args, q), w, q))
+                assert torch.allclose(lz, 2 * lw + lq)
+
+        bogus = te.remote(_bogus_matmul, propagate=lambda x, y: x)
+
+        @te.compile
+        def broken():
+            s = torch.ones(())
+            return bogus(s, s)           # fails on the workers, inside the recording
+
+        with pytest.raises(te.RemoteException):
+            te.inspect(broken())
+        assert te.inspect(a).item() == 3          # the workers carry on
+
+        other = te.Stream("other_for_compile")
+        with other.activate():
+            b = torch.ones(())
+        acc = torch.zeros(())
+
+        @te.compile
+        def add_borrowed():
+            nonlocal acc
+            c, borrow = te.get_active_stream().borrow(b)
+            with borrow:
+                acc += c
+
+        for _ in range(3):
+            add_borrowed()
+        assert te.inspect(acc).item() == 3
+
+        with te.coalescing():
+            t = torch.zeros(3, 4)
+            with te.coalescing():
+                for _ in range(9):
+                    t = t + torch.ones(3, 4)
+        assert te.inspect(t)[0, 0].item() == 9
