@@ -21,6 +21,7 @@ import json
 import os
 import random
 import struct
+import sys
 import threading
 import time
 import traceback
@@ -480,6 +481,11 @@ class Endpoint(Generic[R]):
     def _send(self, args, kwargs, port: Optional[Port], ranks: Optional[List[int]] = None,
               headers: Optional[Dict[str, str]] = None) -> None:
         self._check_signature(args, kwargs)
+        if "monarch_b200.tensor_engine.device_mesh" in sys.modules:
+            from ..tensor_engine import actor_bridge as ab
+            if ab.has_distributed_tensors(args, kwargs):
+                ab.actor_send(self, args, kwargs, port, ranks, headers)
+                return
         self._mesh._cast(("call", self._name, args, kwargs, port), ranks, headers)
 
     def _open(self, once: bool = False) -> Tuple[Port, PortReceiver]:
@@ -606,7 +612,11 @@ def send(endpoint_: Endpoint, args: Tuple, kwargs: Dict, port: Optional[Port] = 
 def as_endpoint(bound_method, *, propagate=None, explicit_response_port=False) -> Endpoint:
     """Treat ``mesh.method`` of an undecorated method as an endpoint."""
     if isinstance(bound_method, Endpoint):
-        return bound_method
+        if propagate is None and not explicit_response_port:
+            return bound_method
+        e = bound_method
+        return Endpoint(e._mesh, e._name, e._fn, explicit_response_port or e._explicit,
+                        propagate if propagate is not None else e._propagate)
     if isinstance(bound_method, _NotAnEndpoint):
         return Endpoint(bound_method.mesh, bound_method.name, bound_method.fn,
                         explicit_response_port, propagate)
@@ -769,6 +779,13 @@ class _ActorState:
         if self.obj is None:
             ctx = Context(self.instance_info, self.instance_info.rank)
             _tls.ctx = ctx
+            bident = self.meta.get("broker_ident")
+            if bident is not None:      # constructor arguments that are distributed tensors
+                from ..tensor_engine import actor_bridge as ab
+                tensors = ab.take_state(instance.proc_id, int(bident))
+                self.args = ab.substitute(self.args, tensors)
+                self.kwargs = ab.substitute(self.kwargs, tensors)
+                self.meta["broker_ident"] = None
             self.obj = self.cls(*self.args, **self.kwargs)
 
     def _run(self, fn, args, kwargs):
@@ -799,6 +816,28 @@ class _ActorState:
         if kind == "init":
             return kind, None, None, (), {}, None, False, point
         _, method, args, kwargs, port = msg
+        bident = env.headers.get("broker_ident")
+        rref_port = None
+        if bident is not None and instance is not None:
+            # the call carries distributed tensors: take this proc's real ones from the broker
+            # (python/monarch/mesh_controller.py actor_send in the reference)
+            from ..tensor_engine import actor_bridge as ab
+            if env.headers.get("broker_rref"):
+                rref_port = ab.BrokerResultPort(instance.proc_id, int(bident))
+            try:
+                tensors = ab.take_state(instance.proc_id, int(bident))
+                args, kwargs = ab.substitute(args, tensors), ab.substitute(kwargs, tensors)
+            except Exception as e:  # noqa: BLE001 - answer with the error, stay alive
+                if rref_port is not None:
+                    rref_port.exception(ActorError(e))
+                elif port is not None:
+                    # no actor context yet at this point: post through the instance itself
+                    body, parts = flatten((_KIND_EXCEPTION, cast_rank, ActorError(e)))
+                    instance.send(port._port_id, body,
+                                  {"kind": _KIND_EXCEPTION, "no_return": "1"}, parts)
+                else:
+                    raise
+                return "undecodable", None, None, (), {}, None, False, point
         if isinstance(port, ReducePort):
             port = ReducePort(port._port_id, port._error_port_id, cast_rank,
                               via=env.headers.get("reduce_via"),
@@ -809,6 +848,8 @@ class _ActorState:
             via = None if explicit else env.headers.get("reduce_via")
             port = Port(port._port_id, cast_rank, via=via, key=env.headers.get("reduce_key"))
         response = port if port is not None else DroppingPort()
+        if rref_port is not None:
+            response = rref_port
         fn = prop._fn if isinstance(prop, EndpointProperty) else getattr(self.cls, method)
         return kind, method, fn, args, kwargs, response, explicit, point
 

@@ -77,16 +77,20 @@ class _Unpickler(pickle.Unpickler):
             if type(raw) is not bytes:
                 raw = bytes(raw)      # same-process delivery hands the sender's view over
             dt = getattr(torch, dtype)
-            if len(raw) == 0:
-                t = torch.empty(shape, dtype=dt)
-            else:
-                # one copy into storage that torch owns (no Python buffer kept alive by a
-                # tensor that may outlive this interpreter thread)
-                t = torch.empty(len(raw), dtype=torch.uint8)
-                import ctypes
-                ctypes.memmove(t.data_ptr(), raw, len(raw))
-                t = t.view(dt).reshape(shape)
-            return t.requires_grad_(req) if req else t
+            # a plain local tensor, whatever dispatch mode is active where the message is
+            # opened (e.g. a reply read inside ``with mesh.activate():``)
+            from torch.utils._python_dispatch import _disable_current_modes
+            with _disable_current_modes():
+                if len(raw) == 0:
+                    t = torch.empty(shape, dtype=dt)
+                else:
+                    # one copy into storage that torch owns (no Python buffer kept alive by
+                    # a tensor that may outlive this interpreter thread)
+                    t = torch.empty(len(raw), dtype=torch.uint8)
+                    import ctypes
+                    ctypes.memmove(t.data_ptr(), raw, len(raw))
+                    t = t.view(dt).reshape(shape)
+                return t.requires_grad_(req) if req else t
         if pid[0] == "b":
             raw = self._parts[pid[1]]
             return raw if type(raw) is bytes else bytes(raw)
@@ -105,4 +109,11 @@ def flatten(obj: Any, extra_pid: Optional[Callable[[Any], Any]] = None) -> Tuple
 
 def unflatten(body: bytes, parts: List[bytes],
               extra_load: Optional[Callable[[Any], Any]] = None) -> Any:
+    torch = _torch()
+    if torch is not None and torch._C._len_torch_dispatch_stack() > 0:
+        # tensors inside the message become plain local tensors, whatever dispatch mode is
+        # active where the message is opened (e.g. a reply read under ``mesh.activate()``)
+        from torch.utils._python_dispatch import _disable_current_modes
+        with _disable_current_modes():
+            return _Unpickler(io.BytesIO(body), list(parts), extra_load).load()
     return _Unpickler(io.BytesIO(body), list(parts), extra_load).load()

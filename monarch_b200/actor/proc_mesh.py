@@ -182,6 +182,12 @@ class ProcMesh(MeshTrait):
         sl = self._shape_.ndslice
         meta = {"labels": self._shape_.labels, "sizes": list(sl.sizes), "ranks": sl.ranks(),
                 "world": self.world, "proc_mesh_ref": ProcMeshRef(self.world, self._shape_)}
+        if "monarch_b200.tensor_engine.device_mesh" in sys.modules:
+            # constructor arguments may be distributed tensors: every actor is built with its
+            # proc's own shard (taken from the proc's tensor worker when the actor starts)
+            from ..tensor_engine import actor_bridge as ab
+            if ab.has_distributed_tensors(args, kwargs):
+                args, kwargs, meta["broker_ident"] = ab.spawn_state(self, args, kwargs)
         params, parts = flatten((cls, args, kwargs, meta))
         if parts:
             raise ValueError("large tensors cannot be passed as spawn arguments; send them "

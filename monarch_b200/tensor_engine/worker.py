@@ -249,6 +249,8 @@ class TensorWorker(Actor):
             torch.cuda.set_device(self.device)
         else:
             self.device = torch.device("cpu")
+        from ..actor import context
+        self.proc_key = context().actor_instance.proc_id   # shared with the proc's actors
         mod = _load_core()
         self.core = mod.WorkerCore(self.rank, Ref) if mod is not None else None
         self.env = _Env(self.core)
@@ -524,6 +526,54 @@ class TensorWorker(Actor):
             run_py(i, bind)
             for rid in drop_after.get(i, ()):
                 self.env.pop(rid, None)
+
+    # ------------------------------------------- actor endpoints called with tensors
+    def _resolve_list(self, refs, seq):
+        """The tensors behind ``refs``, or the first error among them."""
+        out = []
+        for r in refs:
+            v = self._get(r, seq)
+            if isinstance(v, RemoteError):
+                return None, v
+            out.append(v)
+        return out, None
+
+    def _m_actor_call_state(self, ident, refs, stream) -> None:
+        """Hand this proc's tensors for ``refs`` to the actor that handles call ``ident``."""
+        from .actor_bridge import BROKER, CallFailed
+        self.last_seq = ident
+        try:
+            tensors, err = self._resolve_list(refs, ident)
+            if err is not None:
+                BROKER.put(self.proc_key, ident, "state", CallFailed(err.exc_text))
+                return
+            if self.use_cuda:
+                with self._stream_ctx(stream):
+                    torch.cuda.current_stream().synchronize()   # the actor reads them now
+            BROKER.put(self.proc_key, ident, "state", tensors)
+        except Exception as ex:  # noqa: BLE001
+            BROKER.put(self.proc_key, ident, "state", CallFailed(f"{type(ex).__name__}: {ex}"))
+
+    def _m_actor_call_rref(self, ident, refs, results, stream) -> None:
+        """As above, then wait for the actor's return value and keep its tensors under
+        ``results``."""
+        from .actor_bridge import BROKER, CallFailed
+        self._m_actor_call_state(ident, refs, stream)
+        try:
+            res = BROKER.take(self.proc_key, ident, "result")
+            if isinstance(res, CallFailed):
+                raise RuntimeError(res.text)
+            flat = _flatten_tensors(res)
+            if len(flat) != len(results):
+                raise RuntimeError(f"the endpoint returned {len(flat)} tensors, its propagate "
+                                   f"function promised {len(results)}")
+            for r, t in zip(results, flat):
+                self.env[r.id] = t.to(self.device)
+        except Exception as ex:  # noqa: BLE001 - the result refs carry the failure
+            e = RemoteError(ident, self.rank, "actor endpoint (rref)",
+                            f"{type(ex).__name__}: {ex}", traceback.format_exc())
+            self._poison(ident, list(results), e)
+            self._report(e)
 
     # ----------------------------------------------------------------------- pipes
     def _m_create_pipe(self, pipe_id, fspec, max_messages, args, kwargs, labels, offset, sizes,
