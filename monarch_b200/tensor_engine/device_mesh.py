@@ -952,7 +952,15 @@ class DeviceMesh(MeshTrait):
         """Tensor holding each proc's coordinate along ``dim`` (or the flat index over a
         tuple of dims)."""
         dims = (dim,) if isinstance(dim, str) else tuple(dim)
-        key = ",".join(dims)
+        # coordinates are those of *this* mesh; the tensor lives on the active mesh when that
+        # is a part of this one (``with mesh.slice(host=1).activate(): mesh.rank("host")``
+        # gives 1 on every proc of the slice), else on this mesh
+        home = self
+        active = get_active_mesh()
+        if active is not None and active is not self and active.client is self.client and \
+                set(active._ndslice.ranks()) <= set(self._ndslice.ranks()):
+            home = active
+        key = (",".join(dims), id(home) if home is not self else 0)
         if key not in self._rank_tensors:
             labels = list(self._labels)
             sizes = list(self._ndslice.sizes)
@@ -962,7 +970,10 @@ class DeviceMesh(MeshTrait):
                 fake = torch.empty((), dtype=torch.int64)
             idx = [labels.index(d) for d in dims]
             spec = ("pickle", _RankFn(offset, sizes, strides, idx))
-            self._rank_tensors[key] = _send_call(spec, (), {}, fake, self)
+            t = _send_call(spec, (), {}, fake, home)
+            if home is not self:
+                return t          # tied to the life of the sub-mesh object: not cached
+            self._rank_tensors[key] = t
         return self._rank_tensors[key]
 
     @property

@@ -410,3 +410,53 @@ def test_compiled_blocks_with_closures_formals_errors_and_borrows(dm):
                 for _ in range(9):
                     t = t + torch.ones(3, 4)
         assert te.inspect(t)[0, 0].item() == 9
+
+
+# ------------------------- hand-written collectives in remote functions (reference tests) --
+def _udf_all_reduce(t, group=None):
+    import torch.distributed as dist
+    out = t.clone()
+    dist.all_reduce(out, group=group)
+    return out
+
+
+def _udf_barrier(group=None):
+    import torch.distributed as dist
+    dist.barrier(group=group)
+    return torch.ones(())
+
+
+def _append_processed(s):
+    return s + " processed"
+
+
+def test_process_groups_over_dims_and_sub_meshes(dm):
+    """python/tests/test_remote_functions.py of the reference: comms_full_mesh,
+    comms_by_dimension, comms_sub_mesh, barrier, fetch_preprocess."""
+    all_reduce = te.remote(_udf_all_reduce, propagate=lambda t, group=None: t)
+    barrier = te.remote(_udf_barrier, propagate=lambda group=None: torch.ones(()))
+
+    def myrank():
+        return (dm.rank("host") + 1) * 2 + dm.rank("gpu") + 1       # 3 4 / 5 6
+
+    with dm.activate():
+        x = torch.ones((3, 4)) * myrank()
+        full = all_reduce(x, group=dm.process_group(("host", "gpu")))
+        got = te.fetch_shard(full).get(timeout=60)
+        assert got.shape == (3, 4) and got.eq(18).all().item()
+        by_gpu = all_reduce(x, group=dm.process_group(("gpu",)))
+        assert te.fetch_shard(by_gpu).get(timeout=60)[0, 0].item() == 7
+        assert te.fetch_shard(by_gpu, host=1, gpu=1).get(timeout=60)[0, 0].item() == 11
+        by_host = all_reduce(x, group=dm.process_group(("host",)))
+        assert te.fetch_shard(by_host).get(timeout=60)[0, 0].item() == 8
+        assert te.fetch_shard(by_host, host=0, gpu=1).get(timeout=60)[0, 0].item() == 10
+        done = barrier(group=dm.process_group(("host", "gpu")))
+        assert te.fetch_shard(done).get(timeout=60).item() == 1.0
+        assert te.call_on_shard_and_fetch(te.remote(_append_processed),
+                                          "an argument").get(timeout=30) == "an argument processed"
+    # a part of the mesh: the parent's rank tensors and process groups serve it
+    for h, expect in ((1, 11), (0, 7)):
+        with dm.slice(host=h).activate():
+            x = torch.ones((3, 4)) * myrank()
+            r = all_reduce(x, group=dm.process_group(("gpu",)))
+            assert te.fetch_shard(r).get(timeout=60)[0, 0].item() == expect
