@@ -99,8 +99,18 @@ class Remote:
         mesh = _mesh_of(ts) if ts else get_active_mesh()
         if mesh is None:
             raise RuntimeError("no active device mesh")
+        # a propagation function that changes an argument in place (``t.add_(1)``) says that
+        # the worker function does: those tensors are marked as written by the call, so a
+        # failure of the function poisons them too (python/monarch/common/remote.py
+        # ``dtensor_check`` reads the same from the fakes' version counters)
+        before = [t._fake._version for t in ts]
         fake_out = self._fake_outputs(args, kwargs, mesh)
-        return _send_call(_resolve_spec(self._fn), args, kwargs, fake_out, mesh)
+        mutated, seen = [], set()
+        for t, v in zip(ts, before):
+            if t._fake._version != v and id(t) not in seen:
+                seen.add(id(t))
+                mutated.append(t)
+        return _send_call(_resolve_spec(self._fn), args, kwargs, fake_out, mesh, mutated)
 
     def call_on_shard_and_fetch(self, *args, shard=None, **kwargs) -> Future:
         return call_on_shard_and_fetch(self, *args, shard=shard, **kwargs)

@@ -460,3 +460,100 @@ def test_process_groups_over_dims_and_sub_meshes(dm):
             x = torch.ones((3, 4)) * myrank()
             r = all_reduce(x, group=dm.process_group(("gpu",)))
             assert te.fetch_shard(r).get(timeout=60)[0, 0].item() == expect
+
+
+def _udf_mutating_prop(t, *args, **kwargs):
+    t.add_(1)          # "the worker function writes its first argument"
+    return t
+
+
+def _udf_broadcast(tensor, src=None, group=None):
+    import torch.distributed as dist
+    dist.broadcast(tensor, src=src, group=group)
+    return tensor
+
+
+def _udf_all_to_all_single(out, inp, group=None):
+    import torch.distributed as dist
+    dist.all_to_all_single(out, inp, group=group)
+    return out
+
+
+def _udf_all_gather(tensor_list, tensor, group=None):
+    import torch.distributed as dist
+    dist.all_gather(tensor_list, tensor, group=group)
+    return tensor_list
+
+
+def _udf_reduce_scatter_tensor(out, inp, group=None):
+    import torch.distributed as dist
+    dist.reduce_scatter_tensor(out, inp, group=group)
+    return out
+
+
+def _udf_inner_that_fails():
+    raise Exception("Failed to execute the inner function")
+
+
+def _udf_outer_that_calls_inner():
+    _udf_inner_that_fails()
+    return torch.zeros(1)
+
+
+def _udf_returns_exception():
+    return Exception("is a valid value to return")
+
+
+def _udf_fails_in_place(t):
+    raise ValueError("cannot fill")
+
+
+def test_collectives_that_write_their_arguments(dm):
+    """Remote functions that change their arguments in place, told by a propagation function
+    that does the same to the fakes (reference: test_remote_function_broadcast,
+    _all_to_all_single, _all_gather, _reduce_scatter_tensor_sum, test_tensor_dtype_complex,
+    _failure_message_contains_traceback, test_return_exception)."""
+    import itertools
+    broadcast = te.remote(_udf_broadcast, propagate=_udf_mutating_prop)
+    a2a_single = te.remote(_udf_all_to_all_single, propagate=_udf_mutating_prop)
+    rs_tensor = te.remote(_udf_reduce_scatter_tensor, propagate=_udf_mutating_prop)
+    all_gather = te.remote(_udf_all_gather,
+                           propagate=lambda tl, *a, **k: [torch.zeros_like(t) for t in tl])
+    shards = list(itertools.product(range(2), repeat=2))
+    with dm.activate():
+        pg = dm.process_group(("host", "gpu"))
+        for src in (0, 3):
+            rank = 2 * dm.rank("host") + dm.rank("gpu")
+            broadcast(rank, src=src, group=pg)                      # result ignored: in place
+            assert [te.inspect(rank, host=h, gpu=g).item() for h, g in shards] == [src] * 4
+        t_in, t_out = torch.arange(4, dtype=torch.float64), torch.empty(4, dtype=torch.float64)
+        a2a_single(t_out, t_in, group=pg)
+        for h, g in shards:
+            assert te.inspect(t_out, host=h, gpu=g).eq(2 * h + g).all().item()
+        rank = 2 * dm.rank("host") + dm.rank("gpu")
+        outs = all_gather(list(torch.zeros(8).chunk(4)), rank * torch.ones(2), group=pg)
+        assert [x[0].item() for x in te.inspect(outs, host=1, gpu=0)] == [0, 1, 2, 3]
+        out = torch.zeros(2, dtype=torch.int64)
+        rs_tensor(out, torch.arange(8, dtype=torch.int64), group=pg)
+        for h, g in shards:
+            r = 2 * h + g
+            assert te.inspect(out, host=h, gpu=g).tolist() == [8 * r, 8 * r + 4]
+        # complex views pass through the same functions
+        t = torch.rand(2)
+        tl = [torch.rand(2) for _ in range(4)]
+        tl[1] = torch.view_as_complex(tl[1])
+        te.inspect(all_gather(tl, torch.view_as_complex(t), group=pg))
+        # a failure names the frames of the worker's stack
+        x = te.remote(_udf_outer_that_calls_inner, propagate=lambda: torch.zeros(1))()
+        with pytest.raises(te.RemoteException) as ei:
+            te.inspect(x)
+        assert "_udf_outer_that_calls_inner" in str(ei.value)
+        assert "_udf_inner_that_fails" in str(ei.value)
+        # an exception object is a value like any other
+        v = te.call_on_shard_and_fetch(te.remote(_udf_returns_exception)).get(timeout=30)
+        assert isinstance(v, Exception)
+        # a function that was to write its argument and failed leaves the argument failed
+        y = torch.zeros(3)
+        te.remote(_udf_fails_in_place, propagate=_udf_mutating_prop)(y)
+        with pytest.raises(te.RemoteException, match="cannot fill"):
+            te.inspect(y + 1)
