@@ -222,6 +222,10 @@ class Client:
         # asynchronously anyway.  Whatever needs an answer flushes first; a background thread
         # flushes what is left within a millisecond.
         with self._plock:
+            if self._pending_deletes and mesh._workers is self.root_mesh._workers:
+                # refs dropped before this command was issued are dropped before it runs
+                # (joins the run of commands to all workers, so it costs no cast)
+                self._pending.extend((mesh, d) for d in self._flush_deletes(None))
             self._pending.append((mesh, msg))
             if len(self._pending) >= self.eager_batch:
                 self._flush_locked()
@@ -631,6 +635,8 @@ def _collect(obj, out: List[Tensor]) -> None:
     elif isinstance(obj, dict):
         for o in obj.values():
             _collect(o, out)
+    elif getattr(type(obj), "_holds_tensors", False):      # e.g. the key of an OpaqueRef
+        _collect(obj._tensors(), out)
 
 
 def _to_fake(obj):
@@ -642,6 +648,8 @@ def _to_fake(obj):
         return type(obj)(_to_fake(o) for o in obj)
     if isinstance(obj, dict):
         return {k: _to_fake(v) for k, v in obj.items()}
+    if getattr(type(obj), "_holds_tensors", False):
+        return obj._rebuild(_to_fake(obj._tensors()))
     return obj
 
 
@@ -654,8 +662,8 @@ def _to_wire(obj):
         return type(obj)(_to_wire(o) for o in obj)
     if isinstance(obj, dict):
         return {k: _to_wire(v) for k, v in obj.items()}
-    if isinstance(obj, torch.device):
-        return obj
+    if getattr(type(obj), "_holds_tensors", False):
+        return obj._rebuild(_to_wire(obj._tensors()))
     return obj
 
 
@@ -668,6 +676,8 @@ def _wrap_outputs(fake_out, mesh, stream, refs: List[Ref]):
         return type(fake_out)(_wrap_outputs(o, mesh, stream, refs) for o in fake_out)
     if isinstance(fake_out, dict):
         return {k: _wrap_outputs(v, mesh, stream, refs) for k, v in fake_out.items()}
+    if getattr(type(fake_out), "_holds_tensors", False):
+        return fake_out._rebuild(_wrap_outputs(fake_out._tensors(), mesh, stream, refs))
     return fake_out
 
 
@@ -788,8 +798,8 @@ def _propagate(func, args, kwargs):
 
 # operators whose result is a Python value computed from tensor data: the controller holds no
 # data, so these cannot be answered here
-_DATA_DEPENDENT = {"_local_scalar_dense", "item", "is_nonzero", "equal", "nonzero", "unique",
-                   "_unique2", "masked_select"}
+_DATA_DEPENDENT = {"_local_scalar_dense", "item", "is_nonzero", "equal", "allclose", "nonzero",
+                   "unique", "_unique2", "masked_select"}
 
 
 def _dispatch(func, args, kwargs):

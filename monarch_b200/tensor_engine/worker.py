@@ -87,6 +87,8 @@ def _map_refs(obj, fn):
         return type(obj)(_map_refs(o, fn) for o in obj)
     if isinstance(obj, dict):
         return {k: _map_refs(v, fn) for k, v in obj.items()}
+    if getattr(type(obj), "_holds_tensors", False):       # an OpaqueRef: its key tensor
+        return obj._rebuild(_map_refs(obj._tensors(), fn))
     return obj
 
 
@@ -689,6 +691,8 @@ def _flatten_tensors(out) -> List[torch.Tensor]:
         for o in out.values():
             r += _flatten_tensors(o)
         return r
+    if getattr(type(out), "_holds_tensors", False):
+        return _flatten_tensors(out._tensors())
     return []
 
 

@@ -175,3 +175,88 @@ def test_mesh_constructors():
         y = torch.ones(8, 8) @ torch.ones(8, 8)
         assert y.shape == (8, 8)
     assert sims[1].simulator is not None
+
+
+# ------------------------------------------- objects made and named by worker functions --
+class _WorkerFoo:
+    def __init__(self, v):
+        self.v = v
+
+    def add(self, x):
+        return x + self.v
+
+
+def _make_foo(v):
+    return _WorkerFoo(v)
+
+
+def _setup_state():
+    from monarch_b200.opaque_object import OpaqueRef
+    torch.manual_seed(0)
+    model = torch.nn.Linear(4, 2)
+    data = [(torch.randn(8, 4), torch.randn(8, 2)) for _ in range(3)]
+    opt = torch.optim.SGD(model.parameters(), lr=0.1)
+    return [OpaqueRef(model), OpaqueRef(iter(data * 10)), OpaqueRef(torch.nn.MSELoss()),
+            OpaqueRef(opt)]
+
+
+def _iteration(model_ref, data_ref, crit_ref, opt_ref, pg):
+    import torch.distributed as dist
+    model, opt = model_ref.value, opt_ref.value
+    x, y = next(data_ref.value)
+    opt.zero_grad()
+    loss = crit_ref.value(model(x), y)
+    loss.backward()
+    for p in model.parameters():
+        dist.all_reduce(p.grad, group=pg)
+    opt.step()
+    return loss.detach().reshape(1)
+
+
+def _create_ref():
+    from monarch_b200.opaque_object import OpaqueRef
+    return OpaqueRef(object())
+
+
+def test_opaque_refs_made_by_worker_functions(dm):
+    """python/tests/test_remote_functions.py of the reference: test_opaque_object,
+    test_opaqueRef_setup_state_and_iteration, test_opaqueRef_key_deleted."""
+    import gc
+    from monarch_b200.opaque_object import OpaqueObject, OpaqueRef, opaque_method
+    setup_state = te.remote(_setup_state, propagate=lambda: [OpaqueRef(None) for _ in range(4)])
+    iteration = te.remote(_iteration, propagate=lambda m, d, c, o, pg: torch.zeros(1))
+    create_ref = te.remote(_create_ref, propagate=lambda: OpaqueRef(None))
+    alive = te.remote("monarch_b200.opaque_object._keyed_count",
+                      propagate=lambda: torch.zeros((), dtype=torch.int64))
+
+    class Foo(OpaqueObject):
+        @opaque_method
+        def add(self, x):          # the body is the shape rule
+            return x + x
+
+    with dm.activate():
+        f = Foo(_make_foo, 4.0)
+        assert te.inspect(f.add(torch.ones(3, 4))).eq(5.0).all().item()
+        f.hi = 4                   # plain attributes stay on the controller object
+        assert f.hi == 4
+
+        pg = dm.process_group(tuple(dm._labels))
+        model, loader, criterion, optimizer = setup_state()
+        losses = [te.inspect(iteration(model, loader, criterion, optimizer, pg)).item()
+                  for _ in range(5)]
+        assert all(l > 0 for l in losses) and losses[3] < losses[0]
+        with pytest.raises(RuntimeError, match="workers only"):
+            model.value
+        # the wrapped form calls methods of what the worker function made
+        w = OpaqueObject(model)
+        assert w.call_method_on_shard_and_fetch("extra_repr").get(timeout=30).startswith(
+            "in_features=4")
+        del model, loader, criterion, optimizer, w
+        gc.collect()
+        te.inspect(alive())
+        base = te.inspect(alive()).item()
+        ref = create_ref()
+        assert te.inspect(alive()).item() == base + 1
+        del ref
+        gc.collect()
+        assert te.inspect(alive()).item() == base      # the object went with its key
