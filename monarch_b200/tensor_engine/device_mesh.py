@@ -165,6 +165,7 @@ class Client:
         its own)."""
         self.eager_batch = eager_batch
         self._pending: List[Tuple[Any, tuple]] = []
+        self._pending_cmds = 0          # commands in _pending (ref deletions do not count)
         self._plock = threading.RLock()
         self._flusher: Optional[threading.Thread] = None
         self._flush_event = threading.Event()
@@ -227,7 +228,8 @@ class Client:
                 # (joins the run of commands to all workers, so it costs no cast)
                 self._pending.extend((mesh, d) for d in self._flush_deletes(None))
             self._pending.append((mesh, msg))
-            if len(self._pending) >= self.eager_batch:
+            self._pending_cmds += 1
+            if self._pending_cmds >= self.eager_batch:
                 self._flush_locked()
             else:
                 self._kick_flusher()
@@ -241,6 +243,7 @@ class Client:
         if not self._pending:
             return
         batch, self._pending = self._pending, []
+        self._pending_cmds = 0
         self._send_runs(batch)
 
     def _send_runs(self, batch: List[Tuple[Any, tuple]]) -> None:
