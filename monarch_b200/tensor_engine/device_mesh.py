@@ -653,6 +653,8 @@ def _to_fake(obj):
         return {k: _to_fake(v) for k, v in obj.items()}
     if getattr(type(obj), "_holds_tensors", False):
         return obj._rebuild(_to_fake(obj._tensors()))
+    if isinstance(obj, RemoteProcessGroup):
+        return shape_only_group(obj.dims, obj.size())
     return obj
 
 
@@ -919,6 +921,45 @@ class RemoteProcessGroup:
 
     def __repr__(self) -> str:
         return f"RemoteProcessGroup({self.dims})"
+
+
+class _DoneWork:
+    def wait(self, timeout=None):
+        return True
+
+    def is_completed(self):
+        return True
+
+
+def _done(*args, **kwargs):
+    return _DoneWork()
+
+
+_shape_only_group_cls = None
+
+
+def shape_only_group(dims: Tuple[str, ...], size: int):
+    """What a propagation function gets in place of a :class:`RemoteProcessGroup`: a
+    ``torch.distributed`` group of the right size whose collectives do nothing, so worker
+    code that calls ``dist.all_reduce(t, group=pg)`` can be run on fakes for its shapes
+    (python/monarch/common/remote.py ``DummyProcessGroup`` in the reference)."""
+    global _shape_only_group_cls
+    if _shape_only_group_cls is None:
+        import torch.distributed as dist
+
+        class ShapeOnlyProcessGroup(dist.ProcessGroup):
+            def __init__(self, dims, size):
+                super().__init__(0, size)
+                self.dims = tuple(dims)
+
+        for name in ("allreduce", "allreduce_coalesced", "broadcast", "reduce", "allgather",
+                     "_allgather_base", "allgather_coalesced", "allgather_into_tensor_coalesced",
+                     "gather", "scatter", "reduce_scatter", "_reduce_scatter_base",
+                     "reduce_scatter_tensor_coalesced", "alltoall_base", "alltoall", "send",
+                     "recv", "barrier"):
+            setattr(ShapeOnlyProcessGroup, name, _done)
+        _shape_only_group_cls = ShapeOnlyProcessGroup
+    return _shape_only_group_cls(dims, size)
 
 
 class DeviceMesh(MeshTrait):

@@ -260,3 +260,79 @@ def test_opaque_refs_made_by_worker_functions(dm):
         del ref
         gc.collect()
         assert te.inspect(alive()).item() == base      # the object went with its key
+
+
+# ------------------------------------------------ an autograd.Function run on the workers --
+class _BranchingFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, y):
+        ctx.save_for_backward(x)
+        out0 = x * y if x.requires_grad else x + y
+        return out0, y, torch.ones(4), 4
+
+    @staticmethod
+    def backward(ctx, dx1, dx2, dx3, dx4):
+        return dx1, dx2
+
+
+class _MultiplyAllReduce(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, y, pg):
+        import torch.distributed as dist
+        ctx.save_for_backward(x, y)
+        ctx.my_property = True
+        ctx.pg = pg
+        z = x * y
+        dist.all_reduce(z, group=pg)
+        return z
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        import torch.distributed as dist
+        x, y = ctx.saved_tensors
+        assert ctx.my_property
+        gx, gy = grad_output * y, grad_output * x
+        dist.all_reduce(gx, group=ctx.pg)
+        dist.all_reduce(gy, group=ctx.pg)
+        return gx, gy, None
+
+
+def test_remote_autograd_function_from_a_class(dm):
+    """python/tests/test_remote_functions.py::test_remote_autograd_function of the reference,
+    and its process-group-carrying function."""
+    from monarch_b200.cached_remote_function import (RemoteAutogradFunction,
+                                                     remote_autograd_function)
+    fn = remote_autograd_function(_BranchingFunction)
+    assert issubclass(fn, RemoteAutogradFunction) and fn.__name__ == "Remote__BranchingFunction"
+    assert remote_autograd_function(fn) is fn
+    with pytest.raises(TypeError):
+        remote_autograd_function(dict)
+    with dm.activate():
+        x = torch.ones(1, requires_grad=True)
+        y = torch.ones_like(x).requires_grad_(True)
+        outs = fn.apply(x, y)
+        assert outs[3] == 4 and outs[2].shape == (4,)
+        first = te.inspect(outs[0])
+        (outs[0] + outs[1]).sum().backward()
+        gx, gy = te.inspect(x.grad), te.inspect(y.grad)
+        x = x.detach()
+        y.grad = None
+        outs = fn.apply(x, y)                 # the worker sees that x wants no gradient now
+        second = te.inspect(outs[0])
+        (outs[0] + outs[1]).sum().backward()
+        assert x.grad is None
+        gy2 = te.inspect(y.grad)
+    assert first.tolist() == [1.0] and second.tolist() == [2.0]
+    assert gx.tolist() == [1.0] and gy.tolist() == [1.0] and gy2.tolist() == [1.0]
+
+    mul = remote_autograd_function(_MultiplyAllReduce)
+    with dm.activate():
+        pg = dm.process_group(tuple(dm._labels))
+        a = (torch.ones(3) * 2).requires_grad_(True)
+        b = (torch.ones(3) * 3).requires_grad_(True)
+        z = mul.apply(a, b, pg)
+        z.sum().backward()
+        zv, ga, gb = te.inspect(z), te.inspect(a.grad), te.inspect(b.grad)
+    n = 2
+    assert zv.tolist() == [6.0 * n] * 3
+    assert ga.tolist() == [3.0 * n] * 3 and gb.tolist() == [2.0 * n] * 3

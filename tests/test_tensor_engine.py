@@ -450,6 +450,11 @@ def test_process_groups_over_dims_and_sub_meshes(dm):
         by_host = all_reduce(x, group=dm.process_group(("host",)))
         assert te.fetch_shard(by_host).get(timeout=60)[0, 0].item() == 8
         assert te.fetch_shard(by_host, host=0, gpu=1).get(timeout=60)[0, 0].item() == 10
+        # the worker function itself can serve as the shape rule: on fakes the group is a
+        # stand-in whose collectives do nothing
+        itself = te.remote(_udf_all_reduce, propagate=_udf_all_reduce)
+        again = itself(x, group=dm.process_group(("host", "gpu")))
+        assert te.fetch_shard(again).get(timeout=60)[0, 0].item() == 18
         done = barrier(group=dm.process_group(("host", "gpu")))
         assert te.fetch_shard(done).get(timeout=60).item() == 1.0
         assert te.call_on_shard_and_fetch(te.remote(_append_processed),
