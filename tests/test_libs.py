@@ -336,3 +336,30 @@ def test_remote_autograd_function_from_a_class(dm):
     n = 2
     assert zv.tolist() == [6.0 * n] * 3
     assert ga.tolist() == [3.0 * n] * 3 and gb.tolist() == [2.0 * n] * 3
+
+
+def test_opaque_module_in_the_controllers_autograd(dm):
+    """python/tests/test_remote_functions.py::test_opaque_module and
+    ::test_opaque_module_autograd of the reference."""
+    from monarch_b200.opaque_module import OpaqueModule
+    with dm.activate():
+        linear = OpaqueModule("torch.nn.Linear", 3, 3)
+        with torch.no_grad():
+            for p in linear.parameters():
+                p.zero_()                      # writes the workers' parameters
+        out = linear.call_method("forward", lambda x: x.clone(), torch.rand(4, 3))
+        assert te.inspect(out.sum()).item() == 0
+
+        inp = torch.rand(3, 3, requires_grad=True)
+        lin = OpaqueModule("torch.nn.Linear", 3, 3)
+        w, b = lin.parameters()
+        assert w.requires_grad and lin.parameters()[0] is w
+        lin(inp).sum().backward()
+        ig0, wg0, bg0 = te.inspect((inp.grad, w.grad, b.grad))
+        inp.grad = w.grad = b.grad = None
+        (inp @ w.T + b).sum().backward()       # the same computation written out
+        ig1, wg1, bg1 = te.inspect((inp.grad, w.grad, b.grad))
+        with torch.no_grad():
+            y = lin(inp)                       # no graph is recorded without grad mode
+        assert y.grad_fn is None
+    assert torch.allclose(ig0, ig1) and torch.allclose(wg0, wg1) and torch.allclose(bg0, bg1)
