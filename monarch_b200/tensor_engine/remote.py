@@ -68,10 +68,25 @@ def _resolve_spec(fn) -> tuple:
     raise ValueError(f"{fn!r} cannot be sent to the workers as a function")
 
 
+class _TensorMeta(tuple):
+    """(shape, dtype, device) of a tensor a probed call returned."""
+
+    def __new__(cls, *fields):
+        return super().__new__(cls, fields)
+
+
+def _from_meta(meta):
+    return torch.utils._pytree.tree_map(
+        lambda m: torch.empty(m[0], dtype=m[1], device=m[2]) if isinstance(m, _TensorMeta) else m,
+        meta, is_leaf=lambda m: isinstance(m, _TensorMeta))
+
+
 class Remote:
     def __init__(self, fn, propagate=None):
         self._fn = fn
         self._propagate = propagate
+        self._cache: dict = {}
+        self.cache_hits = 0
         if callable(fn):
             functools.update_wrapper(self, fn)
 
@@ -80,14 +95,29 @@ class Remote:
         if callable(p):
             with _propagation():
                 return p(*_to_fake(args), **_to_fake(kwargs))
-        if p == "inspect":
-            # run the real function on one shard and copy the metadata of what comes back
+        if p in ("inspect", "cached"):
+            # run the real function on one shard and copy the metadata of what comes back;
+            # "cached" does so once per signature of the arguments (shapes, dtypes,
+            # requires_grad, plain values) and answers later calls from the table
+            # (python/monarch/common/remote.py ``_cached_propagation`` in the reference)
+            key = None
+            if p == "cached":
+                from ..cached_remote_function import _signature
+                key = _signature(args, kwargs)
+                meta = self._cache.get(key)
+                if meta is not None:
+                    self.cache_hits += 1
+                    with _propagation():
+                        return _from_meta(meta)
             first = {l: 0 for l in mesh._labels}
             sample = call_on_shard_and_fetch(self, *args, shard=first, _raw=True, **kwargs).get()
+            meta = torch.utils._pytree.tree_map(
+                lambda t: _TensorMeta(tuple(t.shape), t.dtype, t.device)
+                if isinstance(t, torch.Tensor) else t, sample)
+            if key is not None:
+                self._cache[key] = meta
             with _propagation():
-                return torch.utils._pytree.tree_map(
-                    lambda t: torch.empty(t.shape, dtype=t.dtype, device=t.device)
-                    if isinstance(t, torch.Tensor) else t, sample)
+                return _from_meta(meta)
         if p is None or p == "mocked":
             return None
         raise ValueError(f"unsupported propagate={p!r}")
@@ -118,7 +148,13 @@ class Remote:
 
 def remote(fn=None, *, propagate=None):
     """``@remote(propagate=lambda x: x)`` marks ``fn`` to run on every worker of the mesh of
-    its tensor arguments; results are distributed tensors shaped like ``propagate``'s."""
+    its tensor arguments; results are distributed tensors shaped like ``propagate``'s.
+
+    ``propagate`` is a function run on fakes (it may be the worker function itself; writing
+    an argument in place there marks the argument as written by the call), ``"inspect"``
+    (run the real function on the first shard and copy the shapes of what returns),
+    ``"cached"`` (the same, once per signature of the arguments), or ``None`` / ``"mocked"``
+    for functions that return no tensors."""
     if fn is None:
         return lambda f: Remote(f, propagate)
     return Remote(fn, propagate)

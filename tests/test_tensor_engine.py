@@ -562,3 +562,25 @@ def test_collectives_that_write_their_arguments(dm):
         te.remote(_udf_fails_in_place, propagate=_udf_mutating_prop)(y)
         with pytest.raises(te.RemoteException, match="cannot fill"):
             te.inspect(y + 1)
+
+
+def _udf_copies(n, t):
+    return [t + i for i in range(n)]
+
+
+def test_cached_propagation_probes_once_per_signature(dm):
+    """python/tests/test_remote_functions.py::test_cached_remote_function of the reference."""
+    fn = te.remote(_udf_copies, propagate="cached")
+    with dm.activate():
+        x, y = torch.ones(3, 4), torch.rand(3, 4)
+        a, _, _ = fn(3, x)
+        b, _, c = fn(3, x)
+        _, _, _ = fn(3, y)              # same shapes and dtype: answered from the table
+        t0, t1 = fn(2, x)               # another plain value: probed again
+        s = t0 + t1
+        assert a.shape == (3, 4) and s.shape == (3, 4)
+        assert fn.cache_hits == 2 and len(fn._cache) == 2
+        assert te.inspect(a).eq(1.0).all().item() and te.inspect(c).eq(3.0).all().item()
+        assert te.inspect(s).eq(3.0).all().item()
+        z = fn(1, torch.ones(2, dtype=torch.int64))[0]
+        assert z.dtype == torch.int64 and len(fn._cache) == 3
