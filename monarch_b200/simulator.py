@@ -141,7 +141,8 @@ class SimWorker:
             if self.rank in ranks:
                 self.groups[key] = ranks
 
-    def _m_reduce(self, seq, result, ref, key, reduction, scatter, inplace, out_ref, stream) -> None:
+    def _m_reduce(self, seq, result, ref, key, reduction, scatter, inplace, out_ref, stream,
+                  in_meta=None) -> None:
         t = self.env.get(ref.id)
         n = len(self.groups.get(key, [0]))
         if not isinstance(t, torch.Tensor):

@@ -150,6 +150,7 @@ class Client:
         self._pending_deletes: List[int] = []
         self._coalesce: Optional[List[Tuple[Any, tuple]]] = None
         self._init_batching(int(os.environ.get("MB200_EAGER_BATCH", "16")))
+        self.check_all_ranks_on_fetch = os.environ.get("MB200_FETCH_CHECKS_ALL_RANKS", "1") == "1"
         self._recording: Optional[List[tuple]] = None
         self._pg_init = False
         self._comms: set = set()
@@ -540,7 +541,8 @@ class Tensor(torch.Tensor):
             result = Tensor(out_fake, m, self.stream)
             res_ref = Ref(result.ref)
         client.send(m, ("reduce", seq, res_ref, Ref(self.ref), key, reduction, scatter, _inplace,
-                        Ref(out.ref) if out is not None else None, self.stream.id))
+                        Ref(out.ref) if out is not None else None, self.stream.id,
+                        (tuple(f.shape), f.dtype)))
         return out if out is not None else result
 
     def reduce_(self, dims, reduction: str = "sum", scatter: bool = False, mesh=None) -> "Tensor":

@@ -181,7 +181,21 @@ def call_on_shard_and_fetch(rfn, *args, shard=None, _raw=False, **kwargs) -> Fut
     tree = (_to_wire(args), _to_wire(kwargs))
     pre = ("pickle", _Apply(fn))
     f = mesh.client.fetch(sub, tree, pre)
-    return Future(lambda t: f.get(t)[0])
+    # the value comes from one shard, but it stands for the whole distributed tensor: the
+    # other ranks are asked whether their shards are sound (a failure on rank 1 is raised
+    # by a fetch from rank 0 too, as in the reference's fetch_shard)
+    chk = None
+    if ts and getattr(mesh.client, "check_all_ranks_on_fetch", False) and len(sub._workers) < len(mesh._workers) \
+            and hasattr(mesh._workers.run_and_reply, "_open"):
+        chk = mesh.client.fetch(mesh, [Ref(t.ref) for t in ts], ("status",))
+
+    def wait(t):
+        v = f.get(t)[0]
+        if chk is not None:
+            chk.get(t)
+        return v
+
+    return Future(wait)
 
 
 class _Apply:

@@ -412,15 +412,24 @@ class TensorWorker(Actor):
                 mine = (g, ranks)
         self.groups[key] = mine
 
-    def _m_reduce(self, seq, result, ref, key, reduction, scatter, inplace, out_ref, stream) -> None:
+    def _m_reduce(self, seq, result, ref, key, reduction, scatter, inplace, out_ref, stream,
+                  in_meta=None) -> None:
         import torch.distributed as dist
         self.last_seq = seq
         try:
             t = self._get(ref, seq)
+            failed = None
             if isinstance(t, RemoteError):
-                self._poison(seq, [result], RemoteError(seq, self.rank, "reduce", t.exc_text, t.tb,
-                                                        dependent_of=t.seq))
-                return
+                failed = RemoteError(seq, self.rank, "reduce", t.exc_text, t.tb,
+                                     dependent_of=t.seq)
+                if in_meta is None:
+                    self._poison(seq, [result], failed)
+                    return
+                # the other ranks of the group do not know that the input failed here and
+                # are entering the collective: take part with a stand-in so that they are
+                # not left waiting, and keep the failure in this rank's result
+                t = torch.zeros(in_meta[0], dtype=in_meta[1], device=self.device)
+                inplace, out_ref = False, None
             g, ranks = self.groups[key]
             n = len(ranks)
             with self._stream_ctx(stream):
@@ -457,7 +466,7 @@ class TensorWorker(Actor):
                 if out_ref is not None:
                     self.env[out_ref.id].copy_(out)
                     out = self.env[out_ref.id]
-            self.env[result.id] = out
+            self.env[result.id] = out if failed is None else failed
         except Exception as ex:  # noqa: BLE001
             e = RemoteError(seq, self.rank, "reduce", f"{type(ex).__name__}: {ex}",
                             traceback.format_exc())
@@ -651,6 +660,8 @@ class TensorWorker(Actor):
         if first_err is not None:
             e = first_err
             return ("error", e.seq, e.rank, e.func, e.exc_text, e.tb, e.dependent_of)
+        if preprocess is not None and preprocess[0] == "status":
+            return ("ok", None)      # "are these values sound here?": no copy, no device sync
         try:
             if preprocess is not None:
                 vals = _resolve_function(preprocess)(vals)

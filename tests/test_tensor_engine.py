@@ -584,3 +584,33 @@ def test_cached_propagation_probes_once_per_signature(dm):
         assert te.inspect(s).eq(3.0).all().item()
         z = fn(1, torch.ones(2, dtype=torch.int64))[0]
         assert z.dtype == torch.int64 and len(fn._cache) == 3
+
+
+def _udf_fails_on_one_rank(x, y, rank, fail_rank=None):
+    if fail_rank is not None and int(rank.item()) != fail_rank:
+        return x + y
+    return x @ y               # 3x4 @ 3x4: raises
+
+
+def test_failure_on_one_rank_of_a_distributed_tensor(dm):
+    """python/tests/test_remote_functions.py::test_distributed_error of the reference: the
+    rank whose input failed still takes part in collectives, fetching any shard of a tensor
+    that failed somewhere raises, and unrelated work goes on."""
+    bogus = te.remote(_udf_fails_on_one_rank, propagate=lambda x, y, r, fail_rank=None: x + y)
+    with dm.activate():
+        x, y = torch.rand(3, 4), torch.rand(3, 4)
+        rank = dm.rank("host") * 2 + dm.rank("gpu")
+        z = bogus(x, y, rank, fail_rank=1)
+        a = (x + y).reduce("gpu")
+        assert te.fetch_shard(a).get(timeout=60).shape == (3, 4)
+        with pytest.raises(te.RemoteException, match="_udf_fails_on_one_rank"):
+            te.fetch_shard(z).get(timeout=60)              # shard of rank 0, failure of rank 1
+        rz = z.reduce("gpu")                               # rank 1 joins with a stand-in
+        with pytest.raises(te.RemoteException, match="_udf_fails_on_one_rank"):
+            te.fetch_shard(rz).get(timeout=60)
+        ok = te.fetch_shard(2 * x, host=0, gpu=1).get(timeout=60)
+        assert ok.shape == (3, 4)
+        # the other pair of ranks reduced among themselves, but the tensor as a whole failed
+        with pytest.raises(te.RemoteException):
+            te.fetch_shard(rz, host=1, gpu=0).get(timeout=60)
+        dm.client.drain_errors()
