@@ -27,6 +27,8 @@ from typing import Any, Dict, List, Optional, Tuple
 
 import torch
 
+from .worker import _seq
+
 _BROKER_TIMEOUT = 120.0
 
 
@@ -102,7 +104,7 @@ def _strip(obj, found: List[Any]):
         found.append(obj)
         return BrokerRef(len(found) - 1)
     if isinstance(obj, (list, tuple)):
-        return type(obj)(_strip(o, found) for o in obj)
+        return _seq(obj, (_strip(o, found) for o in obj))
     if isinstance(obj, dict):
         return {k: _strip(v, found) for k, v in obj.items()}
     return obj
@@ -113,7 +115,7 @@ def substitute(obj, tensors: List[torch.Tensor]):
     if isinstance(obj, BrokerRef):
         return tensors[obj.index]
     if isinstance(obj, (list, tuple)):
-        return type(obj)(substitute(o, tensors) for o in obj)
+        return _seq(obj, (substitute(o, tensors) for o in obj))
     if isinstance(obj, dict):
         return {k: substitute(v, tensors) for k, v in obj.items()}
     return obj

@@ -20,6 +20,7 @@ import itertools
 import os
 import socket
 import threading
+import traceback
 import time
 import warnings
 from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
@@ -31,7 +32,7 @@ from torch.utils._python_dispatch import TorchDispatchMode
 
 from ..actor import Channel, Future
 from ..actor.shape import MeshTrait, Shape
-from .worker import PGRef, Ref, TensorWorker, _map_refs
+from .worker import PGRef, Ref, TensorWorker, _map_refs, _seq
 
 _fake_mode = FakeTensorMode(allow_non_fake_inputs=True)
 
@@ -79,6 +80,7 @@ class Stream:
         client.send(t.mesh, ("borrow_create", b.id, Ref(t.ref), t.stream.id, self.id, Ref(out.ref)))
         t._borrowed_by.append(b)
         b._result = out
+        out._borrow = b
         return out, b
 
     def __repr__(self):
@@ -120,6 +122,8 @@ class Borrow:
             self.origin._borrowed_by.remove(self)
         if self._result is not None:
             self._result._dropped = True
+            # remembered for the message of a later use of the borrowed tensor
+            self._result._dropped_at = "".join(traceback.format_stack(limit=6)[:-1])
 
     def __enter__(self):
         return self
@@ -549,19 +553,23 @@ class Tensor(torch.Tensor):
         return self.reduce(dims, reduction, scatter, mesh, _inplace=True)
 
     def to_mesh(self, mesh: "DeviceMesh", stream: Optional[Stream] = None) -> "Tensor":
-        """Move to another mesh with equal named-dim sizes (point-to-point sends)."""
+        """Move to another mesh (point-to-point sends): rank i of this mesh to rank i of a
+        mesh with as many ranks, or -- when ``mesh`` has every dim of this mesh plus others --
+        each value to all ranks of ``mesh`` with the same coordinates in the shared dims (a
+        broadcast along the other dims, e.g. from ``mesh.slice(host=1)`` to ``mesh``)."""
         _check_usable(self)
         src = self.mesh
         if mesh is src or (mesh._ndslice == src._ndslice):
-            return self
-        if sorted(mesh._ndslice.sizes) != sorted(src._ndslice.sizes) and \
-                len(mesh._ndslice) != len(src._ndslice):
-            raise ValueError(f"cannot move between meshes of different sizes: {src} -> {mesh}")
+            # nothing to send, but the result is a value of its own (writing the original
+            # afterwards must not show through it)
+            return torch.ops.aten.clone.default(self)
+        fr, to = src._ndslice.ranks(), mesh._ndslice.ranks()
+        if len(fr) != len(to):
+            fr = _broadcast_sources(src, mesh)
         client = src.client
         client.ensure_process_group()
         out = Tensor(self._fake, mesh, stream or self.stream)
         seq = client.new_seq()
-        fr, to = src._ndslice.ranks(), mesh._ndslice.ranks()
         root = client.root_mesh
         client.send(root, ("send_meta", Ref(out.ref), tuple(self._fake.shape), self._fake.dtype))
         client.send(root, ("send_tensor", seq, Ref(out.ref), Ref(self.ref), fr, to,
@@ -604,7 +612,9 @@ def _new_fake(shape, like) -> torch.Tensor:
 
 def _check_usable(t: Tensor) -> None:
     if t._dropped:
-        raise RuntimeError("this tensor was dropped (or its borrow has ended)")
+        at = getattr(t, "_dropped_at", None)
+        raise TypeError(f"tensor {tuple(t.shape)} is dropped at:\n{at}" if at else
+                        "this tensor was dropped (or its borrow has ended)")
     for b in t._borrowed_by:
         if b.mutable and get_active_stream() is not b.stream:
             raise RuntimeError("tensor is mutably borrowed by another stream; drop the borrow first")
@@ -650,7 +660,7 @@ def _to_fake(obj):
     if isinstance(obj, torch.Tensor):
         return obj
     if isinstance(obj, (list, tuple)):
-        return type(obj)(_to_fake(o) for o in obj)
+        return _seq(obj, (_to_fake(o) for o in obj))
     if isinstance(obj, dict):
         return {k: _to_fake(v) for k, v in obj.items()}
     if getattr(type(obj), "_holds_tensors", False):
@@ -666,7 +676,7 @@ def _to_wire(obj):
     if isinstance(obj, RemoteProcessGroup):
         return PGRef(obj.key)
     if isinstance(obj, (list, tuple)):
-        return type(obj)(_to_wire(o) for o in obj)
+        return _seq(obj, (_to_wire(o) for o in obj))
     if isinstance(obj, dict):
         return {k: _to_wire(v) for k, v in obj.items()}
     if getattr(type(obj), "_holds_tensors", False):
@@ -680,7 +690,7 @@ def _wrap_outputs(fake_out, mesh, stream, refs: List[Ref]):
         refs.append(Ref(t.ref))
         return t
     if isinstance(fake_out, (list, tuple)):
-        return type(fake_out)(_wrap_outputs(o, mesh, stream, refs) for o in fake_out)
+        return _seq(fake_out, (_wrap_outputs(o, mesh, stream, refs) for o in fake_out))
     if isinstance(fake_out, dict):
         return {k: _wrap_outputs(v, mesh, stream, refs) for k, v in fake_out.items()}
     if getattr(type(fake_out), "_holds_tensors", False):
@@ -697,6 +707,35 @@ def _send_call(fspec, args, kwargs, fake_out, mesh: "DeviceMesh", mutates: Seque
     seq = client.new_seq()
     client.send(mesh, ("call", seq, refs, [Ref(t.ref) for t in mutates], fspec, _to_wire(args),
                        _to_wire(kwargs), stream.id))
+    return out
+
+
+def _broadcast_sources(src: "DeviceMesh", dst: "DeviceMesh") -> List[int]:
+    """For every rank of ``dst`` (in its own order) the rank of ``src`` whose value it gets:
+    the one with the same coordinates in the dims that ``src`` has."""
+    s_nd, d_nd = src._ndslice, dst._ndslice
+    d_labels = list(dst._labels)
+    where = []
+    for l, n in zip(src._labels, s_nd.sizes):
+        if n == 1:
+            where.append(None)
+            continue
+        if l not in d_labels or d_nd.sizes[d_labels.index(l)] != n:
+            raise ValueError(f"cannot move between meshes of different sizes: {src} -> {dst} "
+                             f"(dim {l!r} of the source has no equal dim in the destination)")
+        where.append(d_labels.index(l))
+    out = []
+    for i in range(len(d_nd.ranks())):
+        coords, rest = [], i
+        for n in reversed(d_nd.sizes):
+            coords.append(rest % n)
+            rest //= n
+        coords.reverse()
+        r = s_nd.offset
+        for w, st in zip(where, s_nd.strides):
+            if w is not None:
+                r += coords[w] * st
+        out.append(r)
     return out
 
 
@@ -835,6 +874,15 @@ def _dispatch(func, args, kwargs):
         if a.alias_info is not None and a.alias_info.is_write:
             v = args[i] if i < len(args) else kwargs.get(a.name)
             if isinstance(v, Tensor):
+                if v._borrowed_by and any(b.stream is not get_active_stream()
+                                          for b in v._borrowed_by):
+                    raise TypeError(f"{name}: the tensor would be mutated while stream "
+                                    f"{v._borrowed_by[0].stream.name!r} borrows it; drop the "
+                                    "borrow first")
+                b = getattr(v, "_borrow", None)
+                if b is not None and not b.mutable:
+                    raise TypeError(f"{name}: the tensor would be mutated through a read-only "
+                                    "borrow; borrow it with mutable=True")
                 mutated.append(v)
     if mutated and isinstance(fake_out, torch.Tensor) and len(mutated) == 1:
         client = mesh.client

@@ -80,11 +80,16 @@ def _resolve_function(spec):
     raise ValueError(f"bad function spec {spec!r}")
 
 
+def _seq(like, items):
+    """A list/tuple of ``like``'s type from ``items`` (named tuples take them as fields)."""
+    return type(like)(*items) if hasattr(like, "_fields") else type(like)(items)
+
+
 def _map_refs(obj, fn):
     if isinstance(obj, Ref):
         return fn(obj)
     if isinstance(obj, (list, tuple)):
-        return type(obj)(_map_refs(o, fn) for o in obj)
+        return _seq(obj, (_map_refs(o, fn) for o in obj))
     if isinstance(obj, dict):
         return {k: _map_refs(v, fn) for k, v in obj.items()}
     if getattr(type(obj), "_holds_tensors", False):       # an OpaqueRef: its key tensor
@@ -711,7 +716,7 @@ def _to_cpu(obj):
     if isinstance(obj, torch.Tensor):
         return obj.detach().cpu()
     if isinstance(obj, (list, tuple)):
-        return type(obj)(_to_cpu(o) for o in obj)
+        return _seq(obj, (_to_cpu(o) for o in obj))
     if isinstance(obj, dict):
         return {k: _to_cpu(v) for k, v in obj.items()}
     return obj
