@@ -58,6 +58,11 @@ class WorkerTimeoutError(RuntimeError):
         self.ranks = ranks
 
 
+class _ShapeMismatch(TypeError, ValueError):
+    """Argument errors that the reference reports as TypeError in some places and ValueError
+    in others; callers may catch either."""
+
+
 class Stream:
     _ids = itertools.count(1)
 
@@ -509,6 +514,8 @@ class Tensor(torch.Tensor):
             dims = (dims,)
         dims = tuple(dims)
         m = self.mesh
+        if not dims:                         # () stands for every dim of the mesh
+            dims = tuple(m._labels)
         for d in dims:
             if d not in m._labels:
                 raise KeyError(f"{m} has no dimension {d!r}")
@@ -518,21 +525,36 @@ class Tensor(torch.Tensor):
         for d in dims:
             n *= m.size(d)
         if (reduction == "stack" or scatter) and len(dims) != 1:
-            raise NotImplementedError("stack/scatter reductions take exactly one mesh dim")
+            what = "stack" if reduction == "stack" else f"{reduction} with scatter"
+            raise _ShapeMismatch(f"reduction {what!r} is not valid for multiple dimensions "
+                                 f"{dims}: it takes exactly one mesh dim")
+        if get_active_stream() is not self.stream:
+            raise TypeError(f"WRONG_STREAM: the tensor lives on stream {self.stream.name!r} but "
+                            f"{get_active_stream().name!r} is active; borrow it to that stream "
+                            "first")
         f = self._fake
         if reduction == "stack":
             if scatter:
-                if f.shape[0] != n:
-                    raise ValueError(f"all-to-all needs an outer dim of {n}, got {tuple(f.shape)}")
+                if f.dim() == 0 or f.shape[0] != n:
+                    raise _ShapeMismatch(f"When scattering, the outer dimension must equal the "
+                                         f"size of the reduced mesh dim ({n}); all-to-all got "
+                                         f"{tuple(f.shape)}")
                 out_fake = _new_fake(f.shape, f)
             else:
                 out_fake = _new_fake((n, *f.shape), f)
         elif scatter:
             if f.dim() == 0 or f.shape[0] != n:
-                raise ValueError(f"reduce-scatter needs an outer dim of {n}, got {tuple(f.shape)}")
+                raise _ShapeMismatch(f"When scattering, the outer dimension must equal the size "
+                                     f"of the reduced mesh dim ({n}); reduce-scatter got "
+                                     f"{tuple(f.shape)}")
             out_fake = _new_fake(f.shape[1:], f)
         else:
             out_fake = _new_fake(f.shape, f)
+        if out is not None and (tuple(out._fake.shape) != tuple(out_fake.shape)
+                                or out._fake.dtype != out_fake.dtype):
+            raise ValueError(f"Reduce expects the shape to be {out_fake.shape} and the dtype "
+                             f"{out_fake.dtype}, but out= has {out._fake.shape} and "
+                             f"{out._fake.dtype}")
         if _inplace and tuple(out_fake.shape) != tuple(f.shape):
             raise ValueError("in-place reduce needs matching input and output shapes")
         client = m.client
@@ -743,8 +765,8 @@ def _mesh_of(tensors: List[Tensor]) -> "DeviceMesh":
     m = tensors[0].mesh
     for t in tensors[1:]:
         if t.mesh is not m and t.mesh._ndslice != m._ndslice:
-            raise ValueError(f"tensors live on different meshes ({m} vs {t.mesh}); move one "
-                             "with to_mesh() first")
+            raise _ShapeMismatch(f"WRONG_MESH: tensors live on different meshes ({m} vs "
+                                 f"{t.mesh}); move one with to_mesh() first")
     return m
 
 

@@ -218,3 +218,72 @@ def test_trees_of_tensors(mesh):
         with sub.activate():
             _ = te.reduce_(t, dims=("gpu",), reduction="sum")
             assert (te.inspect(t["a"]).item(), te.inspect(t["b"]).item()) == want
+
+
+def test_argument_errors_are_raised_on_the_controller(mesh):
+    """test_errors, test_sub_mesh_process_grop, test_dim1_mesh, test_fetch."""
+    import itertools
+    with mesh.activate():
+        y = torch.rand(3, 4)
+        with pytest.raises(TypeError, match="WRONG_MESH"):
+            with mesh.slice(host=0).activate():
+                torch.rand(3, 4).add(y)
+        other = te.Stream("other")
+        t = torch.rand(10)
+        with pytest.raises(TypeError, match="WRONG_STREAM"):
+            with other.activate():
+                t.reduce("host", "sum")
+        h, g = mesh.rank("host"), mesh.rank("gpu")
+        for hi, gi in itertools.product(range(2), range(2)):
+            a, b = te.fetch_shard((h, g), {"host": hi, "gpu": gi}).get(timeout=60)
+            assert (a.item(), b.item()) == (hi, gi)
+    h0 = mesh.slice(host=0)
+    assert h0.process_group(("gpu",)) != h0.process_group(("gpu",))
+    with mesh.split(host=("oh", "ih"), ih=1).activate():       # a dim of size one
+        got = te.inspect(torch.ones(3, 4))
+    assert torch.equal(got, torch.ones(3, 4))
+
+
+def test_reduce_forms(mesh):
+    """test_reduce and test_reduce_out."""
+    import itertools
+    with mesh.activate():
+        x = 24 * mesh.rank("host") + 12 * mesh.rank("gpu") + torch.arange(12).reshape(3, 4)
+        y = x.reduce("gpu", "sum")
+        g = x.reduce("gpu", "stack")
+        with pytest.raises(TypeError, match="When scattering"):
+            x.reduce("gpu", "sum", scatter=True)
+        x = x.reshape(2, 6)
+        all_to_all = x.reduce("gpu", "stack", scatter=True)
+        reduce_scatter = x.reduce("gpu", "sum", scatter=True)
+        every = x.reduce((), "sum")                             # () is every dim
+        every_named = x.reduce(("gpu", "host"), "sum")
+        for kw in ({"reduction": "sum", "scatter": True}, {"reduction": "stack"},
+                   {"reduction": "stack", "scatter": True}):
+            with pytest.raises(ValueError, match="is not valid for multiple dimensions"):
+                x.reduce((), **kw)
+        yl, gl, el, enl = (te.inspect(t) for t in (y, g, every, every_named))
+        assert te.inspect(all_to_all).shape == (2, 6) and te.inspect(reduce_scatter).shape == (6,)
+    xs = {(h, g): 24 * h + 12 * g + torch.arange(12).reshape(3, 4)
+          for h, g in itertools.product(range(2), range(2))}
+    assert torch.equal(yl, xs[0, 0] + xs[0, 1])
+    assert torch.equal(gl, torch.stack([xs[0, 0], xs[0, 1]]))
+    total = sum(xs.values()).reshape(el.shape)
+    assert torch.equal(el, total) and torch.equal(enl, total)
+    split = mesh.split(host=("oh", "ih"), ih=1)
+    with split.activate():
+        x = 24 * split.rank("oh") + 12 * split.rank("gpu") + torch.arange(12).reshape(3, 4)
+        inner = te.inspect(x.reduce(("ih", "gpu"), "sum"))
+        outer = te.inspect(x.reduce(("oh", "gpu"), "sum"))
+    assert torch.equal(inner, xs[0, 0] + xs[0, 1]) and torch.equal(outer, total.reshape(3, 4))
+
+    with mesh.activate():
+        inp, wrong, out = torch.rand(2, 4), torch.rand(2, 4), torch.rand(4)
+        with pytest.raises(ValueError, match="Reduce expects the shape to be"):
+            inp.reduce("host", reduction="sum", scatter=True, out=wrong)
+        fresh = inp.reduce("host", reduction="sum", scatter=True)
+        before, want = te.inspect(out), te.inspect(fresh)
+        into = inp.reduce("host", reduction="sum", scatter=True, out=out)
+        assert into is out
+        after = te.inspect(out)
+    assert not torch.equal(before, want) and torch.equal(after, want)
