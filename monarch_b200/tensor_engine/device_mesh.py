@@ -1042,6 +1042,20 @@ class DeviceMesh(MeshTrait):
         self._root = root
         self._rank_tensors: Dict[str, Tensor] = {}
 
+    def __call__(self, **kwargs) -> "DeviceMesh":
+        """``mesh(host=0)`` is ``mesh.slice(host=0)`` (python/monarch/common/device_mesh.py
+        ``DeviceMesh.__call__`` in the reference)."""
+        return self.slice(**kwargs)
+
+    @property
+    def names(self) -> Tuple[str, ...]:
+        return tuple(self._labels)
+
+    @property
+    def processes(self):
+        """The ranks of the mesh as an n-dimensional slice."""
+        return self._ndslice
+
     @property
     def _ndslice(self):
         return self._shape_.ndslice

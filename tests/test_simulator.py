@@ -63,3 +63,40 @@ def test_compile_on_mock_mesh_counts_messages():
         for _ in range(5):
             f(x)
         assert sim.messages(0) - n0 <= 5 * 2     # one replay (+ deletes) per call
+
+
+def test_device_mesh_indexing_reshaping_flattening():
+    """python/tests/test_device_mesh.py of the reference, on simulated workers."""
+    import pytest
+    from monarch_b200.simulator import mock_mesh
+    dm = mock_mesh(hosts=2, gpus=12, trace=False)[0].split(gpus=("b", "c"), c=4).rename(hosts="a")
+    assert dm.names == ("a", "b", "c") and list(dm.processes.sizes) == [2, 3, 4]
+    assert dm(a=0, b=0, c=0).processes.ranks() == [0]
+    x = dm(a=0, b=0)
+    assert x.processes.ranks() == [0, 1, 2, 3] and x.names == ("c",)
+    assert dm(c=slice(None, None, 2)).processes.ranks() == list(range(0, 24, 2))
+    assert dm(b=2, c=3).processes.ranks() == [11, 23]
+
+    dm = mock_mesh(hosts=60, gpus=24, trace=False)[0].rename(hosts="host", gpus="gpu")
+    dm2 = dm.split(host=("dp", "pp"), gpu=("tp",), pp=4)
+    assert dm2.names == ("dp", "pp", "tp")
+    assert list(dm2.processes.sizes) == [15, 4, 24]
+    assert list(dm2.processes.strides) == [4 * 24, 24, 1]
+    dm3 = dm.rename(host="dp", gpu="tp")
+    assert dm3.names == ("dp", "tp") and list(dm3.processes.strides) == list(dm.processes.strides)
+    assert list(dm.split(host=("dp", "pp"), gpu=("tp",), dp=4).processes.sizes) == [4, 15, 24]
+    assert list(dm.split(host=("dp", "pp"), dp=60).processes.sizes) == [60, 1, 24]
+    assert list(dm.split(host=("dp", "pp"), pp=60).processes.sizes) == [1, 60, 24]
+    assert dm.rename(host="dp").names == ("dp", "gpu")
+    for kw, msg in (({"host": ("dp", "pp")}, "Cannot infer size"),
+                    ({"host": ("dp", "pp"), "pp": 4, "ddp": 3}, "unused size constraints"),
+                    ({"host": ("dp", "pp"), "gpu": ("pp",), "dp": 3}, "Duplicate dimension name"),
+                    ({"host": ("dp", "pp"), "dp": 7}, "evenly divided")):
+        with pytest.raises(ValueError, match=msg):
+            dm.split(**kw)
+
+    flat = dm.flatten("gpu")
+    assert flat.names == ("gpu",)
+    assert list(flat.processes.sizes) == [60 * 24] and list(flat.processes.strides) == [1]
+    with pytest.raises(ValueError, match="cannot flatten sparse mesh"):
+        dm(gpu=slice(None, None, 2)).flatten("bad_dim")
