@@ -363,3 +363,56 @@ def test_opaque_module_in_the_controllers_autograd(dm):
             y = lin(inp)                       # no graph is recorded without grad mode
         assert y.grad_fn is None
     assert torch.allclose(ig0, ig1) and torch.allclose(wg0, wg1) and torch.allclose(bg0, bg1)
+
+
+def test_builtin_remote_functions(dm, tmp_path):
+    """python/tests/builtins/test_random.py and test_log.py of the reference."""
+    import logging
+    from monarch_b200.builtins.log import log_remote, set_logging_level_remote
+    from monarch_b200.builtins.random import (get_rng_state_all_cuda_remote,
+                                              get_rng_state_remote, manual_seed_all_cuda_remote,
+                                              manual_seed_cuda_remote, random_seed_remote,
+                                              seed_remote, set_manual_seed_remote,
+                                              set_rng_state_remote)
+    with dm.activate():
+        set_manual_seed_remote(12345)
+        t1 = torch.rand(5, 5)
+        set_manual_seed_remote(12345)
+        t2 = torch.rand(5, 5)
+        set_manual_seed_remote(12345, process_idx=1)
+        t3 = torch.rand(5, 5)
+        set_manual_seed_remote(12345, process_idx=dm.rank(dm._labels[-1]))   # one per worker
+        t4 = torch.rand(5, 5)
+        a, b, c = te.inspect((t1, t2, t3))
+        per_rank = [te.inspect(t4, **{dm._labels[-1]: i}) for i in range(2)]
+        assert torch.equal(a, b) and not torch.equal(a, c)
+        assert torch.equal(per_rank[0], a) and torch.equal(per_rank[1], c)
+
+        s1, s2 = get_rng_state_remote(), get_rng_state_remote()
+        first = torch.rand(3, 3)
+        second = torch.rand(3, 3)
+        s3 = get_rng_state_remote()
+        set_rng_state_remote(s1)
+        third = torch.rand(3, 3)
+        r = te.inspect((s1, s2, s3, first, second, third))
+        assert torch.equal(r[0], r[1]) and not torch.equal(r[0], r[2])
+        assert not torch.equal(r[3], r[4]) and torch.equal(r[3], r[5])
+
+        random_seed_remote()
+        u1 = torch.rand(5, 5)
+        random_seed_remote()
+        u2 = torch.rand(5, 5)
+        seed_remote()
+        u3 = torch.rand(5, 5)
+        u = te.inspect((u1, u2, u3))
+        assert not torch.equal(u[0], u[1]) and not torch.equal(u[1], u[2])
+
+        manual_seed_cuda_remote(7)              # no CUDA here: these do nothing, and say so
+        manual_seed_all_cuda_remote(7)          # by returning without an error
+        assert get_rng_state_all_cuda_remote() == []
+
+        set_logging_level_remote(logging.DEBUG)
+        log_remote("value %s and %s", 1, "two")
+        log_remote("quiet %d", 3, level=logging.DEBUG)
+        log_remote("loud", level=logging.ERROR)
+        te.inspect(torch.zeros(1))              # everything above has run
