@@ -5,14 +5,14 @@ from .rdma import RDMABuffer, RDMAError, is_available
 
 __all__ = ["RDMABuffer", "RDMAError", "is_available"]
 
-from .device_mesh import (Borrow, DeviceMesh, RemoteException, Stream, Tensor,  # noqa: E402
+from .device_mesh import (Borrow, BorrowError, DeviceMesh, RemoteException, Stream, Tensor,  # noqa: E402
                           WorkerTimeoutError, RemoteProcessGroup,
                           get_active_mesh, get_active_stream, no_mesh, reduce, reduce_,
                           slice_mesh, spawn_tensor_engine, to_mesh)
 from .remote import (Remote, call_on_shard_and_fetch, coalescing, compile, fetch_shard,  # noqa: E402
                      inspect, remote, show, function_resolvers)
 
-__all__ += ["WorkerTimeoutError", "RemoteProcessGroup", "Borrow", "DeviceMesh", "RemoteException", "Stream", "Tensor", "get_active_mesh",
+__all__ += ["BorrowError", "WorkerTimeoutError", "RemoteProcessGroup", "Borrow", "DeviceMesh", "RemoteException", "Stream", "Tensor", "get_active_mesh",
             "get_active_stream", "no_mesh", "reduce", "reduce_", "slice_mesh",
             "spawn_tensor_engine", "to_mesh", "Remote", "call_on_shard_and_fetch", "coalescing",
             "compile", "fetch_shard", "inspect", "remote", "show", "function_resolvers"]

@@ -63,6 +63,13 @@ class _ShapeMismatch(TypeError, ValueError):
     in others; callers may catch either."""
 
 
+class BorrowError(RuntimeError):
+    """A tensor was used against the rules of a borrow (written while lent, written through
+    a read-only borrow, used after the borrow was dropped).  Not a TypeError as in the
+    reference: torch turns a TypeError raised under a binary operator (``x += 1``) into
+    Python's "unsupported operand type(s)", which would hide the message."""
+
+
 class Stream:
     _ids = itertools.count(1)
 
@@ -635,8 +642,8 @@ def _new_fake(shape, like) -> torch.Tensor:
 def _check_usable(t: Tensor) -> None:
     if t._dropped:
         at = getattr(t, "_dropped_at", None)
-        raise TypeError(f"tensor {tuple(t.shape)} is dropped at:\n{at}" if at else
-                        "this tensor was dropped (or its borrow has ended)")
+        raise BorrowError(f"tensor {tuple(t.shape)} is dropped at:\n{at}" if at else
+                          "this tensor was dropped (or its borrow has ended)")
     for b in t._borrowed_by:
         if b.mutable and get_active_stream() is not b.stream:
             raise RuntimeError("tensor is mutably borrowed by another stream; drop the borrow first")
@@ -765,8 +772,10 @@ def _mesh_of(tensors: List[Tensor]) -> "DeviceMesh":
     m = tensors[0].mesh
     for t in tensors[1:]:
         if t.mesh is not m and t.mesh._ndslice != m._ndslice:
-            raise _ShapeMismatch(f"WRONG_MESH: tensors live on different meshes ({m} vs "
-                                 f"{t.mesh}); move one with to_mesh() first")
+            # a ValueError, not the reference's TypeError: under ``x + y`` torch would
+            # turn a TypeError into "unsupported operand type(s)" and lose this message
+            raise ValueError(f"WRONG_MESH: tensors live on different meshes ({m} vs "
+                             f"{t.mesh}); move one with to_mesh() first")
     return m
 
 
@@ -898,12 +907,12 @@ def _dispatch(func, args, kwargs):
             if isinstance(v, Tensor):
                 if v._borrowed_by and any(b.stream is not get_active_stream()
                                           for b in v._borrowed_by):
-                    raise TypeError(f"{name}: the tensor would be mutated while stream "
+                    raise BorrowError(f"{name}: the tensor would be mutated while stream "
                                     f"{v._borrowed_by[0].stream.name!r} borrows it; drop the "
                                     "borrow first")
                 b = getattr(v, "_borrow", None)
                 if b is not None and not b.mutable:
-                    raise TypeError(f"{name}: the tensor would be mutated through a read-only "
+                    raise BorrowError(f"{name}: the tensor would be mutated through a read-only "
                                     "borrow; borrow it with mutable=True")
                 mutated.append(v)
     if mutated and isinstance(fake_out, torch.Tensor) and len(mutated) == 1:
