@@ -121,8 +121,19 @@ class RemoteAllocator(_AllocatorBase):
         return Alloc(spec, self.kind, hosts=hosts, procs_per_host=per_host)
 
 
-def proc_mesh_from_alloc(alloc: Alloc):
-    """Build the proc mesh an alloc describes (an alloc can be used once)."""
+def _both(first, second):
+    if first is None or second is None:
+        return first or second
+
+    def run():
+        first()
+        second()
+    return run
+
+
+def proc_mesh_from_alloc(alloc: Alloc, setup=None):
+    """Build the proc mesh an alloc describes (an alloc can be used once).  ``setup`` runs in
+    every proc before actors are spawned (after the alloc's own bootstrap function)."""
     from .proc_mesh import _allocate
     if alloc._used:
         raise RuntimeError("this alloc was already turned into a proc mesh")
@@ -130,13 +141,19 @@ def proc_mesh_from_alloc(alloc: Alloc):
     dims = alloc.extent
     p = alloc.params
     if alloc.kind in ("local", "sim"):
+        if setup is not None:
+            setup()           # the procs of these allocs are threads of this process
         return _allocate(dims, in_process=True)
     if alloc.kind == "process":
+        boot = _both(p.get("bootstrap"), setup)
         if p.get("argv") is not None:
             return _allocate(dims, in_process=False, env=p.get("env"),
-                             bootstrap=p.get("bootstrap"), argv=p["argv"])
-        return _allocate(dims, in_process=False, env=p.get("env"), bootstrap=p.get("bootstrap"))
+                             bootstrap=boot, argv=p["argv"])
+        return _allocate(dims, in_process=False, env=p.get("env"), bootstrap=boot)
     if alloc.kind == "remote":
+        if setup is not None:
+            raise NotImplementedError("setup= is not carried to remotely allocated procs; set "
+                                      "the environment in the allocator's command instead")
         return _allocate(dims, in_process=False, remote_hosts=p["hosts"],
                          procs_per_host=p["procs_per_host"])
     raise ValueError(f"unknown alloc kind {alloc.kind!r}")

@@ -235,10 +235,12 @@ class ProcMesh(MeshTrait):
         return "\n".join(rows)
 
     @staticmethod
-    def from_alloc(alloc) -> "ProcMesh":
-        """The proc mesh described by an :class:`~monarch_b200.actor.allocator.Alloc`."""
+    def from_alloc(alloc, setup: Optional[Callable[[], None]] = None) -> "ProcMesh":
+        """The proc mesh described by an :class:`~monarch_b200.actor.allocator.Alloc`.
+        ``setup`` runs in every proc before any actor is spawned there (environment
+        variables that must be in place before CUDA is initialised, for instance)."""
         from .allocator import proc_mesh_from_alloc
-        return proc_mesh_from_alloc(alloc)
+        return proc_mesh_from_alloc(alloc, setup=setup)
 
     def ledger(self, timeout: float = 5.0) -> Dict[int, List[dict]]:
         """Actor-tree snapshot of every proc of the mesh (hyperactor/src/proc.rs:139-315

@@ -248,7 +248,13 @@ class MeshTrait:
 
     @property
     def _shape(self) -> Shape:
-        return Shape(list(self._labels), self._ndslice)
+        own = self.__dict__.get("_shape_value")
+        return own if own is not None else Shape(list(self._labels), self._ndslice)
+
+    @_shape.setter
+    def _shape(self, shape: Shape) -> None:
+        # implementors commonly keep their shape under this very name
+        self.__dict__["_shape_value"] = shape
 
     # -- selection --------------------------------------------------------------------
     def slice(self, **kwargs):

@@ -292,6 +292,67 @@ def test_allocators_and_from_alloc():
         ra.allocate(AllocSpec(hosts=3, gpus=1))
 
 
+def _set_marks_before_anything_else():
+    import os
+    os.environ["CUDA_CACHE_PATH"] = "/tmp/cuda_cache_test"
+    os.environ["CUDA_LAUNCH_BLOCKING"] = "1"
+
+
+def test_setup_function_runs_in_every_proc_before_actors():
+    """python/tests/test_env_before_cuda.py of the reference: ``from_alloc(alloc, setup=...)``
+    and ``proc_mesh(setup=...)`` prepare the environment of the procs."""
+    from monarch_b200.actor import ProcMesh, proc_mesh
+    from monarch_b200.actor.allocator import AllocSpec, ProcessAllocator
+
+    class Env(Actor):
+        @endpoint
+        def read(self, names):
+            import os
+            return {n: os.environ.get(n, "NOT_SET") for n in names}
+
+    names = ["CUDA_CACHE_PATH", "CUDA_LAUNCH_BLOCKING"]
+    want = {"CUDA_CACHE_PATH": "/tmp/cuda_cache_test", "CUDA_LAUNCH_BLOCKING": "1"}
+    pm = ProcMesh.from_alloc(ProcessAllocator().allocate(AllocSpec(hosts=1, gpus=2)),
+                             setup=_set_marks_before_anything_else)
+    try:
+        got = pm.spawn("env", Env).read.call(names).get(timeout=60)
+        assert all(v == want for v in got.values()) and len(got) == 2
+    finally:
+        pm.stop().get()
+    pm = proc_mesh(gpus=1, setup=_set_marks_before_anything_else)
+    try:
+        assert pm.spawn("env", Env).read.call_one(names).get(timeout=60) == want
+    finally:
+        pm.stop().get()
+
+
+def test_mesh_trait_implementor_keeps_its_shape():
+    """python/tests/test_mesh_trait.py of the reference: the smallest implementor."""
+    from monarch_b200.actor.shape import MeshTrait, Shape, Slice
+
+    class Mesh(MeshTrait):
+        def __init__(self, shape, values):
+            self._shape = shape
+            self._values = values
+
+        def _new_with_shape(self, shape):
+            return Mesh(shape, self._values)
+
+        @property
+        def _ndslice(self):
+            return self._shape.ndslice
+
+        @property
+        def _labels(self):
+            return self._shape.labels
+
+    mesh = Mesh(Shape(["label0", "label1"], Slice(offset=0, sizes=[2, 3], strides=[3, 1])),
+                [1, 2, 3, 4, 5, 6])
+    assert len(mesh) == 6
+    assert mesh.slice(label0=1)._ndslice.ranks() == [3, 4, 5]
+    assert mesh.flatten("all").sizes == {"all": 6}
+
+
 def test_many_client_threads_call_concurrently():
     """Calls issued from several threads of the client at once (they share the channel to
     every proc: the caller-side send path and the writer thread interleave) all get their
