@@ -61,6 +61,10 @@ def test_redelivery_after_connection_drop():
     for i in range(300):
         tx.post(str(i).encode())
         if i in (50, 150):
+            # the accepting side must have the connection before it can be dropped
+            wait_until = time.time() + 10
+            while not got and time.time() < wait_until:
+                time.sleep(0.005)
             N.channel_debug_drop_connections(rx.addr)
     deadline = time.time() + 10
     while len(got) < 300 and time.time() < deadline:
