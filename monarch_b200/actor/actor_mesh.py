@@ -236,25 +236,36 @@ class _Health:
     def __init__(self):
         self.lock = threading.Lock()
         self.mesh_error: Optional[str] = None
-        self.actor_errors: Dict[str, str] = {}
+        # actor name -> {proc rank: first failure there}
+        self.actor_errors: Dict[str, Dict[int, str]] = {}
         self.stopped = False
 
-    def error_for(self, actor_name: str) -> Optional[str]:
+    def error_for(self, actor_name: str, ranks=None) -> Optional[str]:
+        """The failure that concerns the actors ``actor_name`` on ``ranks`` (a callable
+        giving the set of proc ranks, None for all): a slice that does not contain the failed
+        actor stays usable (python/tests/test_actor_error.py ``test_slice_supervision`` in
+        the reference).  A failure of the proc mesh itself concerns everyone."""
         with self.lock:
-            if actor_name in self.actor_errors:
-                return self.actor_errors[actor_name]
+            by_rank = self.actor_errors.get(actor_name)
+            if by_rank:
+                if ranks is None:
+                    return next(iter(by_rank.values()))
+                mine = ranks()
+                for r, msg in by_rank.items():
+                    if r in mine:
+                        return msg
             return self.mesh_error
 
 
 def _recv_checked(receiver, health: Optional[_Health], actor_name: str,
-                  deadline: Optional[float]):
+                  deadline: Optional[float], ranks=None):
     """Wait for the next envelope, waking regularly to notice supervision failures."""
     while True:
         env = receiver.recv(50)
         if env is not None:
             return env
         if health is not None:
-            err = health.error_for(actor_name)
+            err = health.error_for(actor_name, ranks)
             if err is not None:
                 raise SupervisionError(f"actor mesh '{actor_name}' is unhealthy: {err}")
         if deadline is not None and time.monotonic() > deadline:
@@ -279,18 +290,20 @@ def _unpack_batch(data: bytes, parts: List[bytes]) -> "collections.deque":
 
 class PortReceiver(Generic[R]):
     def __init__(self, native_receiver, port_id: str, instance, health: Optional[_Health] = None,
-                 actor_name: str = ""):
+                 actor_name: str = "", ranks=None):
         self._rx = native_receiver
         self._port_id = port_id
         self._instance = instance
         self._health = health
         self._actor_name = actor_name
+        self._ranks = ranks
 
     def _next(self, timeout: Optional[float]) -> Tuple[Optional[int], Any]:
         batch = self.__dict__.get("_batch")
         if not batch:
             deadline = None if timeout is None else time.monotonic() + timeout
-            env = _recv_checked(self._rx, self._health, self._actor_name, deadline)
+            env = _recv_checked(self._rx, self._health, self._actor_name, deadline,
+                                self._ranks)
             if env.headers.get("kind") != "batch":
                 kind, rank, obj = unflatten(env.data, env.parts)
                 if kind == _KIND_EXCEPTION:
@@ -323,10 +336,11 @@ class RankedPortReceiver(Generic[R]):
 
 class Channel(Generic[R]):
     @staticmethod
-    def open(once: bool = False, _health=None, _actor_name="") -> Tuple[Port, PortReceiver]:
+    def open(once: bool = False, _health=None, _actor_name="",
+             _ranks=None) -> Tuple[Port, PortReceiver]:
         inst = context().actor_instance._native
         port_id, rx = inst.open_port(once)
-        return Port(port_id), PortReceiver(rx, port_id, inst, _health, _actor_name)
+        return Port(port_id), PortReceiver(rx, port_id, inst, _health, _actor_name, _ranks)
 
 
 # ------------------------------------------------------------------------- value mesh --
@@ -489,7 +503,8 @@ class Endpoint(Generic[R]):
         self._mesh._cast(("call", self._name, args, kwargs, port), ranks, headers)
 
     def _open(self, once: bool = False) -> Tuple[Port, PortReceiver]:
-        return Channel.open(once, _health=self._mesh._health, _actor_name=self._mesh._name)
+        return Channel.open(once, _health=self._mesh._health, _actor_name=self._mesh._name,
+                            _ranks=self._mesh._rank_set)
 
     # -- adverbs ----------------------------------------------------------------------
     def call(self, *args, **kwargs) -> Future[ValueMesh[R]]:
@@ -711,9 +726,16 @@ class ActorMesh(MeshTrait, Generic[T]):
             raise AttributeError(f"{self._class_name} has no attribute {name!r}")
         return _NotAnEndpoint(self, name, attr if callable(attr) else None)
 
+    def _rank_set(self) -> frozenset:
+        """The proc ranks this (possibly sliced) mesh covers."""
+        rs = self.__dict__.get("_rank_set_")
+        if rs is None:
+            rs = self.__dict__["_rank_set_"] = frozenset(self._shape_.ndslice.ranks())
+        return rs
+
     def _raise_if_unhealthy(self) -> None:
         if self._health is not None:
-            err = self._health.error_for(self._name)
+            err = self._health.error_for(self._name, self._rank_set)
             if err is not None:
                 raise SupervisionError(f"actor mesh '{self._name}' is unhealthy: {err}")
 

@@ -140,7 +140,8 @@ class ProcMesh(MeshTrait):
                 msg = f"actor {actor_id} failed: {ev['message']}"
                 with self._health.lock:
                     if name in self._actor_names:
-                        self._health.actor_errors.setdefault(name, msg)
+                        self._health.actor_errors.setdefault(name, {}).setdefault(
+                            int(ev["rank"]), msg)
                     else:
                         self._health.mesh_error = self._health.mesh_error or msg
                 pe = ProcEvent("actor_failed", ev["rank"], actor_id, ev["message"])

@@ -244,3 +244,46 @@ def test_base_exceptions_take_the_actor_down():
             e.check.call().get(timeout=30)
     finally:
         pm.stop().get()
+
+
+def test_slices_without_the_failed_actor_stay_usable():
+    """python/tests/test_actor_error.py::test_slice_supervision and
+    ::test_mesh_slices_inherit_parent_errors of the reference."""
+    import time
+
+    class Fragile(Actor):
+        @endpoint
+        def fail(self):
+            raise RuntimeError("simulated failure")
+
+        @endpoint
+        def check(self) -> str:
+            return "this is a healthy check"
+
+    class Sturdy(Actor):
+        @endpoint
+        def check(self) -> str:
+            return "this is a healthy check"
+
+    pm = this_host().spawn_procs(per_host={"gpus": 4})
+    try:
+        sturdy = pm.spawn("sturdy", Sturdy)
+        fragile = pm.spawn("fragile", Fragile)
+        upper, second, third = (fragile.slice(gpus=slice(2, 4)), fragile.slice(gpus=2),
+                                fragile.slice(gpus=3))
+        third.fail.broadcast()                  # no reply port: the failure is a crash
+        deadline = time.time() + 20
+        while time.time() < deadline:
+            try:
+                third.check.call().get(timeout=5)
+                time.sleep(0.05)
+            except SupervisionError:
+                break
+        for mesh in (fragile, third, upper):    # everything that contains the failed actor
+            with pytest.raises(SupervisionError, match="unhealthy"):
+                mesh.check.call().get(timeout=20)
+        for mesh in (second, fragile.slice(gpus=1), sturdy):
+            got = mesh.check.call().get(timeout=20)
+            assert set(got.values()) == {"this is a healthy check"}
+    finally:
+        pm.stop().get()
