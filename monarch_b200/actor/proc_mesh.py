@@ -50,6 +50,7 @@ class LogAggregator:
         self._lock = threading.Lock()
         self._groups: Dict[str, List] = {}
         self._t0 = None
+        self._timer: Optional[threading.Timer] = None
 
     def add(self, rank: int, is_err: bool, line: str) -> None:
         import time
@@ -62,6 +63,11 @@ class LogAggregator:
             g[0] += 1
             if now - self._t0 >= self.window:
                 self._flush_locked()
+            elif self._timer is None:
+                # the window closes on time even if no further line arrives
+                self._timer = threading.Timer(self.window - (now - self._t0), self.flush)
+                self._timer.daemon = True
+                self._timer.start()
 
     def _flush_locked(self) -> None:
         for count, line in self._groups.values():
@@ -69,6 +75,9 @@ class LogAggregator:
             print(prefix + line, file=self.out)
         self._groups.clear()
         self._t0 = None
+        if self._timer is not None:
+            self._timer.cancel()
+            self._timer = None
 
     def flush(self) -> None:
         with self._lock:
@@ -271,6 +280,8 @@ class ProcMesh(MeshTrait):
     def logging_option(self, stream_to_client: bool = True, aggregate_window_sec: Optional[float] = 5,
                        level: int = 20) -> Future[None]:
         owner = self._owner
+        if owner._log_aggregator is not None:
+            owner._log_aggregator.flush()      # nothing waits in a window that is going away
         if not stream_to_client:
             owner._log_aggregator = None
             _log_sinks.pop(owner.world, None)

@@ -548,3 +548,53 @@ def test_reference_behaviours_rank_strings_duplicates_and_lost_references():
     kept = this_host().spawn_procs(per_host={"gpus": 1}).spawn("kept", Counter, 3).slice(gpus=0)
     gc.collect()             # the proc mesh object is gone; the actors are not
     assert kept.value.call_one().get(timeout=30) == 3
+
+
+def test_log_streaming_windows_and_flushes():
+    """Log lines of the procs reach the client, similar lines of one window are collapsed,
+    a window closes on time by itself, and changing the options flushes what waits
+    (python/tests/test_python_actors.py::test_actor_log_streaming,
+    ::test_flush_on_disable_aggregation, ::test_adjust_aggregation_window of the reference)."""
+    import io
+    import time
+
+    class Printer(Actor):
+        @endpoint
+        def say(self, what: str) -> bool:
+            print(what, flush=True)
+            return True
+
+    def wait_for(buf, text, secs=10.0):
+        deadline = time.time() + secs
+        while text not in buf.getvalue() and time.time() < deadline:
+            time.sleep(0.05)
+        return buf.getvalue()
+
+    pm = this_host().spawn_procs(per_host={"gpus": 2})
+    try:
+        p = pm.spawn("printer", Printer)
+        pm.logging_option(stream_to_client=True, aggregate_window_sec=60).get()
+        waiting = io.StringIO()
+        pm._owner._log_aggregator.out = waiting
+        p.say.call("has print streaming 7").get(timeout=30)
+        time.sleep(1.0)
+        assert waiting.getvalue() == ""                      # the window is still open
+        pm.logging_option(stream_to_client=True, aggregate_window_sec=None).get()
+        assert waiting.getvalue() == "[2 similar log lines] has print streaming 7\n"
+
+        direct = io.StringIO()
+        pm._owner._log_aggregator.out = direct
+        p.say.call("immediate line").get(timeout=30)
+        assert wait_for(direct, "immediate line\nimmediate line\n").count("immediate line") == 2
+
+        pm.logging_option(stream_to_client=True, aggregate_window_sec=0.5).get()
+        timed = io.StringIO()
+        pm._owner._log_aggregator.out = timed
+        p.say.call("timed line").get(timeout=30)
+        assert "[2 similar log lines] timed line" in wait_for(timed, "timed line")
+
+        pm.logging_option(stream_to_client=False).get()
+        assert pm._owner._log_aggregator is None
+        p.say.call("nobody listens").get(timeout=30)
+    finally:
+        pm.stop().get()
