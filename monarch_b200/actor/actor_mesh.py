@@ -239,6 +239,7 @@ class _Health:
         # actor name -> {proc rank: first failure there}
         self.actor_errors: Dict[str, Dict[int, str]] = {}
         self.stopped = False
+        self.stopped_actors: set = set()      # names of actor meshes stopped by their owner
 
     def error_for(self, actor_name: str, ranks=None) -> Optional[str]:
         """The failure that concerns the actors ``actor_name`` on ``ranks`` (a callable
@@ -735,6 +736,8 @@ class ActorMesh(MeshTrait, Generic[T]):
 
     def _raise_if_unhealthy(self) -> None:
         if self._health is not None:
+            if self._name in self._health.stopped_actors:
+                raise RuntimeError(f"actor mesh '{self._name}' has already been stopped")
             err = self._health.error_for(self._name, self._rank_set)
             if err is not None:
                 raise SupervisionError(f"actor mesh '{self._name}' is unhealthy: {err}")
@@ -766,8 +769,12 @@ class ActorMesh(MeshTrait, Generic[T]):
         pm = self._proc_mesh
         if pm is None:
             raise NotImplementedError("stopping an actor mesh needs its owning proc mesh")
-        return Future(lambda timeout: pm._native.stop_actor(self._name,
-                                                            int((timeout or 5) * 1000)))
+        def run(timeout):
+            if self._health is not None:
+                self._health.stopped_actors.add(self._name)   # later calls fail at once
+            return pm._native.stop_actor(self._name, int((timeout or 5) * 1000))
+
+        return Future(run)
 
     def __reduce__(self):
         return (ActorMesh, (self._class, self._name, self._world, self._shape_, None, None,

@@ -598,3 +598,36 @@ def test_log_streaming_windows_and_flushes():
         p.say.call("nobody listens").get(timeout=30)
     finally:
         pm.stop().get()
+
+
+def test_stopped_actor_mesh_refuses_calls_and_ports_travel_as_arguments():
+    """python/tests/test_python_actors.py::test_actor_mesh_stop,
+    ::test_proc_mesh_stop_after_actor_mesh_stop, ::test_port_as_argument of the reference."""
+    from monarch_b200.actor import Channel
+
+    class Echo(Actor):
+        @endpoint
+        def say(self, what: str) -> str:
+            return what
+
+        @endpoint
+        async def count_into(self, port) -> None:
+            for i in range(100):
+                port.send(i)
+
+    pm = this_host().spawn_procs(per_host={"gpus": 2})
+    try:
+        first, second = pm.spawn("echo", Echo), pm.spawn("echo2", Echo)
+        assert set(first.say.call("hello 1").get(timeout=30).values()) == {"hello 1"}
+        first.stop().get(timeout=30)
+        with pytest.raises(RuntimeError, match="has already been stopped"):
+            first.say.call("hello again").get(timeout=5)
+        with pytest.raises(RuntimeError, match="has already been stopped"):
+            first.slice(gpus=0).say.call_one("hello again").get(timeout=5)
+        assert set(second.say.call("hello 3").get(timeout=30).values()) == {"hello 3"}
+
+        send, recv = Channel.open()
+        second.slice(gpus=1).count_into.broadcast(send)
+        assert [recv.recv().get(timeout=30) for _ in range(100)] == list(range(100))
+    finally:
+        pm.stop().get()              # stopping the procs after one of their actor meshes
