@@ -532,9 +532,11 @@ def this_proc() -> ProcMesh:
 
 def proc_mesh(*, gpus: Optional[int] = None, hosts: int = 1, env: Optional[Dict[str, str]] = None,
               setup: Optional[Callable[[], None]] = None) -> ProcMesh:
-    """Subprocess proc mesh with dims {hosts, gpus} on this box."""
-    if hosts != 1:
-        raise NotImplementedError("this build drives one box")
+    """Subprocess proc mesh with dims {hosts, gpus} on this box (``hosts`` > 1 lays that many
+    groups of procs out on the same box, as the reference's local ``proc_mesh`` does; real
+    hosts come from ``HostMesh.from_allocators``)."""
+    if hosts < 1:
+        raise ValueError("hosts must be at least 1")
     if gpus is None:
         try:
             import torch

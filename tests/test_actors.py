@@ -324,6 +324,12 @@ def test_setup_function_runs_in_every_proc_before_actors():
         assert pm.spawn("env", Env).read.call_one(names).get(timeout=60) == want
     finally:
         pm.stop().get()
+    pm = proc_mesh(gpus=1, hosts=2)            # two "hosts" laid out on this box
+    try:
+        assert pm.sizes == {"hosts": 2, "gpus": 1}
+        assert len(pm.spawn("env", Env).read.call(names).get(timeout=60)) == 2
+    finally:
+        pm.stop().get()
 
 
 def test_mesh_trait_implementor_keeps_its_shape():
