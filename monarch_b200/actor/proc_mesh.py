@@ -423,7 +423,8 @@ def _allocate(dims: Dict[str, int], *, in_process: bool, env: Optional[Dict[str,
         if remote_hosts:
             # every proc is started by the allocator daemon of its host; a local stub per
             # proc relays its output and lifetime (tools/remote_exec.py)
-            argv = [sys.executable, "-m", "monarch_b200.tools.remote_exec", "--"] + argv
+            # (the daemon runs its own program: nothing of `argv` travels)
+            argv = [sys.executable, "-m", "monarch_b200.tools.remote_exec"]
             e["MB200_REMOTE_HOSTS"] = ",".join(remote_hosts)
             e["MB200_PROCS_PER_HOST"] = str(procs_per_host)
             transport = "tcp"

@@ -14,8 +14,8 @@
 //
 // Cross-rank ordering uses monotonically increasing epochs in per-rank flag arrays
 // (flags[slot * kMaxRanks + source_rank]); every wait is bounded and reports through the
-// status word instead of hanging.  No TMA, no multicast loads: peer data moves with
-// per-thread 16-byte loads and stores.
+// status word instead of hanging.  No tensor-map TMA and no multicast loads: peer data
+// moves with per-thread 16-byte loads and stores.
 #include <cuda_bf16.h>
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -54,15 +54,25 @@ __global__ void __launch_bounds__(256)
     if (!block_wait_all(my_flags, world, wait_slot, wait_epoch, status, &sh_ok)) return;
   }
   if (chunk_flags == nullptr) {
-    const int64_t vec_per_shard = shard_elems >> 3;
-    const int64_t total = vec_per_shard * world;
+    // Every thread keeps eight independent 16-byte loads in flight: a pull over NVLink is
+    // bound by outstanding bytes (about 3 us of latency x 770 GB/s = 2.4 MB), not by issue
+    // rate, so a modest grid (128 blocks = 4 MB in flight) saturates the link and leaves the
+    // other SMs to the GEMMs that run beside it.
+    const int64_t vps = shard_elems >> 3;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-      const int k = (int)(i / vec_per_shard);
+    for (int k = 0; k < world; ++k) {
       const int p = (rank + k) % world;  // start with the local shard, stagger peers
-      const int64_t v = i - (int64_t)k * vec_per_shard;
-      const uint4 val = ld_nc_v4(reinterpret_cast<const uint4*>(src.p[p]) + v);
-      reinterpret_cast<uint4*>(dst + (int64_t)p * shard_elems)[v] = val;
+      const uint4* s4 = reinterpret_cast<const uint4*>(src.p[p]);
+      uint4* d4 = reinterpret_cast<uint4*>(dst + (int64_t)p * shard_elems);
+      int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+      for (; i + 7 * stride < vps; i += 8 * stride) {
+        uint4 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = ld_nc_v4(s4 + i + j * stride);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) d4[i + j * stride] = v[j];
+      }
+      for (; i < vps; i += stride) d4[i] = ld_nc_v4(s4 + i);
     }
     return;
   }
@@ -91,7 +101,8 @@ __global__ void __launch_bounds__(256)
 // grads.p[r] points at rank r's gradient buffer for this unit (bf16, `unit_elems` long,
 // unit_elems = world * shard_elems).  This rank owns elements [rank*shard, (rank+1)*shard).
 __global__ void __launch_bounds__(256)
-    rs_adamw_kernel(Peers grads, Peers flags, float* __restrict__ master, float* __restrict__ m,
+    rs_adamw_kernel(Peers grads, const void* mc_grads, Peers flags, float* __restrict__ master,
+                    float* __restrict__ m,
                     float* __restrict__ v, __nv_bfloat16* __restrict__ param_shard,
                     int64_t shard_elems, int rank, int world, int grad_slot, int param_slot,
                     uint32_t epoch, float lr, float beta1, float beta2, float eps, float wd,
@@ -101,24 +112,35 @@ __global__ void __launch_bounds__(256)
   // My gradients for this unit are complete (stream order): tell everyone, then wait for
   // everyone else's.
   if (blockIdx.x == 0) signal_all(flags, world, rank, grad_slot, epoch, threadIdx.x);
-  if (!block_wait_all(flags.p[rank], world, grad_slot, epoch, status, &sh_ok)) return;
+  if (!block_wait_all(flags.p[rank], world, grad_slot, epoch, status, &sh_ok)) {
+    // gave up: still take part in the block count, so that the counter is back at zero
+    // for the next launch even when only some blocks of this one timed out
+    last_block_done(counter);
+    return;
+  }
 
   const int64_t base = (int64_t)rank * shard_elems;
   const int64_t nvec = shard_elems >> 3;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
     float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    uint4 raw[kMaxRanks];
+    if (mc_grads) {
+      // in-switch reduction: one load returns the fp32-accumulated sum of every rank's copy
+      acc8(g, multimem_ld_sum<__nv_bfloat16>(
+                  reinterpret_cast<const __nv_bfloat16*>(mc_grads) + base + i * 8));
+    } else {
+      uint4 raw[kMaxRanks];
 #pragma unroll
-    for (int k = 0; k < kMaxRanks; ++k) {
-      if (k < world) {
-        const int p = (rank + k) % world;
-        raw[k] = ld_nc_v4(reinterpret_cast<const __nv_bfloat16*>(grads.p[p]) + base + i * 8);
+      for (int k = 0; k < kMaxRanks; ++k) {
+        if (k < world) {
+          const int p = (rank + k) % world;
+          raw[k] = ld_nc_v4(reinterpret_cast<const __nv_bfloat16*>(grads.p[p]) + base + i * 8);
+        }
       }
-    }
 #pragma unroll
-    for (int k = 0; k < kMaxRanks; ++k)
-      if (k < world) acc8(g, raw[k]);
+      for (int k = 0; k < kMaxRanks; ++k)
+        if (k < world) acc8(g, raw[k]);
+    }
     float4 p0 = reinterpret_cast<float4*>(master)[i * 2], p1 = reinterpret_cast<float4*>(master)[i * 2 + 1];
     float4 m0 = reinterpret_cast<float4*>(m)[i * 2], m1 = reinterpret_cast<float4*>(m)[i * 2 + 1];
     float4 v0 = reinterpret_cast<float4*>(v)[i * 2], v1 = reinterpret_cast<float4*>(v)[i * 2 + 1];
@@ -157,11 +179,15 @@ __global__ void __launch_bounds__(256)
 // bf16 result into every rank's output.
 template <bool kInFp32>
 __global__ void __launch_bounds__(256)
-    allreduce_kernel(Peers in, Peers out, Peers flags, int64_t n, int rank, int world, float scale,
-                     int slot, uint32_t epoch, unsigned int* counter, int* status) {
+    allreduce_kernel(Peers in, Peers out, const void* mc_in, void* mc_out, Peers flags, int64_t n,
+                     int rank, int world, float scale, int slot, uint32_t epoch,
+                     unsigned int* counter, int* status) {
   __shared__ int sh_ok;
   if (blockIdx.x == 0) signal_all(flags, world, rank, slot, epoch, threadIdx.x);
-  if (!block_wait_all(flags.p[rank], world, slot, epoch, status, &sh_ok)) return;
+  if (!block_wait_all(flags.p[rank], world, slot, epoch, status, &sh_ok)) {
+    last_block_done(counter);  // keep the block count consistent for the next launch
+    return;
+  }
   const int64_t nvec = n >> 3;
   const int64_t per = (nvec + world - 1) / world;
   const int64_t v0 = per * rank;
@@ -170,7 +196,19 @@ __global__ void __launch_bounds__(256)
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = v0 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < v1; i += stride) {
     float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    if (kInFp32) {
+    if (mc_in) {
+      if (kInFp32) {
+        const uint4 a = multimem_ld_sum<float>(reinterpret_cast<const float*>(mc_in) + i * 8);
+        const uint4 b = multimem_ld_sum<float>(reinterpret_cast<const float*>(mc_in) + i * 8 + 4);
+        g[0] = __uint_as_float(a.x); g[1] = __uint_as_float(a.y);
+        g[2] = __uint_as_float(a.z); g[3] = __uint_as_float(a.w);
+        g[4] = __uint_as_float(b.x); g[5] = __uint_as_float(b.y);
+        g[6] = __uint_as_float(b.z); g[7] = __uint_as_float(b.w);
+      } else {
+        acc8(g, multimem_ld_sum<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(mc_in) +
+                                               i * 8));
+      }
+    } else if (kInFp32) {
 #pragma unroll
       for (int k = 0; k < kMaxRanks; ++k) {
         if (k < world) {
@@ -198,10 +236,14 @@ __global__ void __launch_bounds__(256)
     o.y = pack_bf16x2(g[2] * scale, g[3] * scale);
     o.z = pack_bf16x2(g[4] * scale, g[5] * scale);
     o.w = pack_bf16x2(g[6] * scale, g[7] * scale);
+    if (mc_out) {
+      multimem_st_v4(reinterpret_cast<uint4*>(mc_out) + i, o);  // one store reaches every rank
+    } else {
 #pragma unroll
-    for (int k = 0; k < kMaxRanks; ++k)
-      if (k < world)
-        reinterpret_cast<uint4*>(out.p[(rank + k) % world])[i] = o;
+      for (int k = 0; k < kMaxRanks; ++k)
+        if (k < world)
+          reinterpret_cast<uint4*>(out.p[(rank + k) % world])[i] = o;
+    }
   }
   if (last_block_done(counter)) signal_all(flags, world, rank, slot + 1, epoch, threadIdx.x);
 }
@@ -295,14 +337,19 @@ extern "C" int mb200_allgather_pull(void* dst, const void* const* src_ptrs, int6
                                     int* status, void* stream) {
   if (world > kMaxRanks || (shard_elems & 7)) return 1001;
   if (chunk_flags && (chunk_elems & 7)) return 1001;
-  const int grid = n_blocks > 0 ? n_blocks : comm_grid(shard_elems * world / 8, 256 * 8, 296);
+  const int grid = n_blocks > 0 ? n_blocks
+                   : chunk_flags ? comm_grid(shard_elems * world / 8, 256 * 8, 296)
+                                 : comm_grid(shard_elems / 8, 256 * 8, 128);
   allgather_pull_kernel<<<grid, 256, 0, ST(stream)>>>(
       reinterpret_cast<__nv_bfloat16*>(dst), make_peers(src_ptrs, world), shard_elems, rank, world,
       my_flags, wait_slot, wait_epoch, chunk_flags, chunk_elems, chunk_epoch, status);
   return (int)cudaGetLastError();
 }
 
-extern "C" int mb200_rs_adamw(const void* const* grad_ptrs, const void* const* flag_ptrs,
+// mc_grads: multicast mapping of the gradient buffers at the same offset as grad_ptrs (the
+// reduction then happens in the switch), or null for plain peer loads.
+extern "C" int mb200_rs_adamw(const void* const* grad_ptrs, const void* mc_grads,
+                              const void* const* flag_ptrs,
                               float* master, float* m, float* v, void* param_shard,
                               int64_t shard_elems, int rank, int world, int grad_slot,
                               int param_slot, uint32_t epoch, float lr, float beta1, float beta2,
@@ -311,16 +358,19 @@ extern "C" int mb200_rs_adamw(const void* const* grad_ptrs, const void* const* f
   if (world > kMaxRanks || (shard_elems & 7)) return 1001;
   const double bc1 = 1.0 - pow((double)beta1, (double)step);
   const double bc2 = 1.0 - pow((double)beta2, (double)step);
-  const int grid = n_blocks > 0 ? n_blocks : comm_grid(shard_elems / 8, 256 * 4, 592);
+  const int grid = n_blocks > 0 ? n_blocks
+                                 : comm_grid(shard_elems / 8, 256 * 4, mc_grads ? 148 : 592);
   rs_adamw_kernel<<<grid, 256, 0, ST(stream)>>>(
-      make_peers(grad_ptrs, world), make_peers(flag_ptrs, world), master, m, v,
+      make_peers(grad_ptrs, world), mc_grads, make_peers(flag_ptrs, world), master, m, v,
       reinterpret_cast<__nv_bfloat16*>(param_shard), shard_elems, rank, world, grad_slot,
       param_slot, epoch, lr, beta1, beta2, eps, wd, (float)(1.0 / bc1), (float)(1.0 / sqrt(bc2)),
       grad_scale, counter, status);
   return (int)cudaGetLastError();
 }
 
+// mc_in / mc_out: multicast mappings of the input / output buffers (null: peer loads/stores).
 extern "C" int mb200_allreduce_scale_cast(const void* const* in_ptrs, const void* const* out_ptrs,
+                                          const void* mc_in, void* mc_out,
                                           const void* const* flag_ptrs, int64_t n, int in_fp32,
                                           int rank, int world, float scale, int slot,
                                           uint32_t epoch, unsigned int* counter, int n_blocks,
@@ -330,11 +380,13 @@ extern "C" int mb200_allreduce_scale_cast(const void* const* in_ptrs, const void
   Peers in = make_peers(in_ptrs, world), out = make_peers(out_ptrs, world),
         fl = make_peers(flag_ptrs, world);
   if (in_fp32)
-    allreduce_kernel<true><<<grid, 256, 0, ST(stream)>>>(in, out, fl, n, rank, world, scale, slot,
-                                                          epoch, counter, status);
+    allreduce_kernel<true><<<grid, 256, 0, ST(stream)>>>(in, out, mc_in, mc_out, fl, n, rank,
+                                                          world, scale, slot, epoch, counter,
+                                                          status);
   else
-    allreduce_kernel<false><<<grid, 256, 0, ST(stream)>>>(in, out, fl, n, rank, world, scale, slot,
-                                                           epoch, counter, status);
+    allreduce_kernel<false><<<grid, 256, 0, ST(stream)>>>(in, out, mc_in, mc_out, fl, n, rank,
+                                                           world, scale, slot, epoch, counter,
+                                                           status);
   // Results from every rank must have landed before a consumer on this stream reads them.
   wait_kernel<<<1, 32, 0, ST(stream)>>>(fl.p[rank], world, slot + 1, epoch, status);
   return (int)cudaGetLastError();

@@ -2,6 +2,7 @@
 // with bounded waits, and strong (system-scope) 16-byte loads for peer memory.
 #pragma once
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -75,5 +76,46 @@ __device__ __forceinline__ uint4 ld_nc_v4(const void* p) {
   return v;
 }
 
+// ------------------------------------------------------------------------ multimem --
+// NVSwitch multicast ("NVLS") accesses.  `mc` is an address inside a multicast mapping that
+// every rank of the group has bound its own buffer to.  A ld_reduce makes the switch add
+// the ranks' copies (fp32 accumulation for the 16-bit types) and returns one 16-byte
+// vector; a st writes the vector into every rank's copy.
+template <typename T>
+__device__ __forceinline__ uint4 multimem_ld_sum(const void* mc);
+template <>
+__device__ __forceinline__ uint4 multimem_ld_sum<float>(const void* mc) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc)
+               : "memory");
+  return v;
+}
+template <>
+__device__ __forceinline__ uint4 multimem_ld_sum<__nv_bfloat16>(const void* mc) {
+  uint4 v;
+  asm volatile(
+      "multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+      : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+      : "l"(mc)
+      : "memory");
+  return v;
+}
+template <>
+__device__ __forceinline__ uint4 multimem_ld_sum<__half>(const void* mc) {
+  uint4 v;
+  asm volatile(
+      "multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+      : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+      : "l"(mc)
+      : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st_v4(void* mc, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc), "r"(v.x),
+               "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
 
 }  // namespace mb200

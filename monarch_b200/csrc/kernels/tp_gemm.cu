@@ -10,7 +10,8 @@
 //   epilogue warps, tile by tile, while later tiles are still on the tensor cores);
 //   rs_finish sums the slots in fp32 (+ residual) on the owner after a flag barrier.
 //
-// No TMA touches peer memory and nothing is multicast.
+// No tensor-map TMA and no multicast on peer memory: peer data moves with plain loads and
+// stores or with non-multicast bulk copies (cp.async.bulk) issued by the copy CTAs.
 #include <cuda.h>
 #include <cuda_runtime.h>
 

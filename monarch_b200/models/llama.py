@@ -203,6 +203,9 @@ class LocalParamStore:
     def begin_step(self):
         pass
 
+    def begin_eval(self):
+        pass
+
     def pre_forward(self, ui: int):
         pass
 
@@ -466,7 +469,7 @@ class LlamaEngine:
         """Forward only (evaluation): mean token loss."""
         cfg, st = self.cfg, self.store
         B, S = tokens.shape
-        st.begin_step()
+        st.begin_eval()
         st.pre_forward(0)
         x = ops.embedding_fwd(st.unit_params(0)["embed"], tokens.reshape(-1))
         st.post_forward(0)
@@ -485,6 +488,8 @@ class LlamaEngine:
         hf, _ = ops.rmsnorm_fwd(x, wh["final_norm"], cfg.eps)
         logits = ops.gemm(hf, w_out)
         loss = ops.cross_entropy_(logits, targets.reshape(-1), 0.0).mean()
+        if cfg.tie_embeddings:
+            st.post_forward(0)
         st.post_forward(hu)
         return loss
 

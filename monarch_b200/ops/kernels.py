@@ -87,9 +87,9 @@ _OPTIONAL: dict[str, list] = {
     "mb200_wait_flags": [_vp, _i, _i, ctypes.c_uint32, _vp, _vp],
     "mb200_allgather_pull": [_vp, _vp, _i64, _i, _i, _vp, _i, ctypes.c_uint32, _vp, _i64,
                              ctypes.c_uint32, _i, _vp, _vp],
-    "mb200_rs_adamw": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, ctypes.c_uint32, _f, _f,
+    "mb200_rs_adamw": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, ctypes.c_uint32, _f, _f,
                        _f, _f, _f, _i, _f, _vp, _i, _vp, _vp],
-    "mb200_allreduce_scale_cast": [_vp, _vp, _vp, _i64, _i, _i, _i, _f, _i, ctypes.c_uint32, _vp,
+    "mb200_allreduce_scale_cast": [_vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _f, _i, ctypes.c_uint32, _vp,
                                    _i, _vp, _vp],
     "mb200_peer_copy": [_vp, _vp, _i64, _vp, ctypes.c_uint32, _vp, _i, _vp],
     "mb200_enable_peer_access": [_i, _i],
@@ -118,6 +118,10 @@ _OPTIONAL: dict[str, list] = {
     "mb200_moe_combine": [_vp, _i, _i, _i, _vp, _i, _vp, _i, _vp],
     "mb200_pingpong": [_vp, _vp, _vp, _vp, ctypes.c_longlong, _i, ctypes.c_uint32, _i, _vp, _vp,
                        _vp],
+    "mb200_coll_stage": [_vp, _vp, _i64, _vp, _i, _i, _i, ctypes.c_uint32, _vp, _i, _vp],
+    "mb200_coll_reduce": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i, _i, _f, _i, _vp, _i, _i,
+                          _i, _i, ctypes.c_uint32, _vp, _i, _vp, _vp],
+    "mb200_coll_gather": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, ctypes.c_uint32, _i, _vp, _vp],
     "mb200_gather_chunks": [_vp, _vp, ctypes.c_longlong, _i, _i, ctypes.c_longlong,
                             ctypes.c_longlong, ctypes.c_longlong, _vp, ctypes.c_uint32, _vp, _i,
                             ctypes.c_uint32, _i, _vp, _vp],
@@ -138,7 +142,10 @@ def gemm_impl() -> int:
 
 def status_word(device: torch.device | int | None = None) -> torch.Tensor:
     """Per-device int32 status word written by kernels whose bounded waits ran out."""
-    idx = torch.cuda.current_device() if device is None else torch.device(device).index or 0
+    idx = None if device is None else (device if isinstance(device, int)
+                                       else torch.device(device).index)
+    if idx is None:     # no device given, or an index-less "cuda": the current device
+        idx = torch.cuda.current_device()
     t = _status.get(idx)
     if t is None:
         t = torch.zeros(4, dtype=torch.int32, device=f"cuda:{idx}")
@@ -146,15 +153,56 @@ def status_word(device: torch.device | int | None = None) -> torch.Tensor:
     return t
 
 
+_STATUS_TEXT = {1: "mbarrier wait timed out inside a kernel",
+                2: "wait on a peer/ready flag timed out inside a kernel",
+                3: "kernel rejected its arguments",
+                4: "a kernel's bounds check refused an access"}
+
+
+def status_text(v: int) -> str:
+    return _STATUS_TEXT.get(int(v), f"kernel status {int(v)}")
+
+
+def raise_status(v: int, device=None) -> None:
+    """Raise :class:`KernelError` for a non-zero status value already read from the device
+    (and clear the sticky word so that later kernels wait normally again)."""
+    if int(v) != 0:
+        status_word(device).zero_()
+        raise KernelError(status_text(v))
+
+
 def check_status(device=None) -> None:
     """Synchronising check of the status word; raises KernelError on a recorded timeout."""
-    t = status_word(device)
-    v = int(t[0].item())
-    if v != 0:
-        t.zero_()
-        raise KernelError({1: "mbarrier wait timed out inside a kernel",
-                           2: "wait on a peer/ready flag timed out inside a kernel",
-                           3: "kernel rejected its arguments"}.get(v, f"kernel status {v}"))
+    raise_status(int(status_word(device)[0].item()), device)
+
+
+class StatusWatch:
+    """Reads a device's status word without stalling the stream: ``post()`` queues a copy
+    into pinned host memory behind the work issued so far, ``poll()`` raises once such a
+    copy has landed with a non-zero value.  A training loop that never synchronises still
+    learns of a timed-out device-side wait one step later instead of never."""
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+        self._host = torch.zeros(4, dtype=torch.int32).pin_memory()
+        self._event: Optional[torch.cuda.Event] = None
+
+    def post(self) -> None:
+        self._host.copy_(status_word(self.device), non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(self.device))
+        self._event = ev
+
+    def poll(self, wait: bool = False) -> None:
+        ev = self._event
+        if ev is None:
+            return
+        if wait:
+            ev.synchronize()
+        elif not ev.query():
+            return
+        self._event = None
+        raise_status(int(self._host[0]), self.device)
 
 
 def stream_ptr() -> int:

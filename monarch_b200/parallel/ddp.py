@@ -80,6 +80,7 @@ class DDPParamStore(LocalParamStore):
                     self._epoch += 1
                     K.check(K.lib().mb200_allreduce_scale_cast(
                         self._grads_sym.ptrs_at(off), self._grads_sym.ptrs_at(off),
+                        self._grads_sym.mc_at(off), self._grads_sym.mc_at(off),
                         self._flags.ptrs, n, 0, self.rank, self.world, self.reduce_scale, 0,
                         self._epoch, self._flags.counter.data_ptr(), 0,
                         K.status_word(self.device).data_ptr(), K.stream_ptr()),

@@ -135,7 +135,11 @@ class FSDPParamStore:
         self._buf_refs = [0] * n_buffers
         self._buf_age = [0] * n_buffers
         self._clock = 0
+        # Number of training steps begun.  Doubles as the epoch of the cross-rank flags:
+        # the update of step k publishes epoch k, so gathers inside training step k wait
+        # for epoch k-1 and gathers after it (evaluation, checkpointing) for epoch k.
         self.step_count = 0
+        self._in_train_step = False
         self._adam_offset = 0
         self._phase = "fwd"
         self._hyper = dict(lr=1e-4, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1, grad_scale=1.0)
@@ -206,10 +210,9 @@ class FSDPParamStore:
     def _issue_gather(self, ui: int, dst: torch.Tensor, s: int) -> None:
         if self.comm == "fused":
             n_units = len(self.layout.units)
-            wait_epoch = self.step_count - 1 if self.step_count > 1 else 0
             K.check(K.lib().mb200_allgather_pull(
                 dst.data_ptr(), self._shards_sym.ptrs_at(self.shard_offsets[ui]), s, self.rank,
-                self.world, self._flags.my_ptr, n_units + ui, wait_epoch, None, 0, 0, 0,
+                self.world, self._flags.my_ptr, n_units + ui, self._wait_epoch(), None, 0, 0, 0,
                 K.status_word(self.device).data_ptr(), K.stream_ptr()), "allgather_pull")
         else:
             src = self._shard(self.param_shards, ui)
@@ -271,7 +274,18 @@ class FSDPParamStore:
     # --------------------------------------------------------------------- store hooks
     def begin_step(self) -> None:
         self.step_count += 1
+        self._in_train_step = True
         self._phase = "fwd"
+        self._invalidate_gathered()
+
+    def begin_eval(self) -> None:
+        """Start of a forward-only pass: no optimizer step follows, so neither the flag
+        epoch nor AdamW's step moves; gathered copies from before are dropped."""
+        self._in_train_step = False
+        self._phase = "fwd"
+        self._invalidate_gathered()
+
+    def _invalidate_gathered(self) -> None:
         for b in range(len(self._bufs)):  # gathered copies of the previous step are stale
             if self._buf_refs[b] == 0:
                 self._buf_unit[b] = None
@@ -303,7 +317,10 @@ class FSDPParamStore:
         return (self.layout.units[ui].size + self._chunk - 1) // self._chunk
 
     def _wait_epoch(self) -> int:
-        return self.step_count - 1 if self.step_count > 1 else 0
+        """The "shard updated" epoch a gather must see on every rank: the previous step's
+        inside a training step (this step's updates come after its gathers), the last
+        step's outside one.  0 (no wait) before the first update."""
+        return max(0, self.step_count - 1 if self._in_train_step else self.step_count)
 
     def _gather_plain(self, ui: int, b: int, c_end: int) -> None:
         """Pull chunks [frontier, c_end) with the copy-only kernel on the compute stream
@@ -382,8 +399,8 @@ class FSDPParamStore:
             cs.wait_event(ev)
             with torch.cuda.stream(cs):
                 K.check(K.lib().mb200_rs_adamw(
-                    self._grads_sym.ptrs_at(u.offset), self._flags.ptrs,
-                    self._shard(self.master, ui).data_ptr(), self._shard(self.m, ui).data_ptr(),
+                    self._grads_sym.ptrs_at(u.offset), self._grads_sym.mc_at(u.offset),
+                    self._flags.ptrs, self._shard(self.master, ui).data_ptr(), self._shard(self.m, ui).data_ptr(),
                     self._shard(self.v, ui).data_ptr(),
                     self._shard(self.param_shards, ui).data_ptr(), s, self.rank, self.world, ui,
                     n_units + ui, self.step_count, h["lr"], h["beta1"], h["beta2"], h["eps"],
@@ -410,6 +427,7 @@ class FSDPParamStore:
         by :meth:`set_hyper`; this joins the comm stream and records the values for the
         next step."""
         self.set_hyper(lr=lr, beta1=beta1, beta2=beta2, eps=eps, wd=wd, grad_scale=grad_scale)
+        self._in_train_step = False
         if self._cuda and self._comm_stream is not None:
             torch.cuda.current_stream().wait_stream(self._comm_stream)
 
@@ -418,6 +436,7 @@ class FSDPParamStore:
         """All-gather of every unit into one flat bf16 buffer (checkpointing)."""
         if self._cuda:
             torch.cuda.synchronize(self.device)
+            K.check_status(self.device)   # shards behind a timed-out collective are not sound
         dist.barrier(group=self.group)
         full = torch.empty(self.layout.total, dtype=bf16, device=self.device)
         for ui, u in enumerate(self.layout.units):

@@ -9,6 +9,7 @@ touches the memory afterwards is this package's own kernels.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import List, Optional
 
 import torch
@@ -41,13 +42,25 @@ class SymmBuffer:
         self.handle = symm_mem.rendezvous(self.tensor, group)
         self.ptrs: List[int] = [int(p) for p in self.handle.buffer_ptrs]
         assert self.ptrs[self.rank] == self.tensor.data_ptr()
+        # NVSwitch multicast mapping of the same buffers (0 when the fabric or the driver
+        # has no NVLS support): the target of this package's multimem.ld_reduce / multimem.st
         self.multicast_ptr: int = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+        if os.environ.get("MB200_NVLS", "1") == "0":
+            self.multicast_ptr = 0
         self._elt = self.tensor.element_size()
 
     def ptrs_at(self, elem_offset: int):
         """ctypes array of every rank's address of element ``elem_offset``."""
         off = elem_offset * self._elt
         return ptr_array([p + off for p in self.ptrs])
+
+    def mc_at(self, elem_offset: int) -> Optional[int]:
+        """Multicast address of element ``elem_offset`` (None without NVLS): a
+        ``multimem.ld_reduce`` there returns the sum over all ranks' copies, a
+        ``multimem.st`` writes all of them."""
+        if not self.multicast_ptr:
+            return None
+        return self.multicast_ptr + elem_offset * self._elt
 
     def peer_view(self, rank: int, numel: int, offset: int = 0) -> torch.Tensor:
         return self.handle.get_buffer(rank, (numel,), self.tensor.dtype, offset)

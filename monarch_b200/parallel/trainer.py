@@ -59,10 +59,35 @@ class Trainer:
         shape = (micro_batch, seq_len)
         self._tok_dev = torch.empty(shape, dtype=torch.int64, device=self.device)
         self._tgt_dev = torch.empty(shape, dtype=torch.int64, device=self.device)
+        # Device-side waits are bounded and report through a status word; a step whose
+        # collective gave up must not pass for a step that trained.
+        self._watch = None
+        if self.device.type == "cuda":
+            from ..ops.kernels import StatusWatch
+            self._watch = StatusWatch(self.device)
 
     # -------------------------------------------------------------------------------
     def step_device(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
-        """One optimizer step on device-resident inputs; returns the device loss tensor."""
+        """One optimizer step on device-resident inputs; returns the device loss tensor.
+        Never blocks on the device: a bounded wait that ran out inside a kernel of this
+        step raises :class:`~monarch_b200.ops.kernels.KernelError` from the next call (or
+        from :meth:`check`)."""
+        if self._watch is not None:
+            self._watch.poll()
+        loss = self._step_device(tokens, targets)
+        if self._watch is not None:
+            self._watch.post()
+        return loss
+
+    def check(self) -> None:
+        """Wait for the device and raise if any kernel since the last check recorded a
+        failed wait.  Called before anything is written from the parameters."""
+        if self._watch is not None:
+            self._watch.poll(wait=True)
+            from ..ops import kernels as K
+            K.check_status(self.device)
+
+    def _step_device(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         if hasattr(self.store, "set_hyper"):
             self.store.set_hyper(lr=self.lr)  # sharded stores update inside backward
         loss = self.engine.forward_backward(tokens, targets)
@@ -75,7 +100,10 @@ class Trainer:
         self._tok_dev.copy_(tokens, non_blocking=True)
         self._tgt_dev.copy_(targets, non_blocking=True)
         loss = self.step_device(self._tok_dev, self._tgt_dev)
-        return float(loss.item())
+        value = float(loss.item())       # synchronises: the status copy has landed too
+        if self._watch is not None:
+            self._watch.poll(wait=True)
+        return value
 
     @property
     def h2d_bytes_per_step(self) -> int:
@@ -89,6 +117,7 @@ class Trainer:
     def state_dict(self) -> dict:
         """Hugging Face-named model ``state_dict`` (full tensors, on every rank)."""
         from ..models.llama import to_hf_state_dict
+        self.check()
         return to_hf_state_dict(self.cfg, self.layout, self.store.full_params())
 
     def save_checkpoint(self, path: str) -> None:
@@ -98,6 +127,7 @@ class Trainer:
         Hugging Face-named view of the same weights is :meth:`state_dict`."""
         import json
         from ..random import get_rng_state_all
+        self.check()      # never write shards that a timed-out collective left inconsistent
         os.makedirs(path, exist_ok=True)
         sd = {k: (v.detach().cpu() if isinstance(v, torch.Tensor) else v)
               for k, v in self.store.state_dict_shard().items()}

@@ -371,18 +371,11 @@ class Client:
         ranks = self.root_mesh._ndslice.ranks()
         self.send(self.root_mesh, ("init_pg", "127.0.0.1", port, ranks))
 
-    def ensure_comm(self, mesh: "DeviceMesh", dims: Tuple[str, ...]) -> Tuple[int, ...]:
-        """Process groups over ``dims`` of ``mesh``: one group per combination of the other
-        dims' coordinates.  Returns the key workers use to look their group up."""
-        self.ensure_process_group()
+    def _groups_over(self, mesh: "DeviceMesh", dims: Tuple[str, ...]):
         sl = mesh._ndslice
         labels = list(mesh._labels)
         idx = [labels.index(d) for d in dims]
         key = (sl.offset, tuple(sl.sizes), tuple(sl.strides), tuple(idx))
-        hkey = tuple(hash(key) % (1 << 62) for _ in range(1))
-        if key in self._comms:
-            return hkey
-        self._comms.add(key)
         other = [i for i in range(len(labels)) if i not in idx]
         groups: List[List[int]] = []
         for oc in itertools.product(*[range(sl.sizes[i]) for i in other]):
@@ -395,6 +388,51 @@ class Client:
                     coord[i] = c
                 ranks.append(sl.nditem(coord))
             groups.append(ranks)
+        return key, groups
+
+    def ensure_comm(self, mesh: "DeviceMesh", dims: Tuple[str, ...], stream_id: int = 0,
+                    own: bool = False) -> Tuple[int, ...]:
+        """Communicators over ``dims`` of ``mesh``: one per combination of the other dims'
+        coordinates.  Returns the key workers use to look theirs up.
+
+        ``own=True`` (GPU workers, operations the NVLink kernels cover): every member
+        allocates a staging buffer and exports a CUDA IPC handle, the handles come back to
+        the controller in the reply and go out again in the next message -- the bootstrap
+        rides the actor control plane and needs no ``torch.distributed`` (the reference
+        bootstraps NCCL the same way: the unique id travels in a worker message,
+        monarch_tensor_worker/src/lib.rs:303-364).  One communicator per (dims, stream):
+        collectives of two streams may overlap on the GPU and must not share staging.
+        Otherwise: ``torch.distributed`` groups (gloo on CPU workers; NCCL for what the
+        kernels do not cover)."""
+        key, groups = self._groups_over(mesh, dims)
+        if own:
+            okey = ("own", key, stream_id)
+            hkey = (hash(okey) % (1 << 62),)
+            if okey in self._comms:
+                return hkey
+            self.flush()
+            root = self.root_mesh._workers
+            exports = root.comm_export.call(hkey, groups).get(timeout=120)
+            by_rank = {}
+            for point, exp in exports.items():
+                if isinstance(exp, dict) and "error" in exp:
+                    raise RuntimeError(f"communicator over {dims}: {exp['error']}")
+                if exp is not None:
+                    by_rank[exp["rank"]] = exp
+            for ranks in groups:
+                devs = [(by_rank[r]["host"], by_rank[r]["device"]) for r in ranks]
+                if len(set(devs)) != len(devs):
+                    raise RuntimeError(
+                        f"communicator over {dims}: ranks {ranks} share a GPU {devs}; kernels "
+                        "that wait on one another need one GPU per rank")
+            root.comm_connect.broadcast(hkey, by_rank)
+            self._comms.add(okey)
+            return hkey
+        self.ensure_process_group()
+        hkey = (hash(key) % (1 << 62),)
+        if key in self._comms:
+            return hkey
+        self._comms.add(key)
         self.send(self.root_mesh, ("split_comm", hkey, groups))
         return hkey
 
@@ -565,7 +603,8 @@ class Tensor(torch.Tensor):
         if _inplace and tuple(out_fake.shape) != tuple(f.shape):
             raise ValueError("in-place reduce needs matching input and output shapes")
         client = m.client
-        key = client.ensure_comm(m, dims)
+        own = client.use_cuda and _own_collective(f.dtype, reduction)
+        key = client.ensure_comm(m, dims, self.stream.id, own=own)
         seq = client.new_seq()
         if _inplace:
             result = self
@@ -647,6 +686,15 @@ def _check_usable(t: Tensor) -> None:
     for b in t._borrowed_by:
         if b.mutable and get_active_stream() is not b.stream:
             raise RuntimeError("tensor is mutably borrowed by another stream; drop the borrow first")
+
+
+def _own_collective(dtype, reduction: str) -> bool:
+    """Whether GPU workers run this reduce on the package's NVLink kernels (the rest --
+    bitwise reductions, dtypes without an arithmetic kernel -- goes to NCCL)."""
+    if os.environ.get("MB200_TE_COLLECTIVES", "own") != "own":
+        return False
+    from ..parallel import meshcomm
+    return meshcomm.supports(dtype, None if reduction == "stack" else reduction)
 
 
 def reduce(tensors, dims, reduction="sum", scatter=False, mesh=None, _inplace=False):

@@ -118,21 +118,14 @@ def _manager_for_current_proc() -> _Manager:
 
 _peer_cache: Dict[tuple, int] = {}
 _copy_state: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
-_peer_enabled: set = set()
 
 
 def _ensure_peer_access(dev: int, other: int) -> None:
-    """A kernel on ``dev`` is about to dereference memory of device ``other`` (an IPC mapping
-    of another process's buffer is opened on the owner's device): peer access must be on in
-    that direction, or the first access faults."""
-    if dev == other or (dev, other) in _peer_enabled:
-        return
-    from ..ops import kernels as K
-    rc = K.lib().mb200_enable_peer_access(dev, other)
-    if rc == 1003:
-        raise RDMAError(f"GPU {dev} has no peer path to GPU {other}")
-    K.check(rc, "enable_peer_access", 0)
-    _peer_enabled.add((dev, other))
+    from ..ops import ipc
+    try:
+        ipc.ensure_peer_access(dev, other)
+    except ipc.PeerAccessError as e:
+        raise RDMAError(str(e)) from None
 
 
 def _device_copy_ptr(dst_ptr: int, src_ptr: int, nbytes: int, dev_index: int) -> None:
@@ -165,26 +158,9 @@ def _device_copy(dst: torch.Tensor, src: torch.Tensor) -> None:
     _device_copy_ptr(dst.data_ptr(), src.data_ptr(), dst.numel(), idx)
 
 
-_ipc_open: Dict[Tuple[bytes, int], int] = {}   # (handle, reader device) -> mapped base address
-
-
 def _open_ipc(handle: bytes, reader_device: int) -> int:
-    """Map another process's allocation for kernels of ``reader_device`` (once per handle and
-    device; CUDA refuses to open the same handle twice in one process)."""
-    import ctypes
-    from ..ops import kernels as K
-    key = (handle, reader_device)
-    base = _ipc_open.get(key)
-    if base is None:
-        torch.cuda.init()
-        with torch.cuda.device(reader_device):
-            torch.cuda.current_stream()          # makes sure the device's context exists
-            out = ctypes.c_void_p(0)
-            K.check(K.lib().mb200_ipc_open(handle, reader_device, ctypes.byref(out)),
-                    "ipc_open", 0)
-        base = int(out.value)
-        _ipc_open[key] = base
-    return base
+    from ..ops import ipc
+    return ipc.open_ipc(handle, reader_device)
 
 
 class RDMABuffer:

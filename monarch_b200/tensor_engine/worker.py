@@ -263,6 +263,10 @@ class TensorWorker(Actor):
         self.env = _Env(self.core)
         self.streams: Dict[int, Any] = {0: None}
         self.groups: Dict[Tuple[int, ...], Any] = {}
+        # own NVLink communicators: key -> (MeshComm, ranks); and the buffers exported for
+        # communicators whose peers have not been connected yet
+        self.comms: Dict[Tuple[int, ...], Any] = {}
+        self._comm_pending: Dict[Tuple[int, ...], Any] = {}
         self.borrows: Dict[int, Any] = {}
         self.recordings: Dict[int, List[tuple]] = {}
         self.pipes: Dict[int, WorkerPipe] = {}
@@ -313,6 +317,57 @@ class TensorWorker(Actor):
         for m in msgs:
             getattr(self, "_m_" + m[0])(*m[1:])
         return self._fetch(*fetch)
+
+    # ------------------------------------------------- own NVLink communicators
+    @endpoint
+    def comm_export(self, key: Tuple[int, ...], all_groups: List[List[int]]):
+        """First half of a communicator's bootstrap: allocate this rank's flag + staging
+        buffer and return what its peers need to map it (a CUDA IPC handle and where it
+        lives).  The controller hands every member the exports of its group in
+        ``comm_connect``.  Ranks outside every group answer None."""
+        try:
+            mine = next((g for g in all_groups if self.rank in g), None)
+            if mine is None:
+                return None
+            if not self.use_cuda:
+                return {"error": f"worker {self.rank} has no GPU"}
+            import socket
+            from ..ops import ipc
+            from ..parallel.meshcomm import MeshComm
+            torch.cuda.set_device(self.device)
+            local = MeshComm.allocate_local(self.device)
+            torch.cuda.synchronize(self.device)      # zeroed before any peer can touch it
+            exp = ipc.export_handle(local)
+            exp.update(rank=self.rank, host=socket.gethostname())
+            self._comm_pending[key] = (local, list(mine))
+            return exp
+        except Exception as ex:  # noqa: BLE001 - reported to the controller, which raises
+            return {"error": f"{type(ex).__name__}: {ex}"}
+
+    @endpoint
+    def comm_connect(self, key: Tuple[int, ...], exports: Dict[int, dict]) -> None:
+        """Second half: map the peers' buffers.  A failure here surfaces at the first
+        collective that asks for the communicator."""
+        pend = self._comm_pending.pop(key, None)
+        if pend is None:
+            return
+        local, ranks = pend
+        try:
+            from ..parallel.meshcomm import MeshComm
+            torch.cuda.set_device(self.device)
+            comm = MeshComm.from_exports(ranks.index(self.rank), [exports[r] for r in ranks],
+                                         local, self.device)
+            self.comms[key] = (comm, ranks)
+        except Exception as ex:  # noqa: BLE001
+            self.comms[key] = (RuntimeError(f"{type(ex).__name__}: {ex}"), ranks)
+
+    def _own_reduce(self, comm, t, reduction, scatter, inplace):
+        """One reduce message on the NVLink kernels (current stream)."""
+        if reduction == "stack":
+            return comm.all_to_all(t) if scatter else comm.all_gather(t)
+        if scatter:
+            return comm.reduce_scatter(t, reduction)
+        return comm.all_reduce(t, reduction, out=t if inplace else None)
 
     # -------------------------------------------------------------------- messages
     def _m_call(self, seq, results, mutates, fspec, args, kwargs, stream) -> None:
@@ -435,6 +490,18 @@ class TensorWorker(Actor):
                 # not left waiting, and keep the failure in this rank's result
                 t = torch.zeros(in_meta[0], dtype=in_meta[1], device=self.device)
                 inplace, out_ref = False, None
+            own = self.comms.get(key)
+            if own is not None:
+                comm, ranks = own
+                if isinstance(comm, Exception):
+                    raise comm
+                with self._stream_ctx(stream):
+                    out = self._own_reduce(comm, t, reduction, scatter, inplace)
+                    if out_ref is not None:
+                        self.env[out_ref.id].copy_(out)
+                        out = self.env[out_ref.id]
+                self.env[result.id] = out if failed is None else failed
+                return
             g, ranks = self.groups[key]
             n = len(ranks)
             with self._stream_ctx(stream):

@@ -1,16 +1,25 @@
 """Process-allocator daemon: runs on a host and starts procs there on behalf of remote
 clients.
 
-    python -m monarch_b200.tools.process_allocator --addr tcp!0.0.0.0:26600
+    python -m monarch_b200.tools.process_allocator --addr tcp!127.0.0.1:26600 \
+        [--program "python -m monarch_b200.actor.bootstrap_main"]
 
-A client that wants procs on this host connects once per proc (see ``remote_exec``), sends
-one JSON line ``{"argv": [...], "env": {...}, "cwd": ...}`` and then receives JSON lines
-``{"out": text}`` / ``{"err": text}`` / ``{"exit": code}``.  It may send ``{"signal": n}``.
+The daemon decides WHAT runs: its ``--program`` (default: this interpreter running
+``monarch_b200.actor.bootstrap_main``), in its own working directory.  A client only asks
+for one more instance of it: it connects once per proc (see ``remote_exec``), sends one JSON
+line ``{"start": 1, "env": {...}, "token": ...}`` and then receives JSON lines ``{"out": text}`` /
+``{"err": text}`` / ``{"exit": code}``.  Of the client's ``env`` only the bootstrap
+variables pass (prefixes ``HYPERACTOR_``, ``MONARCH_``, ``MB200_`` and the rank/rendezvous
+names in ``ENV_ALLOW``); a request that names a program (``argv``) or a directory (``cwd``)
+is refused.  The default bind is the loopback interface; to serve other hosts bind another
+address and set ``MB200_ALLOCATOR_TOKEN`` on both sides: with a token configured, requests
+without the same token are refused.  It may send ``{"signal": n}``.
 Heartbeats ``{"hb": 1}`` flow both ways every ``--heartbeat`` seconds; when the client has
 been silent for 3 intervals, or its connection drops, the proc is killed (SIGTERM, then
 SIGKILL): a host never keeps orphans of a vanished client.
 
-Parity: monarch_hyperactor/src/bin/process_allocator (the daemon), hyperactor_mesh
+Parity: monarch_hyperactor/src/bin/process_allocator (the daemon; the program is fixed by
+its ``--program`` option, common.rs:41), hyperactor_mesh
 alloc/remoteprocess.rs:73-108 (RemoteProcessAllocator), :940-1085 (heartbeats and the host
 watchdog); Python address syntax ``tcp!host:port`` (python/monarch/_src/actor/allocator.py
 :104-113).
@@ -18,8 +27,10 @@ watchdog); Python address syntax ``tcp!host:port`` (python/monarch/_src/actor/al
 from __future__ import annotations
 
 import argparse
+import hmac
 import json
 import os
+import shlex
 import signal
 import socket
 import subprocess
@@ -36,10 +47,32 @@ def parse_addr(addr: str):
     return host or "127.0.0.1", int(port)
 
 
+#: environment a client may set for the procs it asks for (prefixes and exact names)
+ENV_ALLOW_PREFIX = ("HYPERACTOR_", "MONARCH_", "MB200_", "MASTER_")
+# PYTHONPATH passes because the procs must import the client's actor classes; like the
+# bootstrap function it lets an accepted client choose code, which is what an actor
+# client does anyway -- who may be a client is decided by the bind address and the token.
+ENV_ALLOW = ("CUDA_VISIBLE_DEVICES", "LOCAL_RANK", "RANK", "WORLD_SIZE", "PYTHONPATH")
+#: never taken from a client, whatever its prefix
+ENV_DENY = ("MB200_ALLOCATOR_TOKEN",)
+
+
+def default_program() -> list:
+    return [sys.executable, "-m", "monarch_b200.actor.bootstrap_main"]
+
+
+def filter_env(env: dict) -> dict:
+    """The part of a client's environment request that the daemon honours."""
+    return {str(k): str(v) for k, v in (env or {}).items()
+            if (k.startswith(ENV_ALLOW_PREFIX) or k in ENV_ALLOW) and k not in ENV_DENY}
+
+
 class _Session(threading.Thread):
-    def __init__(self, conn: socket.socket, peer, heartbeat: float, registry: set):
+    def __init__(self, conn: socket.socket, peer, heartbeat: float, registry: set,
+                 program: list, token: str = ""):
         super().__init__(daemon=True)
         self.conn, self.peer, self.hb, self.registry = conn, peer, heartbeat, registry
+        self.program, self.token = list(program), token
         self.proc: subprocess.Popen | None = None
         self._wlock = threading.Lock()
         self._last_seen = time.monotonic()
@@ -89,15 +122,25 @@ class _Session(threading.Thread):
         self.registry.add(self)
         f = self.conn.makefile("rb")
         try:
-            req = json.loads(f.readline() or b"{}")
-            argv = req.get("argv")
-            if not argv:
-                self._send({"exit": 127, "error": "no argv"})
+            try:
+                req = json.loads(f.readline() or b"{}")
+            except ValueError:
+                req = None
+            if not isinstance(req, dict) or not req.get("start"):
+                self._send({"exit": 126, "error": "malformed request"})   # or a port probe
+                return
+            if self.token and not hmac.compare_digest(str(req.get("token") or ""), self.token):
+                self._send({"exit": 126, "error": "bad or missing allocator token"})
+                return
+            if req.get("argv") or req.get("cwd"):
+                self._send({"exit": 126, "error": "this daemon runs its own --program; a "
+                            "request may not name a program or a working directory"})
                 return
             env = dict(os.environ)
-            env.update(req.get("env") or {})
+            env.pop("MB200_ALLOCATOR_TOKEN", None)
+            env.update(filter_env(req.get("env")))
             try:
-                self.proc = subprocess.Popen(argv, env=env, cwd=req.get("cwd") or None,
+                self.proc = subprocess.Popen(self.program, env=env,
                                              stdout=subprocess.PIPE, stderr=subprocess.PIPE,
                                              start_new_session=True)
             except OSError as e:
@@ -138,8 +181,10 @@ class _Session(threading.Thread):
             self.registry.discard(self)
 
 
-def serve(addr: str, heartbeat: float = 5.0, ready=None) -> None:
+def serve(addr: str, heartbeat: float = 5.0, ready=None, program=None, token=None) -> None:
     host, port = parse_addr(addr)
+    program = list(program) if program else default_program()
+    token = os.environ.get("MB200_ALLOCATOR_TOKEN", "") if token is None else token
     srv = socket.socket(socket.AF_INET, socket.SOCK_STREAM)
     srv.setsockopt(socket.SOL_SOCKET, socket.SO_REUSEADDR, 1)
     srv.bind((host, port))
@@ -161,15 +206,18 @@ def serve(addr: str, heartbeat: float = 5.0, ready=None) -> None:
     while True:
         conn, peer = srv.accept()
         conn.setsockopt(socket.IPPROTO_TCP, socket.TCP_NODELAY, 1)
-        _Session(conn, peer, heartbeat, sessions).start()
+        _Session(conn, peer, heartbeat, sessions, program, token).start()
 
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("--addr", default="tcp!0.0.0.0:26600")
+    ap.add_argument("--addr", default="tcp!127.0.0.1:26600")
     ap.add_argument("--heartbeat", type=float, default=5.0)
+    ap.add_argument("--program", default=None,
+                    help="command line of the proc this daemon starts for its clients "
+                         "(default: this interpreter -m monarch_b200.actor.bootstrap_main)")
     a = ap.parse_args(argv)
-    serve(a.addr, a.heartbeat)
+    serve(a.addr, a.heartbeat, program=shlex.split(a.program) if a.program else None)
     return 0
 
 

@@ -2,11 +2,12 @@
 
 The process allocator of the client starts one of these per remote proc:
 
-    python -m monarch_b200.tools.remote_exec -- <argv of the real proc>
+    python -m monarch_b200.tools.remote_exec
 
 It picks the daemon from ``MB200_REMOTE_HOSTS`` (comma-separated ``tcp!host:port``) by the
-proc's rank (``HYPERACTOR_MESH_INDEX`` // ``MB200_PROCS_PER_HOST``), forwards the
-argv and the bootstrap environment, relays the remote stdout/stderr to its own (where the
+proc's rank (``HYPERACTOR_MESH_INDEX`` // ``MB200_PROCS_PER_HOST``), forwards the bootstrap
+environment (the daemon starts its own program; clients cannot name one) and the shared
+``MB200_ALLOCATOR_TOKEN`` when one is set, relays the remote stdout/stderr to its own (where the
 allocator's log tailer reads them), forwards SIGTERM/SIGINT, sends heartbeats, and exits
 with the remote exit code.  Killing it kills the remote proc (the daemon sees the
 connection drop)."""
@@ -20,16 +21,10 @@ import sys
 import threading
 import time
 
-from .process_allocator import parse_addr
-
-_FORWARD = ("HYPERACTOR_", "MONARCH_", "MB200_", "PYTHONPATH", "CUDA_VISIBLE_DEVICES",
-            "LOCAL_RANK", "RANK", "WORLD_SIZE", "MASTER_")
+from .process_allocator import filter_env, parse_addr
 
 
 def main(argv=None) -> int:
-    argv = list(sys.argv[1:] if argv is None else argv)
-    if "--" in argv:
-        argv = argv[argv.index("--") + 1:]
     hosts = [h for h in os.environ.get("MB200_REMOTE_HOSTS", "").split(",") if h]
     if not hosts:
         print("remote_exec: MB200_REMOTE_HOSTS is empty", file=sys.stderr)
@@ -37,7 +32,7 @@ def main(argv=None) -> int:
     rank = int(os.environ.get("HYPERACTOR_MESH_INDEX", "0"))
     per_host = max(1, int(os.environ.get("MB200_PROCS_PER_HOST", "1")))
     host, port = parse_addr(hosts[min(rank // per_host, len(hosts) - 1)])
-    env = {k: v for k, v in os.environ.items() if k.startswith(_FORWARD)}
+    env = filter_env(dict(os.environ))
     env["MB200_LOCAL_INDEX"] = str(rank % per_host)
     hb = float(os.environ.get("MB200_ALLOCATOR_HEARTBEAT", "5"))
     try:
@@ -55,7 +50,7 @@ def main(argv=None) -> int:
             except OSError:
                 pass
 
-    send({"argv": argv, "env": env, "cwd": os.environ.get("MB200_REMOTE_CWD")})
+    send({"start": 1, "env": env, "token": os.environ.get("MB200_ALLOCATOR_TOKEN", "")})
     for s in (signal.SIGTERM, signal.SIGINT):
         signal.signal(s, lambda n, _f: send({"signal": n}))
 

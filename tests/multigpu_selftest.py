@@ -3,7 +3,7 @@
 Run one process per GPU:
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 \
-        --master-port 29511 -m monarch_b200.parallel.selftest [--bench]
+        --master-port 29511 tests/multigpu_selftest.py [--bench]
 
 Each check compares the hand-written kernel against a torch.distributed (NCCL) or plain
 PyTorch fp32 computation of the same thing.  ``--bench`` also prints device-timed
@@ -18,9 +18,11 @@ import sys
 import torch
 import torch.distributed as dist
 
-from ..ops import kernels as K
-from ..ops import reference as R
-from .symm import FlagArray, SymmBuffer, ptr_array
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from monarch_b200.ops import kernels as K  # noqa: E402
+from monarch_b200.ops import reference as R  # noqa: E402
+from monarch_b200.parallel.symm import FlagArray, SymmBuffer, ptr_array  # noqa: E402
 
 bf16 = torch.bfloat16
 
@@ -103,24 +105,37 @@ def main() -> int:
     expect = x.float().clone()
     dist.all_reduce(expect)
     expect /= world
-    torch.cuda.synchronize()
-    dist.barrier()
-    K.check(lib.mb200_allreduce_scale_cast(buf.ptrs_at(0), buf.ptrs_at(0), flags.ptrs, n, 0, rank,
-                                           world, 1.0 / world, 2, 1, flags.counter.data_ptr(), 0,
-                                           status.data_ptr(), K.stream_ptr()), "allreduce", 2)
-    torch.cuda.synchronize()
-    K.check_status()
-    assert _rel(buf.tensor, expect) < 5e-3, _rel(buf.tensor, expect)
-    # fp32 in -> bf16 out
     fin = SymmBuffer(n, torch.float32, dev, zero=False)
-    fin.tensor.copy_(x.float())
-    torch.cuda.synchronize()
-    dist.barrier()
-    K.check(lib.mb200_allreduce_scale_cast(fin.ptrs_at(0), buf.ptrs_at(0), flags.ptrs, n, 1, rank,
-                                           world, 1.0 / world, 2, 2, flags.counter.data_ptr(), 0,
-                                           status.data_ptr(), K.stream_ptr()), "allreduce fp32", 2)
-    torch.cuda.synchronize()
-    assert _rel(buf.tensor, expect) < 5e-3
+    results["nvls_multicast"] = bool(buf.multicast_ptr)
+    ar_epoch = 0
+    # plain peer loads/stores first, then (where the fabric offers a multicast mapping) the
+    # multimem variant: reduction in the switch, one store reaching every rank
+    for use_mc in ([False, True] if buf.multicast_ptr else [False]):
+        mc = (lambda b: b.mc_at(0)) if use_mc else (lambda b: None)
+        buf.tensor.copy_(x)
+        torch.cuda.synchronize()
+        dist.barrier()
+        ar_epoch += 1
+        K.check(lib.mb200_allreduce_scale_cast(buf.ptrs_at(0), buf.ptrs_at(0), mc(buf), mc(buf),
+                                               flags.ptrs, n, 0, rank, world, 1.0 / world, 2,
+                                               ar_epoch, flags.counter.data_ptr(), 0,
+                                               status.data_ptr(), K.stream_ptr()), "allreduce", 2)
+        torch.cuda.synchronize()
+        K.check_status()
+        assert _rel(buf.tensor, expect) < 5e-3, (use_mc, _rel(buf.tensor, expect))
+        # fp32 in -> bf16 out
+        fin.tensor.copy_(x.float())
+        torch.cuda.synchronize()
+        dist.barrier()
+        ar_epoch += 1
+        K.check(lib.mb200_allreduce_scale_cast(fin.ptrs_at(0), buf.ptrs_at(0), mc(fin), mc(buf),
+                                               flags.ptrs, n, 1, rank, world, 1.0 / world, 2,
+                                               ar_epoch, flags.counter.data_ptr(), 0,
+                                               status.data_ptr(), K.stream_ptr()),
+                "allreduce fp32", 2)
+        torch.cuda.synchronize()
+        K.check_status()
+        assert _rel(buf.tensor, expect) < 5e-3, (use_mc, _rel(buf.tensor, expect))
 
     # ----------------------------------------------------- reduce-scatter + AdamW ----
     s = 1 << 18
@@ -130,23 +145,32 @@ def main() -> int:
     g.tensor.copy_(gl)
     gsum = gl.float().clone()
     dist.all_reduce(gsum)
-    master = torch.randn(s, device=dev)
-    m = torch.zeros(s, device=dev)
-    v = torch.zeros(s, device=dev)
-    pshard = torch.empty(s, dtype=bf16, device=dev)
-    pr, mr, vr = R.adamw(master.clone(), m.clone(), v.clone(), gsum[rank * s:(rank + 1) * s], 1e-2,
-                         0.9, 0.95, 1e-8, 0.1, 1, 1.0 / world)
-    torch.cuda.synchronize()
-    dist.barrier()
-    K.check(lib.mb200_rs_adamw(g.ptrs_at(0), flags.ptrs, master.data_ptr(), m.data_ptr(),
-                               v.data_ptr(), pshard.data_ptr(), s, rank, world, 4, 5, 1, 1e-2, 0.9,
-                               0.95, 1e-8, 0.1, 1, 1.0 / world, flags.counter.data_ptr(), 0,
-                               status.data_ptr(), K.stream_ptr()), "rs_adamw")
-    torch.cuda.synchronize()
-    K.check_status()
-    assert torch.allclose(master, pr, atol=2e-5), (master - pr).abs().max()
-    assert torch.allclose(m, mr, atol=1e-5) and torch.allclose(v, vr, atol=1e-5)
-    assert torch.equal(pshard, master.to(bf16))
+    master0 = torch.randn(s, device=dev)
+    pr, mr, vr = R.adamw(master0.clone(), torch.zeros(s, device=dev), torch.zeros(s, device=dev),
+                         gsum[rank * s:(rank + 1) * s], 1e-2, 0.9, 0.95, 1e-8, 0.1, 1, 1.0 / world)
+    for ei, use_mc in enumerate([False, True] if g.multicast_ptr else [False]):
+        master = master0.clone()
+        m = torch.zeros(s, device=dev)
+        v = torch.zeros(s, device=dev)
+        pshard = torch.empty(s, dtype=bf16, device=dev)
+        torch.cuda.synchronize()
+        dist.barrier()
+        K.check(lib.mb200_rs_adamw(g.ptrs_at(0), g.mc_at(0) if use_mc else None, flags.ptrs,
+                                   master.data_ptr(), m.data_ptr(), v.data_ptr(),
+                                   pshard.data_ptr(), s, rank, world, 4, 5, 1 + ei, 1e-2, 0.9,
+                                   0.95, 1e-8, 0.1, 1, 1.0 / world, flags.counter.data_ptr(), 0,
+                                   status.data_ptr(), K.stream_ptr()), "rs_adamw")
+        torch.cuda.synchronize()
+        K.check_status()
+        # the switch returns the fp32-accumulated sum rounded to bf16 once
+        if use_mc:
+            assert torch.allclose(master, pr, atol=3e-4), (master - pr).abs().max()
+            assert torch.allclose(m, mr, rtol=2e-2, atol=1e-4), (m - mr).abs().max()
+            assert torch.allclose(v, vr, rtol=3e-2, atol=1e-4), (v - vr).abs().max()
+        else:
+            assert torch.allclose(master, pr, atol=2e-5), (master - pr).abs().max()
+            assert torch.allclose(m, mr, atol=1e-5) and torch.allclose(v, vr, atol=1e-5)
+        assert torch.equal(pshard, master.to(bf16))
 
     # ------------------------------------------- fused all-gather -> GEMM ------------------
     # W [N, K] sits at an offset inside a flat buffer sharded over the ranks; one kernel
@@ -208,7 +232,7 @@ def main() -> int:
             K.check(lib.mb200_allgather_pull(ub2.data_ptr(), shard2.ptrs_at(0), sh2, rank, world,
                                              flags.my_ptr, 0, 0, None, 0, 0, 0, status.data_ptr(),
                                              K.stream_ptr()), "ag")
-            from .. import ops as _ops
+            from monarch_b200 import ops as _ops
             _ops.gemm(xb, ub2[: Ng2 * Kg2].view(Ng2, Kg2), out=ob)
 
         def nccl_sep():
@@ -216,7 +240,7 @@ def main() -> int:
             torch.matmul(xb, ub2[: Ng2 * Kg2].view(Ng2, Kg2).t(), out=ob)
 
         def gemm_only():
-            from .. import ops as _ops
+            from monarch_b200 import ops as _ops
             _ops.gemm(xb, ub2[: Ng2 * Kg2].view(Ng2, Kg2), out=ob)
 
         t_f, t_s, t_n, t_g = (_time(f, dev) for f in (fused, separate, nccl_sep, gemm_only))
@@ -283,8 +307,8 @@ def main() -> int:
     results["gemm_rs_rel_err"] = _rel(out_rs, expect_rs)
 
     # ------------------------------------------- fused FSDP == library-collective FSDP --
-    from ..models import PRESETS, LlamaEngine, ParamLayout
-    from .fsdp import FSDPParamStore
+    from monarch_b200.models import PRESETS, LlamaEngine, ParamLayout
+    from monarch_b200.parallel.fsdp import FSDPParamStore
     cfg = PRESETS["tiny"]
     layout = ParamLayout(cfg)
     S = 128
@@ -323,7 +347,7 @@ def main() -> int:
 
     # --------------------------------------------------------- DDP fused == library ----
     try:
-        from .ddp import DDPParamStore
+        from monarch_b200.parallel.ddp import DDPParamStore
         outs = {}
         for mode in ("fused", "nccl"):
             st = DDPParamStore(layout, dev, seed=3, init_std=0.05, comm=mode, bucket_bytes=1 << 18)
@@ -341,7 +365,7 @@ def main() -> int:
         pass
 
     # ------------------------------- tensor x pipeline parallel: fused == library path ----
-    from .pipelining import PipelineTrainer
+    from monarch_b200.parallel.pipelining import PipelineTrainer
     tp_n = 2 if world < 8 else 4
     pp_n = world // tp_n
     if pp_n * tp_n == world:
@@ -366,7 +390,7 @@ def main() -> int:
         results["tp_pp"] = {"mesh": f"pp{pp_n}xtp{tp_n}", "losses": plosses["fused"]}
 
     # ------------------------------- expert parallel: fused dispatch/combine == all-to-all ----
-    from .ep import EPComm
+    from monarch_b200.parallel.ep import EPComm
     Te, de, Fe, ke = 512, 256, 512, 2
     ge = torch.Generator().manual_seed(900 + rank)
     xe = torch.randn(Te, de, generator=ge).to(dev).to(bf16)
@@ -399,7 +423,7 @@ def main() -> int:
     # ------------------------------------------------- GPU-driven ping-pong (ranks 0, 1) ----
     # No host in the loop: each side's kernel stores into the other's memory over NVLink and
     # polls its own flag (bounded).  Rank 0 leads; the other ranks sit this one out.
-    from .symm import MAX_RANKS
+    from monarch_b200.parallel.symm import MAX_RANKS
     pp_slot = 15
     pp_rows = []
     pp_base = 0
@@ -440,17 +464,22 @@ def main() -> int:
             out = torch.empty(n, dtype=bf16, device=dev)
             ep = [10]
 
-            def ours_ar():
+            def ours_ar(mc=True):
                 ep[0] += 1
                 K.check(lib.mb200_allreduce_scale_cast(
-                    buf.ptrs_at(0), buf.ptrs_at(0), flags.ptrs, n, 0, rank, world, 1.0 / world, 6,
+                    buf.ptrs_at(0), buf.ptrs_at(0), buf.mc_at(0) if mc else None,
+                    buf.mc_at(0) if mc else None, flags.ptrs, n, 0, rank, world, 1.0 / world, 6,
                     ep[0], flags.counter.data_ptr(), 0, status.data_ptr(), K.stream_ptr()),
                     "allreduce", 2)
+
+            def ours_ar_p2p():
+                ours_ar(False)
 
             def nccl_ar():
                 dist.all_reduce(buf.tensor)
 
             t_o = _time(ours_ar, dev)
+            t_p = _time(ours_ar_p2p, dev)
             t_n = _time(nccl_ar, dev)
             bus = lambda ms: 2 * (world - 1) / world * n * 2 / (ms / 1e3) / 1e9
             shard_n = n // world
@@ -467,7 +496,9 @@ def main() -> int:
             t_oag = _time(ours_ag, dev)
             t_nag = _time(nccl_ag, dev)
             agbw = lambda ms: (world - 1) / world * shard_n * world * 2 / (ms / 1e3) / 1e9
-            rows.append({"bytes": n * 2, "allreduce_ms": t_o, "allreduce_busbw_gbs": bus(t_o),
+            rows.append({"bytes": n * 2, "nvls": bool(buf.multicast_ptr),
+                         "allreduce_ms": t_o, "allreduce_busbw_gbs": bus(t_o),
+                         "allreduce_p2p_ms": t_p, "allreduce_p2p_busbw_gbs": bus(t_p),
                          "nccl_allreduce_ms": t_n, "nccl_busbw_gbs": bus(t_n),
                          "allgather_ms": t_oag, "allgather_rx_gbs": agbw(t_oag),
                          "nccl_allgather_ms": t_nag, "nccl_allgather_rx_gbs": agbw(t_nag)})

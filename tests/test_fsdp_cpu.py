@@ -27,9 +27,18 @@ def _worker(rank, world, port, preset, out_dir):
         st.set_hyper(lr=1e-2)
         losses.append(eng.forward_backward(toks[rank, step], toks[rank, (step + 1) % 3]).item())
         eng.optimizer_step(1e-2)
+        if step == 0:
+            # an evaluation pass between two training steps must move neither the flag
+            # epoch nor AdamW's step
+            before = st.step_count
+            ev = eng.forward_loss(toks[rank, 2], toks[rank, 0])
+            assert st.step_count == before
+            dist.all_reduce(ev)
+            eval_loss = ev.item() / world
     full = st.full_params()
     if rank == 0:
-        torch.save({"params": full, "losses": losses}, os.path.join(out_dir, "r0.pt"))
+        torch.save({"params": full, "losses": losses, "eval": eval_loss},
+                   os.path.join(out_dir, "r0.pt"))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -56,6 +65,10 @@ def test_fsdp_two_ranks_matches_single_process(preset):
         tgt = torch.cat([toks[r, (step + 1) % 3] for r in range(world)])
         eng.forward_backward(tok, tgt)
         eng.optimizer_step(1e-2)
+        if step == 0:
+            ev = eng.forward_loss(torch.cat([toks[r, 2] for r in range(world)]),
+                                  torch.cat([toks[r, 0] for r in range(world)])).item()
+            assert abs(ev - got["eval"]) < 2e-2 * abs(ev), (ev, got["eval"])
     ref = st.params.float()
     out = got["params"].float()
     rel = ((out - ref).norm() / ref.norm()).item()

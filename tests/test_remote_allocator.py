@@ -68,3 +68,58 @@ def test_cli_roundtrip(tmp_path, monkeypatch):
     assert run("bounce", "x").returncode == 0
     assert run("stop", "x").returncode == 0
     assert "x" not in run("list").stdout
+
+
+def _ask(port, req):
+    import json
+    import socket
+    c = socket.create_connection(("127.0.0.1", port), timeout=10)
+    c.sendall((json.dumps(req) + "\n").encode())
+    f = c.makefile("rb")
+    for line in f:
+        msg = json.loads(line)
+        if "exit" in msg or "pid" in msg:
+            c.close()
+            return msg
+    c.close()
+    return {}
+
+
+def test_daemon_runs_only_its_own_program_and_checks_the_token():
+    """A client cannot name the program, the working directory or arbitrary environment, and
+    with a token configured a request without it is refused."""
+    import threading
+    from monarch_b200.tools import process_allocator as pa
+    ports = []
+    started = threading.Event()
+    prog = [sys.executable, "-c", "import os,sys; print(os.environ.get('MB200_X'), "
+            "os.environ.get('LD_PRELOAD'), os.environ.get('MB200_ALLOCATOR_TOKEN')); sys.exit(7)"]
+    threading.Thread(target=pa.serve, args=("tcp!127.0.0.1:0",), daemon=True,
+                     kwargs=dict(heartbeat=1.0, ready=lambda p: (ports.append(p), started.set()),
+                                 program=prog, token="s3cret")).start()
+    assert started.wait(10)
+    port = ports[0]
+    assert _ask(port, {"start": 1, "env": {}})["exit"] == 126                 # no token
+    assert _ask(port, {"start": 1, "token": "wrong"})["exit"] == 126
+    r = _ask(port, {"start": 1, "token": "s3cret", "argv": ["/bin/sh", "-c", "id"]})
+    assert r["exit"] == 126 and "own --program" in r["error"]
+    assert _ask(port, {"start": 1, "token": "s3cret", "cwd": "/tmp"})["exit"] == 126
+    assert _ask(port, {})["exit"] == 126                                        # a port probe
+    assert pa.filter_env({"MB200_X": "1", "LD_PRELOAD": "x", "PATH": "y", "HOME": "/",
+                          "MB200_ALLOCATOR_TOKEN": "t", "RANK": "3"}) == {"MB200_X": "1",
+                                                                          "RANK": "3"}
+    # a well-formed request starts the daemon's program with the filtered environment
+    import json
+    import socket
+    c = socket.create_connection(("127.0.0.1", port), timeout=10)
+    c.sendall((json.dumps({"start": 1, "token": "s3cret",
+                           "env": {"MB200_X": "hello", "LD_PRELOAD": "evil.so"}}) + "\n").encode())
+    out, code = "", None
+    for line in c.makefile("rb"):
+        msg = json.loads(line)
+        out += msg.get("out", "")
+        if "exit" in msg:
+            code = msg["exit"]
+            break
+    c.close()
+    assert code == 7 and out.split() == ["hello", "None", "None"], (code, out)

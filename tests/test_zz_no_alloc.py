@@ -33,8 +33,11 @@ def _symbol():
     return fn
 
 
-@pytest.mark.parametrize("rows,d", [(1000, 4096), (77, 8192)])
-def test_noalloc_matches_regular_entry_point_twice(rows, d):
+# (1000, 8192): more row blocks than the built-in scratch has room for at this width, so
+# the entry point has to clip its block count; (77, 8192) and (1000, 4096) stay below it.
+@pytest.mark.parametrize("rows,d,accumulate", [(1000, 4096, 0), (77, 8192, 0), (1000, 8192, 0),
+                                               (300, 2048, 1)])
+def test_noalloc_matches_regular_entry_point_twice(rows, d, accumulate):
     from monarch_b200 import ops
     fn = _symbol()
     stream = torch.cuda.current_stream().cuda_stream
@@ -45,17 +48,22 @@ def test_noalloc_matches_regular_entry_point_twice(rows, d):
         dy = torch.randn(rows, d, device="cuda", dtype=bf16)
         dres = torch.randn(rows, d, device="cuda", dtype=bf16)
         _, rstd = ops.rmsnorm_fwd(x, w, 1e-5)
-        dw_ref = torch.zeros(d, device="cuda", dtype=bf16)
-        dx_ref = ops.rmsnorm_bwd(dy, x, w, rstd, dw_ref, dres=dres)
+        dw0 = (0.5 * torch.randn(d, device="cuda")).to(bf16) if accumulate else \
+            torch.zeros(d, device="cuda", dtype=bf16)
+        dw_ref = dw0.clone()
+        dx_ref = ops.rmsnorm_bwd(dy, x, w, rstd, dw_ref, accumulate=bool(accumulate), dres=dres)
         dx = torch.empty_like(x)
-        dw = torch.zeros(d, device="cuda", dtype=bf16)
+        dw = dw0.clone()
         torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
+        free_before = torch.cuda.mem_get_info()[0]   # sees cudaMalloc, not only torch's pool
         rc = fn(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dres.data_ptr(),
-                dx.data_ptr(), dw.data_ptr(), 0, rows, d, stream)
+                dx.data_ptr(), dw.data_ptr(), accumulate, rows, d, stream)
         assert rc == 0, rc
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == before
+        if call == 1:   # the first call on a device may page the library's own image in
+            assert torch.cuda.mem_get_info()[0] == free_before
         assert _rel(dx, dx_ref) < 6e-3, (call, _rel(dx, dx_ref))
         assert _rel(dw, dw_ref) < 6e-3, (call, _rel(dw, dw_ref))
 
