@@ -436,7 +436,109 @@ class ProcessAlloc : public Alloc {
   std::atomic<bool> stopped_{false};
 };
 
+// Allocation whose procs are hosted by processes someone else started.
+class AttachAllocImpl : public AttachAlloc {
+ public:
+  AttachAllocImpl(std::string world, size_t n, std::string transport)
+      : world_(std::move(world)), n_(n), transport_(std::move(transport)) {
+    rx_ = serve(ChannelAddr::any(transport_ == "tcp" ? ChannelAddr::Tcp : ChannelAddr::Unix));
+    ctrl_.resize(n_);
+    thr_ = std::thread([this] { control_loop(); });
+  }
+  ~AttachAllocImpl() override { stop(); }
+  std::string world() const override { return world_; }
+  size_t size() const override { return n_; }
+  std::optional<ProcEvent> next(int64_t t) override { return events_.pop(t); }
+  std::string transport() const override { return transport_; }
+  std::string bootstrap_addr() const override { return rx_->addr().to_string(); }
+
+  void stop() override {
+    if (stopped_.exchange(true)) return;
+    rx_->close();
+    if (thr_.joinable()) thr_.join();   // the control thread owned ctrl_ until here
+    for (auto& c : ctrl_) {
+      if (c) {
+        Frame f;
+        f.head = "X";
+        c->post(std::move(f));
+      }
+    }
+    // the hosts stop their actors and drop the connection; give the frames time to leave
+    std::this_thread::sleep_for(std::chrono::milliseconds(50));
+    for (auto& c : ctrl_)
+      if (c) c->close();
+  }
+
+ private:
+  void control_loop() {
+    auto last_check = std::chrono::steady_clock::now();
+    while (!rx_->closed()) {
+      auto f = rx_->recv(100);
+      auto now = std::chrono::steady_clock::now();
+      if (now - last_check > std::chrono::milliseconds(500)) {
+        last_check = now;
+        for (size_t i = 0; i < n_; ++i) {   // a host that went away took its proc with it
+          if (ctrl_[i] && !gone_[i] && !stopped_ && ctrl_[i]->status() == TxStatus::Closed) {
+            gone_[i] = true;
+            ProcEvent e;
+            e.kind = ProcEvent::Failed;
+            e.rank = (int64_t)i;
+            e.proc_id = ProcId{world_, (int64_t)i}.to_string();
+            e.reason = "lost the connection to the process hosting it";
+            events_.push(std::move(e));
+          }
+        }
+      }
+      if (!f || f->head.empty()) continue;
+      try {
+        Reader r(std::string_view(f->head).substr(1));
+        if (f->head[0] == 'H') {
+          int64_t idx = r.i64();
+          std::string ctrl = r.str();
+          if (idx < 0 || (size_t)idx >= n_ || ctrl_[idx]) continue;   // unknown or duplicate
+          ctrl_[idx] = dial(ChannelAddr::parse(ctrl));
+          ProcEvent c;
+          c.kind = ProcEvent::Created;
+          c.rank = idx;
+          events_.push(std::move(c));
+          Writer w;
+          w.buf = "S";
+          w.str(ProcId{world_, idx}.to_string());
+          w.str(transport_);
+          Frame s;
+          s.head = std::move(w.buf);
+          ctrl_[idx]->post(std::move(s));
+        } else if (f->head[0] == 'R') {
+          ProcEvent e;
+          e.kind = ProcEvent::Running;
+          e.rank = r.i64();
+          e.proc_id = r.str();
+          e.addr = r.str();
+          events_.push(std::move(e));
+        }
+      } catch (const std::exception& ex) {
+        MB_LOG(Warn, std::string("attach alloc: bad control frame: ") + ex.what());
+      }
+    }
+  }
+
+  std::string world_;
+  size_t n_;
+  std::string transport_;
+  std::shared_ptr<Rx> rx_;
+  std::deque<std::shared_ptr<Tx>> ctrl_;
+  std::map<size_t, bool> gone_;
+  EventQueue events_;
+  std::thread thr_;
+  std::atomic<bool> stopped_{false};
+};
+
 }  // namespace
+
+std::shared_ptr<AttachAlloc> make_attach_alloc(const std::string& world, size_t n,
+                                               const std::string& transport) {
+  return std::make_shared<AttachAllocImpl>(world, n, transport);
+}
 
 std::shared_ptr<Alloc> make_local_alloc(const std::string& world, size_t n,
                                         std::shared_ptr<Router> router) {
@@ -448,17 +550,12 @@ std::shared_ptr<Alloc> make_process_alloc(const std::string& world, size_t n,
 }
 
 // ----------------------------------------------------------------- child bootstrap ----
-int bootstrap_main() {
-  const char* addr_s = std::getenv("HYPERACTOR_MESH_BOOTSTRAP_ADDR");
-  const char* idx_s = std::getenv("HYPERACTOR_MESH_INDEX");
-  if (!addr_s || !idx_s) return 1;
-  ::prctl(PR_SET_PDEATHSIG, SIGKILL);  // never outlive the allocator
+namespace {
+// The proc-hosting side of the bootstrap protocol.  `child`: this process was started by
+// the allocator for this purpose (it dies with the allocator and exits when told to stop);
+// otherwise the process only hosts the proc and the function returns when the mesh stops.
+int bootstrap_loop(const std::string& addr_s, int64_t index, bool child) {
   const pid_t parent = ::getppid();
-  const int64_t index = std::stoll(idx_s);
-  if (std::getenv("MONARCH_ERROR_DURING_BOOTSTRAP_FOR_TESTING")) {
-    std::fprintf(stderr, "bootstrap: injected failure (MONARCH_ERROR_DURING_BOOTSTRAP_FOR_TESTING)\n");
-    ::_exit(17);
-  }
   auto to_parent = dial(ChannelAddr::parse(addr_s));
   ChannelAddr::Kind kind = ChannelAddr::parse(addr_s).kind;
   auto ctrl = serve(ChannelAddr::any(kind == ChannelAddr::Tcp ? ChannelAddr::Tcp : ChannelAddr::Unix));
@@ -481,9 +578,13 @@ int bootstrap_main() {
     auto now = std::chrono::steady_clock::now();
     if (now - last_check > std::chrono::milliseconds(hb_ms)) {
       last_check = now;
-      if (::getppid() != parent || to_parent->status() == TxStatus::Closed) {
-        MB_LOG(Warn, "bootstrap: allocator is gone, exiting");
-        ::_exit(1);
+      if ((child && ::getppid() != parent) || to_parent->status() == TxStatus::Closed) {
+        MB_LOG(Warn, "bootstrap: allocator is gone");
+        if (child) ::_exit(1);
+        if (proc) proc->stop_all(Config::global().get_int("STOP_ACTOR_TIMEOUT_MS"));
+        server.reset();
+        ctrl->close();
+        return 1;
       }
     }
     if (!f || f->head.empty()) continue;
@@ -511,9 +612,30 @@ int bootstrap_main() {
       if (proc) proc->stop_all(Config::global().get_int("STOP_ACTOR_TIMEOUT_MS"));
       std::fflush(stdout);
       std::fflush(stderr);
-      ::_exit(0);
+      if (child) ::_exit(0);
+      server.reset();
+      ctrl->close();
+      to_parent->close();
+      return 0;
     }
   }
+}
+}  // namespace
+
+int bootstrap_main() {
+  const char* addr_s = std::getenv("HYPERACTOR_MESH_BOOTSTRAP_ADDR");
+  const char* idx_s = std::getenv("HYPERACTOR_MESH_INDEX");
+  if (!addr_s || !idx_s) return 1;
+  ::prctl(PR_SET_PDEATHSIG, SIGKILL);  // never outlive the allocator
+  if (std::getenv("MONARCH_ERROR_DURING_BOOTSTRAP_FOR_TESTING")) {
+    std::fprintf(stderr, "bootstrap: injected failure (MONARCH_ERROR_DURING_BOOTSTRAP_FOR_TESTING)\n");
+    ::_exit(17);
+  }
+  return bootstrap_loop(addr_s, std::stoll(idx_s), true);
+}
+
+int bootstrap_attach(const std::string& addr, int64_t index) {
+  return bootstrap_loop(addr, index, false);
 }
 
 // --------------------------------------------------------------------- mesh agent ----

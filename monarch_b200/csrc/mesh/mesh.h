@@ -104,6 +104,25 @@ std::shared_ptr<Alloc> make_process_alloc(const std::string& world, size_t n,
 // environment does not describe a bootstrap, in which case it returns 1.
 int bootstrap_main();
 
+// Procs that are NOT started by the allocator: processes launched by something else (an
+// SPMD launcher such as torchrun, a batch scheduler) join the mesh by dialling
+// `bootstrap_addr()` with their rank (`bootstrap_attach`).  The allocator waits for `n` of
+// them; a joined proc that drops its control connection is reported as failed.
+// (The reference gets externally started procs through its allocator daemons,
+// hyperactor_mesh/src/alloc/remoteprocess.rs; this is the in-box form of the same idea.)
+class AttachAlloc : public Alloc {
+ public:
+  virtual std::string bootstrap_addr() const = 0;
+};
+std::shared_ptr<AttachAlloc> make_attach_alloc(const std::string& world, size_t n,
+                                               const std::string& transport);
+
+// Host one proc of an attach allocation inside the calling process: announces `index` to
+// the allocator at `addr`, creates the proc with its mesh agent when told to and serves it
+// until the allocator stops the mesh or goes away; then stops the proc's actors and
+// RETURNS (the hosting process lives on).  0 on an orderly stop, 1 when the allocator vanished.
+int bootstrap_attach(const std::string& addr, int64_t index);
+
 // --------------------------------------------------------------------- comm actor ----
 ActorHooks make_comm_actor(const std::shared_ptr<Proc>& proc);
 ActorHooks make_mesh_agent(const std::shared_ptr<Proc>& proc, std::shared_ptr<Router> router);

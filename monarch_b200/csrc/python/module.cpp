@@ -743,6 +743,22 @@ PYBIND11_MODULE(_native, m) {
     py::gil_scoped_release rel;
     return bootstrap_main();
   });
+  m.def("bootstrap_attach", [](const std::string& addr, int64_t index) {
+    py::gil_scoped_release rel;
+    return bootstrap_attach(addr, index);
+  }, py::arg("addr"), py::arg("index"),
+  "Host proc `index` of the attach allocation listening at `addr` in this process; returns "
+  "when the mesh is stopped.");
+  py::class_<AttachAlloc, std::shared_ptr<AttachAlloc>>(m, "AttachAlloc")
+      .def(py::init([](const std::string& world, size_t n, const std::string& transport) {
+             return make_attach_alloc(world, n, transport);
+           }),
+           py::arg("world"), py::arg("n"), py::arg("transport") = "unix")
+      .def_property_readonly("bootstrap_addr", &AttachAlloc::bootstrap_addr)
+      .def("stop", [](AttachAlloc& a) {
+        py::gil_scoped_release rel;
+        a.stop();
+      });
 
   py::class_<ProcMesh, std::shared_ptr<ProcMesh>>(m, "ProcMesh")
       .def_static(
@@ -754,6 +770,14 @@ PYBIND11_MODULE(_native, m) {
                                       timeout_ms);
           },
           py::arg("world"), py::arg("n"), py::arg("timeout_ms") = 30000)
+      .def_static(
+          "allocate_attached",
+          [](std::shared_ptr<AttachAlloc> alloc, int64_t timeout_ms) {
+            py::gil_scoped_release rel;
+            auto& c = client_ctx();
+            return ProcMesh::allocate(alloc, c.router, c.proc, timeout_ms);
+          },
+          py::arg("alloc"), py::arg("timeout_ms") = 120000)
       .def_static(
           "allocate_process",
           [](const std::string& world, size_t n, std::vector<std::string> argv,

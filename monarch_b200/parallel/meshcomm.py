@@ -222,8 +222,9 @@ class MeshComm:
                 so = list(z)
                 nbs[self.rank], so[self.rank] = nb, out_off
                 self._gather(so, z, nbs, rp + off, SLOT_RESULT, epoch)
-        if out is not None and res is not out:
-            out.copy_(res.view_as(out))
+        if out is not None:
+            if res is not out:
+                out.copy_(res.view_as(out))
             return out
         return res.view_as(t)
 

@@ -38,10 +38,11 @@ def main() -> int:
         tri = n * (n + 1) / 2
         base = torch.arange(1, 7, dtype=torch.float32).reshape(2, 3)      # controller-local
         with dm.activate():
-            r = dm.rank("gpus").to(torch.float32)
-            x = (r + 1) * torch.arange(1, 7, dtype=torch.float32).reshape(2, 3)
-            y = (r + 1) * torch.ones(n, 5) * torch.arange(1, n + 1, dtype=torch.float32)[:, None]
-            big = (r + 1) * torch.ones(24 * 1024 * 1024 // 4 + 3)
+            r = dm.rank("gpus").to(torch.float32).cuda()
+            x = (r + 1) * torch.arange(1, 7, dtype=torch.float32, device="cuda").reshape(2, 3)
+            y = (r + 1) * torch.ones(n, 5, device="cuda") * \
+                torch.arange(1, n + 1, dtype=torch.float32, device="cuda")[:, None]
+            big = (r + 1) * torch.ones(24 * 1024 * 1024 // 4 + 3, device="cuda")
             got = {
                 "sum": [te.inspect(x.reduce("gpus", "sum"), gpus=g) for g in range(n)],
                 "avg": te.inspect(x.reduce("gpus", "avg"), gpus=n - 1),
@@ -87,7 +88,8 @@ def main() -> int:
         results["launches_per_worker"] = [s["launches"] for s in state]
         # an operation outside the kernels' coverage falls back to NCCL, initialised on demand
         with dm.activate():
-            bits = (dm.rank("gpus") + 1).to(torch.int32) * torch.ones(4, dtype=torch.int32)
+            bits = (dm.rank("gpus") + 1).to(torch.int32).cuda() * \
+                torch.ones(4, dtype=torch.int32, device="cuda")
             bo = te.inspect(bits.reduce("gpus", "bor"), gpus=0)
         want = 0
         for g in range(n):

@@ -28,16 +28,16 @@ def _launches(dm):
     def count(_t):
         from monarch_b200.ops import kernels as K
         return K.launch_count
-    return te.call_on_shard_and_fetch(count, torch.zeros(1), shard={"gpus": 0}).get()
+    return te.call_on_shard_and_fetch(count, torch.zeros(1, device="cuda"), shard={"gpus": 0}).get()
 
 
 def test_ops_run_on_the_device_and_match_torch(dm):
     from monarch_b200 import tensor_engine as te
     with dm.activate():
-        a = torch.arange(12, dtype=torch.float32).reshape(3, 4)
+        a = torch.arange(12, dtype=torch.float32, device="cuda").reshape(3, 4)
         b = 2 * a + 1
         c = (b @ b.t()).relu().sum()
-        w = torch.ones(4, 4, dtype=torch.bfloat16)
+        w = torch.ones(4, 4, dtype=torch.bfloat16, device="cuda")
         d = (a.to(torch.bfloat16) @ w).float()
         where = te.call_on_shard_and_fetch(lambda t: str(t.device), b, shard={"gpus": 0}).get()
         got_b, got_c, got_d = te.inspect(b), te.inspect(c), te.inspect(d)
@@ -53,7 +53,7 @@ def test_reduce_variants_use_the_nvlink_kernels(dm):
     from monarch_b200 import tensor_engine as te
     with dm.activate():
         before = _launches(dm)
-        x = torch.arange(6, dtype=torch.float32).reshape(1, 6) + 1
+        x = torch.arange(6, dtype=torch.float32, device="cuda").reshape(1, 6) + 1
         r_sum = te.inspect(x.reduce("gpus", "sum"))
         r_avg = te.inspect(x.reduce("gpus", "avg"))
         r_max = te.inspect(x.to(torch.bfloat16).reduce("gpus", "max"))
@@ -63,7 +63,7 @@ def test_reduce_variants_use_the_nvlink_kernels(dm):
         y = x.clone()
         y.reduce_("gpus", "sum")
         r_in = te.inspect(y)
-        o = torch.zeros(1, 6)
+        o = torch.zeros(1, 6, device="cuda")
         x.reduce("gpus", "sum", out=o)
         r_out = te.inspect(o)
         after = _launches(dm)
@@ -81,7 +81,7 @@ def test_borrow_between_two_cuda_streams(dm):
     from monarch_b200 import tensor_engine as te
     side = te.Stream("side")
     with dm.activate():
-        x = torch.ones(1 << 20)
+        x = torch.ones(1 << 20, device="cuda")
         for _ in range(8):
             x = x * 1.0 + 1.0            # work in flight on the main stream
         y, borrow = side.borrow(x, mutable=True)
@@ -99,7 +99,7 @@ def test_borrow_between_two_cuda_streams(dm):
 def test_to_mesh_and_fetch_shard(dm):
     from monarch_b200 import tensor_engine as te
     with dm.activate():
-        f = (dm.rank("gpus") + 3).to(torch.float32) * torch.ones(2, 2)
+        f = (dm.rank("gpus") + 3).to(torch.float32).cuda() * torch.ones(2, 2, device="cuda")
         g = f.to_mesh(dm)
         g.add_(1)
         assert te.fetch_shard(f, gpus=0).get().tolist() == [[3.0, 3.0], [3.0, 3.0]]
