@@ -1,17 +1,28 @@
 #!/usr/bin/env python
 """Headline benchmark: training throughput (tokens/s) of Llama-3-8B, bf16 with fp32
 AdamW master weights, sequence length 8192, micro-batch 1 per GPU, activation
-checkpointing; FSDP over the mesh dim ``gpu`` when run on more than one GPU.
+checkpointing; FSDP over the mesh dim ``gpus`` when run on more than one GPU.
 
-    python bench.py --gpus 1 --steps 10 --warmup 3
+    python bench.py --gpus 1 --steps 8 --warmup 3
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
-        --master-port 29500 bench.py --gpus 8 --steps 10 --warmup 3
+        --master-port 29500 bench.py --gpus 8 --steps 8 --warmup 3
 
-Prints ONE JSON line on rank 0.  ``value`` is the device-timed whole-job tokens/s
-(CUDA events around exactly ``steps`` optimizer steps, max over ranks); ``e2e`` is the
-same metric through the public ``Trainer.step`` call with the batch copied from pinned
-host memory and the loss read back every step.  Synthetic token ids, random-init
-weights.  ``--impl reference`` reports why the upstream reference cannot run here.
+The step is driven the way a user of the framework drives it: the processes of the launch
+form a proc mesh (``attach_proc_mesh``), rank 0 is the controller, a ``TrainerActor`` is
+spawned on every proc and the controller sends endpoint calls.
+
+* ``value``: device-timed whole-job tokens/s -- one ``timed_steps`` call; inside it every
+  rank runs ``warmup`` untimed steps and then exactly ``steps`` optimizer steps between two
+  CUDA events with a barrier + synchronize on both sides; the maximum over the ranks counts.
+* ``e2e``: the same metric through ``trainers.step.call(i).get()`` once per step: every step
+  copies its batch from pinned host memory, runs, and reads the loss back to the host, and
+  the reply travels over the actor mesh to the controller, whose clock times the loop.
+* ``vs_baseline``: ``value`` divided by the same measurement of the library arm in the same
+  run (``baseline``: stock torch modules, cuBLAS, SDPA, fused torch AdamW, ``fully_shard`` over
+  NCCL for more than one GPU) -- what the reference's tensor worker would execute for this
+  program.  The reference itself cannot be built offline (``--impl reference`` says why).
+
+Prints ONE JSON line on rank 0.  Synthetic token ids, random-init weights.
 """
 from __future__ import annotations
 
@@ -43,6 +54,11 @@ def parse():
     ap.add_argument("--microbatches", type=int, default=8,
                     help="micro-batches per step of a pipeline-parallel run (ppPxtpT)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--cpu", action="store_true",
+                    help="run the same flow on CPU ranks (gloo, library collectives): a check of "
+                         "the harness, not a benchmark")
+    ap.add_argument("--no-baseline", action="store_true",
+                    help="skip the library arm (vs_baseline stays null)")
     return ap.parse_args()
 
 
@@ -54,6 +70,43 @@ def reference_unavailable():
                        "of the reference tree fails at metadata: No module named 'setuptools_rust')",
     }))
     return 0
+
+
+def run_arm(mesh, impl: str, args, e2e: bool):
+    """Spawn the trainers of one arm on ``mesh``, measure, release them."""
+    from monarch_b200.parallel.trainer_actor import TrainerActor
+    spec = {"impl": impl, "model": args.model, "seq_len": args.seq, "micro_batch": args.micro_batch,
+            "parallelism": args.parallelism, "comm": args.comm,
+            "recompute_layers": args.recompute_layers, "microbatches": args.microbatches,
+            "schedule": args.schedule, "cuda": not args.cpu}
+    trainers = mesh.spawn(f"trainer_{impl}", TrainerActor, spec)
+    info = [v for _, v in trainers.info.call().get(timeout=1800).items()]
+    timed = [v for _, v in trainers.timed_steps.call(args.warmup, args.steps).get(timeout=3600).items()]
+    ms = max(t["ms"] for t in timed)
+    tokens_per_step = info[0]["tokens_per_step"]
+    r0 = next(t for t in timed if t["rank"] == 0)
+    out = {"impl": impl, "value": tokens_per_step * args.steps / (ms / 1e3),
+           "ms_per_step": ms / args.steps, "clocks": r0["clocks"], "launches": r0["launches"],
+           "loss": next((t["loss"] for t in timed if t["loss"] is not None), None),
+           "max_mem_gb": max(t["max_mem_gb"] for t in timed), "info": info[0],
+           "tokens_per_step": tokens_per_step, "e2e": None}
+    if e2e:
+        for i in range(2):
+            trainers.step.call(i).get(timeout=1800)
+        trainers.sync.call().get(timeout=600)
+        t0 = time.perf_counter()
+        for i in range(args.steps):
+            trainers.step.call(i).get(timeout=1800)
+        trainers.sync.call().get(timeout=600)
+        wall = time.perf_counter() - t0
+        out["e2e"] = {"value": tokens_per_step * args.steps / wall, "unit": "tokens/s",
+                      "ms_per_step": wall * 1e3 / args.steps,
+                      "h2d_bytes_per_step": info[0]["h2d_bytes_per_step"],
+                      "d2h_bytes_per_step": info[0]["d2h_bytes_per_step"],
+                      "api": "attach_proc_mesh -> ProcMesh.spawn(TrainerActor) -> "
+                             "trainers.step.call(i).get() per step (controller wall clock)"}
+    trainers.release.call().get(timeout=600)
+    return out
 
 
 def main():
@@ -69,129 +122,77 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if world != args.gpus and world > 1:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
+    if not args.cpu:
+        torch.cuda.set_device(local_rank)
+        dev = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+        if args.cpu:
+            dist.init_process_group("gloo")
+        else:
+            dist.init_process_group("nccl", device_id=dev)
 
-    from monarch_b200.ops import kernels as K
-    from monarch_b200.parallel.trainer import Trainer
-    from monarch_b200.utils.clocks import ClockSampler
-
-    def barrier():
+    from monarch_b200.actor import attach_proc_mesh
+    mesh, hosted = attach_proc_mesh({"gpus": world}, rank=rank, world=world)
+    if mesh is None:
+        # this rank hosts its proc of the mesh: its trainer actors run here until the
+        # controller stops the mesh
+        hosted.join()
         if world > 1:
             dist.barrier()
-        torch.cuda.synchronize()
+            dist.destroy_process_group()
+        return 0
 
+    from monarch_b200.models import PRESETS
     import re
     m_pp = re.fullmatch(r"pp(\d+)xtp(\d+)", args.parallelism)
-    n_mb = 1
-    if args.impl == "aten":
-        from monarch_b200.parallel.aten_baseline import AtenTrainer
-        trainer = AtenTrainer(args.model, args.seq, args.micro_batch, device=dev)
-    elif m_pp:
-        from monarch_b200.parallel.pipelining import PipelineTrainer
-        n_mb = args.microbatches
-        trainer = PipelineTrainer(args.model, int(m_pp.group(1)), int(m_pp.group(2)), args.seq,
-                                  args.micro_batch, n_mb, device=dev, comm=args.comm,
-                                  schedule=args.schedule)
-    elif args.parallelism == "ep":
-        from monarch_b200.parallel.ep import MoETrainer
-        trainer = MoETrainer(args.model, args.seq, args.micro_batch, device=dev, comm=args.comm)
-    else:
-        trainer = Trainer(args.model, seq_len=args.seq, micro_batch=args.micro_batch,
-                          recompute_layers=args.recompute_layers,
-                          parallelism=args.parallelism, device=dev, comm=args.comm)
-    cfg = trainer.cfg
-    B, S = args.micro_batch, args.seq
-    gen = torch.Generator().manual_seed(1234 + rank)
-    n_batches = 4
-    shape = (n_mb, B, S) if m_pp else (B, S)
-    if m_pp:
-        gen = torch.Generator().manual_seed(1234)  # one data-parallel replica: same batch
-    host_tok = [torch.randint(0, cfg.vocab, shape, generator=gen).pin_memory()
-                for _ in range(n_batches)]
-    host_tgt = [torch.randint(0, cfg.vocab, shape, generator=gen).pin_memory()
-                for _ in range(n_batches)]
-    dev_tok = [t.to(dev) for t in host_tok]
-    dev_tgt = [t.to(dev) for t in host_tgt]
+    res = run_arm(mesh, args.impl, args, e2e=not args.no_e2e)
+    base = None
+    if args.impl == "ours" and not args.no_baseline and not m_pp and args.parallelism != "ep":
+        base = run_arm(mesh, "aten", args, e2e=False)
+    mesh.stop().get()
+    hosted.join(timeout=60)
 
-    # ---- device-timed region -------------------------------------------------------
-    for i in range(args.warmup):
-        trainer.step_device(dev_tok[i % n_batches], dev_tgt[i % n_batches])
-    barrier()
-    K.check_status()
-    sampler = ClockSampler(local_rank).start()
-    l0 = K.launch_count
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(args.steps):
-        loss = trainer.step_device(dev_tok[i % n_batches], dev_tgt[i % n_batches])
-    e1.record()
-    barrier()
-    clocks = sampler.stop()
-    launches = K.launch_count - l0
-    K.check_status()
-    ms = e0.elapsed_time(e1)
-    if m_pp and world > 1:
-        dist.all_reduce(loss, op=dist.ReduceOp.MAX)  # the last stage holds the loss
-    final_loss = float(loss.item())
-    t = torch.tensor([ms], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
-    tokens_per_step = n_mb * B * S if m_pp else B * S * world
-    value = tokens_per_step * args.steps / (ms / 1e3)
-
-    # ---- end-to-end through Trainer.step (pinned H2D every step, loss D2H every step)
-    e2e = None
-    if not args.no_e2e:
-        for i in range(2):
-            trainer.step(host_tok[i % n_batches], host_tgt[i % n_batches])
-        barrier()
-        e0.record()
-        t0 = time.perf_counter()
-        for i in range(args.steps):
-            trainer.step(host_tok[i % n_batches], host_tgt[i % n_batches])
-        e1.record()
-        barrier()
-        wall = time.perf_counter() - t0
-        ems = max(e0.elapsed_time(e1), wall * 1e3)
-        t = torch.tensor([ems], device=dev, dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ems = float(t.item())
-        e2e = {"value": tokens_per_step * args.steps / (ems / 1e3), "unit": "tokens/s",
-               "ms_per_step": ems / args.steps,
-               "h2d_bytes_per_step": trainer.h2d_bytes_per_step,
-               "d2h_bytes_per_step": trainer.d2h_bytes_per_step}
-
-    if rank == 0:
-        par = trainer.parallelism if (world == 1 or m_pp) else f"{trainer.parallelism}{world}"
-        flops_tok = cfg.flops_per_token(S, recompute=True)
-        out = {
-            "metric": "tokens/s Llama-3-8B FSDP-on-mesh" if args.model == "llama3-8b"
-                      else f"tokens/s {args.model}",
-            "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "impl": args.impl,
-            "config": {"model": args.model,
-                       "global_batch": n_mb * B if m_pp else B * world, "seq_len": S,
-                       "parallelism": par,
-                       "activation_checkpointing": True if args.recompute_layers is None else
-                       f"first {args.recompute_layers} layers recomputed, the rest kept",
-                       "optimizer": "AdamW fp32 master", "comm": args.comm,
-                       **({"fsdp_gather": os.environ.get("MB200_FSDP_GATHER", "prefetch")}
-                          if par.startswith("fsdp") else {}),
-                       "l2": "per-step working set (>100 GB of weights and optimizer state) "
-                             "is far larger than the 126 MB L2"},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "loss": final_loss,
-            "max_mem_gb": torch.cuda.max_memory_allocated() / 1e9,
-            "model_tflops_per_gpu": flops_tok * tokens_per_step / world * args.steps / (ms / 1e3) / 1e12,
-        }
-        print(json.dumps(out))
+    cfg = PRESETS[args.model]
+    S, B = args.seq, args.micro_batch
+    par = res["info"]["parallelism"]
+    if world > 1 and not m_pp:
+        par = f"{par}{world}"
+    per_gpu = res["tokens_per_step"] / world * args.steps / (res["ms_per_step"] * args.steps / 1e3)
+    out = {
+        "metric": "tokens/s Llama-3-8B FSDP-on-mesh" if args.model == "llama3-8b"
+                  else f"tokens/s {args.model}",
+        "value": res["value"], "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": (res["value"] / base["value"]) if base else None,
+        "dtype": "bf16", "data": "synthetic", "impl": args.impl,
+        "config": {"model": args.model,
+                   "global_batch": args.microbatches * B if m_pp else B * world, "seq_len": S,
+                   "parallelism": par,
+                   "activation_checkpointing": True if args.recompute_layers is None else
+                   f"first {args.recompute_layers} layers recomputed, the rest kept",
+                   "optimizer": "AdamW fp32 master", "comm": args.comm,
+                   **({"fsdp_gather": res["info"]["fsdp_gather"]} if par.startswith("fsdp") else {}),
+                   "driven_by": "actor mesh over the launch's processes (attach_proc_mesh); "
+                                "TrainerActor.timed_steps",
+                   "l2": "per-step working set (>100 GB of weights and optimizer state) "
+                         "is far larger than the 126 MB L2"},
+        "clocks": res["clocks"], "e2e": res["e2e"], "gpu_launches": res["launches"],
+        "loss": res["loss"], "max_mem_gb": res["max_mem_gb"],
+        # model FLOPs (3x forward; recomputation not counted) and what the hardware executed
+        "model_tflops_per_gpu": cfg.flops_per_token(S) * per_gpu / 1e12,
+        "hardware_tflops_per_gpu": cfg.flops_per_token(S, recompute=True) * per_gpu / 1e12
+        if args.recompute_layers is None else None,
+        "baseline": None if base is None else {
+            "impl": "aten: stock torch modules (cuBLAS, SDPA), autograd checkpointing, fused "
+                    "torch AdamW on fp32 masters" + ("; fully_shard over NCCL" if world > 1 else ""),
+            "value": base["value"], "unit": "tokens/s", "ms_per_step": base["ms_per_step"],
+            "clocks": base["clocks"], "max_mem_gb": base["max_mem_gb"], "loss": base["loss"],
+            "note": "same run, same processes, same steps/warm-up, measured after this "
+                    "package's arm released its memory"},
+    }
+    print(json.dumps(out))
+    sys.stdout.flush()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

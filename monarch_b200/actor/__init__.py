@@ -10,6 +10,7 @@ from .proc_mesh import (HostMesh, ProcEvent, ProcMesh, fake_in_process_host,
                         get_or_spawn_controller, hosts_from_config, local_proc_mesh, proc_mesh,
                         sim_proc_mesh, this_host, this_proc)
 from .shape import Extent, Point, Shape
+from .attach import HostedProc, attach_proc_mesh
 
 
 def debug_controller():
@@ -23,5 +24,5 @@ __all__ = [
     "ValueMesh", "debug_controller", "endpoint", "Endpoint", "Extent", "Future", "HostMesh",
     "hosts_from_config", "this_host", "this_proc", "get_or_spawn_controller", "local_proc_mesh",
     "proc_mesh", "ProcMesh", "ProcEvent", "Shape", "sim_proc_mesh", "SupervisionError",
-    "fake_in_process_host",
+    "fake_in_process_host", "attach_proc_mesh", "HostedProc",
 ]

@@ -37,6 +37,7 @@ from .. import _native as N
 from .proc_mesh import ProcMesh, _shape_from_dims
 
 _counter = itertools.count()
+_stores: list = []     # rendezvous stores stay up for the life of the process: late ranks read them
 
 
 class HostedProc:
@@ -72,6 +73,7 @@ def _exchange_addr(addr: Optional[str], rank: int, world: int, tag: str) -> str:
     store = dist.TCPStore(os.environ.get("MASTER_ADDR", "127.0.0.1"),
                           int(os.environ.get("MASTER_PORT", "29500")) + 1, world,
                           is_master=(rank == 0), timeout=timedelta(seconds=120))
+    _stores.append(store)
     if rank == 0:
         store.set(tag, addr)
         return addr

@@ -211,7 +211,29 @@ __global__ void __launch_bounds__(256) coll_reduce_kernel(const ReduceArgs a) {
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   constexpr bool kMc = McOk<T>::value && OP == kSum;
   const bool use_mc = kMc && a.mc_in != nullptr;
-  for (int64_t i = a.lo + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < a.hi; i += stride) {
+  int64_t i = a.lo + (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if constexpr (kMc) {
+    // the pure in-switch case (sum, no scale, full vectors): four reductions in flight per
+    // thread, results to the local tensor and/or to every rank through one multicast store
+    if (use_mc && !a.apply_scale && (a.mc_out || !a.out_peers.p[0])) {
+      for (; i + 3 * stride < a.hi; i += 4 * stride) {
+        if (a.out_local && ((i + 3 * stride - a.lo) << 4) + 16 > a.valid_bytes_local) break;
+        uint4 r4[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          r4[j] = multimem_ld_sum<T>(reinterpret_cast<const uint4*>(a.mc_in) + i + j * stride);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int64_t ij = i + j * stride;
+          if (a.out_local)
+            *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(a.out_local) +
+                                      ((ij - a.lo) << 4)) = r4[j];
+          if (a.mc_out) multimem_st_v4(reinterpret_cast<uint4*>(a.mc_out) + ij, r4[j]);
+        }
+      }
+    }
+  }
+  for (; i < a.hi; i += stride) {
     uint4 r;
     if (use_mc && !a.apply_scale) {
       if constexpr (kMc) r = multimem_ld_sum<T>(reinterpret_cast<const uint4*>(a.mc_in) + i);

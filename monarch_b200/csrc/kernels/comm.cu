@@ -122,25 +122,9 @@ __global__ void __launch_bounds__(256)
   const int64_t base = (int64_t)rank * shard_elems;
   const int64_t nvec = shard_elems >> 3;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
-    float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    if (mc_grads) {
-      // in-switch reduction: one load returns the fp32-accumulated sum of every rank's copy
-      acc8(g, multimem_ld_sum<__nv_bfloat16>(
-                  reinterpret_cast<const __nv_bfloat16*>(mc_grads) + base + i * 8));
-    } else {
-      uint4 raw[kMaxRanks];
-#pragma unroll
-      for (int k = 0; k < kMaxRanks; ++k) {
-        if (k < world) {
-          const int p = (rank + k) % world;
-          raw[k] = ld_nc_v4(reinterpret_cast<const __nv_bfloat16*>(grads.p[p]) + base + i * 8);
-        }
-      }
-#pragma unroll
-      for (int k = 0; k < kMaxRanks; ++k)
-        if (k < world) acc8(g, raw[k]);
-    }
+  const float decay = 1.f - lr * wd;
+  // AdamW on vector i (8 elements) of the shard given the summed gradient g
+  auto update = [&](int64_t i, const float (&g)[8]) {
     float4 p0 = reinterpret_cast<float4*>(master)[i * 2], p1 = reinterpret_cast<float4*>(master)[i * 2 + 1];
     float4 m0 = reinterpret_cast<float4*>(m)[i * 2], m1 = reinterpret_cast<float4*>(m)[i * 2 + 1];
     float4 v0 = reinterpret_cast<float4*>(v)[i * 2], v1 = reinterpret_cast<float4*>(v)[i * 2 + 1];
@@ -150,7 +134,7 @@ __global__ void __launch_bounds__(256)
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
       const float gg = g[k] * grad_scale;
-      pv[k] *= (1.f - lr * wd);
+      pv[k] *= decay;
       mv[k] = beta1 * mv[k] + (1.f - beta1) * gg;
       vv[k] = beta2 * vv[k] + (1.f - beta2) * gg * gg;
       pv[k] -= lr * inv_bc1 * mv[k] / (sqrtf(vv[k]) * inv_sqrt_bc2 + eps);
@@ -167,6 +151,45 @@ __global__ void __launch_bounds__(256)
     o.z = pack_bf16x2(pv[4], pv[5]);
     o.w = pack_bf16x2(pv[6], pv[7]);
     reinterpret_cast<uint4*>(param_shard)[i] = o;
+  };
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (mc_grads) {
+    // In-switch reduction: one load returns the fp32-accumulated sum of every rank's copy.
+    // Four of them in flight per thread keep the link busy with a grid that leaves most SMs
+    // to the backward pass running beside this kernel.
+    const __nv_bfloat16* mc = reinterpret_cast<const __nv_bfloat16*>(mc_grads) + base;
+    for (; i + 3 * stride < nvec; i += 4 * stride) {
+      uint4 r[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) r[j] = multimem_ld_sum<__nv_bfloat16>(mc + (i + j * stride) * 8);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        acc8(g, r[j]);
+        update(i + j * stride, g);
+      }
+    }
+    for (; i < nvec; i += stride) {
+      float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      acc8(g, multimem_ld_sum<__nv_bfloat16>(mc + i * 8));
+      update(i, g);
+    }
+  } else {
+    for (; i < nvec; i += stride) {
+      float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      uint4 raw[kMaxRanks];
+#pragma unroll
+      for (int k = 0; k < kMaxRanks; ++k) {
+        if (k < world) {
+          const int p = (rank + k) % world;
+          raw[k] = ld_nc_v4(reinterpret_cast<const __nv_bfloat16*>(grads.p[p]) + base + i * 8);
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < kMaxRanks; ++k)
+        if (k < world) acc8(g, raw[k]);
+      update(i, g);
+    }
   }
   // The updated bf16 shard is what peers gather next step: announce it once every block
   // of this launch has finished.
@@ -194,7 +217,29 @@ __global__ void __launch_bounds__(256)
   int64_t v1 = v0 + per;
   if (v1 > nvec) v1 = nvec;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t i = v0 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < v1; i += stride) {
+  int64_t i = v0 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (mc_in && mc_out && !kInFp32) {
+    // both halves through the switch: four reductions in flight per thread, each result
+    // scaled and written to every rank with one multicast store
+    const __nv_bfloat16* mi = reinterpret_cast<const __nv_bfloat16*>(mc_in);
+    for (; i + 3 * stride < v1; i += 4 * stride) {
+      uint4 r[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) r[j] = multimem_ld_sum<__nv_bfloat16>(mi + (i + j * stride) * 8);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        acc8(g, r[j]);
+        uint4 o;
+        o.x = pack_bf16x2(g[0] * scale, g[1] * scale);
+        o.y = pack_bf16x2(g[2] * scale, g[3] * scale);
+        o.z = pack_bf16x2(g[4] * scale, g[5] * scale);
+        o.w = pack_bf16x2(g[6] * scale, g[7] * scale);
+        multimem_st_v4(reinterpret_cast<uint4*>(mc_out) + i + j * stride, o);
+      }
+    }
+  }
+  for (; i < v1; i += stride) {
     float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     if (mc_in) {
       if (kInFp32) {
@@ -359,7 +404,7 @@ extern "C" int mb200_rs_adamw(const void* const* grad_ptrs, const void* mc_grads
   const double bc1 = 1.0 - pow((double)beta1, (double)step);
   const double bc2 = 1.0 - pow((double)beta2, (double)step);
   const int grid = n_blocks > 0 ? n_blocks
-                                 : comm_grid(shard_elems / 8, 256 * 4, mc_grads ? 148 : 592);
+                                 : comm_grid(shard_elems / 8, 256 * 4, mc_grads ? 296 : 592);
   rs_adamw_kernel<<<grid, 256, 0, ST(stream)>>>(
       make_peers(grad_ptrs, world), mc_grads, make_peers(flag_ptrs, world), master, m, v,
       reinterpret_cast<__nv_bfloat16*>(param_shard), shard_elems, rank, world, grad_slot,

@@ -81,6 +81,8 @@ class WorkerCore {
     env_[id] = std::make_shared<RemoteErr>(RemoteErr{seq, rank, std::move(func), std::move(text),
                                                      std::move(tb), dep});
   }
+  // The index of the GPU this worker owns (-1: a CPU worker).
+  void set_cuda_index(int64_t idx) { cuda_index_ = idx; }
   bool contains(int64_t id) const { return env_.count(id) != 0; }
   py::object get(int64_t id) const {
     auto it = env_.find(id);
@@ -176,6 +178,7 @@ class WorkerCore {
 
  private:
   int64_t rank_;
+  int64_t cuda_index_ = -1;
   py::object ref_type_;
   std::unordered_map<int64_t, Value> env_;
   std::unordered_map<int64_t, std::vector<RecItem>> recordings_;
@@ -282,6 +285,11 @@ class WorkerCore {
       return a;
     }
     a.constant = torch::jit::toIValue(h, type);
+    // The controller names "the worker's GPU" as cuda or cuda:<its own current index>; every
+    // worker owns exactly one GPU, so any CUDA device in an argument means that one (the
+    // reference gets the same effect by showing each worker process a single device).
+    if (cuda_index_ >= 0 && a.constant.isDevice() && a.constant.toDevice().is_cuda())
+      a.constant = c10::IValue(c10::Device(c10::DeviceType::CUDA, (c10::DeviceIndex)cuda_index_));
     return a;
   }
 
@@ -417,6 +425,7 @@ PYBIND11_MODULE(_tensor_worker, m) {
       .def(py::init<int64_t, py::object>(), py::arg("rank"), py::arg("ref_type"))
       .def("set", &WorkerCore::set)
       .def("set_error", &WorkerCore::set_error)
+      .def("set_cuda_index", &WorkerCore::set_cuda_index)
       .def("get", &WorkerCore::get)
       .def("pop", &WorkerCore::pop)
       .def("contains", &WorkerCore::contains)

@@ -55,17 +55,24 @@ class LlamaConfig:
             n += self.vocab * self.d
         return n
 
-    def flops_per_token(self, seq_len: int, recompute: bool = True) -> float:
-        """Model FLOPs per token for one training step (fwd + bwd [+ recomputed fwd]); with
-        experts, the ``top_k`` active ones."""
+    def flops_per_token(self, seq_len: int, recompute: bool = False) -> float:
+        """FLOPs per token of one training step; with experts, the ``top_k`` active ones.
+
+        ``recompute=False``: *model* FLOPs, the figure MFU is quoted on -- forward plus
+        twice that for backward (3x the forward, attention included).
+        ``recompute=True``: what the hardware executes with every layer checkpointed -- the
+        GEMMs of the forward run once more (4x), while attention's forward is not repeated
+        (its output and log-sum-exp are kept) but its backward recomputes the scores
+        (2.5x its forward), 3.5x in all."""
         act = self.top_k if self.n_experts else 1
         mm = self.n_layers * (self.qkv_dim * self.d + self.d * self.d +
                               act * 3 * self.ffn * self.d + self.n_experts * self.d)
         mm += self.vocab * self.d
         attn = self.n_layers * 2 * seq_len * self.d / 2  # causal QK^T + PV, per token
-        fwd = 2 * mm + 2 * attn
-        return fwd * (4 if recompute else 3)
-
+        if not recompute:
+            return 3 * (2 * mm + 2 * attn)
+        head = self.vocab * self.d                       # the head is not checkpointed
+        return 2 * (4 * (mm - head) + 3 * head) + 2 * attn * 3.5
 
 PRESETS: dict[str, LlamaConfig] = {
     "llama3-8b": LlamaConfig(128256, 4096, 32, 32, 8, 14336, 1e-5, 500000.0, False, "llama3-8b"),

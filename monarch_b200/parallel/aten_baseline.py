@@ -34,7 +34,11 @@ class AtenTrainer:
         if self.world > 1:
             # fp32 master parameters, sharded; bf16 all-gathered compute copies
             from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
-            mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
+            # inputs are not cast at module boundaries: the activations are bf16 already (the
+            # embedding's gathered weight is), and the fp32 rotary tables must stay fp32 in
+            # the forward and in the checkpointed recomputation alike
+            mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32,
+                                      cast_forward_inputs=False)
             for blk in net.model.layers:
                 fully_shard(blk, mp_policy=mp)
             fully_shard(net, mp_policy=mp)

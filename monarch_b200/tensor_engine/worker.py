@@ -260,6 +260,8 @@ class TensorWorker(Actor):
         self.proc_key = context().actor_instance.proc_id   # shared with the proc's actors
         mod = _load_core()
         self.core = mod.WorkerCore(self.rank, Ref) if mod is not None else None
+        if self.core is not None and self.use_cuda:
+            self.core.set_cuda_index(self.device.index)
         self.env = _Env(self.core)
         self.streams: Dict[int, Any] = {0: None}
         self.groups: Dict[Tuple[int, ...], Any] = {}
@@ -293,6 +295,17 @@ class TensorWorker(Actor):
     def _report(self, err: RemoteError) -> None:
         if self.error_port is not None and err.dependent_of is None:
             self.error_port.send(("error", err.seq, self.rank, err.func, err.exc_text, err.tb))
+
+    def _localize(self, obj):
+        """``obj`` with every ``torch.device("cuda", i)`` replaced by this worker's GPU: a
+        worker owns one GPU, whatever index the controller's process happened to name."""
+        if isinstance(obj, torch.device):
+            return self.device if obj.type == "cuda" else obj
+        if isinstance(obj, (list, tuple)):
+            return _seq(obj, (self._localize(o) for o in obj))
+        if isinstance(obj, dict):
+            return {key: self._localize(v) for key, v in obj.items()}
+        return obj
 
     def _stream_ctx(self, stream_id: int):
         s = self.streams.get(stream_id)
@@ -404,6 +417,8 @@ class TensorWorker(Actor):
                                 dependent_of=dep.seq)
                 self._poison(seq, results + mutates, e)
                 return
+            if self.use_cuda:      # any CUDA device named by the controller is this worker's
+                a, k = self._localize(a), self._localize(k)
             fn = _resolve_function(fspec)
             with self._stream_ctx(stream):
                 out = fn(*a, **k)

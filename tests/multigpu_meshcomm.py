@@ -43,7 +43,7 @@ def _check_comm(comm: MeshComm, rank: int, world: int, dev, tag: str, results: d
                     continue
                 if op == "product" and n > 1000:
                     continue
-                acc = x.double() if dtype.is_floating_point else x.clone()
+                acc = x.clone().double() if dtype.is_floating_point else x.clone()
                 dist.all_reduce(acc, op=red)
                 if op == "avg":
                     acc = acc / world
