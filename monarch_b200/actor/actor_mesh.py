@@ -262,7 +262,10 @@ def _recv_checked(receiver, health: Optional[_Health], actor_name: str,
                   deadline: Optional[float], ranks=None):
     """Wait for the next envelope, waking regularly to notice supervision failures."""
     while True:
-        env = receiver.recv(50)
+        slice_ms = 50
+        if deadline is not None:   # a poll (deadline now) must not sit out a whole slice
+            slice_ms = max(0, min(50, int((deadline - time.monotonic()) * 1000)))
+        env = receiver.recv(slice_ms) if slice_ms > 0 else receiver.try_recv()
         if env is not None:
             return env
         if health is not None:
@@ -317,8 +320,13 @@ class PortReceiver(Generic[R]):
             raise obj
         return rank, obj
 
+    def _arm(self, wake) -> None:
+        """``wake()`` after every delivery to this port (None: stop); lets a coroutine sleep
+        until a message is there instead of parking a thread in ``recv``."""
+        self._rx.set_notify(wake)
+
     def recv(self) -> Future[R]:
-        return Future(lambda timeout: self._next(timeout)[1])
+        return Future(lambda timeout: self._next(timeout)[1], arm=self._arm)
 
     def ranked(self) -> "RankedPortReceiver[R]":
         return RankedPortReceiver(self)
@@ -332,7 +340,7 @@ class RankedPortReceiver(Generic[R]):
         self._inner = inner
 
     def recv(self) -> Future[Tuple[int, R]]:
-        return Future(lambda timeout: self._inner._next(timeout))
+        return Future(lambda timeout: self._inner._next(timeout), arm=self._inner._arm)
 
 
 class Channel(Generic[R]):
@@ -515,19 +523,27 @@ class Endpoint(Generic[R]):
         self._send(args, kwargs, port, headers=self._gather_headers(port, n))
         shape = shape_normalised(self._mesh._shape)
 
+        out: List[Any] = [None] * n
+        got = [0]
+
         def wait(timeout: Optional[float]) -> ValueMesh[R]:
+            # resumable: a wait that timed out keeps what has arrived so far
             deadline = None if timeout is None else time.monotonic() + timeout
-            out: List[Any] = [None] * n
             try:
-                for _ in range(n):
+                while got[0] < n:
                     left = None if deadline is None else max(deadline - time.monotonic(), 0.0)
                     rank, v = rx._next(left)
                     out[rank] = v
-            finally:
+                    got[0] += 1
+            except TimeoutError:
+                raise
+            except BaseException:
                 rx.close()
+                raise
+            rx.close()
             return ValueMesh(shape, out)
 
-        return Future(wait)
+        return Future(wait, arm=rx._arm)
 
     def _gather_headers(self, port: Port, n: int) -> Optional[Dict[str, str]]:
         """Replies of a cast to more than a few actors come back gathered along the cast
@@ -544,7 +560,7 @@ class Endpoint(Generic[R]):
         self._mesh._raise_if_unhealthy()
         port, rx = self._open(once=True)
         self._send(args, kwargs, port)
-        return Future(lambda timeout: rx._next(timeout)[1])
+        return Future(lambda timeout: rx._next(timeout)[1], arm=rx._arm)
 
     def choose(self, *args, **kwargs) -> Future[R]:
         """Load-balanced call to one actor of the mesh, picked by a deterministic PRNG."""
@@ -552,7 +568,7 @@ class Endpoint(Generic[R]):
         port, rx = self._open(once=True)
         ranks = self._mesh._shape.ndslice.ranks()
         self._send(args, kwargs, port, [_choose_rng.choice(ranks)])
-        return Future(lambda timeout: rx._next(timeout)[1])
+        return Future(lambda timeout: rx._next(timeout)[1], arm=rx._arm)
 
     def stream(self, *args, **kwargs) -> Iterator[Future[R]]:
         self._mesh._raise_if_unhealthy()
@@ -560,7 +576,7 @@ class Endpoint(Generic[R]):
         n = len(self._mesh)
         self._send(args, kwargs, port)
         for _ in range(n):
-            yield Future(lambda timeout: rx._next(timeout)[1])
+            yield Future(lambda timeout: rx._next(timeout)[1], arm=rx._arm)
 
     def reduce(self, *args, reducer: str = "sum_f32", **kwargs) -> Future:
         """Call every actor and fold the returned tensors element-wise in the native

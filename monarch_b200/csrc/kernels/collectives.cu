@@ -31,12 +31,14 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <type_traits>
+
 #include "comm.cuh"
 
 namespace mb200 {
 
 enum : int { kF32 = 0, kBF16 = 1, kF16 = 2, kF64 = 3, kI32 = 4, kI64 = 5 };
-enum : int { kSum = 0, kProd = 1, kMin = 2, kMax = 3 };
+enum : int { kSum = 0, kProd = 1, kMin = 2, kMax = 3, kBand = 4, kBor = 5, kBxor = 6 };
 
 // ------------------------------------------------------------- 16-byte vector traits --
 template <typename T>
@@ -127,10 +129,16 @@ struct VT<int64_t> {
 
 template <int OP, typename A>
 __device__ __forceinline__ A combine(A x, A y) {
-  if (OP == kSum) return x + y;
-  if (OP == kProd) return x * y;
-  if (OP == kMin) return y < x ? y : x;
-  return y > x ? y : x;
+  if constexpr (OP == kSum) return x + y;
+  if constexpr (OP == kProd) return x * y;
+  if constexpr (OP == kMin) return y < x ? y : x;
+  if constexpr (OP == kMax) return y > x ? y : x;
+  if constexpr (std::is_integral<A>::value) {   // bitwise reductions: integer types only
+    if constexpr (OP == kBand) return x & y;
+    if constexpr (OP == kBor) return x | y;
+    if constexpr (OP == kBxor) return x ^ y;
+  }
+  return x;
 }
 
 template <typename T>
@@ -356,7 +364,13 @@ static int launch_reduce_op(int op, int grid, cudaStream_t st, const ReduceArgs&
     case kProd: coll_reduce_kernel<T, kProd><<<grid, 256, 0, st>>>(a); break;
     case kMin: coll_reduce_kernel<T, kMin><<<grid, 256, 0, st>>>(a); break;
     case kMax: coll_reduce_kernel<T, kMax><<<grid, 256, 0, st>>>(a); break;
-    default: return 1001;
+    default:
+      if constexpr (std::is_integral<T>::value) {
+        if (op == kBand) { coll_reduce_kernel<T, kBand><<<grid, 256, 0, st>>>(a); break; }
+        if (op == kBor) { coll_reduce_kernel<T, kBor><<<grid, 256, 0, st>>>(a); break; }
+        if (op == kBxor) { coll_reduce_kernel<T, kBxor><<<grid, 256, 0, st>>>(a); break; }
+      }
+      return 1001;
   }
   return (int)cudaGetLastError();
 }

@@ -157,8 +157,11 @@ std::vector<std::string> to_strings(const std::vector<py::object>& parts) {
 
 }  // namespace
 
+void bind_tasks(py::module_& m);   // tasks.cpp
+
 PYBIND11_MODULE(_native, m) {
   m.doc() = "monarch_b200 native runtime";
+  bind_tasks(m);
 
   // ------------------------------------------------------------------ ndslice ----
   py::register_exception<NdError>(m, "NdSliceError", PyExc_ValueError);

@@ -20,9 +20,14 @@
 #include <c10/core/Stream.h>
 #include <c10/core/impl/VirtualGuardImpl.h>
 
+#include <atomic>
+#include <condition_variable>
+#include <deque>
+#include <functional>
 #include <memory>
 #include <mutex>
 #include <string>
+#include <thread>
 #include <unordered_map>
 #include <variant>
 #include <vector>
@@ -62,9 +67,180 @@ struct RecItem {
   std::vector<int64_t> drop;     // refs of the recording that are dead after this item
 };
 
+// One OS thread per named stream (monarch_tensor_worker/src/stream.rs:542-588 gives every
+// StreamActor a dedicated thread): the worker actor only routes messages; each stream's
+// commands run in arrival order on its own thread, so a command that blocks on the host
+// (a user function waiting for something another stream produces, a collective's
+// bootstrap) holds up its own stream only.  Tasks are Python callables executed with the
+// GIL held; operator calls release it inside the dispatcher as before.
+class StreamThread {
+ public:
+  StreamThread(int64_t id, py::object on_start) : id_(id) {
+    auto* cell = new py::object(std::move(on_start));
+    thr_ = std::thread([this, cell] { loop(cell); });
+  }
+  ~StreamThread() { stop(); }
+
+  // GIL held by the caller; the callable is released under the GIL on the stream thread.
+  void submit(py::object fn) {
+    auto* cell = new py::object(std::move(fn));
+    {
+      std::lock_guard<std::mutex> g(mu_);
+      q_.push_back(cell);
+      ++pending_;
+    }
+    cv_.notify_all();
+  }
+
+  // GIL released by the caller.
+  void drain() {
+    std::unique_lock<std::mutex> lk(mu_);
+    idle_cv_.wait(lk, [&] { return pending_ == 0 || stop_; });
+  }
+
+  void stop() {
+    {
+      std::lock_guard<std::mutex> g(mu_);
+      if (stop_) return;
+      stop_ = true;
+    }
+    cv_.notify_all();
+    idle_cv_.notify_all();
+    if (thr_.joinable()) {
+      if (thr_.get_id() == std::this_thread::get_id())
+        thr_.detach();
+      else {
+        py::gil_scoped_release rel;
+        thr_.join();
+      }
+    }
+  }
+
+  int64_t pending() {
+    std::lock_guard<std::mutex> g(mu_);
+    return pending_;
+  }
+
+ private:
+  void run_cell(py::object* cell) {
+    py::gil_scoped_acquire g;
+    std::unique_ptr<py::object> own(cell);
+    try {
+      (*own)();
+    } catch (py::error_already_set& e) {
+      e.discard_as_unraisable("tensor worker stream thread");
+    }
+    own.reset();
+  }
+  void loop(py::object* on_start) {
+    if (!Py_IsInitialized()) return;
+    run_cell(on_start);
+    while (true) {
+      py::object* cell = nullptr;
+      {
+        std::unique_lock<std::mutex> lk(mu_);
+        cv_.wait(lk, [&] { return stop_ || !q_.empty(); });
+        if (q_.empty()) break;       // stop requested and nothing left
+        cell = q_.front();
+        q_.pop_front();
+      }
+      if (!Py_IsInitialized()) break;
+      run_cell(cell);
+      {
+        std::lock_guard<std::mutex> g(mu_);
+        --pending_;
+      }
+      idle_cv_.notify_all();
+    }
+  }
+  int64_t id_;
+  std::thread thr_;
+  std::mutex mu_;
+  std::condition_variable cv_, idle_cv_;
+  std::deque<py::object*> q_;
+  int64_t pending_ = 0;
+  bool stop_ = false;
+};
+
+// Rendezvous of all stream threads: every stream runs `arrive()` in its queue position; the
+// last to arrive performs the action; with hold=true the others wait for it to finish
+// (a barrier across streams), otherwise they carry on at once.
+struct Fence {
+  std::mutex mu;
+  std::condition_variable cv;
+  int remaining;
+  bool done = false;
+  explicit Fence(int n) : remaining(n) {}
+};
+
 class WorkerCore {
  public:
   WorkerCore(int64_t rank, py::object ref_type) : rank_(rank), ref_type_(std::move(ref_type)) {}
+  ~WorkerCore() { stop_threads(); }
+
+  // ------------------------------------------------------------------ stream threads
+  // Start the thread of stream `id`; `on_start` runs first on it (device, current stream).
+  void start_stream_thread(int64_t id, py::object on_start) {
+    if (threads_.count(id)) return;
+    threads_[id] = std::make_unique<StreamThread>(id, std::move(on_start));
+  }
+  bool has_stream_thread(int64_t id) const { return threads_.count(id) != 0; }
+  void submit(int64_t id, py::object fn) {
+    auto it = threads_.find(id);
+    if (it == threads_.end()) throw py::key_error("stream " + std::to_string(id) + " has no thread");
+    it->second->submit(std::move(fn));
+  }
+  // `action` (may be None) runs once every stream has reached this point of its queue.
+  void fence(py::object action, bool hold) {
+    if (threads_.empty()) {
+      if (!action.is_none()) action();
+      return;
+    }
+    auto f = std::make_shared<Fence>((int)threads_.size());
+    auto act = std::make_shared<py::object>(std::move(action));
+    for (auto& kv : threads_) {
+      kv.second->submit(py::cpp_function([f, act, hold]() {
+        bool last;
+        {
+          std::lock_guard<std::mutex> g(f->mu);
+          last = --f->remaining == 0;
+        }
+        if (last) {
+          if (!act->is_none()) {
+            try {
+              (*act)();
+            } catch (py::error_already_set& e) {
+              e.discard_as_unraisable("tensor worker fence action");
+            }
+          }
+          *act = py::none();
+          {
+            std::lock_guard<std::mutex> g(f->mu);
+            f->done = true;
+          }
+          f->cv.notify_all();
+        } else if (hold) {
+          py::gil_scoped_release rel;
+          std::unique_lock<std::mutex> lk(f->mu);
+          f->cv.wait(lk, [&] { return f->done; });
+        }
+      }));
+    }
+  }
+  // Wait until every stream has run everything submitted so far.
+  void drain() {
+    py::gil_scoped_release rel;
+    for (auto& kv : threads_) kv.second->drain();
+  }
+  void stop_threads() {
+    for (auto& kv : threads_) kv.second->stop();
+    threads_.clear();
+  }
+  int64_t pending() {
+    int64_t n = 0;
+    for (auto& kv : threads_) n += kv.second->pending();
+    return n;
+  }
 
   // ------------------------------------------------------------------ environment
   void set(int64_t id, py::object v) {
@@ -183,6 +359,7 @@ class WorkerCore {
   std::unordered_map<int64_t, Value> env_;
   std::unordered_map<int64_t, std::vector<RecItem>> recordings_;
   std::unordered_map<int64_t, py::object> streams_;
+  std::unordered_map<int64_t, std::unique_ptr<StreamThread>> threads_;
 
   static py::object to_py(const Value& v) {
     if (std::holds_alternative<std::monostate>(v)) return py::none();
@@ -437,5 +614,12 @@ PYBIND11_MODULE(_tensor_worker, m) {
            py::arg("drop_after") = std::unordered_map<int64_t, std::vector<int64_t>>{})
       .def("call_recording", &WorkerCore::call_recording)
       .def("has_recording", &WorkerCore::has_recording)
-      .def("create_stream", &WorkerCore::create_stream);
+      .def("create_stream", &WorkerCore::create_stream)
+      .def("start_stream_thread", &WorkerCore::start_stream_thread)
+      .def("has_stream_thread", &WorkerCore::has_stream_thread)
+      .def("submit", &WorkerCore::submit)
+      .def("fence", &WorkerCore::fence, py::arg("action"), py::arg("hold") = true)
+      .def("drain", &WorkerCore::drain)
+      .def("pending", &WorkerCore::pending)
+      .def("stop_threads", &WorkerCore::stop_threads);
 }

@@ -13,7 +13,8 @@ not matter to the collectives:
   and exchange over an existing process group and also yields an NVSwitch multicast
   mapping, which switches sums of f32/bf16/f16 to ``multimem.ld_reduce`` / ``multimem.st``.
 
-Operations: ``all_reduce`` (sum, avg, product, min, max), ``reduce_scatter``,
+Operations: ``all_reduce`` (sum, avg, product, min, max; band, bor, bxor on int32/int64),
+``reduce_scatter``,
 ``all_gather``, ``all_to_all``, ``broadcast``, ``reduce`` (to a root), ``barrier``.  They
 are asynchronous on the current CUDA stream; every rank of the group must issue the same
 sequence.  Tensors larger than the staging capacity are moved in chunks.
@@ -39,7 +40,9 @@ SLOT_STAGED, SLOT_RESULT, SLOT_BARRIER = 0, 1, 2
 
 _DT = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2, torch.float64: 3, torch.int32: 4,
        torch.int64: 5}
-_OP = {"sum": 0, "avg": 0, "product": 1, "prod": 1, "min": 2, "max": 3}
+_OP = {"sum": 0, "avg": 0, "product": 1, "prod": 1, "min": 2, "max": 3, "band": 4, "bor": 5,
+       "bxor": 6}
+_BITWISE = ("band", "bor", "bxor")
 
 
 def default_capacity() -> int:
@@ -51,6 +54,8 @@ def supports(dtype: torch.dtype, reduction: Optional[str] = None) -> bool:
     take any dtype; reductions the six arithmetic ones)."""
     if reduction is None:
         return True
+    if reduction in _BITWISE:
+        return dtype in (torch.int32, torch.int64)
     return dtype in _DT and reduction in _OP
 
 
@@ -197,7 +202,7 @@ class MeshComm:
                    scale: Optional[float] = None) -> torch.Tensor:
         """Element-wise ``op`` over the ranks; every rank gets the result (bit-identical on
         all ranks).  ``avg`` is a sum scaled by 1/world.  ``out`` may be ``t`` itself."""
-        if t.dtype not in _DT or op not in _OP:
+        if not supports(t.dtype, op):
             raise TypeError(f"all_reduce: unsupported {t.dtype} / {op!r}")
         src = self._check(t)
         if op == "avg":
@@ -231,7 +236,7 @@ class MeshComm:
     def reduce_scatter(self, t: torch.Tensor, op: str = "sum",
                        scale: Optional[float] = None) -> torch.Tensor:
         """``t``: [world, ...]; rank r gets ``op`` over the ranks of slice r."""
-        if t.dtype not in _DT or op not in _OP:
+        if not supports(t.dtype, op):
             raise TypeError(f"reduce_scatter: unsupported {t.dtype} / {op!r}")
         if t.dim() == 0 or t.shape[0] != self.world:
             raise ValueError(f"reduce_scatter needs an outer dim of {self.world}, got "
@@ -310,7 +315,7 @@ class MeshComm:
     def reduce(self, t: torch.Tensor, root: int, op: str = "sum",
                scale: Optional[float] = None) -> Optional[torch.Tensor]:
         """``op`` over the ranks, delivered to ``root`` only (other ranks get None)."""
-        if t.dtype not in _DT or op not in _OP:
+        if not supports(t.dtype, op):
             raise TypeError(f"reduce: unsupported {t.dtype} / {op!r}")
         src = self._check(t)
         if op == "avg":

@@ -641,7 +641,7 @@ class Tensor(torch.Tensor):
         root = client.root_mesh
         client.send(root, ("send_meta", Ref(out.ref), tuple(self._fake.shape), self._fake.dtype))
         client.send(root, ("send_tensor", seq, Ref(out.ref), Ref(self.ref), fr, to,
-                           self.stream.id))
+                           self.stream.id, out.stream.id))
         return out
 
     def slice_mesh(self, **kwargs) -> "Tensor":
@@ -1040,7 +1040,10 @@ class RemoteProcessGroup:
     def __init__(self, dims: Tuple[str, ...], mesh: "DeviceMesh"):
         self.dims = tuple(dims)
         self.device_mesh = mesh
-        self.key = mesh.client.ensure_comm(mesh, self.dims)
+        # GPU workers: a process group over the package's NVLink collectives (no NCCL
+        # bootstrap); CPU workers: a gloo group
+        own = mesh.client.use_cuda and os.environ.get("MB200_TE_COLLECTIVES", "own") == "own"
+        self.key = mesh.client.ensure_comm(mesh, self.dims, stream_id=0, own=own)
 
     def size(self) -> int:
         n = 1

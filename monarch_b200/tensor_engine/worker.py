@@ -23,7 +23,7 @@ from typing import Any, Dict, List, Optional, Tuple
 
 import torch
 
-from ..actor import Actor, current_rank, endpoint
+from ..actor import Actor, context, current_rank, endpoint
 from ..actor.actor_mesh import Port
 
 
@@ -256,7 +256,6 @@ class TensorWorker(Actor):
             torch.cuda.set_device(self.device)
         else:
             self.device = torch.device("cpu")
-        from ..actor import context
         self.proc_key = context().actor_instance.proc_id   # shared with the proc's actors
         mod = _load_core()
         self.core = mod.WorkerCore(self.rank, Ref) if mod is not None else None
@@ -269,16 +268,33 @@ class TensorWorker(Actor):
         # communicators whose peers have not been connected yet
         self.comms: Dict[Tuple[int, ...], Any] = {}
         self._comm_pending: Dict[Tuple[int, ...], Any] = {}
+        self._own_pgs: Dict[Tuple[int, ...], Any] = {}
         self.borrows: Dict[int, Any] = {}
         self.recordings: Dict[int, List[tuple]] = {}
         self.pipes: Dict[int, WorkerPipe] = {}
         self.pg_ready = False
         self.error_port: Optional[Port] = None
         self.last_seq = -1
+        # One OS thread per stream inside the native core (MB200_WORKER_THREADS=0: every
+        # command runs on the actor's thread in arrival order, as a single queue).
+        self.threaded = self.core is not None and \
+            os.environ.get("MB200_WORKER_THREADS", "1") == "1"
+        self._borrow_route: Dict[int, Tuple[int, int]] = {}
+        if self.threaded:
+            self._start_stream_thread(0)
 
     # ---------------------------------------------------------------------- helpers
     def _get(self, ref: Ref, seq: int):
         if isinstance(ref, PGRef):
+            own = self.comms.get(ref.key)
+            if own is not None:           # a process group over the NVLink collectives
+                if isinstance(own[0], Exception):
+                    raise own[0]
+                pg = self._own_pgs.get(ref.key)
+                if pg is None:
+                    from ..parallel.mesh_process_group import MeshProcessGroup
+                    pg = self._own_pgs[ref.key] = MeshProcessGroup(own[0])
+                return pg
             ent = self.groups.get(ref.key)
             if ent is None:
                 raise KeyError(f"process group {ref.key} does not include worker {self.rank}")
@@ -323,13 +339,131 @@ class TensorWorker(Actor):
     def run(self, msgs: List[tuple]) -> None:
         """A batch of worker messages (one for eager dispatch, many under coalescing)."""
         for m in msgs:
-            getattr(self, "_m_" + m[0])(*m[1:])
+            self._route(m)
 
     @endpoint
     def run_and_reply(self, msgs: List[tuple], fetch: tuple) -> Any:
         for m in msgs:
-            getattr(self, "_m_" + m[0])(*m[1:])
+            self._route(m)
+        self._drain()
         return self._fetch(*fetch)
+
+    # ------------------------------------------------------------ per-stream threads
+    # position of the stream id in the messages that run on one stream
+    _STREAM_ARG = {"call": 7, "reduce": 9, "send_tensor": 6, "pipe_recv": 4, "pipe_send": 4,
+                   "actor_call_state": 3, "actor_call_rref": 4}
+
+    def _start_stream_thread(self, stream_id: int) -> None:
+        if self.core.has_stream_thread(stream_id):
+            return
+
+        def on_start():
+            if self.use_cuda:
+                torch.cuda.set_device(self.device)
+                s = self.streams.get(stream_id)
+                if s is not None:
+                    torch.cuda.set_stream(s)      # this thread's current stream from now on
+        self.core.start_stream_thread(stream_id, on_start)
+
+    def _route(self, m: tuple) -> None:
+        """Hand a message to the thread of the stream it belongs to; messages that belong
+        to no stream wait for every stream to reach them (deletions without holding the
+        streams up, the rest as a barrier across streams)."""
+        kind = m[0]
+        if not self.threaded:
+            getattr(self, "_m_" + kind)(*m[1:])
+            return
+        from ..actor import actor_mesh as _am
+        ctx = context()           # the actor's context of this message, for user functions
+
+        def handler():
+            _am._tls.ctx = ctx
+            getattr(self, "_m_" + kind)(*m[1:])
+        pos = self._STREAM_ARG.get(kind)
+        if pos is not None:
+            stream = m[pos]
+            self._start_stream_thread(stream)
+            self.core.submit(stream, handler)
+            if kind == "send_tensor" and len(m) > 7 and m[7] is not None and m[7] != stream:
+                self._order_after(stream, m[7])    # the result is used on another stream
+        elif kind == "create_stream":
+            self._m_create_stream(*m[1:])
+            self._start_stream_thread(m[1])
+        elif kind == "borrow_create":
+            self._route_borrow_create(*m[1:])
+        elif kind == "borrow_drop":
+            self._route_borrow_drop(*m[1:])
+        else:
+            self.core.fence(handler, kind != "delete")
+
+    def _order_after(self, first: int, then: int) -> None:
+        """Everything handed to stream ``then`` from here on runs after what stream ``first``
+        has been handed so far (host order by a flag, device order by a CUDA event)."""
+        self._start_stream_thread(then)
+        issued, box = threading.Event(), {}
+
+        def on_first():
+            if self.use_cuda:
+                box["ev"] = torch.cuda.Event()
+                box["ev"].record(torch.cuda.current_stream())
+            issued.set()
+
+        def on_then():
+            issued.wait()
+            if self.use_cuda:
+                torch.cuda.current_stream().wait_event(box["ev"])
+        self.core.submit(first, on_first)
+        self.core.submit(then, on_then)
+
+    def _route_borrow_create(self, borrow_id, ref, from_stream, to_stream, result) -> None:
+        """The borrowing stream may use the value once the producing stream has issued
+        everything it was sent before the borrow: a host-side flag carries that, a CUDA
+        event the device-side order."""
+        self._start_stream_thread(from_stream)
+        self._start_stream_thread(to_stream)
+        self._borrow_route[borrow_id] = (from_stream, to_stream)
+        issued, box = threading.Event(), {}
+
+        def on_from():
+            if self.use_cuda:
+                box["ev"] = torch.cuda.Event()
+                box["ev"].record(torch.cuda.current_stream())
+            issued.set()
+
+        def on_to():
+            issued.wait()
+            if self.use_cuda:
+                torch.cuda.current_stream().wait_event(box["ev"])
+            self.env[result.id] = self.env.get(ref.id)
+            self.borrows[borrow_id] = (from_stream, to_stream)
+        self.core.submit(from_stream, on_from)
+        self.core.submit(to_stream, on_to)
+
+    def _route_borrow_drop(self, borrow_id) -> None:
+        route = self._borrow_route.pop(borrow_id, None)
+        if route is None:
+            return
+        from_stream, to_stream = route
+        issued, box = threading.Event(), {}
+
+        def on_to():
+            if self.use_cuda:
+                box["ev"] = torch.cuda.Event()
+                box["ev"].record(torch.cuda.current_stream())
+            self.borrows.pop(borrow_id, None)
+            issued.set()
+
+        def on_from():
+            issued.wait()
+            if self.use_cuda:
+                torch.cuda.current_stream().wait_event(box["ev"])
+        self.core.submit(to_stream, on_to)
+        self.core.submit(from_stream, on_from)
+
+    def _drain(self) -> None:
+        """Wait until every stream thread has run what it was handed so far."""
+        if self.threaded:
+            self.core.drain()
 
     # ------------------------------------------------- own NVLink communicators
     @endpoint
@@ -445,7 +579,9 @@ class TensorWorker(Actor):
             self.streams[stream_id] = torch.cuda.Stream(device=self.device) \
                 if (self.use_cuda and not default) else None
             if self.core is not None:
-                self.core.create_stream(stream_id, self.streams[stream_id])
+                # with a thread per stream the thread's current stream is set once, at start
+                self.core.create_stream(stream_id,
+                                        None if self.threaded else self.streams[stream_id])
 
     def _m_borrow_create(self, borrow_id, ref, from_stream, to_stream, result) -> None:
         # the borrowing stream waits for the producing stream; the value is aliased
@@ -560,8 +696,11 @@ class TensorWorker(Actor):
             self._poison(seq, [result], e)
             self._report(e)
 
-    def _m_send_tensor(self, seq, result, ref, from_ranks, to_ranks, stream) -> None:
-        """Point-to-point move between equally shaped sub-meshes (pipeline activations)."""
+    def _m_send_tensor(self, seq, result, ref, from_ranks, to_ranks, stream,
+                       to_stream=None) -> None:
+        """Point-to-point move between equally shaped sub-meshes (pipeline activations).
+        Runs on the source tensor's stream; ``to_stream`` is the stream the result lives on
+        (the router orders that stream behind this transfer)."""
         import torch.distributed as dist
         try:
             pairs = list(zip(from_ranks, to_ranks))
@@ -761,6 +900,7 @@ class TensorWorker(Actor):
 
     @endpoint
     def fetch(self, seq, ref_tree, preprocess=None):
+        self._drain()
         return self._fetch(seq, ref_tree, preprocess)
 
     @endpoint
@@ -771,6 +911,7 @@ class TensorWorker(Actor):
 
     @endpoint
     def sync(self) -> int:
+        self._drain()
         if self.use_cuda:
             torch.cuda.synchronize(self.device)
         return self.last_seq

@@ -66,6 +66,15 @@ def _check_comm(comm: MeshComm, rank: int, world: int, dev, tag: str, results: d
                     assert _rel(ref, y) <= 4e-3, (tag, "ranks differ", dtype, n, op)
                 else:
                     assert torch.equal(ref, y), (tag, "ranks differ", dtype, n, op)
+            if not dtype.is_floating_point:     # bitwise reductions (NCCL has none: fold by hand)
+                parts = [torch.empty_like(x) for _ in range(world)]
+                dist.all_gather(parts, x)
+                for op, f in (("band", torch.bitwise_and), ("bor", torch.bitwise_or),
+                              ("bxor", torch.bitwise_xor)):
+                    acc = parts[0]
+                    for p in parts[1:]:
+                        acc = f(acc, p)
+                    assert torch.equal(comm.all_reduce(x, op), acc), (tag, dtype, n, op)
     results[f"{tag}_allreduce_16bit_worst_rel"] = worst
     # reduce-scatter, all-gather, all-to-all, broadcast, root reduce; ragged sizes
     for dtype, cols in ((torch.float32, 1001), (torch.bfloat16, 40_003), (torch.float32, 2_500_000)):

@@ -25,6 +25,23 @@ def _dist_state(_t):
             "launches": K.launch_count, "device": torch.cuda.current_device()}
 
 
+def _udf_collectives(x, pg):
+    """Worker-side code written against torch.distributed; the group runs on the package's
+    NVLink kernels."""
+    import torch.distributed as dist
+    assert pg.getBackendName() == "mb200"
+    out = x.clone()
+    dist.all_reduce(out, group=pg)
+    parts = [torch.empty_like(x) for _ in range(pg.size())]
+    dist.all_gather(parts, x, group=pg)
+    rs = torch.empty(x.numel() // pg.size(), device=x.device, dtype=x.dtype)
+    dist.reduce_scatter_tensor(rs, x.reshape(-1).contiguous(), group=pg)
+    b = x.clone()
+    dist.broadcast(b, pg.size() - 1, group=pg)
+    dist.barrier(group=pg)
+    return out, torch.stack(parts), rs, b
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=2)
@@ -62,6 +79,13 @@ def main() -> int:
             # a large tensor: the two-shot path and chunking through the staging area
             s = big.reduce("gpus", "sum")
             got["big"] = te.inspect(torch.stack([s.min(), s.max()]), gpus=n - 1)
+            # torch.distributed code inside a remote function, on a group over the kernels
+            udf = te.remote(_udf_collectives,
+                            propagate=lambda t, pg: (t, torch.stack([t] * pg.size()),
+                                                     t.reshape(-1)[: t.numel() // pg.size()], t))
+            w = (r + 1) * torch.ones(2 * n, device="cuda")
+            u_sum, u_parts, u_rs, u_b = udf(w, dm.process_group("gpus"))
+            got["udf"] = [te.inspect((u_sum, u_parts, u_rs, u_b), gpus=g) for g in range(n)]
             # a collective on a second stream (its own communicator)
             side = te.Stream("side")
             b, borrow = side.borrow(x)
@@ -76,6 +100,13 @@ def main() -> int:
             want = torch.stack([torch.full((5,), float((p + 1) * (g + 1))) for p in range(n)])
             assert torch.equal(got["a2a"][g], want), (g, got["a2a"][g])
             assert torch.equal(got["stack"][g], base * (g + 1))
+        for g in range(n):
+            u_sum, u_parts, u_rs, u_b = got["udf"][g]
+            assert torch.equal(u_sum, torch.full((2 * n,), tri)), (g, u_sum)
+            assert torch.equal(u_parts, torch.stack([torch.full((2 * n,), float(p + 1))
+                                                     for p in range(n)]))
+            assert torch.equal(u_rs, torch.full((2,), tri)) and torch.equal(
+                u_b, torch.full((2 * n,), float(n)))
         assert torch.allclose(got["avg"], base * tri / n)
         assert torch.equal(got["max"], base * n) and torch.equal(got["min"], base)
         assert torch.equal(got["bf16"].float(), base * tri)
@@ -86,15 +117,25 @@ def main() -> int:
         assert sorted(s["device"] for s in state) == list(range(n)), state
         assert all(s["launches"] > 20 for s in state), state
         results["launches_per_worker"] = [s["launches"] for s in state]
-        # an operation outside the kernels' coverage falls back to NCCL, initialised on demand
+        # bitwise reductions of integers run on the kernels too (NCCL has none)
         with dm.activate():
             bits = (dm.rank("gpus") + 1).to(torch.int32).cuda() * \
                 torch.ones(4, dtype=torch.int32, device="cuda")
             bo = te.inspect(bits.reduce("gpus", "bor"), gpus=0)
+            still = te.call_on_shard_and_fetch(_dist_state, bits, shard={"gpus": 0}).get()
         want = 0
         for g in range(n):
             want |= g + 1
         assert bo.tolist() == [want] * 4, bo
+        assert not still["dist_initialized"]
+        # a dtype outside the kernels' coverage falls back to NCCL, initialised on demand
+        with dm.activate():
+            small = (dm.rank("gpus") + 1).to(torch.uint8).cuda() * \
+                torch.ones(4, dtype=torch.uint8, device="cuda")
+            sm = te.inspect(small.reduce("gpus", "sum"), gpus=0)
+            now = te.call_on_shard_and_fetch(_dist_state, small, shard={"gpus": 0}).get()
+        assert sm.tolist() == [int(tri)] * 4, sm
+        assert now["dist_initialized"]
         print("TENSOR ENGINE MULTIGPU OK " + json.dumps(results))
         return 0
     finally:

@@ -43,6 +43,9 @@ def test_all_reduce_of_one_rank_is_the_identity(comm, dtype, n):
         K.check_status("cuda")
         assert y.shape == x.shape and y.dtype == dtype
         assert torch.equal(y, x), (op, dtype, n)
+    if not dtype.is_floating_point and dtype in (torch.int32, torch.int64):
+        for op in ("band", "bor", "bxor"):
+            assert torch.equal(comm.all_reduce(x, op), x), (op, dtype, n)
     z = x.clone()
     assert comm.all_reduce(z, "sum", out=z) is z
     torch.cuda.synchronize()

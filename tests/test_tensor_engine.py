@@ -614,3 +614,39 @@ def test_failure_on_one_rank_of_a_distributed_tensor(dm):
         with pytest.raises(te.RemoteException):
             te.fetch_shard(rz, host=1, gpu=0).get(timeout=60)
         dm.client.drain_errors()
+
+
+# -------------------------------------------------------- one host thread per stream --
+import threading as _threading  # noqa: E402
+
+_GATE = _threading.Event()       # lives in every worker process (this module is imported there)
+
+
+def _wait_for_gate(x):
+    if not _GATE.wait(30):
+        raise RuntimeError("nobody opened the gate: the streams share one host thread")
+    _GATE.clear()
+    return x + 1
+
+
+def _open_gate(x):
+    _GATE.set()
+    return x * 2
+
+
+def test_user_functions_of_two_streams_run_on_separate_host_threads(dm):
+    """A function on the main stream blocks on the host until a function on a second
+    stream releases it: possible only because every stream has its own OS thread in the
+    worker (monarch_tensor_worker/src/stream.rs:542-588 in the reference)."""
+    wait = te.remote(_wait_for_gate, propagate=lambda x: x)
+    release = te.remote(_open_gate, propagate=lambda x: x)
+    side = te.Stream("gatekeeper")
+    with dm.activate():
+        x = torch.ones(2)
+        waited = wait(x)                       # main stream: parks its thread on the host
+        after = waited + 1                     # queued behind it on the same stream
+        with side.activate():
+            z = torch.ones(2)
+            opened = release(z)                # side stream: runs meanwhile
+            assert te.inspect(opened).tolist() == [2.0, 2.0]
+        assert te.inspect(after).tolist() == [3.0, 3.0]

@@ -104,3 +104,29 @@ def test_to_mesh_and_fetch_shard(dm):
         g.add_(1)
         assert te.fetch_shard(f, gpus=0).get().tolist() == [[3.0, 3.0], [3.0, 3.0]]
         assert te.fetch_shard(g, gpus=0).get().tolist() == [[4.0, 4.0], [4.0, 4.0]]
+
+
+def _udf_collectives(x, pg):
+    """Worker-side code written against torch.distributed: the group it receives runs on the
+    package's NVLink kernels (backend name "mb200"), not on NCCL."""
+    import torch.distributed as dist
+    assert pg.getBackendName() == "mb200" and not dist.is_initialized()
+    out = x.clone()
+    dist.all_reduce(out, group=pg)
+    gathered = torch.empty(pg.size() * x.numel(), device=x.device, dtype=x.dtype)
+    dist.all_gather_into_tensor(gathered, x.reshape(-1), group=pg)
+    mx = x.clone()
+    dist.all_reduce(mx, op=dist.ReduceOp.MAX, group=pg)
+    dist.broadcast(mx, 0, group=pg)
+    dist.barrier(group=pg)
+    return out + gathered.view(pg.size(), *x.shape).sum(0) + mx
+
+
+def test_user_defined_function_gets_a_process_group_over_the_nvlink_kernels(dm):
+    from monarch_b200 import tensor_engine as te
+    fn = te.remote(_udf_collectives, propagate=lambda x, pg: x)
+    with dm.activate():
+        pg = dm.process_group("gpus")
+        x = torch.arange(4, dtype=torch.float32, device="cuda") + 1
+        got = te.inspect(fn(x, pg))
+    assert got.tolist() == [3.0, 6.0, 9.0, 12.0]
