@@ -4,10 +4,12 @@ op by op to a worker, dispatched inside a ``coalescing()`` block, replayed as a 
 recording, and as one remote function.  Small tensors on purpose: the numbers are the cost of
 the controller -> worker path per op, not of the math.
 
-    python benchmarks/dispatch.py [--iters 2000] [--size 100] [--cuda] [--mock]
+    python benchmarks/dispatch.py [--iters 2000] [--size 100] [--cuda] [--mock] [--null-device]
 
 ``--mock`` runs the controller against simulated workers (no processes): the cost of the
-front-end alone.  Parity: python/tests/dispatch_bench.py of the reference (local vs dispatched
+front-end alone.  ``--null-device`` runs real worker processes whose tensors are shape-only
+(nothing is computed or copied): the cost of the controller -> worker path for a program
+written for GPUs, measurable on a box without one.  Parity: python/tests/dispatch_bench.py of the reference (local vs dispatched
 vs remote function vs coalesced; the reference publishes the harness, not numbers)."""
 import argparse
 import json
@@ -51,11 +53,13 @@ def main():
     ap.add_argument("--size", type=int, default=100)
     ap.add_argument("--cuda", action="store_true")
     ap.add_argument("--mock", action="store_true")
+    ap.add_argument("--null-device", action="store_true")
     ap.add_argument("--out")
     a = ap.parse_args()
     n, ops = a.iters, 3 * a.iters
     dev = "cuda" if a.cuda else "cpu"
-    out = {"iters": n, "ops": ops, "size": a.size, "device": dev, "mock": a.mock}
+    out = {"iters": n, "ops": ops, "size": a.size, "device": dev, "mock": a.mock,
+           "null_device": a.null_device}
 
     x0 = torch.ones(a.size, a.size, device=dev)
     t = timed(lambda: (loop(n, x0), torch.cuda.synchronize() if a.cuda else None))
@@ -67,7 +71,7 @@ def main():
         pm = None
     else:
         pm = this_host().spawn_procs(per_host={"gpus": 1})
-        mesh = te.spawn_tensor_engine(pm, use_cuda=a.cuda)
+        mesh = te.spawn_tensor_engine(pm, use_cuda=a.cuda, null_device=a.null_device)
     try:
         with mesh.activate():
             x = torch.ones(a.size, a.size)

@@ -467,6 +467,7 @@ class WorkerCore {
     // reference gets the same effect by showing each worker process a single device).
     if (cuda_index_ >= 0 && a.constant.isDevice() && a.constant.toDevice().is_cuda())
       a.constant = c10::IValue(c10::Device(c10::DeviceType::CUDA, (c10::DeviceIndex)cuda_index_));
+
     return a;
   }
 

@@ -603,8 +603,11 @@ class Tensor(torch.Tensor):
         if _inplace and tuple(out_fake.shape) != tuple(f.shape):
             raise ValueError("in-place reduce needs matching input and output shapes")
         client = m.client
-        own = client.use_cuda and _own_collective(f.dtype, reduction)
-        key = client.ensure_comm(m, dims, self.stream.id, own=own)
+        if getattr(client, "null_device", False):
+            key = ("null", n)              # shape-only workers: no communicator exists
+        else:
+            own = client.use_cuda and _own_collective(f.dtype, reduction)
+            key = client.ensure_comm(m, dims, self.stream.id, own=own)
         seq = client.new_seq()
         if _inplace:
             result = self
@@ -782,8 +785,14 @@ def _send_call(fspec, args, kwargs, fake_out, mesh: "DeviceMesh", mutates: Seque
     refs: List[Ref] = []
     out = _wrap_outputs(fake_out, mesh, stream, refs)
     seq = client.new_seq()
-    client.send(mesh, ("call", seq, refs, [Ref(t.ref) for t in mutates], fspec, _to_wire(args),
-                       _to_wire(kwargs), stream.id))
+    msg = ("call", seq, refs, [Ref(t.ref) for t in mutates], fspec, _to_wire(args),
+           _to_wire(kwargs), stream.id)
+    if getattr(client, "null_device", False):
+        # shape-only workers do not run the function: they need the results' metadata
+        flat: List[Tensor] = []
+        _collect(out, flat)
+        msg += ([(tuple(t._fake.shape), t._fake.dtype) for t in flat],)
+    client.send(mesh, msg)
     return out
 
 
@@ -1208,13 +1217,18 @@ class _RankFn:
         return torch.tensor(flat, dtype=torch.int64)
 
 
-def spawn_tensor_engine(proc_mesh, use_cuda: Optional[bool] = None) -> DeviceMesh:
-    """Spawn tensor workers on every proc of ``proc_mesh`` and return its DeviceMesh."""
+def spawn_tensor_engine(proc_mesh, use_cuda: Optional[bool] = None,
+                        null_device: bool = False) -> DeviceMesh:
+    """Spawn tensor workers on every proc of ``proc_mesh`` and return its DeviceMesh.
+    ``null_device=True``: the workers execute nothing -- every result is a zero tensor of the
+    shape the controller computed, nothing is copied or reduced -- so what is left is the
+    per-command cost of the controller, the messaging and the workers' hosts."""
     if use_cuda is None:
         use_cuda = torch.cuda.is_available()
     name = f"tensor_engine_workers_{next(_engine_ids)}"
-    workers = proc_mesh.spawn(name, TensorWorker, use_cuda)
-    client = Client(proc_mesh, workers, use_cuda)
+    workers = proc_mesh.spawn(name, TensorWorker, use_cuda and not null_device, null_device)
+    client = Client(proc_mesh, workers, use_cuda and not null_device)
+    client.null_device = bool(null_device)
     dm = DeviceMesh(client, Shape(list(proc_mesh._labels), proc_mesh._ndslice), workers)
     client.root_mesh = dm
     return dm

@@ -117,7 +117,6 @@ def _manager_for_current_proc() -> _Manager:
 
 
 _peer_cache: Dict[tuple, int] = {}
-_copy_state: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
 
 
 def _ensure_peer_access(dev: int, other: int) -> None:
@@ -130,22 +129,15 @@ def _ensure_peer_access(dev: int, other: int) -> None:
 
 def _device_copy_ptr(dst_ptr: int, src_ptr: int, nbytes: int, dev_index: int) -> None:
     """nbytes from src_ptr to dst_ptr with the peer-copy kernel running on ``dev_index``
-    (either pointer may be a mapping of another process's / GPU's memory)."""
+    (either pointer may be a mapping of another process's / GPU's memory), queued on the
+    caller's current stream of that device behind whatever produced the source.  Returns when
+    the bytes have landed: waiting for the stream is waiting for the transfer, so no
+    completion flag has to be zeroed, published and read back per call."""
     from ..ops import kernels as K
-    dev = torch.device("cuda", dev_index)
-    st = _copy_state.get(dev_index)
-    if st is None:
-        st = (torch.zeros(4, dtype=torch.int32, device=dev),
-              torch.zeros(4, dtype=torch.int32, device=dev))
-        _copy_state[dev_index] = st
-    done, counter = st
-    with torch.cuda.device(dev):
-        done.zero_()
-        K.check(K.lib().mb200_peer_copy(dst_ptr, src_ptr, nbytes, done.data_ptr(), 1,
-                                        counter.data_ptr(), 0, K.stream_ptr()), "peer_copy")
+    with torch.cuda.device(dev_index):
+        K.check(K.lib().mb200_peer_copy(dst_ptr, src_ptr, nbytes, None, 0, None, 0,
+                                        K.stream_ptr()), "peer_copy")
         torch.cuda.current_stream().synchronize()
-        if int(done[0].item()) != 1:
-            raise RDMAError("peer copy did not publish its completion flag")
 
 
 def _device_copy(dst: torch.Tensor, src: torch.Tensor) -> None:

@@ -246,10 +246,17 @@ class WorkerPipe:
 
 
 class TensorWorker(Actor):
-    def __init__(self, use_cuda: bool):
+    def __init__(self, use_cuda: bool, null_device: bool = False):
+        """``null_device``: operators are not executed -- every result is a zero tensor of the
+        shape and dtype the controller computed; copies and collectives move nothing.  What
+        remains is the host-side cost per command (controller, messaging, worker routing),
+        which is how the dispatch overhead of a program written for GPUs is measured on a box
+        without one (the reference patches the CUDA driver's entry points for this,
+        python/monarch/common/mock_cuda.cpp:32-100; here it is a switch in the worker)."""
         self.rank = current_rank().rank
         self.world = current_rank().extent.nelements
-        self.use_cuda = bool(use_cuda and torch.cuda.is_available())
+        self.null_device = bool(null_device)
+        self.use_cuda = bool(use_cuda and torch.cuda.is_available()) and not self.null_device
         if self.use_cuda:
             n = torch.cuda.device_count()
             self.device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", self.rank)) % n)
@@ -517,8 +524,13 @@ class TensorWorker(Actor):
         return comm.all_reduce(t, reduction, out=t if inplace else None)
 
     # -------------------------------------------------------------------- messages
-    def _m_call(self, seq, results, mutates, fspec, args, kwargs, stream) -> None:
+    def _m_call(self, seq, results, mutates, fspec, args, kwargs, stream, metas=None) -> None:
         self.last_seq = seq
+        if self.null_device and metas is not None:
+            # not executed: results of the announced shapes stand in (see __init__)
+            for r, (shape, dtype) in zip(results, metas):
+                self.env[r.id] = torch.zeros(shape, dtype=dtype)
+            return
         fname = fspec[1] if isinstance(fspec[1], str) else getattr(fspec[1], "__name__", "udf")
         if self.core is not None and fspec[0] == "op":
             # ATen operator: resolved, checked for poisoned inputs, dispatched and stored
@@ -641,6 +653,19 @@ class TensorWorker(Actor):
                 # not left waiting, and keep the failure in this rank's result
                 t = torch.zeros(in_meta[0], dtype=in_meta[1], device=self.device)
                 inplace, out_ref = False, None
+            if self.null_device:      # nothing moves: only the result's shape exists
+                n = max(1, int(key[-1])) if isinstance(key, tuple) and len(key) > 1 else 1
+                if reduction == "stack":
+                    out = torch.empty_like(t) if scatter else \
+                        torch.zeros((n, *t.shape), dtype=t.dtype)
+                elif scatter:
+                    out = torch.zeros(t.shape[1:], dtype=t.dtype)
+                else:
+                    out = t if inplace else torch.empty_like(t)
+                if out_ref is not None:
+                    out = self.env[out_ref.id]
+                self.env[result.id] = out
+                return
             own = self.comms.get(key)
             if own is not None:
                 comm, ranks = own

@@ -650,3 +650,29 @@ def test_user_functions_of_two_streams_run_on_separate_host_threads(dm):
             opened = release(z)                # side stream: runs meanwhile
             assert te.inspect(opened).tolist() == [2.0, 2.0]
         assert te.inspect(after).tolist() == [3.0, 3.0]
+
+
+def test_null_device_workers_execute_nothing_but_keep_shapes():
+    """The switch that stands in for the reference's mock_cuda: programs run end to end,
+    results have the right shapes and dtypes, nothing is computed (values are zeros)."""
+    pm = this_host().spawn_procs(per_host={"gpus": 2})
+    mesh = te.spawn_tensor_engine(pm, use_cuda=False, null_device=True)
+    try:
+        with mesh.activate():
+            a = torch.ones(3, 4)
+            b = (2 * a + 1) @ torch.ones(4, 5, dtype=torch.float64).float()
+            got = te.inspect(b, gpus=1)
+            assert got.shape == (3, 5) and got.dtype == torch.float32 and got.eq(0).all()
+            s = b.reduce("gpus", "stack")
+            assert te.inspect(s).shape == (2, 3, 5)
+            r = torch.ones(2, 6).reduce("gpus", "sum", scatter=True)
+            assert te.inspect(r).shape == (6,)
+            side = te.Stream("null-side")
+            y, borrow = side.borrow(a)
+            with side.activate():
+                z = y + 1
+                assert te.inspect(z).shape == (3, 4)
+            borrow.drop()
+    finally:
+        mesh.exit()
+        pm.stop().get()
