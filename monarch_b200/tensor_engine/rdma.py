@@ -8,14 +8,16 @@ ibverbs queue pairs and bounces GPU tensors through the host; here
 * GPU buffers are first class: the owner exports a CUDA IPC handle, the peer maps it and a
   hand-written copy kernel moves the bytes with in-kernel NVLink loads/stores
   (``peer_copy``), publishing a completion flag; no host bounce;
-* host buffers in the same process are copied directly; across processes the owner's
-  manager actor serves the bytes as out-of-band frame parts over the actor channels
-  (no ibverbs device exists on this class of box).
+* host buffers in the same process are copied directly; between processes of one box they
+  are read and written in place with ``process_vm_readv`` / ``process_vm_writev`` (one copy);
+  otherwise the owner's manager actor -- a native actor, ``csrc/rdma/rdma_manager.cpp`` --
+  serves the bytes as out-of-band frame parts over the actor channels (no ibverbs device
+  exists on this class of box).
 """
 from __future__ import annotations
 
 import itertools
-import pickle
+import os
 import threading
 import time
 import warnings
@@ -42,57 +44,51 @@ def is_available() -> bool:
 
 
 class _Manager:
-    """Per-proc registry of exported buffers plus the actor that serves remote requests."""
+    """The proc's RDMA manager: a native actor (``_native.RdmaManager``) owns the registry and
+    answers remote handles without entering Python; this object registers buffers with it and
+    keeps the tensors alive while they are exported."""
 
     def __init__(self, proc):
+        from .. import _native as N
         self.proc = proc
         self.proc_id = proc.proc_id
         self.buffers: Dict[int, torch.Tensor] = {}
-        self.instance = proc.spawn(_MANAGER_NAME, self._on_message,
-                                   on_undeliverable=lambda *a: True)
-        self.actor_id = self.instance.actor_id
+        self.native = N.RdmaManager(proc, _MANAGER_NAME, self._serve_cuda_bytes)
+        self.actor_id = self.native.actor_id
 
-    def register(self, t: torch.Tensor) -> int:
-        bid = next(_ids)
-        self.buffers[bid] = t
-        return bid
+    def register(self, t: torch.Tensor) -> dict:
+        """Export ``t`` (1-D uint8 view of a contiguous tensor); returns what a handle carries."""
+        import socket
+        info = {"nbytes": t.numel(), "cuda": t.is_cuda, "device": t.device.index if t.is_cuda
+                else -1, "addr": t.data_ptr(), "pid": os.getpid(), "host": socket.gethostname(),
+                "ipc_handle": b"", "ipc_offset": 0}
+        if t.is_cuda:
+            from ..ops import ipc
+            exp = ipc.export_handle(t)
+            info["ipc_handle"], info["ipc_offset"] = exp["handle"], exp["offset"]
+        bid = self.native.register(info["addr"], info["nbytes"], info["cuda"], info["device"],
+                                   info["ipc_handle"], info["ipc_offset"], info["host"])
+        self.buffers[bid] = t        # the owner must not free it while peers may touch it
+        info["id"] = bid
+        info["valid_addr"] = self.native.get(bid)["valid_addr"]
+        return info
 
-    def _on_message(self, inst, env) -> None:
-        req = unflatten(env.data, env.parts)
-        op, bid, reply = req[0], req[1], req[-1]
-        try:
-            t = self.buffers.get(bid)
-            if t is None:
-                raise RDMAError(f"buffer {bid} is not registered on {self.proc_id} (dropped?)")
-            raw = _as_bytes(t)
-            if op == "read":
-                _, _, off, n, _ = req
-                _check_range(raw, off, n)
-                body, parts = flatten(("ok", raw[off: off + n].cpu()))
-            elif op == "write":
-                _, _, off, data, _ = req
-                _check_range(raw, off, data.numel())
-                raw[off: off + data.numel()].copy_(data)
-                body, parts = flatten(("ok", None))
-            elif op == "cuda_handle":
-                import ctypes
-                from ..ops import kernels as K
-                h = ctypes.create_string_buffer(64)
-                off, size = ctypes.c_int64(0), ctypes.c_int64(0)
-                K.check(K.lib().mb200_ipc_export(raw.data_ptr(), h, ctypes.byref(off),
-                                                 ctypes.byref(size)), "ipc_export", 0)
-                # the owner must not free or reuse the allocation while peers map it: the
-                # registry keeps the tensor alive until drop()
-                body, parts = flatten(("ok", (bytes(h.raw), int(off.value), raw.numel(),
-                                              raw.device.index or 0)))
-            elif op == "drop":
-                self.buffers.pop(bid, None)
-                body, parts = flatten(("ok", None))
-            else:
-                raise RDMAError(f"unknown rdma op {op!r}")
-        except Exception as e:  # noqa: BLE001 - reported to the requester
-            body, parts = flatten(("err", f"{type(e).__name__}: {e}"))
-        inst.send(reply, body, {"kind": "rdma_reply", "no_return": "1"}, parts)
+    def drop(self, bid: int) -> None:
+        self.native.drop(bid)
+        self.buffers.pop(bid, None)
+
+    def _serve_cuda_bytes(self, info: dict, op: str, off: int, n: int, payload):
+        """GPU bytes over messages, for requesters that cannot map the buffer (no peer path,
+        a host-side destination): called by the native manager actor."""
+        t = self.buffers.get(info["id"])
+        if t is None:
+            raise RDMAError(f"buffer {info['id']} is not registered (dropped?)")
+        raw = _as_bytes(t)
+        if op == "read":
+            return raw[off: off + n].cpu().numpy().tobytes()
+        data = torch.frombuffer(bytearray(payload), dtype=torch.uint8)
+        raw[off: off + data.numel()].copy_(data)
+        return None
 
 
 def _as_bytes(t: torch.Tensor) -> torch.Tensor:
@@ -166,19 +162,23 @@ class RDMABuffer:
         mgr = _manager_for_current_proc()
         self._owner = mgr.actor_id
         self._owner_proc = mgr.proc_id
-        self._id = mgr.register(data)
-        self._nbytes = data.numel()
-        self._cuda = data.is_cuda
-        self._device_index = data.device.index if data.is_cuda else None
+        self._info = mgr.register(data)
 
     # handles travel by value; the memory stays with the owner
     def __reduce__(self):
-        return (_rebuild, (self._owner, self._owner_proc, self._id, self._nbytes, self._cuda,
-                           self._device_index))
+        return (_rebuild, (self._owner, self._owner_proc, self._info))
 
     @property
     def nbytes(self) -> int:
-        return self._nbytes
+        return self._info["nbytes"]
+
+    @property
+    def _id(self) -> int:
+        return self._info["id"]
+
+    @property
+    def _cuda(self) -> bool:
+        return self._info["cuda"]
 
     # ------------------------------------------------------------------------------
     def _local_tensor(self) -> Optional[torch.Tensor]:
@@ -187,59 +187,77 @@ class RDMABuffer:
             return _as_bytes(m.buffers[self._id])
         return None
 
-    def _request(self, msg: tuple, timeout: float) -> Any:
+    def _request(self, op: str, timeout: float, offset: int = 0, length: int = 0,
+                 payload: Optional[bytes] = None):
+        """One round trip to the owner's manager actor; returns the reply envelope."""
         inst = context().actor_instance._native
         port, rx = inst.open_port(True)
-        body, parts = flatten((*msg, port))
-        inst.send(self._owner + "[0]", body, {"kind": "rdma"}, parts)
+        headers = {"kind": "rdma", "rdma_op": op, "rdma_id": str(self._id),
+                   "rdma_offset": str(offset), "rdma_len": str(length), "rdma_reply": port}
+        inst.send(self._owner + "[0]", b"", headers, [payload] if payload is not None else [])
         env = rx.recv(int(timeout * 1000))
         if env is None:
             inst.close_port(port)
             raise TimeoutError(f"RDMA operation on {self._owner} timed out after {timeout} s")
-        status, payload = unflatten(env.data, env.parts)
-        if status != "ok":
-            raise RDMAError(payload)
-        return payload
+        if env.headers.get("rdma_status") != "ok":
+            raise RDMAError(bytes(env.data).decode(errors="replace"))
+        return env
 
-    def _peer_pointer(self, reader_device: int, timeout: float) -> int:
+    def _same_host(self) -> bool:
+        import socket
+        return self._info["host"] == socket.gethostname()
+
+    def _peer_pointer(self, reader_device: int) -> int:
         """Address, valid for kernels of ``reader_device`` in this process, of byte 0 of the
-        owner's buffer."""
+        owner's GPU buffer (the handle carries the IPC export, so no round trip is needed)."""
         key = (self._owner, self._id, reader_device)
         p = _peer_cache.get(key)
         if p is None:
-            handle, off, nbytes, _owner_dev = self._request(("cuda_handle", self._id), timeout)
-            if nbytes != self._nbytes:
-                raise RDMAError("the owner's buffer changed size")
-            p = _open_ipc(handle, reader_device) + off
+            self._request("info", 3)          # refuses a handle whose buffer was dropped
+            _ensure_peer_access(reader_device, self._info["device"])
+            p = _open_ipc(self._info["ipc_handle"], reader_device) + self._info["ipc_offset"]
             _peer_cache[key] = p
         return p
+
+    def _check(self, offset: int, n: int) -> None:
+        if offset < 0 or offset + n > self.nbytes:
+            raise RDMAError(f"range [{offset}, {offset + n}) outside a buffer of "
+                            f"{self.nbytes} bytes")
 
     def read_into(self, dst: torch.Tensor, offset: int = 0, timeout: float = 3) -> Future[None]:
         """Copy ``dst.nbytes`` bytes starting at ``offset`` of the remote buffer into ``dst``."""
         d = _as_bytes(dst)
 
         def run(_t):
+            from .. import _native as N
             n = d.numel()
-            if offset < 0 or offset + n > self._nbytes:
-                raise RDMAError(f"range [{offset}, {offset + n}) outside a buffer of "
-                                f"{self._nbytes} bytes")
+            self._check(offset, n)
             local = self._local_tensor()
             if local is not None:
                 src = local[offset: offset + n]
-                if src.is_cuda or d.is_cuda:
-                    if src.is_cuda and d.is_cuda:
-                        _device_copy(d, src)
-                    else:
-                        d.copy_(src)
+                if src.is_cuda and d.is_cuda:
+                    _device_copy(d, src)
                 else:
                     d.copy_(src)
                 return None
-            if self._cuda and d.is_cuda:
+            if self._cuda and d.is_cuda and self._same_host():
                 idx = d.device.index or 0
-                _device_copy_ptr(d.data_ptr(), self._peer_pointer(idx, timeout) + offset, n, idx)
+                _device_copy_ptr(d.data_ptr(), self._peer_pointer(idx) + offset, n, idx)
                 return None
-            data = self._request(("read", self._id, offset, n), timeout)
-            d.copy_(data)
+            if not self._cuda and self._same_host():
+                # one copy, straight out of the owner's address space
+                host = d if not d.is_cuda else torch.empty(n, dtype=torch.uint8).pin_memory()
+                rc = N.rdma_host_read(self._info["pid"], self._info["addr"] + offset,
+                                      host.data_ptr(), n, self._info["valid_addr"], self._id)
+                if rc == 0:
+                    if host is not d:
+                        d.copy_(host)
+                    return None
+                if rc == -2:
+                    raise RDMAError(f"buffer {self._id} is not registered on {self._owner} "
+                                    "(dropped?)")
+            env = self._request("read", timeout, offset, n)
+            d.copy_(torch.frombuffer(bytearray(env.parts[0]), dtype=torch.uint8))
             return None
 
         return Future(run)
@@ -249,10 +267,9 @@ class RDMABuffer:
         s = _as_bytes(src)
 
         def run(_t):
+            from .. import _native as N
             n = s.numel()
-            if offset < 0 or offset + n > self._nbytes:
-                raise RDMAError(f"range [{offset}, {offset + n}) outside a buffer of "
-                                f"{self._nbytes} bytes")
+            self._check(offset, n)
             local = self._local_tensor()
             if local is not None:
                 dst = local[offset: offset + n]
@@ -261,11 +278,20 @@ class RDMABuffer:
                 else:
                     dst.copy_(s)
                 return None
-            if self._cuda and s.is_cuda:
+            if self._cuda and s.is_cuda and self._same_host():
                 idx = s.device.index or 0
-                _device_copy_ptr(self._peer_pointer(idx, timeout) + offset, s.data_ptr(), n, idx)
+                _device_copy_ptr(self._peer_pointer(idx) + offset, s.data_ptr(), n, idx)
                 return None
-            self._request(("write", self._id, offset, s.cpu()), timeout)
+            if not self._cuda and self._same_host():
+                host = s if not s.is_cuda else s.cpu()
+                rc = N.rdma_host_write(self._info["pid"], self._info["addr"] + offset,
+                                       host.data_ptr(), n, self._info["valid_addr"], self._id)
+                if rc == 0:
+                    return None
+                if rc == -2:
+                    raise RDMAError(f"buffer {self._id} is not registered on {self._owner} "
+                                    "(dropped?)")
+            self._request("write", timeout, offset, n, s.cpu().numpy().tobytes())
             return None
 
         return Future(run)
@@ -274,17 +300,16 @@ class RDMABuffer:
         def run(_t):
             m = _managers.get(self._owner_proc)
             if m is not None:
-                m.buffers.pop(self._id, None)
+                m.drop(self._id)
             else:
-                self._request(("drop", self._id), 3)
+                self._request("drop", 3)
             for k in [k for k in _peer_cache if k[:2] == (self._owner, self._id)]:
                 _peer_cache.pop(k, None)
             return None
         return Future(run)
 
 
-def _rebuild(owner, owner_proc, bid, nbytes, cuda, device_index) -> RDMABuffer:
+def _rebuild(owner, owner_proc, info) -> RDMABuffer:
     b = RDMABuffer.__new__(RDMABuffer)
-    b._owner, b._owner_proc, b._id, b._nbytes = owner, owner_proc, bid, nbytes
-    b._cuda, b._device_index = cuda, device_index
+    b._owner, b._owner_proc, b._info = owner, owner_proc, dict(info)
     return b
