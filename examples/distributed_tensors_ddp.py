@@ -4,7 +4,10 @@ one Python process drives every worker of the mesh, gradients are produced one a
 ``grad_generator`` and all-reduced on a ``comm`` stream (borrowed across streams) while the
 rest of backward runs, then the whole step is compiled into a recording.
 
-    python examples/distributed_tensors_ddp.py
+    python examples/distributed_tensors_ddp.py [--cuda] [--procs 4]
+
+With ``--cuda`` every worker owns one GPU and the gradient reductions run on this package's
+NVLink collectives (communicators bootstrapped over actor messages, one per stream).
 
 Parity: docs/source/examples/distributed_tensors.py:192-342 of the reference (DDP with
 ``grad.reduce_("dp", "sum")`` on a comms stream through ``borrow``)."""
@@ -18,20 +21,21 @@ from monarch_b200 import tensor_engine as te  # noqa: E402
 from monarch_b200.actor import this_host  # noqa: E402
 
 
-def run(steps: int = 8, procs: int = 4):
+def run(steps: int = 8, procs: int = 4, cuda: bool = False):
     pm = this_host().spawn_procs(per_host={"gpus": procs})
-    mesh = te.spawn_tensor_engine(pm, use_cuda=False).rename(gpus="dp")
+    mesh = te.spawn_tensor_engine(pm, use_cuda=cuda).rename(gpus="dp")
+    dev = "cuda" if cuda else "cpu"
     comm = te.Stream("comm")
     try:
         with mesh.activate():
             from monarch_b200 import random as mrandom
             mrandom.manual_seed(0)              # same weights on every worker ...
-            w1 = torch.randn(16, 32) * 0.1
-            w2 = torch.randn(32, 4) * 0.1
+            w1 = torch.randn(16, 32, device=dev) * 0.1
+            w2 = torch.randn(32, 4, device=dev) * 0.1
             mrandom.manual_seed(1, per_rank=True)   # ... different data
             losses = []
             for step in range(steps):
-                x = torch.randn(64, 16)          # every rank draws its own batch
+                x = torch.randn(64, 16, device=dev)   # every rank draws its own batch
                 y = (x[:, :4] > 0).to(torch.float32)
                 h = (x @ w1).relu()
                 out = h @ w2
@@ -62,4 +66,10 @@ def run(steps: int = 8, procs: int = 4):
 
 
 if __name__ == "__main__":
-    print(run())
+    import argparse
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--cuda", action="store_true")
+    ap.add_argument("--procs", type=int, default=4)
+    ap.add_argument("--steps", type=int, default=8)
+    a = ap.parse_args()
+    print(run(a.steps, a.procs, a.cuda))
