@@ -80,21 +80,26 @@ def _compile_many(jobs: list[tuple[list[str], Path]]) -> None:
             f.result()
 
 
-def build_kernels(force: bool = False) -> Path:
+def build_kernels(force: bool = False, checked: bool = False) -> Path:
+    """``checked=True`` builds ``_mb200_kernels_checked.so``: the same kernels with
+    ``-DMB200_BOUNDS_CHECK``, in which the collectives validate every peer access against a
+    table of registered address ranges and report violations through the status word instead
+    of touching the memory (selected at run time with ``MB200_KERNEL_LIB=checked``)."""
     kdir = CSRC / "kernels"
-    target = ROOT / "ops" / "_mb200_kernels.so"
+    target = ROOT / "ops" / ("_mb200_kernels_checked.so" if checked else "_mb200_kernels.so")
     srcs = sorted(kdir.glob("*.cu"))
-    stamp = _stamp(_deps([kdir]), CUDA_FLAGS)
+    flags = CUDA_FLAGS + (["-DMB200_BOUNDS_CHECK"] if checked else [])
+    stamp = _stamp(_deps([kdir]), flags)
     if not force and _up_to_date(target, stamp):
         return target
-    odir = OBJ / "kernels"
+    odir = OBJ / ("kernels_checked" if checked else "kernels")
     odir.mkdir(parents=True, exist_ok=True)
     jobs = []
     objs = []
     for s in srcs:
         o = odir / (s.stem + ".o")
         objs.append(str(o))
-        jobs.append(([NVCC, *CUDA_FLAGS, "-I", str(kdir), "-c", str(s), "-o", str(o)],
+        jobs.append(([NVCC, *flags, "-I", str(kdir), "-c", str(s), "-o", str(o)],
                      odir / (s.stem + ".log")))
     _compile_many(jobs)
     _run([NVCC, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", *objs, "-o", str(target)])
@@ -219,6 +224,7 @@ def build_tensor_worker(force: bool = False) -> Path:
 
 def build_all(force: bool = False) -> None:
     build_kernels(force)
+    build_kernels(force, checked=True)
     build_native(force)
     build_gradgen(force)
     build_tensor_worker(force)
@@ -228,6 +234,7 @@ if __name__ == "__main__":
     what = [a for a in sys.argv[1:] if not a.startswith("-")] or ["all"]
     force = "--force" in sys.argv
     for w in what:
-        {"kernels": build_kernels, "native": build_native, "gradgen": build_gradgen,
+        {"kernels": build_kernels, "kernels_checked": lambda f: build_kernels(f, checked=True),
+         "native": build_native, "gradgen": build_gradgen,
          "tensor_worker": build_tensor_worker, "all": build_all}[w](force)
         print("built", w)

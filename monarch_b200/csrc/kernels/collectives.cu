@@ -33,6 +33,7 @@
 
 #include <type_traits>
 
+#define MB200_BOUNDS_TU 1
 #include "comm.cuh"
 
 namespace mb200 {
@@ -289,7 +290,7 @@ __global__ void __launch_bounds__(256) coll_reduce_kernel(const ReduceArgs a) {
     } else if (a.out_peers.p[0]) {
 #pragma unroll
       for (int k = 0; k < kMaxRanks; ++k)
-        if (k < a.world) reinterpret_cast<uint4*>(a.out_peers.p[(a.rank + k) % a.world])[i] = r;
+        if (k < a.world) st_v4(reinterpret_cast<uint4*>(a.out_peers.p[(a.rank + k) % a.world]) + i, r);
     }
   }
   if (a.signal_slot >= 0 && last_block_done(a.counter))
@@ -463,4 +464,22 @@ extern "C" int mb200_coll_gather(const void* const* src_ptrs, const int64_t* src
   dim3 grid(gx, world);
   coll_gather_kernel<<<grid, 256, 0, ST(stream)>>>(a);
   return (int)cudaGetLastError();
+}
+
+// ---- checked builds: this translation unit's table of allowed address ranges ----------
+extern "C" int mb200_bounds_register_coll(const void* base, int64_t size) {
+#ifdef MB200_BOUNDS_ACTIVE
+  return bounds_table_add(reinterpret_cast<unsigned long long>(base), (unsigned long long)size);
+#else
+  (void)base; (void)size;
+  return 0;
+#endif
+}
+extern "C" int mb200_bounds_reset_coll(int* status) {
+#ifdef MB200_BOUNDS_ACTIVE
+  return bounds_table_reset(status);
+#else
+  (void)status;
+  return 0;
+#endif
 }

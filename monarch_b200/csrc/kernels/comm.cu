@@ -22,6 +22,7 @@
 #include <string.h>
 #include <stdint.h>
 
+#define MB200_BOUNDS_TU 1
 #include "comm.cuh"
 #include "mb200.h"
 
@@ -287,7 +288,7 @@ __global__ void __launch_bounds__(256)
 #pragma unroll
       for (int k = 0; k < kMaxRanks; ++k)
         if (k < world)
-          reinterpret_cast<uint4*>(out.p[(rank + k) % world])[i] = o;
+          st_v4(reinterpret_cast<uint4*>(out.p[(rank + k) % world]) + i, o);
     }
   }
   if (last_block_done(counter)) signal_all(flags, world, rank, slot + 1, epoch, threadIdx.x);
@@ -595,4 +596,22 @@ extern "C" int mb200_pingpong(void* my_buf, void* peer_buf, uint32_t* my_flag, u
                                               peer_flag, nbytes / 16, iters, base, leader, status,
                                               elapsed_ns);
   return (int)cudaGetLastError();
+}
+
+// ---- checked builds: this translation unit's table of allowed address ranges ----------
+extern "C" int mb200_bounds_register_comm(const void* base, int64_t size) {
+#ifdef MB200_BOUNDS_ACTIVE
+  return bounds_table_add(reinterpret_cast<unsigned long long>(base), (unsigned long long)size);
+#else
+  (void)base; (void)size;
+  return 0;
+#endif
+}
+extern "C" int mb200_bounds_reset_comm(int* status) {
+#ifdef MB200_BOUNDS_ACTIVE
+  return bounds_table_reset(status);
+#else
+  (void)status;
+  return 0;
+#endif
 }

@@ -18,6 +18,7 @@ enum : int {
   kStatusMbarTimeout = 1,   // an mbarrier wait ran out (pipeline stall)
   kStatusFlagTimeout = 2,   // a global-memory flag wait ran out (peer never signalled)
   kStatusBadArgs = 3,
+  kStatusBounds = 4,        // a checked build refused an access outside the registered ranges
 };
 
 // ~1.5 s at 1.4-1.9 GHz. Far beyond any legitimate wait inside one kernel.

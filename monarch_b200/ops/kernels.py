@@ -14,7 +14,10 @@ from typing import Optional
 
 import torch
 
-_SO = Path(__file__).resolve().parent / "_mb200_kernels.so"
+#: MB200_KERNEL_LIB=checked loads the build whose collectives bounds-check every peer access
+CHECKED = os.environ.get("MB200_KERNEL_LIB", "") == "checked"
+_SO = Path(__file__).resolve().parent / ("_mb200_kernels_checked.so" if CHECKED
+                                         else "_mb200_kernels.so")
 _lib: Optional[ctypes.CDLL] = None
 _status: dict[int, torch.Tensor] = {}
 
@@ -32,7 +35,7 @@ def lib() -> ctypes.CDLL:
         if not _SO.exists():
             if os.environ.get("MB200_NO_AUTOBUILD") != "1":
                 from .. import _build
-                _build.build_kernels()
+                _build.build_kernels(checked=CHECKED)
         if not _SO.exists():
             raise KernelError(f"{_SO} is missing: run `python -m monarch_b200._build kernels`")
         _lib = ctypes.CDLL(str(_SO))
@@ -122,10 +125,30 @@ _OPTIONAL: dict[str, list] = {
     "mb200_coll_reduce": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i, _i, _f, _i, _vp, _i, _i,
                           _i, _i, ctypes.c_uint32, _vp, _i, _vp, _vp],
     "mb200_coll_gather": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, ctypes.c_uint32, _i, _vp, _vp],
+    "mb200_bounds_enabled": [],
+    "mb200_bounds_reset": [_vp],
+    "mb200_bounds_register": [_vp, _i64],
     "mb200_gather_chunks": [_vp, _vp, ctypes.c_longlong, _i, _i, ctypes.c_longlong,
                             ctypes.c_longlong, ctypes.c_longlong, _vp, ctypes.c_uint32, _vp, _i,
                             ctypes.c_uint32, _i, _vp, _vp],
 }
+
+
+_bounds_ready: set = set()
+
+
+def bounds_register(ptr: int, nbytes: int, device=None) -> None:
+    """In a checked build: allow the collectives of ``device`` to touch ``[ptr, ptr+nbytes)``
+    (a local buffer, a peer mapping or a multicast mapping).  A no-op in the regular build."""
+    l = lib()
+    if not l.mb200_bounds_enabled():
+        return
+    idx = status_word(device).device.index
+    with torch.cuda.device(idx):
+        if idx not in _bounds_ready:
+            check(l.mb200_bounds_reset(status_word(idx).data_ptr()), "bounds_reset", 0)
+            _bounds_ready.add(idx)
+        check(l.mb200_bounds_register(ptr, nbytes), "bounds_register", 0)
 
 
 def set_gemm_impl(impl: int) -> None:

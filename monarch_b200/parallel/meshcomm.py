@@ -90,6 +90,10 @@ class MeshComm:
         if local.numel() < self.buffer_bytes(self.cap):
             raise ValueError("communicator buffer is smaller than its capacity needs")
         self._keepalive = keepalive
+        for p in self.ptrs:                     # checked builds: the ranges kernels may touch
+            K.bounds_register(p, self.buffer_bytes(self.cap), self.device)
+        if self.mc_ptr:
+            K.bounds_register(self.mc_ptr, self.buffer_bytes(self.cap), self.device)
         self._flag_ptrs = _ptr_array(self.ptrs)
         self._counter = torch.zeros(8, dtype=torch.int32, device=self.device)
         self.epoch = 0

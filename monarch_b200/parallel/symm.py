@@ -48,6 +48,11 @@ class SymmBuffer:
         if os.environ.get("MB200_NVLS", "1") == "0":
             self.multicast_ptr = 0
         self._elt = self.tensor.element_size()
+        nbytes = numel * self._elt
+        for p in self.ptrs:                     # checked builds: the ranges kernels may touch
+            K.bounds_register(p, nbytes, device)
+        if self.multicast_ptr:
+            K.bounds_register(self.multicast_ptr, nbytes, device)
 
     def ptrs_at(self, elem_offset: int):
         """ctypes array of every rank's address of element ``elem_offset``."""
