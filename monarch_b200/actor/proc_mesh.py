@@ -554,11 +554,40 @@ def local_proc_mesh(*, gpus: Optional[int] = None, hosts: int = 1) -> ProcMesh:
 
 
 def sim_proc_mesh(*, gpus: int = 1, hosts: int = 1, racks: int = 1, zones: int = 1, dcs: int = 1,
-                  regions: int = 1) -> ProcMesh:
-    """A large in-process mesh with topology dims, for exercising casts without hardware."""
-    dims = {k: v for k, v in (("regions", regions), ("dcs", dcs), ("zones", zones),
-                              ("racks", racks), ("hosts", hosts), ("gpus", gpus)) if v > 1}
-    return _allocate(dims or {"gpus": 1}, in_process=True)
+                  regions: int = 1, network: bool = False) -> ProcMesh:
+    """A large in-process mesh with topology dims, for exercising casts without hardware.
+
+    ``network=True``: the procs talk through ``sim:`` channels -- every message crosses a
+    simulated network and pays the latency of the distance between the two procs' hosts
+    (same host, same rack, same zone, ...; ``configure_simnet``), on the simulated clock
+    when ``telemetry.use_sim_clock()`` is on, so cast trees and protocols can be costed
+    against a topology.  (hyperactor/src/channel/sim.rs, simnet.rs in the reference.)"""
+    named = [(k, v) for k, v in (("regions", regions), ("dcs", dcs), ("zones", zones),
+                                 ("racks", racks), ("hosts", hosts), ("gpus", gpus))]
+    dims = {k: v for k, v in named if v > 1}
+    if not network:
+        return _allocate(dims or {"gpus": 1}, in_process=True)
+    dims = dims or {"gpus": 1}
+    import itertools as _it
+    nodes = []
+    for coord in _it.product(*[range(v) for v in dims.values()]):
+        # the node is the proc's host: every topology level above "gpus"
+        parts = [f"{k}{c}" for k, c in zip(dims, coord) if k != "gpus"]
+        nodes.append(".".join(parts) or "host0")
+    world = f"sim{next(_world_counter)}_{os.getpid()}"
+    native = N.ProcMesh.allocate_sim(world, nodes)
+    return ProcMesh(native, _shape_from_dims(dims), in_process=True)
+
+
+def configure_simnet(latency_us, bandwidth_gbs: float = 0.0) -> None:
+    """Latencies (microseconds) of the simulated network by node distance: index 0 within a
+    host, 1 between hosts of a rack, 2 between racks, ...; optionally the link bandwidth."""
+    N.simnet_configure([float(x) for x in latency_us], float(bandwidth_gbs))
+
+
+def simnet_stats() -> dict:
+    """Frames, bytes and summed simulated latency that crossed the simulated network."""
+    return N.simnet_stats()
 
 
 # ---------------------------------------------------------------------- controllers ----

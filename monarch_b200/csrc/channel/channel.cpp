@@ -46,6 +46,18 @@ ChannelAddr ChannelAddr::parse(const std::string& s) {
   } else if (starts("local:")) {
     a.kind = Local;
     a.id = std::stoull(s.substr(6));
+  } else if (starts("sim:")) {
+    a.kind = Sim;
+    std::string rest = s.substr(4);
+    auto arrow = rest.find("->");
+    if (arrow != std::string::npos) {
+      a.src_node = rest.substr(0, arrow);
+      rest = rest.substr(arrow + 2);
+    }
+    auto slash = rest.rfind('/');
+    if (slash == std::string::npos) throw ChannelError("bad sim address: " + s);
+    a.node = rest.substr(0, slash);
+    a.id = std::stoull(rest.substr(slash + 1));
   } else {
     throw ChannelError("unsupported channel address: " + s);
   }
@@ -62,6 +74,9 @@ std::string ChannelAddr::to_string() const {
     case Tcp: return "tcp:" + host + ":" + std::to_string(port);
     case Unix: return "unix:" + path;
     case Local: return "local:" + std::to_string(id);
+    case Sim:
+      return "sim:" + (src_node.empty() ? std::string() : src_node + "->") + node + "/" +
+             std::to_string(id);
   }
   return "";
 }
@@ -174,6 +189,159 @@ class LocalTx : public Tx {
  private:
   uint64_t id_;
   std::atomic<bool> closed_{false};
+};
+
+// ------------------------------------------------------------------ sim transport --
+// hyperactor/src/simnet.rs schedules events on a simulated clock; here one scheduler thread
+// owns a time-ordered queue of deliveries.
+double telemetry_now_us_for_sim();   // defined below: the telemetry clock (sim or real)
+
+class SimNet {
+ public:
+  static SimNet& get() {
+    static SimNet* n = new SimNet();
+    return *n;
+  }
+  void configure(const std::vector<double>& lat, double bw_gbs) {
+    std::lock_guard<std::mutex> g(mu_);
+    if (!lat.empty()) lat_ = lat;
+    if (bw_gbs > 0) bytes_per_us_ = bw_gbs * 1e3;
+  }
+  double latency_us(const std::string& a, const std::string& b, size_t bytes, int* dist_out) {
+    std::lock_guard<std::mutex> g(mu_);
+    int d = simnet_distance(a, b);
+    if (d >= (int)lat_.size()) d = (int)lat_.size() - 1;
+    *dist_out = d;
+    return lat_[d] + (double)bytes / bytes_per_us_;
+  }
+  // `deliver` runs on the scheduler thread once simulated time reaches now + delay.
+  // `chan_ready_us` (per channel, owned by the caller under its own lock) keeps one
+  // channel's frames in order when a later, smaller frame would otherwise overtake.
+  void schedule(double delay_us, size_t bytes, int dist, double* chan_ready_us,
+                std::function<void()> deliver) {
+    {
+      std::lock_guard<std::mutex> g(mu_);
+      double at = now_locked() + delay_us;
+      if (chan_ready_us) {
+        if (at < *chan_ready_us) at = *chan_ready_us;
+        *chan_ready_us = at;
+      }
+      q_.push_back(Ev{at, seq_++, std::move(deliver)});
+      std::push_heap(q_.begin(), q_.end(), later);
+      stats_.frames++;
+      stats_.bytes += bytes;
+      stats_.latency_us_total += delay_us;
+      stats_.by_distance[dist < 8 ? dist : 7]++;
+      if (!started_) {
+        started_ = true;
+        std::thread([this] { run(); }).detach();
+      }
+    }
+    cv_.notify_all();
+  }
+  SimNetStats stats() {
+    std::lock_guard<std::mutex> g(mu_);
+    return stats_;
+  }
+  void reset_stats() {
+    std::lock_guard<std::mutex> g(mu_);
+    stats_ = SimNetStats{};
+  }
+
+ private:
+  struct Ev {
+    double at;
+    uint64_t seq;
+    std::function<void()> fn;
+  };
+  static bool later(const Ev& a, const Ev& b) {
+    return a.at > b.at || (a.at == b.at && a.seq > b.seq);
+  }
+  double now_locked() { return telemetry_now_us_for_sim(); }
+  void run();
+  std::mutex mu_;
+  std::condition_variable cv_;
+  std::vector<Ev> q_;
+  uint64_t seq_ = 0;
+  bool started_ = false;
+  std::vector<double> lat_{2.0, 10.0, 50.0, 500.0, 5000.0};
+  double bytes_per_us_ = 50e3;   // 50 GB/s
+  SimNetStats stats_;
+};
+
+std::mutex g_sim_mu;
+std::map<std::string, std::weak_ptr<FrameQueue>> g_sim;   // "node/id" -> queue
+uint64_t g_sim_next = 1;
+
+class SimRx : public Rx {
+ public:
+  SimRx(std::string node, uint64_t id, std::shared_ptr<FrameQueue> q)
+      : node_(std::move(node)), id_(id), q_(std::move(q)) {}
+  ~SimRx() override { close(); }
+  std::optional<Frame> recv(int64_t t) override { return q_->pop(t); }
+  ChannelAddr addr() const override {
+    ChannelAddr a;
+    a.kind = ChannelAddr::Sim;
+    a.node = node_;
+    a.id = id_;
+    return a;
+  }
+  void close() override {
+    q_->close();
+    std::lock_guard<std::mutex> g(g_sim_mu);
+    g_sim.erase(node_ + "/" + std::to_string(id_));
+  }
+  bool closed() const override { return q_->closed(); }
+
+ private:
+  std::string node_;
+  uint64_t id_;
+  std::shared_ptr<FrameQueue> q_;
+};
+
+class SimTx : public Tx {
+ public:
+  explicit SimTx(ChannelAddr a) : addr_(std::move(a)) {}
+  void post(Frame f, std::function<void(Frame&&)> on_fail) override {
+    auto q = lookup();
+    if (!q || q->closed() || closed_) {
+      channel_stats().undeliverable++;
+      if (on_fail) on_fail(std::move(f));
+      return;
+    }
+    channel_stats().frames_sent++;
+    int dist = 0;
+    const size_t bytes = f.size();
+    const double lat = SimNet::get().latency_us(addr_.src_node.empty() ? addr_.node : addr_.src_node,
+                                                addr_.node, bytes, &dist);
+    auto cell = std::make_shared<Frame>(std::move(f));
+    std::lock_guard<std::mutex> g(order_mu_);
+    SimNet::get().schedule(lat, bytes, dist, &ready_us_, [q, cell, on_fail] {
+      if (q->closed()) {
+        channel_stats().undeliverable++;
+        if (on_fail) on_fail(std::move(*cell));
+        return;
+      }
+      q->push(std::move(*cell));
+    });
+  }
+  TxStatus status() const override {
+    auto q = lookup();
+    return (!closed_ && q && !q->closed()) ? TxStatus::Active : TxStatus::Closed;
+  }
+  ChannelAddr addr() const override { return addr_; }
+  void close() override { closed_ = true; }
+
+ private:
+  std::shared_ptr<FrameQueue> lookup() const {
+    std::lock_guard<std::mutex> g(g_sim_mu);
+    auto it = g_sim.find(addr_.node + "/" + std::to_string(addr_.id));
+    return it == g_sim.end() ? nullptr : it->second.lock();
+  }
+  ChannelAddr addr_;
+  std::atomic<bool> closed_{false};
+  std::mutex order_mu_;
+  double ready_us_ = 0;
 };
 
 // ------------------------------------------------------------------ socket helpers --
@@ -803,6 +971,19 @@ class NetTx : public Tx {
 }  // namespace
 
 std::shared_ptr<Rx> serve(const ChannelAddr& addr) {
+  if (addr.kind == ChannelAddr::Sim) {
+    std::lock_guard<std::mutex> g(g_sim_mu);
+    uint64_t id = addr.id ? addr.id : g_sim_next++;
+    if (addr.id) g_sim_next = std::max(g_sim_next, addr.id + 1);
+    std::string node = addr.node.empty() ? "node0" : addr.node;
+    std::string key = node + "/" + std::to_string(id);
+    auto it = g_sim.find(key);
+    if (it != g_sim.end() && !it->second.expired())
+      throw ChannelError("sim channel " + key + " already served");
+    auto q = std::make_shared<FrameQueue>();
+    g_sim[key] = q;
+    return std::make_shared<SimRx>(node, id, q);
+  }
   if (addr.kind == ChannelAddr::Local) {
     std::lock_guard<std::mutex> g(g_local_mu);
     uint64_t id = addr.id ? addr.id : g_local_next++;
@@ -819,8 +1000,61 @@ std::shared_ptr<Rx> serve(const ChannelAddr& addr) {
 
 std::shared_ptr<Tx> dial(const ChannelAddr& addr) {
   if (addr.kind == ChannelAddr::Local) return std::make_shared<LocalTx>(addr.id);
+  if (addr.kind == ChannelAddr::Sim) return std::make_shared<SimTx>(addr);
   return std::make_shared<NetTx>(addr);
 }
+
+// ------------------------------------------------------------------------- simnet --
+namespace {
+double telemetry_now_us_for_sim() { return telemetry_now_us(); }
+
+void SimNet::run() {
+  std::unique_lock<std::mutex> lk(mu_);
+  while (true) {
+    cv_.wait(lk, [&] { return !q_.empty(); });
+    std::pop_heap(q_.begin(), q_.end(), later);
+    Ev ev = std::move(q_.back());
+    q_.pop_back();
+    const double now = telemetry_now_us();
+    if (ev.at > now) {
+      if (sim_clock_in_use()) {
+        sim_clock_advance_us(ev.at - now);      // nothing earlier is pending: jump there
+      } else {
+        // real time: sleep until it is due (an earlier delivery may be scheduled meanwhile)
+        const double wait_us = ev.at - now;
+        q_.push_back(std::move(ev));
+        std::push_heap(q_.begin(), q_.end(), later);
+        cv_.wait_for(lk, std::chrono::microseconds((int64_t)wait_us + 1));
+        continue;
+      }
+    }
+    lk.unlock();
+    ev.fn();
+    lk.lock();
+  }
+}
+}  // namespace
+
+int simnet_distance(const std::string& a, const std::string& b) {
+  auto split = [](const std::string& s) {
+    std::vector<std::string> out;
+    size_t i = 0;
+    while (i <= s.size()) {
+      size_t j = s.find('.', i);
+      if (j == std::string::npos) j = s.size();
+      out.push_back(s.substr(i, j - i));
+      i = j + 1;
+    }
+    return out;
+  };
+  auto pa = split(a), pb = split(b);
+  size_t common = 0;
+  while (common < pa.size() && common < pb.size() && pa[common] == pb[common]) ++common;
+  return (int)(std::max(pa.size(), pb.size()) - common);
+}
+void simnet_configure(const std::vector<double>& lat, double bw) { SimNet::get().configure(lat, bw); }
+SimNetStats simnet_stats() { return SimNet::get().stats(); }
+void simnet_reset_stats() { SimNet::get().reset_stats(); }
 
 void debug_drop_connections(const ChannelAddr& addr) {
   std::lock_guard<std::mutex> g(g_tx_mu);

@@ -4,7 +4,8 @@
 // `local:n`; `dial` / `serve`; Tx/Rx), channel/net.rs (frames = 8-byte big-endian length +
 // payload; Init / Message(seq) frames; Ack responses; outbox + unacked queue; reconnect
 // with exponential backoff; delivery timeout after which messages are returned),
-// channel/local.rs (in-process transport).
+// channel/local.rs (in-process transport), channel/sim.rs + simnet.rs (`sim:` addresses:
+// in-process delivery after a simulated network latency, see SimNet below).
 //
 // Design: one sender thread per dialled channel (owns the socket, the outbox and the
 // unacked queue) and one reader thread per accepted connection.  A multi-part message
@@ -27,11 +28,16 @@
 namespace mb {
 
 struct ChannelAddr {
-  enum Kind { Tcp, Unix, Local } kind = Local;
+  enum Kind { Tcp, Unix, Local, Sim } kind = Local;
   std::string host;  // tcp
   int port = 0;      // tcp (0 = any)
   std::string path;  // unix ("" = any: an abstract/temporary path is chosen)
-  uint64_t id = 0;   // local (0 = any)
+  uint64_t id = 0;   // local, sim (0 = any)
+  // sim: `sim:<node>/<id>`; a dialled address may name the sender's node as well,
+  // `sim:<src>-><node>/<id>` -- the latency of a frame depends on both.  Nodes are dotted
+  // paths ("dc0.rack1.host3"); the distance of two nodes is the number of trailing
+  // components in which they differ.
+  std::string node, src_node;
 
   static ChannelAddr parse(const std::string& s);
   static ChannelAddr any(Kind k);
@@ -79,6 +85,22 @@ class Rx {
 
 std::shared_ptr<Rx> serve(const ChannelAddr& addr);
 std::shared_ptr<Tx> dial(const ChannelAddr& addr);
+
+// Simulated network behind `sim:` channels: every frame is delivered after
+//   latency_us[distance(src, dst)] + bytes / bandwidth
+// in simulated time.  While the telemetry sim clock is in use (use_sim_clock) the scheduler
+// jumps the clock to each delivery's time, so a run costs no wall-clock waiting and the
+// clock reads the critical-path latency of what was sent; with the real clock, deliveries
+// are delayed in real time.  Frames of one channel stay in order.
+struct SimNetStats {
+  uint64_t frames = 0, bytes = 0;
+  double latency_us_total = 0;   // sum of the simulated latencies of all delivered frames
+  uint64_t by_distance[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+};
+void simnet_configure(const std::vector<double>& latency_us_by_distance, double bandwidth_gbs);
+SimNetStats simnet_stats();
+void simnet_reset_stats();
+int simnet_distance(const std::string& a, const std::string& b);
 
 // Counters for tests / metrics (process-wide).
 struct ChannelStats {

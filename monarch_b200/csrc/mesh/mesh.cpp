@@ -244,6 +244,61 @@ class LocalAlloc : public Alloc {
   std::atomic<bool> stopped_{false};
 };
 
+// ---------------------------------------------------------------------- sim alloc ----
+class SimAlloc : public Alloc {
+ public:
+  SimAlloc(std::string world, std::vector<std::string> nodes)
+      : world_(std::move(world)), nodes_(std::move(nodes)) {
+    for (size_t i = 0; i < nodes_.size(); ++i) {
+      auto router = std::make_shared<Router>();
+      auto p = Proc::create(ProcId{world_, (int64_t)i}, router);
+      router->bind_local(p);
+      router->set_home(p);
+      ChannelAddr a = ChannelAddr::any(ChannelAddr::Sim);
+      a.node = nodes_[i];
+      auto rx = serve(a);
+      std::string addr = rx->addr().to_string();
+      servers_.push_back(std::make_unique<MailboxServer>(rx, std::make_shared<ProcSender>(p)));
+      p->spawn("mesh_agent", make_mesh_agent(p, router));
+      procs_.push_back(p);
+      routers_.push_back(router);
+      ProcEvent e;
+      e.kind = ProcEvent::Running;
+      e.rank = (int64_t)i;
+      e.proc_id = p->id().to_string();
+      e.addr = addr;
+      events_.push(std::move(e));
+    }
+  }
+  ~SimAlloc() override { stop(); }
+  std::string world() const override { return world_; }
+  size_t size() const override { return nodes_.size(); }
+  std::optional<ProcEvent> next(int64_t t) override { return events_.pop(t); }
+  std::string transport() const override { return "sim"; }
+  void stop() override {
+    if (stopped_.exchange(true)) return;
+    for (size_t i = 0; i < procs_.size(); ++i) {
+      procs_[i]->stop_all(Config::global().get_int("STOP_ACTOR_TIMEOUT_MS"));
+      ProcEvent e;
+      e.kind = ProcEvent::Stopped;
+      e.rank = (int64_t)i;
+      e.proc_id = procs_[i]->id().to_string();
+      e.reason = "stopped";
+      events_.push(std::move(e));
+    }
+    servers_.clear();
+  }
+
+ private:
+  std::string world_;
+  std::vector<std::string> nodes_;
+  std::vector<std::shared_ptr<Proc>> procs_;
+  std::vector<std::shared_ptr<Router>> routers_;
+  std::vector<std::unique_ptr<MailboxServer>> servers_;
+  EventQueue events_;
+  std::atomic<bool> stopped_{false};
+};
+
 // ------------------------------------------------------------------ process alloc ----
 std::string describe_wait_status(int st, int* code) {
   if (WIFEXITED(st)) {
@@ -538,6 +593,10 @@ class AttachAllocImpl : public AttachAlloc {
 std::shared_ptr<AttachAlloc> make_attach_alloc(const std::string& world, size_t n,
                                                const std::string& transport) {
   return std::make_shared<AttachAllocImpl>(world, n, transport);
+}
+
+std::shared_ptr<Alloc> make_sim_alloc(const std::string& world, std::vector<std::string> nodes) {
+  return std::make_shared<SimAlloc>(world, std::move(nodes));
 }
 
 std::shared_ptr<Alloc> make_local_alloc(const std::string& world, size_t n,
@@ -1015,7 +1074,11 @@ static std::string client_server_addr(const std::shared_ptr<Proc>& client,
   std::string key = client->id().to_string() + "/" + transport;
   auto it = servers->find(key);
   if (it == servers->end()) {
-    auto rx = serve(ChannelAddr::any(transport == "tcp" ? ChannelAddr::Tcp : ChannelAddr::Unix));
+    ChannelAddr any = ChannelAddr::any(transport == "tcp"   ? ChannelAddr::Tcp
+                                       : transport == "sim" ? ChannelAddr::Sim
+                                                            : ChannelAddr::Unix);
+    if (transport == "sim") any.node = "client";
+    auto rx = serve(any);
     it = servers->emplace(key, std::make_unique<MailboxServer>(
                                    rx, std::make_shared<ProcSender>(client))).first;
   }
@@ -1062,10 +1125,20 @@ std::shared_ptr<ProcMesh> ProcMesh::allocate(std::shared_ptr<Alloc> alloc,
     }
   }
   std::string client_addr;
+  const bool sim = alloc->transport() == "sim";
+  // on sim channels the latency depends on who dials: every address handed out names the
+  // dialling node as its source
+  auto from_node = [&](const std::string& addr, const std::string& src_node) {
+    if (!sim) return addr;
+    ChannelAddr a = ChannelAddr::parse(addr);
+    a.src_node = src_node;
+    return a.to_string();
+  };
   if (!local) {
     client_addr = client_server_addr(pm->client_, alloc->transport());
     for (auto& kv : addrs)
-      pm->router_->bind_addr(pm->proc_id(kv.first).to_string(), ChannelAddr::parse(kv.second));
+      pm->router_->bind_addr(pm->proc_id(kv.first).to_string(),
+                             ChannelAddr::parse(from_node(kv.second, "client")));
   }
   // Configure agents: full address book, supervision sink.
   auto replies = std::make_shared<QueueSink>();
@@ -1074,14 +1147,15 @@ std::shared_ptr<ProcMesh> ProcMesh::allocate(std::shared_ptr<Alloc> alloc,
     Writer w;
     w.i64((int64_t)rank);
     w.u32((uint32_t)(addrs.size() + 2));
+    const std::string my_node = sim ? ChannelAddr::parse(addrs[(int64_t)rank]).node : "";
     for (auto& kv : addrs) {
       w.str(pm->proc_id(kv.first).to_string());
-      w.str(kv.second);
+      w.str(from_node(kv.second, my_node));
     }
     w.str(pm->client_->id().to_string());
-    w.str(client_addr);
+    w.str(from_node(client_addr, my_node));
     w.str("*");  // default route: anything unknown goes through the client's router
-    w.str(client_addr);
+    w.str(from_node(client_addr, my_node));
     write_port(w, pm->supervisor_port_);
     write_port(w, reply_port);
     pm->client_inst_->send(PortId{ActorId{pm->proc_id((int64_t)rank), "mesh_agent", 0}, kPortMessage},

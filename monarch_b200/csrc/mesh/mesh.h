@@ -89,6 +89,13 @@ class Alloc {
 std::shared_ptr<Alloc> make_local_alloc(const std::string& world, size_t n,
                                         std::shared_ptr<Router> router);
 
+// N procs inside this process whose mailboxes are reached through `sim:` channels: every
+// message between procs (and between the client and a proc) crosses the simulated network
+// (channel.h SimNet) and pays the latency of the distance between the two nodes.
+// `nodes[i]` names the node of proc i ("dc0.rack1.host3"); the client sits on node "client".
+// (hyperactor_mesh/src/alloc/sim.rs in the reference.)
+std::shared_ptr<Alloc> make_sim_alloc(const std::string& world, std::vector<std::string> nodes);
+
 struct ProcessAllocOptions {
   std::vector<std::string> argv;             // bootstrap command
   std::map<std::string, std::string> env;    // extra environment for every child

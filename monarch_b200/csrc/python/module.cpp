@@ -748,6 +748,23 @@ PYBIND11_MODULE(_native, m) {
     py::gil_scoped_release rel;
     return bootstrap_main();
   });
+  m.def("simnet_configure", &simnet_configure, py::arg("latency_us_by_distance"),
+        py::arg("bandwidth_gbs") = 0.0,
+        "Latency (microseconds) per node distance 0, 1, 2, ... and the link bandwidth of the "
+        "simulated network behind sim: channels.");
+  m.def("simnet_stats", [] {
+    SimNetStats s = simnet_stats();
+    py::dict d;
+    d["frames"] = s.frames;
+    d["bytes"] = s.bytes;
+    d["latency_us_total"] = s.latency_us_total;
+    py::list by;
+    for (int i = 0; i < 8; ++i) by.append(s.by_distance[i]);
+    d["frames_by_distance"] = by;
+    return d;
+  });
+  m.def("simnet_reset_stats", &simnet_reset_stats);
+  m.def("simnet_distance", &simnet_distance);
   m.def("bootstrap_attach", [](const std::string& addr, int64_t index) {
     py::gil_scoped_release rel;
     return bootstrap_attach(addr, index);
@@ -775,6 +792,15 @@ PYBIND11_MODULE(_native, m) {
                                       timeout_ms);
           },
           py::arg("world"), py::arg("n"), py::arg("timeout_ms") = 30000)
+      .def_static(
+          "allocate_sim",
+          [](const std::string& world, std::vector<std::string> nodes, int64_t timeout_ms) {
+            py::gil_scoped_release rel;
+            auto& c = client_ctx();
+            return ProcMesh::allocate(make_sim_alloc(world, std::move(nodes)), c.router, c.proc,
+                                      timeout_ms);
+          },
+          py::arg("world"), py::arg("nodes"), py::arg("timeout_ms") = 60000)
       .def_static(
           "allocate_attached",
           [](std::shared_ptr<AttachAlloc> alloc, int64_t timeout_ms) {

@@ -374,6 +374,7 @@ uint64_t thread_tag() {
 
 void use_sim_clock() { sim_clock().on = true; }
 void use_real_clock() { sim_clock().on = false; }
+bool sim_clock_in_use() { return sim_clock().on; }
 void sim_clock_advance_us(double us) {
   std::lock_guard<std::mutex> g(sim_clock().mu);
   sim_clock().t_us += us;

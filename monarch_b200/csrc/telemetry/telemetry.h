@@ -173,6 +173,7 @@ uint64_t current_span_id();
 void use_sim_clock();
 void use_real_clock();
 void sim_clock_advance_us(double us);
+bool sim_clock_in_use();
 double telemetry_now_us();
 const std::string& execution_id();
 
