@@ -5,6 +5,13 @@
     python benchmarks/profile_case.py elementwise     # one launch of each memory-bound kernel
     python benchmarks/profile_case.py attn            # attention forward + backward, S=4096, 16q/4kv
     python benchmarks/profile_case.py step            # 2-layer Llama-3-8B-shaped training steps
+    python benchmarks/profile_case.py collectives     # the NVLink kernels as a group of one rank
+
+A profiler replays each captured launch many times, so kernels that wait for a peer cannot be
+captured in a multi-rank run; ``collectives`` runs them as a group of one rank on one GPU (the
+flag waits see the rank's own signal).  What such a capture shows is the kernels' own cost --
+instruction mix, registers, the HBM side of the traffic; NVLink traffic needs peers and is
+measured with CUDA events in the multi-GPU harnesses instead.
 
 Inputs are larger than the 126 MB L2 but only a few hundred MB, so a multi-pass capture
 finishes in about a minute.
@@ -82,6 +89,49 @@ def step_case(layers=2, steps=2):
     torch.cuda.synchronize()
 
 
+def collectives_case():
+    """allreduce / reduce-scatter+AdamW / all-gather on symmetric buffers and the staged mesh
+    collectives, 64 MiB each, world size 1."""
+    import torch.distributed as dist
+    from monarch_b200.parallel.meshcomm import MeshComm
+    from monarch_b200.parallel.symm import FlagArray, SymmBuffer
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29577")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
+    lib, st = K.lib(), K.status_word(dev)
+    n = 32 << 20                                   # bf16 elements: 64 MiB
+    flags = FlagArray(8, dev)
+    buf = SymmBuffer(n, bf16, dev, zero=False)
+    buf.tensor.normal_()
+    for epoch in (1, 2):
+        K.check(lib.mb200_allreduce_scale_cast(buf.ptrs_at(0), buf.ptrs_at(0), None, None,
+                                               flags.ptrs, n, 0, 0, 1, 1.0, 0, epoch,
+                                               flags.counter.data_ptr(), 0, st.data_ptr(),
+                                               K.stream_ptr()), "allreduce", 2)
+    master = torch.randn(n, device=dev)
+    m, v = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+    shard = torch.empty(n, dtype=bf16, device=dev)
+    for epoch in (1, 2):
+        K.check(lib.mb200_rs_adamw(buf.ptrs_at(0), None, flags.ptrs, master.data_ptr(),
+                                   m.data_ptr(), v.data_ptr(), shard.data_ptr(), n, 0, 1, 2, 3,
+                                   epoch, 1e-3, 0.9, 0.95, 1e-8, 0.1, epoch, 1.0,
+                                   flags.counter.data_ptr(), 0, st.data_ptr(), K.stream_ptr()),
+                "rs_adamw")
+    full = torch.empty(n, dtype=bf16, device=dev)
+    for _ in range(2):
+        K.check(lib.mb200_allgather_pull(full.data_ptr(), buf.ptrs_at(0), n, 0, 1, flags.my_ptr,
+                                         0, 0, None, 0, 0, 0, st.data_ptr(), K.stream_ptr()),
+                "allgather_pull")
+    comm = MeshComm.from_process_group(None, dev, 64 << 20)
+    x = torch.randn(n // 2, device=dev)             # 64 MiB of fp32
+    comm.all_reduce(x, "sum")                       # stage + two-shot reduce + copy-out
+    comm.all_gather(x)
+    torch.cuda.synchronize()
+    dist.destroy_process_group()
+
+
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
     if what == "gemm":
@@ -92,5 +142,7 @@ if __name__ == "__main__":
         attn_case()
     elif what == "step":
         step_case()
+    elif what == "collectives":
+        collectives_case()
     K.check_status()
     print("ok", what)

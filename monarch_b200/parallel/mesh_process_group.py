@@ -44,6 +44,13 @@ class MeshProcessGroup(dist.ProcessGroup):
     def __init__(self, comm: MeshComm):
         super().__init__(comm.rank, comm.world)
         self.comm = comm
+        # torch.distributed looks groups up in its registry (rank translation for
+        # broadcast / reduce roots, get_world_size ...): enter this one, with the ranks of the
+        # group as the "global" ranks user code names (src=0 is the group's first member)
+        from torch.distributed import distributed_c10d as c10d
+        c10d._world.pg_map[self] = ("mb200", None)
+        c10d._world.pg_names[self] = f"mb200_{id(self):x}"
+        c10d._world.pg_group_ranks[self] = {r: r for r in range(comm.world)}
 
     def getBackendName(self) -> str:
         return "mb200"
