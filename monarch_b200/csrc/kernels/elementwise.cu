@@ -82,16 +82,23 @@ __global__ void __launch_bounds__(256)
 constexpr int RMS_BWD_THREADS = 256;
 constexpr int RMS_BWD_MAXCH = 4;  // d <= 256*8*4 = 8192
 
-__global__ void __launch_bounds__(RMS_BWD_THREADS)
+// One block walks rows blockIdx.x, blockIdx.x + gridDim.x, ...; a thread owns NCH chunks of
+// 8 columns.  NCH is a template parameter so that the per-thread arrays are sized for the
+// actual row length: with d = 4096 (NCH 2) the kernel needs about half the registers of the
+// d = 8192 instance and two to three blocks are resident per SM -- rows in different phases
+// (loads, block reduction, stores) overlap, which is what a kernel with a reduction in the
+// middle of every row needs to stream at HBM speed.
+template <int NCH>
+__global__ void __launch_bounds__(RMS_BWD_THREADS, NCH <= 2 ? 3 : 1)
     rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                        const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
                        const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
                        float* __restrict__ dw_partial, int rows, int d) {
   __shared__ float red[33];
-  float wv[RMS_BWD_MAXCH][8];
-  float acc[RMS_BWD_MAXCH][8];
+  float wv[NCH][8];
+  float acc[NCH][8];
 #pragma unroll
-  for (int ch = 0; ch < RMS_BWD_MAXCH; ++ch) {
+  for (int ch = 0; ch < NCH; ++ch) {
     const int c = threadIdx.x * 8 + ch * RMS_BWD_THREADS * 8;
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[ch][i] = 0.f;
@@ -101,20 +108,25 @@ __global__ void __launch_bounds__(RMS_BWD_THREADS)
     const __nv_bfloat16* xr = x + (size_t)row * d;
     const __nv_bfloat16* gr = dy + (size_t)row * d;
     const float rs = rstd[row];
-    float xh[RMS_BWD_MAXCH][8], g[RMS_BWD_MAXCH][8];
+    float xh[NCH][8], g[NCH][8];
     float dot = 0.f;
 #pragma unroll
-    for (int ch = 0; ch < RMS_BWD_MAXCH; ++ch) {
+    for (int ch = 0; ch < NCH; ++ch) {
       const int c = threadIdx.x * 8 + ch * RMS_BWD_THREADS * 8;
       if (c < d) {
-        float dyv[8];
         load8(xr + c, xh[ch]);
-        load8(gr + c, dyv);
+        load8(gr + c, g[ch]);
+      }
+    }
+#pragma unroll
+    for (int ch = 0; ch < NCH; ++ch) {
+      const int c = threadIdx.x * 8 + ch * RMS_BWD_THREADS * 8;
+      if (c < d) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           xh[ch][i] *= rs;
-          acc[ch][i] += dyv[i] * xh[ch][i];
-          g[ch][i] = dyv[i] * wv[ch][i];
+          acc[ch][i] += g[ch][i] * xh[ch][i];
+          g[ch][i] *= wv[ch][i];
           dot += g[ch][i] * xh[ch][i];
         }
       }
@@ -122,7 +134,7 @@ __global__ void __launch_bounds__(RMS_BWD_THREADS)
     dot = block_sum(dot, red) / d;
     __nv_bfloat16* dxr = dx + (size_t)row * d;
 #pragma unroll
-    for (int ch = 0; ch < RMS_BWD_MAXCH; ++ch) {
+    for (int ch = 0; ch < NCH; ++ch) {
       const int c = threadIdx.x * 8 + ch * RMS_BWD_THREADS * 8;
       if (c < d) {
         float o[8];
@@ -140,7 +152,7 @@ __global__ void __launch_bounds__(RMS_BWD_THREADS)
   }
   float* out = dw_partial + (size_t)blockIdx.x * d;
 #pragma unroll
-  for (int ch = 0; ch < RMS_BWD_MAXCH; ++ch) {
+  for (int ch = 0; ch < NCH; ++ch) {
     const int c = threadIdx.x * 8 + ch * RMS_BWD_THREADS * 8;
     if (c < d) {
       *reinterpret_cast<float4*>(out + c) = make_float4(acc[ch][0], acc[ch][1], acc[ch][2], acc[ch][3]);
@@ -150,14 +162,45 @@ __global__ void __launch_bounds__(RMS_BWD_THREADS)
   }
 }
 
-__global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, int nblocks, int d,
-                                         __nv_bfloat16* __restrict__ dw, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= d) return;
+// Column sums of the [nblocks, d] partials.  A block covers 32 columns: its 8 thread rows
+// stride over the partial rows (each warp reads 128 contiguous bytes per row) and are
+// combined through shared memory, so d / 32 blocks share the work instead of d / 256.
+__global__ void __launch_bounds__(256)
+    rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, int nblocks, int d,
+                             __nv_bfloat16* __restrict__ dw, int accumulate) {
+  __shared__ float sh[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + tx;
   float s = 0.f;
-  for (int b = 0; b < nblocks; ++b) s += partial[(size_t)b * d + c];
-  if (accumulate) s += __bfloat162float(dw[c]);
-  dw[c] = __float2bfloat16(s);
+  if (c < d)
+    for (int b = ty; b < nblocks; b += 8) s += partial[(size_t)b * d + c];
+  sh[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && c < d) {
+#pragma unroll
+    for (int k = 1; k < 8; ++k) s += sh[k][tx];
+    if (accumulate) s += __bfloat162float(dw[c]);
+    dw[c] = __float2bfloat16(s);
+  }
+}
+
+// Launches the backward pair: nb row-striding blocks, then the column reduction.
+static void launch_rmsnorm_bwd(int nb, const __nv_bfloat16* dy, const __nv_bfloat16* x,
+                               const __nv_bfloat16* w, const float* rstd,
+                               const __nv_bfloat16* dres, __nv_bfloat16* dx, float* dw_partial,
+                               __nv_bfloat16* dw, int dw_accumulate, int rows, int d,
+                               cudaStream_t st) {
+  const int nch = (d + RMS_BWD_THREADS * 8 - 1) / (RMS_BWD_THREADS * 8);
+  if (nch <= 1)
+    rmsnorm_bwd_kernel<1><<<nb, RMS_BWD_THREADS, 0, st>>>(dy, x, w, rstd, dres, dx, dw_partial,
+                                                          rows, d);
+  else if (nch == 2)
+    rmsnorm_bwd_kernel<2><<<nb, RMS_BWD_THREADS, 0, st>>>(dy, x, w, rstd, dres, dx, dw_partial,
+                                                          rows, d);
+  else
+    rmsnorm_bwd_kernel<4><<<nb, RMS_BWD_THREADS, 0, st>>>(dy, x, w, rstd, dres, dx, dw_partial,
+                                                          rows, d);
+  rmsnorm_dw_reduce_kernel<<<(d + 31) / 32, 256, 0, st>>>(dw_partial, nb, d, dw, dw_accumulate);
 }
 
 // --------------------------------------------------------------------- RoPE --
@@ -434,7 +477,7 @@ extern "C" int mb200_rmsnorm_fwd(const void* x, const void* w, void* y, float* r
 }
 
 extern "C" int mb200_rmsnorm_bwd_blocks(int rows) {
-  const int cap = 148 * 4;
+  const int cap = 148 * 3;   // one resident wave: three blocks per SM at d <= 4096
   return rows < cap ? rows : cap;
 }
 
@@ -444,10 +487,8 @@ extern "C" int mb200_rmsnorm_bwd(const void* dy, const void* x, const void* w, c
   if (rows <= 0) return 0;
   if (d % 8 || d > RMS_BWD_THREADS * 8 * RMS_BWD_MAXCH) return 1001;
   const int nb = mb200_rmsnorm_bwd_blocks(rows);
-  rmsnorm_bwd_kernel<<<nb, RMS_BWD_THREADS, 0, ST(stream)>>>(CBF(dy), CBF(x), CBF(w), rstd, CBF(dres),
-                                                              BF(dx), dw_partial, rows, d);
-  rmsnorm_dw_reduce_kernel<<<(d + 255) / 256, 256, 0, ST(stream)>>>(dw_partial, nb, d, BF(dw),
-                                                                    dw_accumulate);
+  launch_rmsnorm_bwd(nb, CBF(dy), CBF(x), CBF(w), rstd, CBF(dres), BF(dx), dw_partial, BF(dw),
+                     dw_accumulate, rows, d, ST(stream));
   return (int)cudaGetLastError();
 }
 
@@ -590,9 +631,7 @@ extern "C" int mb200_rmsnorm_bwd_noalloc(const void* dy, const void* x, const vo
   int nb = mb200_rmsnorm_bwd_blocks(rows);
   const int cap = MB200_NOALLOC_SCRATCH_FLOATS / d;
   if (nb > cap) nb = cap;
-  rmsnorm_bwd_kernel<<<nb, RMS_BWD_THREADS, 0, ST(stream)>>>(CBF(dy), CBF(x), CBF(w), rstd,
-                                                              CBF(dres), BF(dx), scratch, rows, d);
-  rmsnorm_dw_reduce_kernel<<<(d + 255) / 256, 256, 0, ST(stream)>>>(scratch, nb, d, BF(dw),
-                                                                    dw_accumulate);
+  launch_rmsnorm_bwd(nb, CBF(dy), CBF(x), CBF(w), rstd, CBF(dres), BF(dx), scratch, BF(dw),
+                     dw_accumulate, rows, d, ST(stream));
   return (int)cudaGetLastError();
 }

@@ -32,6 +32,31 @@ constexpr int G2_B_BYTES = G2_HALF * G2_BK * 2;
 constexpr int G2_STAGE_BYTES = G2_A_BYTES + G2_B_BYTES;
 constexpr int G2_SMEM_BYTES = G2_STAGES * G2_STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 
+// Tile t of the persistent schedule -> (m block, n block).  Tiles are walked in groups of
+// G2_GROUP_M m-blocks across all n-blocks: the CTA pairs that run at the same time then
+// share about G2_GROUP_M A panels and npairs / G2_GROUP_M B panels (instead of every A
+// panel and two or three B panels with a plain m-fastest walk), and the next wave reuses
+// the same B panels while they are still in L2.  Kernels whose B operand arrives chunk by
+// chunk (`ordered`: a gather fused into the GEMM) keep the n-major walk that follows the
+// order in which the chunks land, rotated by `rot`.
+constexpr int G2_GROUP_M = 8;
+__device__ __forceinline__ void tile_coords(int t, int m_blocks, int n_blocks, int rot,
+                                            bool ordered, int& m_blk, int& n_blk) {
+  if (ordered) {
+    m_blk = t % m_blocks;
+    n_blk = t / m_blocks + rot;
+    if (n_blk >= n_blocks) n_blk -= n_blocks;
+    return;
+  }
+  const int per_group = G2_GROUP_M * n_blocks;
+  const int group = t / per_group;
+  const int first_m = group * G2_GROUP_M;
+  const int gm = (m_blocks - first_m) < G2_GROUP_M ? (m_blocks - first_m) : G2_GROUP_M;
+  const int in_group = t - group * per_group;
+  m_blk = first_m + in_group % gm;
+  n_blk = in_group / gm;
+}
+
 struct Gemm2Shared {
   uint64_t full[G2_STAGES];    // used in the even CTA: loads of both CTAs complete here
   uint64_t empty[G2_STAGES];   // per CTA, signalled by the pair's MMA commit
@@ -91,9 +116,8 @@ __device__ __forceinline__ void gemm2_cta_body(const CUtensorMap* tmA, const CUt
       int stage = 0;
       uint32_t phase = 0;
       for (int t = vpair; t < num_tiles; t += npairs) {
-        const int m_blk = t % m_blocks;
-        int n_blk = t / m_blocks + p.n_blk_rot;
-        if (n_blk >= n_blocks) n_blk -= n_blocks;
+        int m_blk, n_blk;
+        tile_coords(t, m_blocks, n_blocks, p.n_blk_rot, p.b_ready != nullptr, m_blk, n_blk);
         const int m0 = m_blk * G2_BM + (int)cta * G2_HALF;
         const int n0 = n_blk * G2_BN + (int)cta * G2_HALF;
         bool ok = true;
@@ -199,9 +223,8 @@ __device__ __forceinline__ void gemm2_cta_body(const CUtensorMap* tmA, const CUt
                                   ((reinterpret_cast<uintptr_t>(p.R) & 15) == 0)));
     const uint32_t empty0 = mapa_u32(smem_u32(&sh->tmem_empty[0]), 0);
     for (int t = vpair; t < num_tiles; t += npairs) {
-      const int m_blk = t % m_blocks;
-      int n_blk = t / m_blocks + p.n_blk_rot;
-      if (n_blk >= n_blocks) n_blk -= n_blocks;
+      int m_blk, n_blk;
+      tile_coords(t, m_blocks, n_blocks, p.n_blk_rot, p.b_ready != nullptr, m_blk, n_blk);
       const int row = m_blk * G2_BM + (int)cta * G2_HALF + quad * 32 + lane;
       const int n0 = n_blk * G2_BN;
       if (!mbar_wait(&sh->tmem_full[acc], acc_phase, abort_word, p.status)) break;
