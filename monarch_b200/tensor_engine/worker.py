@@ -914,10 +914,12 @@ class TensorWorker(Actor):
         if preprocess is not None and preprocess[0] == "status":
             return ("ok", None)      # "are these values sound here?": no copy, no device sync
         try:
+            if self.use_cuda:
+                # the values may come from any named stream; this thread's stream is ordered
+                # after none of them, so wait for the device before touching the data
+                torch.cuda.synchronize(self.device)
             if preprocess is not None:
                 vals = _resolve_function(preprocess)(vals)
-            if self.use_cuda:
-                torch.cuda.current_stream().synchronize()
             return ("ok", _to_cpu(vals))
         except Exception as ex:  # noqa: BLE001
             return ("error", seq, self.rank, "fetch", f"{type(ex).__name__}: {ex}",

@@ -111,7 +111,8 @@ def main() -> int:
         assert torch.equal(got["max"], base * n) and torch.equal(got["min"], base)
         assert torch.equal(got["bf16"].float(), base * tri)
         assert got["stack"].shape == (n, 2, 3)
-        assert torch.equal(got["inplace"], base * tri) and torch.equal(got["side"], base * tri)
+        assert torch.equal(got["inplace"], base * tri), got["inplace"]
+        assert torch.equal(got["side"], base * tri), got["side"]
         assert got["big"].tolist() == [tri, tri], got["big"]
         assert all(not s["dist_initialized"] for s in state), state
         assert sorted(s["device"] for s in state) == list(range(n)), state
