@@ -19,6 +19,7 @@ import functools
 import inspect
 import json
 import os
+import pickle
 import random
 import struct
 import sys
@@ -504,7 +505,8 @@ class Endpoint(Generic[R]):
     def _send(self, args, kwargs, port: Optional[Port], ranks: Optional[List[int]] = None,
               headers: Optional[Dict[str, str]] = None) -> None:
         self._check_signature(args, kwargs)
-        if "monarch_b200.tensor_engine.device_mesh" in sys.modules:
+        if "monarch_b200.tensor_engine.device_mesh" in sys.modules and \
+                not getattr(self._fn, "_wire_messages_only", False):
             from ..tensor_engine import actor_bridge as ab
             if ab.has_distributed_tensors(args, kwargs):
                 ab.actor_send(self, args, kwargs, port, ranks, headers)
@@ -759,8 +761,15 @@ class ActorMesh(MeshTrait, Generic[T]):
                 raise SupervisionError(f"actor mesh '{self._name}' is unhealthy: {err}")
 
     def _cast(self, message: Tuple, ranks: Optional[List[int]] = None,
-              extra_headers: Optional[Dict[str, str]] = None) -> None:
-        body, parts = flatten(message)
+              extra_headers: Optional[Dict[str, str]] = None, plain: bool = False) -> None:
+        """``plain``: the caller vouches that the message holds only data that the C pickler
+        handles by itself (no functions or classes defined outside importable modules, no
+        large tensors worth sending out of band); it is then serialised without the
+        per-object Python hooks of the general pickler."""
+        if plain:
+            body, parts = pickle.dumps(message, protocol=pickle.HIGHEST_PROTOCOL), []
+        else:
+            body, parts = flatten(message)
         sl = self._shape_.ndslice
         root = self._root_slice
         if ranks is None and sl == root:

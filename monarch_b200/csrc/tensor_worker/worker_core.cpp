@@ -15,6 +15,7 @@
 // tracking is left to ATen: results that alias inputs share storage as usual).
 #include <torch/csrc/jit/python/pybind_utils.h>
 #include <torch/extension.h>
+#include <torch/csrc/Dtype.h>
 
 #include <ATen/core/dispatch/Dispatcher.h>
 #include <c10/core/Stream.h>
@@ -22,10 +23,12 @@
 
 #include <atomic>
 #include <condition_variable>
+#include <cstring>
 #include <deque>
 #include <functional>
 #include <memory>
 #include <mutex>
+#include <optional>
 #include <string>
 #include <thread>
 #include <unordered_map>
@@ -58,6 +61,9 @@ struct OpCall {
   c10::OperatorHandle op;
   std::vector<Arg> args;
   int64_t stream = 0;
+  // torch.cuda.Stream to enter around the launch (borrowed: the core's stream table owns
+  // it), or null when the executing thread's current stream is already the right one
+  PyObject* py_stream = nullptr;
   explicit OpCall(c10::OperatorHandle h) : op(std::move(h)) {}
 };
 
@@ -71,8 +77,10 @@ struct RecItem {
 // StreamActor a dedicated thread): the worker actor only routes messages; each stream's
 // commands run in arrival order on its own thread, so a command that blocks on the host
 // (a user function waiting for something another stream produces, a collective's
-// bootstrap) holds up its own stream only.  Tasks are Python callables executed with the
-// GIL held; operator calls release it inside the dispatcher as before.
+// bootstrap) holds up its own stream only.  A task is either a Python callable, executed
+// with the GIL held, or a native closure (an operator call parsed into an OpCall, a
+// deletion), executed without ever taking the GIL: the actor's thread can unpickle and
+// parse the next batch while this one computes.
 class StreamThread {
  public:
   StreamThread(int64_t id, py::object on_start) : id_(id) {
@@ -81,15 +89,21 @@ class StreamThread {
   }
   ~StreamThread() { stop(); }
 
+  struct Task {
+    py::object* fn = nullptr;          // owned; released under the GIL
+    std::function<void()> native;      // used when fn is null
+  };
+
   // GIL held by the caller; the callable is released under the GIL on the stream thread.
   void submit(py::object fn) {
-    auto* cell = new py::object(std::move(fn));
-    {
-      std::lock_guard<std::mutex> g(mu_);
-      q_.push_back(cell);
-      ++pending_;
-    }
-    cv_.notify_all();
+    Task t;
+    t.fn = new py::object(std::move(fn));
+    push(std::move(t));
+  }
+  void submit_native(std::function<void()> fn) {
+    Task t;
+    t.native = std::move(fn);
+    push(std::move(t));
   }
 
   // GIL released by the caller.
@@ -132,20 +146,37 @@ class StreamThread {
     }
     own.reset();
   }
+  void push(Task t) {
+    {
+      std::lock_guard<std::mutex> g(mu_);
+      q_.push_back(std::move(t));
+      ++pending_;
+    }
+    cv_.notify_all();
+  }
   void loop(py::object* on_start) {
     if (!Py_IsInitialized()) return;
     run_cell(on_start);
     while (true) {
-      py::object* cell = nullptr;
+      Task task;
       {
         std::unique_lock<std::mutex> lk(mu_);
         cv_.wait(lk, [&] { return stop_ || !q_.empty(); });
         if (q_.empty()) break;       // stop requested and nothing left
-        cell = q_.front();
+        task = std::move(q_.front());
         q_.pop_front();
       }
       if (!Py_IsInitialized()) break;
-      run_cell(cell);
+      if (task.fn != nullptr) {
+        run_cell(task.fn);
+      } else {
+        try {
+          task.native();
+        } catch (const std::exception&) {
+          // native tasks report their own failures; nothing may escape the thread
+        }
+        task.native = nullptr;
+      }
       {
         std::lock_guard<std::mutex> g(mu_);
         --pending_;
@@ -157,7 +188,7 @@ class StreamThread {
   std::thread thr_;
   std::mutex mu_;
   std::condition_variable cv_, idle_cv_;
-  std::deque<py::object*> q_;
+  std::deque<Task> q_;
   int64_t pending_ = 0;
   bool stop_ = false;
 };
@@ -243,45 +274,125 @@ class WorkerCore {
   }
 
   // ------------------------------------------------------------------ environment
+  // The table is shared by the actor's thread and the stream threads.  Native tasks touch it
+  // without the GIL, so `env_mu_` guards it; the methods below are called from Python (GIL
+  // held) and take the mutex inside.  Values that own a Python reference are never destroyed
+  // by a native task: it parks them in `graveyard_`, emptied by the next GIL-holding call.
   void set(int64_t id, py::object v) {
+    Value nv;
     if (v.is_none()) {
-      env_[id] = std::monostate{};
+      nv = std::monostate{};
     } else if (THPVariable_Check(v.ptr())) {
-      env_[id] = THPVariable_Unpack(v.ptr());
+      nv = THPVariable_Unpack(v.ptr());
     } else {
-      env_[id] = std::move(v);
+      nv = std::move(v);
+    }
+    Value old;
+    std::vector<Value> dead;
+    {
+      std::lock_guard<std::mutex> g(env_mu_);
+      auto& slot = env_[id];
+      old = std::move(slot);
+      slot = std::move(nv);
+      dead.swap(graveyard_);
     }
   }
   void set_error(int64_t id, int64_t seq, int64_t rank, std::string func, std::string text,
                  std::string tb, int64_t dep) {
-    env_[id] = std::make_shared<RemoteErr>(RemoteErr{seq, rank, std::move(func), std::move(text),
-                                                     std::move(tb), dep});
+    Value old;
+    std::lock_guard<std::mutex> g(env_mu_);
+    auto& slot = env_[id];
+    old = std::move(slot);
+    slot = std::make_shared<RemoteErr>(RemoteErr{seq, rank, std::move(func), std::move(text),
+                                                 std::move(tb), dep});
   }
   // The index of the GPU this worker owns (-1: a CPU worker).
   void set_cuda_index(int64_t idx) { cuda_index_ = idx; }
-  bool contains(int64_t id) const { return env_.count(id) != 0; }
-  py::object get(int64_t id) const {
-    auto it = env_.find(id);
-    if (it == env_.end()) throw py::key_error("Ref(" + std::to_string(id) + ")");
-    return to_py(it->second);
+  bool contains(int64_t id) {
+    std::lock_guard<std::mutex> g(env_mu_);
+    return env_.count(id) != 0;
+  }
+  py::object get(int64_t id) {
+    Value v;
+    {
+      std::lock_guard<std::mutex> g(env_mu_);
+      auto it = env_.find(id);
+      if (it == env_.end()) throw py::key_error("Ref(" + std::to_string(id) + ")");
+      v = it->second;
+    }
+    return to_py(v);
   }
   py::object pop(int64_t id) {
-    auto it = env_.find(id);
-    if (it == env_.end()) return py::none();
-    py::object v = to_py(it->second);
-    env_.erase(it);
-    return v;
+    Value v;
+    {
+      std::lock_guard<std::mutex> g(env_mu_);
+      auto it = env_.find(id);
+      if (it == env_.end()) return py::none();
+      v = std::move(it->second);
+      env_.erase(it);
+    }
+    return to_py(v);
   }
   void erase(const std::vector<int64_t>& ids) {
-    for (auto i : ids) env_.erase(i);
+    std::vector<Value> dead;     // destroyed after the mutex is released (GIL held here)
+    std::lock_guard<std::mutex> g(env_mu_);
+    dead.swap(graveyard_);
+    for (auto i : ids) {
+      auto it = env_.find(i);
+      if (it == env_.end()) continue;
+      dead.push_back(std::move(it->second));
+      env_.erase(it);
+    }
   }
-  size_t size() const { return env_.size(); }
-  int64_t live_bytes() const {
+  size_t size() {
+    std::lock_guard<std::mutex> g(env_mu_);
+    return env_.size();
+  }
+  int64_t live_bytes() {
+    std::lock_guard<std::mutex> g(env_mu_);
     int64_t n = 0;
     for (auto& kv : env_)
       if (auto* t = std::get_if<at::Tensor>(&kv.second))
         if (t->defined()) n += (int64_t)t->numel() * t->element_size();
     return n;
+  }
+
+  // ------------------------------------------------------------------ message batches
+  // `report(err_tuple)` is called (GIL taken for it) when a native task fails on its own.
+  void set_report(py::object report) { report_ = std::move(report); }
+  void set_null_device(bool on) { null_device_ = on; }
+  int64_t last_seq() const { return last_seq_.load(); }
+
+  // Route one batch of worker messages (monarch_messages/src/worker.rs WorkerMessage:
+  // CallFunction, DeleteRefs, ...).  Operator calls are decoded here into native OpCall
+  // structs and queued on the thread of their stream, deletions into a native rendezvous of
+  // all streams; both then run without the GIL.  Every other message, and any call whose
+  // arguments the native decoder does not take, goes to `fallback(msg)` (the Python router),
+  // in order.
+  int64_t route_batch(py::list msgs, py::object fallback) {
+    int64_t native = 0;
+    for (auto h : msgs) {
+      py::tuple m = py::reinterpret_borrow<py::tuple>(h);
+      bool done = false;
+      if (!threads_.empty() && m.size() >= 2 && PyUnicode_Check(m[0].ptr())) {
+        const char* kind = PyUnicode_AsUTF8(m[0].ptr());
+        if (kind != nullptr && std::strcmp(kind, "call") == 0 && m.size() == 8) {
+          done = route_call(m);
+        } else if (kind != nullptr && std::strcmp(kind, "call") == 0 && m.size() == 9 &&
+                   null_device_ && !m[8].is_none()) {
+          done = route_null_call(m);
+        } else if (kind != nullptr && std::strcmp(kind, "delete") == 0 && m.size() == 2) {
+          auto ids = std::make_shared<std::vector<int64_t>>(m[1].cast<std::vector<int64_t>>());
+          fence_native([this, ids]() { erase_nogil(*ids); });
+          done = true;
+        }
+      }
+      if (done)
+        ++native;
+      else
+        fallback(m);
+    }
+    return native;
   }
 
   // ------------------------------------------------------------------ operator calls
@@ -343,7 +454,7 @@ class WorkerCore {
         fallback(it.index, bind);
       }
       // temporaries of the recording die after their last use
-      for (int64_t id : it.drop) env_.erase(id);
+      if (!it.drop.empty()) erase(it.drop);
     }
     return native;
   }
@@ -360,6 +471,134 @@ class WorkerCore {
   std::unordered_map<int64_t, std::vector<RecItem>> recordings_;
   std::unordered_map<int64_t, py::object> streams_;
   std::unordered_map<int64_t, std::unique_ptr<StreamThread>> threads_;
+  std::mutex env_mu_;
+  std::vector<Value> graveyard_;     // guarded by env_mu_
+  py::object report_ = py::none();
+  std::atomic<int64_t> last_seq_{-1};
+  bool null_device_ = false;
+
+  // An operator call of a batch: parse with the GIL, run on the stream's thread without.
+  bool route_call(const py::tuple& m) {
+    py::handle spec = m[4];
+    if (!PyTuple_Check(spec.ptr()) || PyTuple_GET_SIZE(spec.ptr()) != 2) return false;
+    py::handle tag = PyTuple_GET_ITEM(spec.ptr(), 0), name = PyTuple_GET_ITEM(spec.ptr(), 1);
+    if (!PyUnicode_Check(tag.ptr()) || !PyUnicode_Check(name.ptr())) return false;
+    if (std::strcmp(PyUnicode_AsUTF8(tag.ptr()), "op") != 0) return false;
+    std::shared_ptr<OpCall> call;
+    StreamThread* thr = nullptr;
+    try {
+      const int64_t stream = m[7].cast<int64_t>();
+      auto it = threads_.find(stream);
+      if (it == threads_.end()) return false;
+      thr = it->second.get();
+      call = parse_call(m[1].cast<int64_t>(), refs_of(m[2]), refs_of(m[3]),
+                        name.cast<std::string>(), m[5], m[6], stream);
+    } catch (py::error_already_set& e) {
+      e.restore();
+      PyErr_Clear();
+      return false;
+    } catch (const std::exception&) {
+      return false;            // unusual argument structure: Python runs this one
+    }
+    thr->submit_native([this, call]() {
+      int64_t prev = last_seq_.load();
+      while (prev < call->seq && !last_seq_.compare_exchange_weak(prev, call->seq)) {
+      }
+      ErrPtr e = run_impl(*call, nullptr, false);
+      if (e && e->dependent_of < 0) {
+        py::gil_scoped_acquire g;
+        if (!report_.is_none()) {
+          try {
+            report_(err_tuple(*e, false));
+          } catch (py::error_already_set& ex) {
+            ex.discard_as_unraisable("tensor worker error report");
+          }
+        }
+      }
+    });
+    return true;
+  }
+
+  // Shape-only workers: the controller announces the results' metadata and nothing is
+  // executed; zero tensors of those shapes stand in.
+  bool route_null_call(const py::tuple& m) {
+    struct Meta {
+      std::vector<int64_t> shape;
+      at::ScalarType dtype;
+    };
+    auto metas = std::make_shared<std::vector<Meta>>();
+    std::vector<int64_t> results;
+    StreamThread* thr = nullptr;
+    int64_t seq = 0;
+    try {
+      seq = m[1].cast<int64_t>();
+      results = refs_of(m[2]);
+      auto it = threads_.find(m[7].cast<int64_t>());
+      if (it == threads_.end()) return false;
+      thr = it->second.get();
+      for (auto h : m[8]) {
+        py::tuple mt = py::reinterpret_borrow<py::tuple>(h);
+        if (!THPDtype_Check(mt[1].ptr())) return false;
+        metas->push_back(Meta{mt[0].cast<std::vector<int64_t>>(),
+                              reinterpret_cast<THPDtype*>(mt[1].ptr())->scalar_type});
+      }
+    } catch (py::error_already_set& e) {
+      e.restore();
+      PyErr_Clear();
+      return false;
+    } catch (const std::exception&) {
+      return false;
+    }
+    if (metas->size() != results.size()) return false;
+    thr->submit_native([this, metas, results, seq]() {
+      int64_t prev = last_seq_.load();
+      while (prev < seq && !last_seq_.compare_exchange_weak(prev, seq)) {
+      }
+      for (size_t i = 0; i < results.size(); ++i)
+        assign(results[i], at::zeros((*metas)[i].shape, at::TensorOptions().dtype((*metas)[i].dtype)));
+    });
+    return true;
+  }
+
+  // `action` runs (without the GIL) once every stream has reached this point of its queue;
+  // no stream waits for it.
+  void fence_native(std::function<void()> action) {
+    auto remaining = std::make_shared<std::atomic<int>>((int)threads_.size());
+    auto act = std::make_shared<std::function<void()>>(std::move(action));
+    for (auto& kv : threads_) {
+      kv.second->submit_native([remaining, act]() {
+        if (remaining->fetch_sub(1) == 1) (*act)();
+      });
+    }
+  }
+
+  void erase_nogil(const std::vector<int64_t>& ids) {
+    std::vector<Value> dead;   // tensors: freed here, after the mutex is released
+    {
+      std::lock_guard<std::mutex> g(env_mu_);
+      for (auto i : ids) {
+        auto it = env_.find(i);
+        if (it == env_.end()) continue;
+        if (std::holds_alternative<py::object>(it->second))
+          graveyard_.push_back(std::move(it->second));
+        else
+          dead.push_back(std::move(it->second));
+        env_.erase(it);
+      }
+    }
+  }
+
+  // Store `v` under `id`; callable without the GIL.
+  void assign(int64_t id, Value v) {
+    Value old;
+    std::lock_guard<std::mutex> g(env_mu_);
+    auto& slot = env_[id];
+    if (std::holds_alternative<py::object>(slot))
+      graveyard_.push_back(std::move(slot));
+    else
+      old = std::move(slot);
+    slot = std::move(v);
+  }
 
   static py::object to_py(const Value& v) {
     if (std::holds_alternative<std::monostate>(v)) return py::none();
@@ -399,6 +638,8 @@ class WorkerCore {
     call->mutates = std::move(mutates);
     call->name = qualname;
     call->stream = stream;
+    auto sit = streams_.find(stream);
+    if (sit != streams_.end() && !sit->second.is_none()) call->py_stream = sit->second.ptr();
     const auto& schema = call->op.schema();
     const auto& sargs = schema.arguments();
     size_t pos = 0;
@@ -473,11 +714,12 @@ class WorkerCore {
 
   // Resolve one ref; records the first poisoned input in `dep`.
   bool resolve(int64_t id, const std::unordered_map<int64_t, int64_t>* bind, at::Tensor& out,
-               ErrPtr& dep, bool& is_none) const {
+               ErrPtr& dep, bool& is_none) {
     if (bind) {
       auto b = bind->find(id);
       if (b != bind->end()) id = b->second;
     }
+    std::lock_guard<std::mutex> g(env_mu_);
     auto it = env_.find(id);
     if (it == env_.end()) throw std::runtime_error("Ref(" + std::to_string(id) + ") is not defined");
     is_none = false;
@@ -502,14 +744,25 @@ class WorkerCore {
     return b == bind->end() ? id : b->second;
   }
 
-  py::object poison(const OpCall& c, const std::unordered_map<int64_t, int64_t>* bind,
-                    ErrPtr e) {
-    for (auto r : c.results) env_[rebound(r, bind)] = e;
-    for (auto r : c.mutates) env_[rebound(r, bind)] = e;
+  ErrPtr poison(const OpCall& c, const std::unordered_map<int64_t, int64_t>* bind, ErrPtr e) {
+    for (auto r : c.results) assign(rebound(r, bind), e);
+    for (auto r : c.mutates) assign(rebound(r, bind), e);
+    return e;
+  }
+
+  // GIL held by the caller.
+  py::object run(const OpCall& c, const std::unordered_map<int64_t, int64_t>* bind) {
+    ErrPtr e = run_impl(c, bind, true);
+    if (!e) return py::none();
     return err_tuple(*e, false);
   }
 
-  py::object run(const OpCall& c, const std::unordered_map<int64_t, int64_t>* bind) {
+  // Executes one operator call; null on success, else the error that now poisons its
+  // results.  `gil_held` says whether the calling thread holds the GIL (it is released
+  // around the dispatcher call); a native task passes false and never takes it, except to
+  // enter a torch.cuda.Stream context where the call names one.
+  ErrPtr run_impl(const OpCall& c, const std::unordered_map<int64_t, int64_t>* bind,
+                  bool gil_held) {
     ErrPtr dep;
     try {
       const auto& schema = c.op.schema();
@@ -553,13 +806,17 @@ class WorkerCore {
         slots[i] = *sargs[i].default_value();
       }
       torch::jit::Stack stack(slots.begin(), slots.end());
-      {
+      if (c.py_stream == nullptr && !gil_held) {
+        c.op.callBoxed(stack);       // the thread's current stream is the call's stream
+      } else {
+        std::optional<py::gil_scoped_acquire> take;
+        if (!gil_held) take.emplace();
         py::object guard;
-        auto sit = streams_.find(c.stream);
-        bool has_stream = sit != streams_.end() && !sit->second.is_none();
+        const bool has_stream = c.py_stream != nullptr;
         if (has_stream) {
-          // torch.cuda.stream(s) context: enter/exit around the launch (GIL is held)
-          guard = py::module_::import("torch").attr("cuda").attr("stream")(sit->second);
+          // torch.cuda.stream(s) context: enter/exit around the launch
+          guard = py::module_::import("torch").attr("cuda").attr("stream")(
+              py::reinterpret_borrow<py::object>(c.py_stream));
           guard.attr("__enter__")();
         }
         try {
@@ -585,8 +842,8 @@ class WorkerCore {
         throw std::runtime_error(c.name + " returned " + std::to_string(flat.size()) +
                                  " tensors, controller expected " +
                                  std::to_string(c.results.size()));
-      for (size_t i = 0; i < flat.size(); ++i) env_[rebound(c.results[i], bind)] = flat[i];
-      return py::none();
+      for (size_t i = 0; i < flat.size(); ++i) assign(rebound(c.results[i], bind), flat[i]);
+      return nullptr;
     } catch (const std::exception& ex) {
       auto e = std::make_shared<RemoteErr>(
           RemoteErr{c.seq, rank_, c.name, std::string("RuntimeError: ") + ex.what(), "", -1});
@@ -619,6 +876,10 @@ PYBIND11_MODULE(_tensor_worker, m) {
       .def("start_stream_thread", &WorkerCore::start_stream_thread)
       .def("has_stream_thread", &WorkerCore::has_stream_thread)
       .def("submit", &WorkerCore::submit)
+      .def("route_batch", &WorkerCore::route_batch)
+      .def("set_report", &WorkerCore::set_report)
+      .def("set_null_device", &WorkerCore::set_null_device)
+      .def("last_seq", &WorkerCore::last_seq)
       .def("fence", &WorkerCore::fence, py::arg("action"), py::arg("hold") = true)
       .def("drain", &WorkerCore::drain)
       .def("pending", &WorkerCore::pending)

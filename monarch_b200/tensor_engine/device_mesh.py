@@ -213,7 +213,7 @@ class Client:
         """Refs are dropped on every worker, whichever sub-mesh the next message goes to."""
         d = self._flush_deletes(None)
         if d:
-            self.root_mesh._workers.run.broadcast(d)
+            _cast_run(self.root_mesh._workers, d)
 
     def _flush_deletes(self, mesh) -> List[tuple]:
         with self._lock:
@@ -233,7 +233,7 @@ class Client:
         if self.eager_batch <= 1:
             self._watch()
             self._send_deletes()
-            mesh._workers.run.broadcast([msg])
+            _cast_run(mesh._workers, [msg])
             return
         # eager commands are handed to the workers a few at a time: every cast costs the
         # controller a pickle and a trip through the native runtime, and the workers execute
@@ -274,7 +274,7 @@ class Client:
             else:
                 runs.append((mesh, [msg]))
         for mesh, msgs in runs:
-            mesh._workers.run.broadcast(msgs)
+            _cast_run(mesh._workers, msgs)
         # refs dropped by the controller go last: a buffered command may still name them
         # (a ref that is already dropped cannot appear in any later command)
         self._send_deletes()
@@ -503,18 +503,45 @@ class Client:
         self._flush_event.set()
 
 
+def _cast_run(workers, msgs: List[tuple]) -> None:
+    """``workers.run.broadcast(msgs)``.  Operator calls and deletions hold only refs, numbers,
+    strings, dtypes and the like (an ATen operator takes no callables), so batches of those
+    skip the general pickler, whose per-object hooks cost more than the cast itself."""
+    plain = True
+    for m in msgs:
+        k = m[0]
+        if not (k == "delete" or (k == "call" and m[4][0] == "op")):
+            plain = False
+            break
+    if not plain or not hasattr(workers, "_cast"):      # (simulated workers have no cast)
+        workers.run.broadcast(msgs)
+        return
+    workers._raise_if_unhealthy()
+    workers._cast(("call", "run", (msgs,), {}, None), plain=True)
+
+
 # ----------------------------------------------------------------------------- tensor --
 class Tensor(torch.Tensor):
     """A tensor that lives on every proc of a device mesh.  The controller holds only its
     metadata (a FakeTensor); data is named by ``ref`` on the workers."""
 
     @staticmethod
-    def __new__(cls, fake: torch.Tensor, mesh: "DeviceMesh", stream: Stream):
-        r = torch.Tensor._make_wrapper_subclass(
-            cls, fake.size(), strides=fake.stride(), storage_offset=fake.storage_offset(),
-            dtype=fake.dtype, device=fake.device, layout=fake.layout,
-            requires_grad=fake.requires_grad)
-        r._fake = fake
+    def __new__(cls, fake, mesh: "DeviceMesh", stream: Stream):
+        if type(fake) is _LazyFake:
+            # metadata remembered from an earlier propagation of the same operator: the
+            # FakeTensor itself (30 us to build) is made only if something asks for it
+            _, shape, stride, dtype, device, req = fake.t
+            r = torch.Tensor._make_wrapper_subclass(
+                cls, shape, strides=stride, dtype=dtype, device=device, requires_grad=req)
+            r._fake_obj = None
+            r._tmpl = fake.t
+        else:
+            r = torch.Tensor._make_wrapper_subclass(
+                cls, fake.size(), strides=fake.stride(), storage_offset=fake.storage_offset(),
+                dtype=fake.dtype, device=fake.device, layout=fake.layout,
+                requires_grad=fake.requires_grad)
+            r._fake_obj = fake
+            r._tmpl = None
         r.mesh = mesh
         r.stream = stream
         r.ref = mesh.client.new_ref()
@@ -524,6 +551,18 @@ class Tensor(torch.Tensor):
 
     def __init__(self, *a, **k):
         pass
+
+    @property
+    def _fake(self) -> torch.Tensor:
+        f = self._fake_obj
+        if f is None:
+            prev = getattr(_tls, "propagating", False)
+            _tls.propagating = True        # the factory call below is not a mesh operation
+            try:
+                f = self._fake_obj = _from_template(self._tmpl)
+            finally:
+                _tls.propagating = prev
+        return f
 
     def __repr__(self, *, tensor_contents=None):
         return f"monarch_b200.Tensor(mesh={self.mesh}, ref={self.ref}, fake={self._fake})"
@@ -765,7 +804,7 @@ def _to_wire(obj):
 
 
 def _wrap_outputs(fake_out, mesh, stream, refs: List[Ref]):
-    if isinstance(fake_out, torch.Tensor):
+    if type(fake_out) is _LazyFake or isinstance(fake_out, torch.Tensor):
         t = Tensor(fake_out, mesh, stream)
         refs.append(Ref(t.ref))
         return t
@@ -791,7 +830,7 @@ def _send_call(fspec, args, kwargs, fake_out, mesh: "DeviceMesh", mutates: Seque
         # shape-only workers do not run the function: they need the results' metadata
         flat: List[Tensor] = []
         _collect(out, flat)
-        msg += ([(tuple(t._fake.shape), t._fake.dtype) for t in flat],)
+        msg += ([(tuple(t.shape), t.dtype) for t in flat],)
     client.send(mesh, msg)
     return out
 
@@ -867,7 +906,9 @@ def _op_is_functional(func) -> bool:
 def _arg_sig(o):
     tp = type(o)
     if tp is Tensor:
-        f = o._fake
+        f = o._fake_obj
+        if f is None:
+            return o._tmpl
         return ("T", tuple(f.shape), f.stride(), f.dtype, f.device, f.requires_grad)
     if tp in _PLAIN_ARG_TYPES:
         return (tp, o)
@@ -890,14 +931,24 @@ def _out_template(o):
     raise _Uncacheable()
 
 
-def _from_template(t):
+class _LazyFake:
+    """Stands for the FakeTensor that ``_from_template(t)`` would build."""
+    __slots__ = ("t",)
+
+    def __init__(self, t):
+        self.t = t
+
+
+def _from_template(t, lazy: bool = False):
     if t[0] == "T":
+        if lazy:
+            return _LazyFake(t)
         _, shape, stride, dtype, device, req = t
         meta = torch.empty_strided(shape, stride, dtype=dtype, device="meta")
         f = _FakeTensor(_fake_mode, meta, device)
         return f.requires_grad_(True) if req else f
     if t[0] == "S":
-        return t[1](_from_template(x) for x in t[2])
+        return t[1](_from_template(x, lazy) for x in t[2])
     return t[1]
 
 
@@ -910,12 +961,7 @@ def _propagate(func, args, kwargs):
                    torch.is_grad_enabled())
             tmpl = _prop_cache.get(key)
             if tmpl is not None:
-                prev = getattr(_tls, "propagating", False)
-                _tls.propagating = True
-                try:
-                    return _from_template(tmpl)
-                finally:
-                    _tls.propagating = prev
+                return _from_template(tmpl, lazy=True)
         except (_Uncacheable, TypeError):     # TypeError: an unhashable argument
             key = None
     with _propagation():
@@ -936,8 +982,25 @@ _DATA_DEPENDENT = {"_local_scalar_dense", "item", "is_nonzero", "equal", "allclo
                    "unique", "_unique2", "masked_select"}
 
 
+_op_info: Dict[Any, tuple] = {}
+
+
+def _info_of(func) -> tuple:
+    """(data dependent?, wire name, [(position, name) of arguments the operator writes])."""
+    info = _op_info.get(func)
+    if info is None:
+        schema = func._schema
+        short = schema.name.split("::")[1]
+        writes = [(i, a.name) for i, a in enumerate(schema.arguments)
+                  if a.alias_info is not None and a.alias_info.is_write]
+        info = _op_info[func] = (short in _DATA_DEPENDENT,
+                                 f"{func.namespace}.{short}.{func._overloadname}", writes)
+    return info
+
+
 def _dispatch(func, args, kwargs):
-    if func._schema.name.split("::")[1] in _DATA_DEPENDENT:
+    data_dependent, name, writes = _info_of(func)
+    if data_dependent:
         raise RuntimeError(
             f"{func._schema.name} needs the values of a distributed tensor, which live on the "
             "workers.  Bring them to the controller with fetch_shard(t).get() or inspect(t), "
@@ -954,13 +1017,11 @@ def _dispatch(func, args, kwargs):
         if mesh is None:
             raise RuntimeError("no active device mesh")
     fake_out = _propagate(func, args, kwargs)
-    name = f"{func.namespace}.{func._schema.name.split('::')[1]}.{func._overloadname}"
     # in-place / out= ops return their (already remote) argument: alias, do not re-ref
     mutated: List[Tensor] = []
-    schema = func._schema
-    for i, a in enumerate(schema.arguments):
-        if a.alias_info is not None and a.alias_info.is_write:
-            v = args[i] if i < len(args) else kwargs.get(a.name)
+    if writes:
+        for i, arg_name in writes:
+            v = args[i] if i < len(args) else kwargs.get(arg_name)
             if isinstance(v, Tensor):
                 if v._borrowed_by and any(b.stream is not get_active_stream()
                                           for b in v._borrowed_by):

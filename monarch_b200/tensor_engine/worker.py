@@ -288,6 +288,8 @@ class TensorWorker(Actor):
             os.environ.get("MB200_WORKER_THREADS", "1") == "1"
         self._borrow_route: Dict[int, Tuple[int, int]] = {}
         if self.threaded:
+            self.core.set_report(lambda err: self._report(RemoteError(*err[:5])))
+            self.core.set_null_device(self.null_device)
             self._start_stream_thread(0)
 
     # ---------------------------------------------------------------------- helpers
@@ -345,15 +347,22 @@ class TensorWorker(Actor):
     @endpoint
     def run(self, msgs: List[tuple]) -> None:
         """A batch of worker messages (one for eager dispatch, many under coalescing)."""
-        for m in msgs:
-            self._route(m)
+        self._route_all(msgs)
 
     @endpoint
     def run_and_reply(self, msgs: List[tuple], fetch: tuple) -> Any:
-        for m in msgs:
-            self._route(m)
+        self._route_all(msgs)
         self._drain()
         return self._fetch(*fetch)
+
+    def _route_all(self, msgs: List[tuple]) -> None:
+        if self.threaded:
+            # operator calls and deletions are decoded and queued by the native core and run
+            # on the stream threads without the GIL; the rest comes back to _route in order
+            self.core.route_batch(msgs, self._route)
+        else:
+            for m in msgs:
+                self._route(m)
 
     # ------------------------------------------------------------ per-stream threads
     # position of the stream id in the messages that run on one stream
@@ -934,14 +943,24 @@ class TensorWorker(Actor):
     def progress(self) -> int:
         """Watchdog ping: answered in command order, so a reply means that everything sent
         before it has been executed (not necessarily finished on the GPU)."""
-        return self.last_seq
+        return self._last_seq()
 
     @endpoint
     def sync(self) -> int:
         self._drain()
         if self.use_cuda:
             torch.cuda.synchronize(self.device)
-        return self.last_seq
+        return self._last_seq()
+
+    def _last_seq(self) -> int:
+        return max(self.last_seq, self.core.last_seq()) if self.core is not None \
+            else self.last_seq
+
+
+# the worker's endpoints take wire messages (refs, not distributed tensors): casts to them
+# skip the scan for distributed tensors that other actors' endpoints need
+for _n in ("run", "fetch", "progress", "sync"):
+    TensorWorker.__dict__[_n]._fn._wire_messages_only = True
 
 
 def _flatten_tensors(out) -> List[torch.Tensor]:
