@@ -310,8 +310,9 @@ class _Compiled:
             batch, client._coalesce = client._coalesce, None
         msgs = []
         for m, msg in batch:
-            if m._workers is not mesh._workers:
-                raise RuntimeError("compile() supports functions that stay on one mesh")
+            if m._workers is not mesh._workers and m._ndslice != mesh._ndslice:
+                raise RuntimeError("compile() supports functions that stay on one mesh (a "
+                                   f"{msg[0]!r} message goes to {m}, the recording to {mesh})")
             msgs.append(msg)
         outs: list = []
         _collect(out, outs)

@@ -31,6 +31,15 @@ def test_distributed_tensor_ddp():
     assert out["loss_last"] < out["loss_first"]
 
 
+def test_llama_ddp_over_distributed_tensors_compiled_step():
+    """The whole training step (forward, controller-side autograd, bucketed gradient
+    all-reduce, foreach AdamW with the step count on the workers) as one recording."""
+    out = _load("llama_ddp_distributed_tensors").run(
+        model="tiny", procs=2, cuda=False, seq=32, micro_batch=2, steps=3, warmup=2)
+    assert out["replicas_in_sync"] and out["compiled"]
+    assert out["loss_last"] < out["loss_first"]
+
+
 def test_lazy_top_level_api():
     import monarch_b200 as m
     assert m.DeviceMesh is m.tensor_engine.DeviceMesh and callable(m.remote)
