@@ -109,7 +109,7 @@ def collectives_case():
         K.check(lib.mb200_allreduce_scale_cast(buf.ptrs_at(0), buf.ptrs_at(0), None, None,
                                                flags.ptrs, n, 0, 0, 1, 1.0, 0, epoch,
                                                flags.counter.data_ptr(), 0, st.data_ptr(),
-                                               K.stream_ptr()), "allreduce", 2)
+                                               K.stream_ptr()), "allreduce")
     master = torch.randn(n, device=dev)
     m, v = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
     shard = torch.empty(n, dtype=bf16, device=dev)

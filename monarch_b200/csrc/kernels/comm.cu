@@ -291,7 +291,12 @@ __global__ void __launch_bounds__(256)
           st_v4(reinterpret_cast<uint4*>(out.p[(rank + k) % world]) + i, o);
     }
   }
-  if (last_block_done(counter)) signal_all(flags, world, rank, slot + 1, epoch, threadIdx.x);
+  if (last_block_done(counter)) {
+    signal_all(flags, world, rank, slot + 1, epoch, threadIdx.x);
+    // every rank's share of the result must have landed here before a consumer on this
+    // stream reads it: the last block stays until all ranks have said so (bounded wait)
+    block_wait_all(flags.p[rank], world, slot + 1, epoch, status, &sh_ok);
+  }
 }
 
 // ----------------------------------------------------------------------- peer copy ----
@@ -433,8 +438,6 @@ extern "C" int mb200_allreduce_scale_cast(const void* const* in_ptrs, const void
     allreduce_kernel<false><<<grid, 256, 0, ST(stream)>>>(in, out, mc_in, mc_out, fl, n, rank,
                                                            world, scale, slot, epoch, counter,
                                                            status);
-  // Results from every rank must have landed before a consumer on this stream reads them.
-  wait_kernel<<<1, 32, 0, ST(stream)>>>(fl.p[rank], world, slot + 1, epoch, status);
   return (int)cudaGetLastError();
 }
 

@@ -832,7 +832,9 @@ class WorkerCore {
       std::vector<at::Tensor> flat;
       for (auto& v : stack) {
         if (v.isTensor()) {
-          flat.push_back(v.toTensor());
+          // an undefined tensor is an optional output that is absent (None on the
+          // controller, which counts only the tensors it saw during propagation)
+          if (v.toTensor().defined()) flat.push_back(v.toTensor());
         } else if (v.isTensorList()) {
           for (const at::Tensor& t : v.toTensorList()) flat.push_back(t);
         }

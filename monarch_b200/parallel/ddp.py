@@ -84,7 +84,7 @@ class DDPParamStore(LocalParamStore):
                         self._flags.ptrs, n, 0, self.rank, self.world, self.reduce_scale, 0,
                         self._epoch, self._flags.counter.data_ptr(), 0,
                         K.status_word(self.device).data_ptr(), K.stream_ptr()),
-                        "allreduce_scale_cast", 2)
+                        "allreduce_scale_cast")
                 else:
                     g = self.grads[off: off + n]
                     if g.dtype == bf16 and dist.get_backend(self.group) != "nccl":

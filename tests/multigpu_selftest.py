@@ -119,7 +119,7 @@ def main() -> int:
         K.check(lib.mb200_allreduce_scale_cast(buf.ptrs_at(0), buf.ptrs_at(0), mc(buf), mc(buf),
                                                flags.ptrs, n, 0, rank, world, 1.0 / world, 2,
                                                ar_epoch, flags.counter.data_ptr(), 0,
-                                               status.data_ptr(), K.stream_ptr()), "allreduce", 2)
+                                               status.data_ptr(), K.stream_ptr()), "allreduce")
         torch.cuda.synchronize()
         K.check_status()
         assert _rel(buf.tensor, expect) < 5e-3, (use_mc, _rel(buf.tensor, expect))
@@ -488,7 +488,7 @@ def main() -> int:
                     buf.ptrs_at(0), buf.ptrs_at(0), buf.mc_at(0) if mc else None,
                     buf.mc_at(0) if mc else None, flags.ptrs, n, 0, rank, world, 1.0 / world, 6,
                     ep[0], flags.counter.data_ptr(), 0, status.data_ptr(), K.stream_ptr()),
-                    "allreduce", 2)
+                    "allreduce")
 
             def ours_ar_p2p():
                 ours_ar(False)
