@@ -159,11 +159,13 @@ std::vector<std::string> to_strings(const std::vector<py::object>& parts) {
 
 void bind_tasks(py::module_& m);   // tasks.cpp
 void bind_rdma(py::module_& m);    // rdma_bindings.cpp
+void bind_controller(py::module_& m);  // controller_bindings.cpp
 
 PYBIND11_MODULE(_native, m) {
   m.doc() = "monarch_b200 native runtime";
   bind_tasks(m);
   bind_rdma(m);
+  bind_controller(m);
 
   // ------------------------------------------------------------------ ndslice ----
   py::register_exception<NdError>(m, "NdSliceError", PyExc_ValueError);

@@ -290,8 +290,7 @@ def mock_mesh(hosts: int = 1, gpus: int = 1, cost: Optional[CostModel] = None,
     client.proc_mesh = _PM()
     client.workers = workers
     client.use_cuda = False
-    client._seq = itertools.count(1)
-    client._ref = itertools.count(1)
+    client._init_history(n)
     client._lock = threading.RLock()
     client._pending_deletes = []
     client._coalesce = None

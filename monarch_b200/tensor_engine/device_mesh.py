@@ -160,8 +160,7 @@ class Client:
         self.proc_mesh = proc_mesh
         self.workers = workers
         self.use_cuda = use_cuda
-        self._seq = itertools.count(1)
-        self._ref = itertools.count(1)
+        self._init_history(len(workers))
         self._lock = threading.RLock()
         self._pending_deletes: List[int] = []
         self._coalesce: Optional[List[Tuple[Any, tuple]]] = None
@@ -176,6 +175,12 @@ class Client:
         workers.configure.call(port).get(timeout=60)
         self._closed = False
         self._init_watchdog(float(os.environ.get("MB200_OPERATION_TIMEOUT", "120")))
+
+    def _init_history(self, world: int) -> None:
+        """Sequence numbers, ref ids, the invocations in flight, the workers' progress and
+        what is known to be poisoned live in the native ``ControllerHistory``."""
+        from .. import _native as N
+        self.history = N.ControllerHistory(world)
 
     def _init_batching(self, eager_batch: int) -> None:
         """``eager_batch``: how many eager commands may wait for one cast (1 sends each on
@@ -200,14 +205,27 @@ class Client:
         self._failed: Optional[Exception] = None
 
     def new_seq(self) -> int:
-        return next(self._seq)
+        return self.history.next_seq()
 
     def new_ref(self) -> int:
-        return next(self._ref)
+        return self.history.next_ref()
 
     def delete_ref(self, ref: int) -> None:
         with self._lock:
             self._pending_deletes.append(ref)
+
+    def known_failure(self, t: "Tensor") -> Optional["RemoteException"]:
+        """The failure that poisons ``t`` as far as the controller has heard (error reports
+        arrive asynchronously), without asking the workers; None if it knows of none."""
+        self.drain_errors()
+        origin = self.history.ref_failed(t.ref)
+        if origin < 0:
+            return None
+        f = self.history.failure(origin)
+        if f is None:
+            return None
+        seq, rank, name, text = f
+        return RemoteException(seq, rank, name, text, "", None)
 
     def _send_deletes(self) -> None:
         """Refs are dropped on every worker, whichever sub-mesh the next message goes to."""
@@ -220,6 +238,7 @@ class Client:
             if not self._pending_deletes:
                 return []
             ids, self._pending_deletes = self._pending_deletes, []
+        self.history.forget_refs(ids)
         return [("delete", ids)]
 
     def send(self, mesh: "DeviceMesh", msg: tuple) -> None:
@@ -305,31 +324,32 @@ class Client:
         if self.operation_timeout <= 0 or self._closed:
             return
         now = time.monotonic()
-        p = self._ping
-        if p is not None:
+        h = self.history
+        if self._ping is not None:
+            rx = self._ping
             while True:
-                env = p["rx"]._rx.try_recv()
+                env = rx._rx.try_recv()
                 if env is None:
                     break
                 from ..actor.pickle import unflatten
                 _, rank, last_seq = unflatten(env.data, env.parts)
-                p["seen"][rank] = last_seq
-            if len(p["seen"]) == p["n"]:
-                p["rx"].close()
-                self._ping = None
-            elif now - p["t"] > self.operation_timeout and not p["reported"]:
-                p["reported"] = True
-                missing = sorted(set(range(p["n"])) - set(p["seen"]))
-                stall = {"ranks": missing, "waited_s": now - p["t"], "controller_seq": p["seq"],
-                         "last_seq_of_responders": dict(p["seen"])}
+                if h.ping_answered(rank, last_seq):
+                    rx.close()
+                    self._ping = None
+                    break
+            stall = h.stalled(now, self.operation_timeout) if self._ping is not None else None
+            if stall is not None:
                 self.stalls.append(stall)
-                msg = (f"tensor workers {missing} made no progress for {now - p['t']:.1f} s "
-                       f"(operation timeout {self.operation_timeout:.1f} s, controller at seq "
-                       f"{p['seq']})")
+                at = h.describe(h.min_completed() + 1)
+                msg = (f"tensor workers {stall['ranks']} made no progress for "
+                       f"{stall['waited_s']:.1f} s (operation timeout "
+                       f"{self.operation_timeout:.1f} s, controller at seq "
+                       f"{stall['controller_seq']}"
+                       + (f", oldest unfinished command {at[0]}" if at else "") + ")")
                 import logging
                 logging.getLogger("monarch_b200.tensor_engine").warning(msg)
                 if self.fail_on_worker_timeout:
-                    self._failed = WorkerTimeoutError(msg, missing)
+                    self._failed = WorkerTimeoutError(msg, stall["ranks"])
                     raise self._failed
         if self._ping is None and now - self._last_ping >= self.progress_interval:
             self.flush()     # the ping stands behind everything issued so far
@@ -337,8 +357,8 @@ class Client:
             port, rx = ep._open()
             ep._send((), {}, port)
             self._last_ping = now
-            self._ping = {"rx": rx, "t": now, "n": len(self.root_mesh._workers), "seen": {},
-                          "seq": next(self._seq), "reported": False}
+            self._ping = rx
+            h.ping_sent(h.next_seq(), now)
 
     def _ensure_stream(self, s: Stream) -> None:
         if s.id not in self._streams_made:
@@ -485,13 +505,18 @@ class Client:
         return r[1]
 
     def drain_errors(self) -> List[tuple]:
-        while True:
+        while self._err_rx is not None:
             env = self._err_rx._rx.try_recv()
             if env is None:
                 break
             from ..actor.pickle import unflatten
             _, _, payload = unflatten(env.data, env.parts)
             self.errors.append(payload)
+            if isinstance(payload, tuple) and len(payload) >= 5 and payload[0] == "error":
+                # poison, on the controller's books, what the failed command defines and
+                # everything issued since that read it
+                self.history.fail(int(payload[1]), int(payload[2]), str(payload[3]),
+                                  str(payload[4]))
         return self.errors
 
     def shutdown(self) -> None:
@@ -654,6 +679,9 @@ class Tensor(torch.Tensor):
         else:
             result = Tensor(out_fake, m, self.stream)
             res_ref = Ref(result.ref)
+        client.history.add_invocation(
+            seq, f"reduce.{reduction}",
+            [res_ref.id] + ([out.ref] if out is not None else []), [self.ref])
         client.send(m, ("reduce", seq, res_ref, Ref(self.ref), key, reduction, scatter, _inplace,
                         Ref(out.ref) if out is not None else None, self.stream.id,
                         (tuple(f.shape), f.dtype)))
@@ -817,13 +845,22 @@ def _wrap_outputs(fake_out, mesh, stream, refs: List[Ref]):
     return fake_out
 
 
-def _send_call(fspec, args, kwargs, fake_out, mesh: "DeviceMesh", mutates: Sequence[Tensor] = ()):
+def _send_call(fspec, args, kwargs, fake_out, mesh: "DeviceMesh", mutates: Sequence[Tensor] = (),
+               uses: Optional[List[Tensor]] = None):
     stream = get_active_stream()
     client = mesh.client
     client._ensure_stream(stream)
     refs: List[Ref] = []
     out = _wrap_outputs(fake_out, mesh, stream, refs)
     seq = client.new_seq()
+    if uses is None:
+        uses = []
+        _collect(args, uses)
+        _collect(kwargs, uses)
+    f = fspec[1]
+    client.history.add_invocation(
+        seq, f if isinstance(f, str) else getattr(f, "__name__", "function"),
+        [r.id for r in refs] + [t.ref for t in mutates], [t.ref for t in uses])
     msg = ("call", seq, refs, [Ref(t.ref) for t in mutates], fspec, _to_wire(args),
            _to_wire(kwargs), stream.id)
     if getattr(client, "null_device", False):
@@ -1036,10 +1073,12 @@ def _dispatch(func, args, kwargs):
     if mutated and isinstance(fake_out, torch.Tensor) and len(mutated) == 1:
         client = mesh.client
         stream = get_active_stream()
-        client.send(mesh, ("call", client.new_seq(), [], [Ref(t.ref) for t in mutated],
+        seq = client.new_seq()
+        client.history.add_invocation(seq, name, [t.ref for t in mutated], [t.ref for t in ts])
+        client.send(mesh, ("call", seq, [], [Ref(t.ref) for t in mutated],
                            ("op", name), _to_wire(args), _to_wire(kwargs), stream.id))
         return mutated[0]
-    return _send_call(("op", name), args, kwargs, fake_out, mesh, mutated)
+    return _send_call(("op", name), args, kwargs, fake_out, mesh, mutated, ts)
 
 
 # ------------------------------------------------------------------------ device mesh --

@@ -89,6 +89,55 @@ def test_remote_functions_and_errors(dm):
         assert tuple(got) == (4, 2)
 
 
+def test_controller_history_tracks_failures_and_progress(dm):
+    """The native controller history learns of a failure from the error port and poisons,
+    on the controller's books, the failed command's results, the commands already issued
+    that read them, and commands issued later -- no round trip to the workers."""
+    import time
+
+    @te.remote(propagate=lambda x: x)
+    def boom(x):
+        raise ValueError("boom")
+
+    client = dm.client
+    with dm.activate():
+        a = torch.ones(3)
+        good = a + 1
+        bad = boom(a)
+        dep = bad * 2                     # issued before the failure is known
+        te.inspect(good)                  # the workers have passed `boom` by now
+        deadline = time.monotonic() + 10
+        while client.known_failure(bad) is None and time.monotonic() < deadline:
+            time.sleep(0.01)
+        f = client.known_failure(bad)
+        assert f is not None and "boom" in f.exc_text
+        assert client.known_failure(dep) is not None          # forward pass over live commands
+        later = dep - 1                                           # issued after: inherits at once
+        assert client.history.ref_failed(later.ref) == client.history.ref_failed(bad.ref)
+        assert client.known_failure(good) is None
+        # deleting the tensors forgets their poison
+        ref = bad.ref
+        del bad, dep, later
+        client.flush()
+        client._send_deletes()
+        assert client.history.ref_failed(ref) == -1
+    # progress: a ping answered by every rank retires what they have passed
+    h = client.history
+    before = h.live_invocations()
+    client._last_ping = -1e9
+    client.operation_timeout, saved = 60.0, client.operation_timeout
+    try:
+        deadline = time.monotonic() + 10
+        client._watch()
+        while client._ping is not None and time.monotonic() < deadline:
+            time.sleep(0.01)
+            client._watch()
+    finally:
+        client.operation_timeout = saved
+    assert client._ping is None and h.min_completed() > 0
+    assert h.live_invocations() < max(before, 1)
+
+
 def test_remote_inspect_propagation(dm):
     @te.remote(propagate="inspect")
     def weird(x):
