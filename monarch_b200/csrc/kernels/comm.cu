@@ -452,6 +452,21 @@ extern "C" int mb200_peer_copy(void* dst, const void* src, int64_t nbytes, uint3
   return (int)cudaGetLastError();
 }
 
+// The same, and wait for it: one call for a one-sided transfer whose caller blocks until the
+// bytes have landed (RDMABuffer.read_into / write_from).  Waiting for the stream is waiting
+// for the transfer; no completion flag is involved.
+extern "C" int mb200_peer_copy_sync(void* dst, const void* src, int64_t nbytes, int n_blocks,
+                                    void* stream) {
+  if (nbytes <= 0) return 0;
+  const int grid = n_blocks > 0 ? n_blocks : comm_grid(nbytes / 16 + 1, 256 * 8, 296);
+  peer_copy_kernel<<<grid, 256, 0, ST(stream)>>>(reinterpret_cast<uint8_t*>(dst),
+                                                 reinterpret_cast<const uint8_t*>(src), nbytes,
+                                                 nullptr, 0, nullptr);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  return (int)cudaStreamSynchronize(ST(stream));
+}
+
 // Let kernels running on device `dev` dereference memory that lives on device `peer` (memory
 // opened through CUDA IPC or allocated by this process).  Idempotent.  Returns 0, or 1003 when
 // the two devices have no peer path.

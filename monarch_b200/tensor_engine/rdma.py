@@ -91,6 +91,9 @@ class _Manager:
         return None
 
 
+_hostname: Optional[str] = None
+
+
 def _as_bytes(t: torch.Tensor) -> torch.Tensor:
     if not t.is_contiguous():
         raise ValueError("RDMABuffer needs a contiguous tensor")
@@ -130,10 +133,13 @@ def _device_copy_ptr(dst_ptr: int, src_ptr: int, nbytes: int, dev_index: int) ->
     the bytes have landed: waiting for the stream is waiting for the transfer, so no
     completion flag has to be zeroed, published and read back per call."""
     from ..ops import kernels as K
+    if torch.cuda.current_device() == dev_index:       # the usual case: no device switch
+        K.check(K.lib().mb200_peer_copy_sync(dst_ptr, src_ptr, nbytes, 0, K.stream_ptr()),
+                "peer_copy")
+        return
     with torch.cuda.device(dev_index):
-        K.check(K.lib().mb200_peer_copy(dst_ptr, src_ptr, nbytes, None, 0, None, 0,
-                                        K.stream_ptr()), "peer_copy")
-        torch.cuda.current_stream().synchronize()
+        K.check(K.lib().mb200_peer_copy_sync(dst_ptr, src_ptr, nbytes, 0, K.stream_ptr()),
+                "peer_copy")
 
 
 def _device_copy(dst: torch.Tensor, src: torch.Tensor) -> None:
@@ -204,8 +210,11 @@ class RDMABuffer:
         return env
 
     def _same_host(self) -> bool:
-        import socket
-        return self._info["host"] == socket.gethostname()
+        global _hostname
+        if _hostname is None:
+            import socket
+            _hostname = socket.gethostname()
+        return self._info["host"] == _hostname
 
     def _peer_pointer(self, reader_device: int) -> int:
         """Address, valid for kernels of ``reader_device`` in this process, of byte 0 of the
