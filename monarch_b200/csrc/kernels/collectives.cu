@@ -206,6 +206,13 @@ struct ReduceArgs {
   uint32_t epoch;
   unsigned int* counter;
   int* status;
+  // one-launch form for small tensors: the kernel first copies stage_bytes from stage_src to
+  // this rank's staging (stage_dst) and publishes `epoch` in wait_slot itself.  The blocks
+  // then wait for that flag too, so the grid must be co-resident (the launcher caps it).
+  const uint8_t* stage_src;
+  uint8_t* stage_dst;
+  int64_t stage_bytes;
+  unsigned int* stage_counter;
 };
 
 template <typename T, int OP>
@@ -213,6 +220,17 @@ __global__ void __launch_bounds__(256) coll_reduce_kernel(const ReduceArgs a) {
   using V = VT<T>;
   using Acc = typename V::Acc;
   __shared__ int sh_ok;
+  if (a.stage_src != nullptr) {
+    const int64_t sstride = (int64_t)gridDim.x * blockDim.x;
+    const int64_t t0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t nvec = a.stage_bytes >> 4;       // both pointers are 16-byte aligned
+    for (int64_t v = t0; v < nvec; v += sstride)
+      reinterpret_cast<uint4*>(a.stage_dst)[v] = reinterpret_cast<const uint4*>(a.stage_src)[v];
+    for (int64_t b = (nvec << 4) + t0; b < a.stage_bytes; b += sstride)
+      a.stage_dst[b] = a.stage_src[b];
+    if (last_block_done(a.stage_counter))
+      signal_all(a.flags, a.world, a.rank, a.wait_slot, a.epoch, threadIdx.x);
+  }
   if (!block_wait_all(a.flags.p[a.rank], a.world, a.wait_slot, a.epoch, a.status, &sh_ok)) {
     if (a.signal_slot >= 0) last_block_done(a.counter);
     return;
@@ -404,9 +422,18 @@ extern "C" int mb200_coll_reduce(const void* const* in_ptrs, const void* mc_in,
                                  float scale, int apply_scale, const void* const* flag_ptrs,
                                  int rank, int world, int wait_slot, int signal_slot,
                                  uint32_t epoch, unsigned int* counter, int n_blocks, int* status,
-                                 void* stream) {
+                                 void* stream, const void* stage_src, void* stage_dst,
+                                 int64_t stage_bytes, unsigned int* stage_counter) {
   if (world > kMaxRanks || world < 1 || hi < lo) return 1001;
+  if (stage_src != nullptr &&
+      (((reinterpret_cast<uintptr_t>(stage_src) | reinterpret_cast<uintptr_t>(stage_dst)) & 15) != 0 ||
+       stage_counter == nullptr || stage_bytes < 0))
+    return 1001;
   ReduceArgs a{};
+  a.stage_src = reinterpret_cast<const uint8_t*>(stage_src);
+  a.stage_dst = reinterpret_cast<uint8_t*>(stage_dst);
+  a.stage_bytes = stage_bytes;
+  a.stage_counter = stage_counter;
   a.in = peers_of(in_ptrs, world);
   a.out_peers = peers_of(out_ptrs, world);
   a.mc_in = mc_in;
@@ -425,7 +452,8 @@ extern "C" int mb200_coll_reduce(const void* const* in_ptrs, const void* mc_in,
   a.epoch = epoch;
   a.counter = counter;
   a.status = status;
-  const int grid = n_blocks > 0 ? n_blocks : grid_for(hi - lo, 256 * 4, 296);
+  int grid = n_blocks > 0 ? n_blocks : grid_for(hi - lo, 256 * 4, 296);
+  if (stage_src != nullptr && grid > 148) grid = 148;   // its blocks wait on one another
   cudaStream_t st = ST(stream);
   switch (dtype) {
     case kF32: return launch_reduce_op<float>(op, grid, st, a);

@@ -124,7 +124,7 @@ _OPTIONAL: dict[str, list] = {
                        _vp],
     "mb200_coll_stage": [_vp, _vp, _i64, _vp, _i, _i, _i, ctypes.c_uint32, _vp, _i, _vp],
     "mb200_coll_reduce": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i, _i, _f, _i, _vp, _i, _i,
-                          _i, _i, ctypes.c_uint32, _vp, _i, _vp, _vp],
+                          _i, _i, ctypes.c_uint32, _vp, _i, _vp, _vp, _vp, _vp, _i64, _vp],
     "mb200_coll_gather": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, ctypes.c_uint32, _i, _vp, _vp],
     "mb200_bounds_enabled": [],
     "mb200_bounds_reset": [_vp],

@@ -96,6 +96,9 @@ class MeshComm:
             K.bounds_register(self.mc_ptr, self.buffer_bytes(self.cap), self.device)
         self._flag_ptrs = _ptr_array(self.ptrs)
         self._counter = torch.zeros(8, dtype=torch.int32, device=self.device)
+        self._counter_p = self._counter.data_ptr()
+        self._status_p = K.status_word(self.device).data_ptr()
+        self._at_cache: dict = {}
         self.epoch = 0
         self._barrier_epoch = 0
         # below this many bytes an all-reduce is one pass in which every rank combines the
@@ -162,17 +165,24 @@ class MeshComm:
         return self.epoch, base, base + self.cap
 
     def _at(self, off: int):
-        return _ptr_array([p + off for p in self.ptrs])
+        arr = self._at_cache.get(off)
+        if arr is None:          # the offsets are the few region starts of the two halves
+            arr = _ptr_array([p + off for p in self.ptrs])
+            if len(self._at_cache) < 1024:
+                self._at_cache[off] = arr
+        return arr
 
     def _stage(self, src_ptr: int, nbytes: int, in_off: int, epoch: int) -> None:
         K.check(K.lib().mb200_coll_stage(self.ptrs[self.rank] + in_off, src_ptr, nbytes,
                                          self._flag_ptrs, self.rank, self.world, SLOT_STAGED,
-                                         epoch, self._counter.data_ptr(), 0, K.stream_ptr()),
+                                         epoch, self._counter_p, 0, K.stream_ptr()),
                 "coll_stage")
         self.launches += 1
 
     def _reduce(self, in_off, out_off, out_local, lo, hi, valid, dt, op, scale, epoch,
-                to_peers: bool) -> None:
+                to_peers: bool, stage_src: Optional[int] = None, stage_bytes: int = 0) -> None:
+        """``stage_src``: the kernel stages that many bytes itself before it combines (one
+        launch instead of two; for tensors small enough that its grid is co-resident)."""
         mc_ok = self.mc_ptr and op == 0 and dt in (0, 1, 2)
         K.check(K.lib().mb200_coll_reduce(
             self._at(in_off), (self.mc_ptr + in_off) if mc_ok else None,
@@ -180,8 +190,10 @@ class MeshComm:
             (self.mc_ptr + out_off) if (to_peers and self.mc_ptr) else None,
             out_local, lo, hi, valid, dt, op, float(scale if scale is not None else 1.0),
             0 if scale is None else 1, self._flag_ptrs, self.rank, self.world, SLOT_STAGED,
-            SLOT_RESULT if to_peers else -1, epoch, self._counter.data_ptr() + 4, 0,
-            self._status(), K.stream_ptr()), "coll_reduce")
+            SLOT_RESULT if to_peers else -1, epoch, self._counter_p + 4, 0,
+            self._status_p, K.stream_ptr(), stage_src,
+            (self.ptrs[self.rank] + in_off) if stage_src is not None else None, stage_bytes,
+            self._counter_p if stage_src is not None else None), "coll_reduce")
         self.launches += 1
 
     def _gather(self, src_off: Sequence[int], dst_off: Sequence[int], nbytes: Sequence[int],
@@ -217,11 +229,13 @@ class MeshComm:
         sp, rp = src.data_ptr(), res.data_ptr()
         for off, nb in plan_chunks(src.numel() * src.element_size(), self.cap):
             epoch, in_off, out_off = self._next()
-            self._stage(sp + off, nb, in_off, epoch)
             nvec = (nb + 15) // 16
             if nb <= self.one_shot_bytes or self.world == 1:
-                self._reduce(in_off, out_off, rp + off, 0, nvec, nb, dt, opc, scale, epoch, False)
+                # one launch: stage, publish, wait for the peers, combine everything
+                self._reduce(in_off, out_off, rp + off, 0, nvec, nb, dt, opc, scale, epoch, False,
+                             stage_src=sp + off, stage_bytes=nb)
             else:
+                self._stage(sp + off, nb, in_off, epoch)
                 per = (nvec + self.world - 1) // self.world
                 lo = min(nvec, per * self.rank)
                 self._reduce(in_off, out_off, None, lo, min(nvec, lo + per), 0, dt, opc, scale,

@@ -48,6 +48,7 @@ class SymmBuffer:
         if os.environ.get("MB200_NVLS", "1") == "0":
             self.multicast_ptr = 0
         self._elt = self.tensor.element_size()
+        self._ptr_arrays: dict = {}
         nbytes = numel * self._elt
         for p in self.ptrs:                     # checked builds: the ranges kernels may touch
             K.bounds_register(p, nbytes, device)
@@ -56,8 +57,13 @@ class SymmBuffer:
 
     def ptrs_at(self, elem_offset: int):
         """ctypes array of every rank's address of element ``elem_offset``."""
-        off = elem_offset * self._elt
-        return ptr_array([p + off for p in self.ptrs])
+        arr = self._ptr_arrays.get(elem_offset)
+        if arr is None:       # trainers ask for the same few offsets (buckets, units) every step
+            off = elem_offset * self._elt
+            arr = ptr_array([p + off for p in self.ptrs])
+            if len(self._ptr_arrays) < 4096:
+                self._ptr_arrays[elem_offset] = arr
+        return arr
 
     def mc_at(self, elem_offset: int) -> Optional[int]:
         """Multicast address of element ``elem_offset`` (None without NVLS): a
