@@ -79,6 +79,8 @@ class Future(Generic[R]):
                 self._cond.notify_all()
 
     def get(self, timeout: Optional[float] = None) -> R:
+        if self._value is not _UNSET:        # settled: no lock needed to read it
+            return self._value
         self._run(timeout)
         if self._exc is not None:
             raise self._exc

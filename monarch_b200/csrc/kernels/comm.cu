@@ -467,6 +467,13 @@ extern "C" int mb200_peer_copy_sync(void* dst, const void* src, int64_t nbytes, 
   return (int)cudaStreamSynchronize(ST(stream));
 }
 
+// One asynchronous device-to-device copy on the copy engines (either pointer may be a mapping
+// of a peer's memory): the SM-free way to move a shard when GEMMs own the SMs.
+extern "C" int mb200_memcpy_d2d_async(void* dst, const void* src, int64_t nbytes, void* stream) {
+  if (nbytes <= 0) return 0;
+  return (int)cudaMemcpyAsync(dst, src, (size_t)nbytes, cudaMemcpyDeviceToDevice, ST(stream));
+}
+
 // Let kernels running on device `dev` dereference memory that lives on device `peer` (memory
 // opened through CUDA IPC or allocated by this process).  Idempotent.  Returns 0, or 1003 when
 // the two devices have no peer path.

@@ -317,10 +317,11 @@ def main() -> int:
     outs = {}
     # "fused": reductions in the switch where the fabric has multicast; "fused-p2p": the same
     # kernels on plain peer loads (fp32 sum of all ranks, no intermediate rounding)
-    for mode in ("fused", "fused-p2p", "fused-gemm", "nccl"):
+    # "fused-dma": parameter shards gathered by the copy engines instead of a pull kernel
+    for mode in ("fused", "fused-p2p", "fused-gemm", "fused-dma", "nccl"):
         os.environ["MB200_NVLS"] = "0" if mode == "fused-p2p" else "1"
         st = FSDPParamStore(layout, dev, seed=3, init_std=0.05, comm=mode.split("-")[0],
-                            gather="gemm" if mode.endswith("-gemm") else "prefetch",
+                            gather={"fused-gemm": "gemm", "fused-dma": "dma"}.get(mode, "prefetch"),
                             gather_chunk=1 << 15)
         os.environ.pop("MB200_NVLS", None)
         eng = LlamaEngine(cfg, st, S)
@@ -359,6 +360,9 @@ def main() -> int:
     assert rel_g < 2e-2, f"in-GEMM gathering diverges from prefetch gathering: {rel_g}"
     for la, lb in zip(outs["fused-gemm"][1], outs["fused"][1]):
         assert abs(la - lb) < 2e-2 * abs(lb), (outs["fused-gemm"][1], outs["fused"][1])
+    rel_d = _rel(outs["fused-dma"][0], outs["fused"][0])
+    assert rel_d < 2e-2, f"copy-engine gathering diverges from prefetch gathering: {rel_d}"
+    results["fsdp_dma_gather_rel_diff"] = rel_d
     results["fsdp_gemm_gather_rel_diff"] = rel_g
     results["fsdp_gemm_gather_losses"] = outs["fused-gemm"][1]
     results["fsdp_losses"] = outs["fused"][1]
