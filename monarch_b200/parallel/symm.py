@@ -45,7 +45,12 @@ class SymmBuffer:
         # NVSwitch multicast mapping of the same buffers (0 when the fabric or the driver
         # has no NVLS support): the target of this package's multimem.ld_reduce / multimem.st
         self.multicast_ptr: int = int(getattr(self.handle, "multicast_ptr", 0) or 0)
-        if os.environ.get("MB200_NVLS", "1") == "0":
+        # MB200_NVLS: "0" never, "1" whenever there is a mapping, unset: from 4 ranks up.
+        # With two ranks a rank reads one peer either way and the trip through the switch's
+        # reduction unit only adds latency (256 MiB all-reduce: 645 GB/s on plain peer loads,
+        # 379 GB/s through multimem); with four the in-switch sum wins (649 against 613).
+        nvls = os.environ.get("MB200_NVLS", "auto")
+        if nvls == "0" or (nvls != "1" and self.world < 4):
             self.multicast_ptr = 0
         self._elt = self.tensor.element_size()
         self._ptr_arrays: dict = {}

@@ -58,6 +58,9 @@ def main() -> int:
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
+    # the multimem variants are checked and measured at every world size (the package's own
+    # default turns them on from 4 ranks up)
+    os.environ["MB200_NVLS"] = "1"
     bench = "--bench" in sys.argv
     lib = K.lib()
     status = K.status_word(dev)
@@ -323,7 +326,7 @@ def main() -> int:
         st = FSDPParamStore(layout, dev, seed=3, init_std=0.05, comm=mode.split("-")[0],
                             gather={"fused-gemm": "gemm", "fused-dma": "dma"}.get(mode, "prefetch"),
                             gather_chunk=1 << 15)
-        os.environ.pop("MB200_NVLS", None)
+        os.environ["MB200_NVLS"] = "1"
         eng = LlamaEngine(cfg, st, S)
         p_init = st.full_params().float()
         losses = []
