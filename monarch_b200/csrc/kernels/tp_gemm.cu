@@ -60,10 +60,19 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 }
 
 // out[r, c] = sum_s staging[s][r][c] (+ residual[r, c]); fp32 accumulation, bf16 out.
+// With epoch != 0 the kernel is also the barrier between the GEMMs that filled the staging
+// slots and this sum: block 0 tells every peer that this rank's GEMM has finished (true by
+// stream order), every block waits (bounded) until all peers have said the same.
 __global__ void __launch_bounds__(256)
     rs_finish_kernel(const __nv_bfloat16* __restrict__ staging, int world, int rows, int N, int ld,
                      const __nv_bfloat16* __restrict__ residual, int ldr,
-                     __nv_bfloat16* __restrict__ out, int ldo) {
+                     __nv_bfloat16* __restrict__ out, int ldo, Peers flags, int rank, int slot,
+                     uint32_t epoch, int* status) {
+  if (epoch != 0) {
+    __shared__ int sh_ok;
+    if (blockIdx.x == 0) signal_all(flags, world, rank, slot, epoch, threadIdx.x);
+    if (!block_wait_all(flags.p[rank], world, slot, epoch, status, &sh_ok)) return;
+  }
   const int vec_per_row = N >> 3;
   const long long total = (long long)rows * vec_per_row;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -208,8 +217,39 @@ extern "C" int mb200_gemm_rs(const void* A, const void* B, int M, int N, int K, 
   return launch_gemm(ta, tb, p, a_mn, b_mn, grid, st);
 }
 
+static int rs_finish_launch(const void* staging, int world, int rows, int N, int ld,
+                            const void* residual, int ldr, void* out, int ldo,
+                            const void* const* flag_ptrs, int rank, int slot, uint32_t epoch,
+                            int* status, void* stream);
+
+static Peers tp_peers(const void* const* ptrs, int world) {
+  Peers p{};
+  if (ptrs != nullptr)
+    for (int i = 0; i < world && i < kMaxRanks; ++i) p.p[i] = const_cast<void*>(ptrs[i]);
+  return p;
+}
+
 extern "C" int mb200_rs_finish(const void* staging, int world, int rows, int N, int ld,
                                const void* residual, int ldr, void* out, int ldo, void* stream) {
+  return rs_finish_launch(staging, world, rows, N, ld, residual, ldr, out, ldo, nullptr, 0, 0, 0,
+                          nullptr, stream);
+}
+
+// The sum, preceded inside the same launch by the cross-rank barrier that orders it after
+// every rank's mb200_gemm_rs (flag slot `slot`, a fresh `epoch` per call).
+extern "C" int mb200_rs_finish_sync(const void* staging, int world, int rows, int N, int ld,
+                                    const void* residual, int ldr, void* out, int ldo,
+                                    const void* const* flag_ptrs, int rank, int slot,
+                                    uint32_t epoch, int* status, void* stream) {
+  if (flag_ptrs == nullptr || epoch == 0 || world > kMaxRanks) return 1001;
+  return rs_finish_launch(staging, world, rows, N, ld, residual, ldr, out, ldo, flag_ptrs, rank,
+                          slot, epoch, status, stream);
+}
+
+static int rs_finish_launch(const void* staging, int world, int rows, int N, int ld,
+                            const void* residual, int ldr, void* out, int ldo,
+                            const void* const* flag_ptrs, int rank, int slot, uint32_t epoch,
+                            int* status, void* stream) {
   if ((N & 7) || (ld & 7) || (ldo & 7) || (residual && (ldr & 7))) return 1001;
   if (rows <= 0 || N <= 0) return 0;
   const long long total = (long long)rows * (N >> 3);
@@ -219,6 +259,7 @@ extern "C" int mb200_rs_finish(const void* staging, int world, int rows, int N, 
   rs_finish_kernel<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(staging), world, rows, N, ld,
       reinterpret_cast<const __nv_bfloat16*>(residual), ldr,
-      reinterpret_cast<__nv_bfloat16*>(out), ldo);
+      reinterpret_cast<__nv_bfloat16*>(out), ldo,
+      tp_peers(flag_ptrs, world), rank, slot, epoch, status);
   return (int)cudaGetLastError();
 }

@@ -113,6 +113,8 @@ _OPTIONAL: dict[str, list] = {
                         _vp, _vp],
     "mb200_gemm_rs": [_vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _i, _i, _i, _i, _vp, _vp],
     "mb200_rs_finish": [_vp, _i, _i, _i, _i, _vp, _i, _vp, _i, _vp],
+    "mb200_rs_finish_sync": [_vp, _i, _i, _i, _i, _vp, _i, _vp, _i, _vp, _i, _i, ctypes.c_uint32,
+                             _vp, _vp],
     "mb200_moe_route": [_vp, _i, _i, _i, _vp, _vp, _vp],
     "mb200_moe_gather_gemm": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp,
                               _vp, ctypes.c_uint32, _vp, _i, _i, _i, _vp, _i, _i, _vp, _vp],

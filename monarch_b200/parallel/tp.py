@@ -9,9 +9,13 @@ scattered back to T/tp rows per rank.  With ``comm="fused"`` both are one kernel
 * ``ag_gemm``  = ``mb200_ag_a_gemm``: copy CTAs pull the peers' rows over NVLink while the
   tcgen05 GEMM CTAs consume row blocks as they land; the gathered input stays resident
   for the weight-gradient GEMM of the backward pass.
-* ``gemm_rs``  = ``mb200_gemm_rs`` + ``mb200_rs_finish``: the GEMM epilogue stores each bf16
-  partial tile straight into the owner rank's staging slot; after a flag barrier the owner
-  sums the slots in fp32 together with the residual.
+* ``gemm_rs``  = ``mb200_gemm_rs`` + ``mb200_rs_finish_sync``: the GEMM epilogue stores each
+  bf16 partial tile straight into the owner rank's staging slot; the owner's next launch is
+  the flag barrier and the fp32 sum of the slots together with the residual.
+
+The cross-rank handshakes ride in launches that do work anyway (the copy of the local rows
+publishes "rows in place", the GEMM's copy CTAs wait for it; the sum kernel signals and waits
+for "tiles stored"): four launches per gather-GEMM / GEMM-scatter pair instead of six.
 
 ``comm="nccl"`` runs the same schedule with torch.distributed collectives and separate
 GEMMs (the library baseline; under gloo it is the CPU test path).
@@ -38,6 +42,8 @@ class TPComm:
     """Buffers, flags and the two fused primitives of one tensor-parallel group."""
 
     CHUNK = 1 << 16  # elements per readiness flag of a gathered activation
+    SLOT_ROWS = 2    # flag slot: "my rows of the activation are in my symmetric buffer"
+    SLOT_TILES = 3   # flag slot: "my GEMM has stored its partial tiles"
 
     def __init__(self, group, device, rows_local: int, d: int, comm: str = "fused"):
         self.group = group
@@ -52,11 +58,13 @@ class TPComm:
         self._n_ag = 0
         self._n_rs = 0
         self._epoch = 0
+        self._rs_epoch = 0
         if comm == "fused":
             from .symm import FlagArray, SymmBuffer
             n = rows_local * d
             # two shard buffers / two staging buffers used alternately: a buffer is written
-            # again only after a barrier that every rank reaches after its last read of it
+            # again only after a flag handshake that every rank passes after its last read of
+            # it (the handshake of the call in between)
             self._shard = [SymmBuffer(n, bf16, self.device, group, zero=False) for _ in range(2)]
             self._staging = [SymmBuffer(self.world * n, bf16, self.device, group)
                              for _ in range(2)]
@@ -76,15 +84,27 @@ class TPComm:
             return ops.gemm(x_full, w, b_mn=b_mn), x_full
         sb = self._shard[self._n_ag & 1]
         self._n_ag += 1
-        sb.tensor.view(self.rows_local, d).copy_(x_local)
-        self._flags.barrier(0)  # every rank's rows are in place
         self._epoch += 1
+        xl = x_local.contiguous()
+        if xl.data_ptr() % 16 == 0:
+            # one launch copies this rank's rows into its symmetric buffer and publishes
+            # "rows in place" on every rank; the copy CTAs of the GEMM launch wait for all
+            # ranks' flags before they pull (no separate barrier launch)
+            K.check(K.lib().mb200_coll_stage(
+                sb.tensor.data_ptr(), xl.data_ptr(), xl.numel() * 2, self._flags.ptrs, self.rank,
+                self.world, self.SLOT_ROWS, self._epoch, self._flags.counter.data_ptr(), 0,
+                K.stream_ptr()), "coll_stage")
+            wait_slot, wait_epoch = self.SLOT_ROWS, self._epoch
+        else:
+            sb.tensor.view(self.rows_local, d).copy_(xl)
+            self._flags.barrier(0)  # every rank's rows are in place
+            wait_slot, wait_epoch = 0, 0
         out = torch.empty(T, N, dtype=bf16, device=x_local.device)
         K.check(K.lib().mb200_ag_a_gemm(
             x_full.data_ptr(), sb.ptrs_at(0), self.rows_local * d, self.rank, self.world, T, d,
             w.data_ptr(), w.stride(0), int(b_mn), N, out.data_ptr(), N, None, 0, self.CHUNK,
-            self._chunk_flags.data_ptr(), self._epoch, self._flags.my_ptr, 0, 0, 12,
-            K.status_word(self.device).data_ptr(), K.stream_ptr()), "ag_a_gemm")
+            self._chunk_flags.data_ptr(), self._epoch, self._flags.my_ptr, wait_slot, wait_epoch,
+            12, K.status_word(self.device).data_ptr(), K.stream_ptr()), "ag_a_gemm")
         return out, x_full
 
     # ------------------------------------------------------------ GEMM -> reduce-scatter
@@ -109,13 +129,15 @@ class TPComm:
             a.data_ptr(), w.data_ptr(), T, N, Kd, a.stride(0), w.stride(0), 0, int(b_mn),
             st.ptrs_at(0), self.world, self.rows_local, N, self.rank, K.gemm_impl(),
             K.status_word(self.device).data_ptr(), K.stream_ptr()), "gemm_rs")
-        self._flags.barrier(1)  # every rank's partial tiles have landed
+        # the sum's launch is also the barrier that says every rank's partial tiles have landed
+        self._rs_epoch += 1
         out = torch.empty(self.rows_local, N, dtype=bf16, device=a.device)
-        K.check(K.lib().mb200_rs_finish(
+        K.check(K.lib().mb200_rs_finish_sync(
             st.tensor.data_ptr(), self.world, self.rows_local, N, N,
             0 if residual_local is None else residual_local.data_ptr(),
             0 if residual_local is None else residual_local.stride(0), out.data_ptr(), N,
-            K.stream_ptr()), "rs_finish")
+            self._flags.ptrs, self.rank, self.SLOT_TILES, self._rs_epoch,
+            K.status_word(self.device).data_ptr(), K.stream_ptr()), "rs_finish")
         return out
 
     def all_reduce_(self, t: torch.Tensor) -> None:
