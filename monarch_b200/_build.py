@@ -222,7 +222,22 @@ def build_tensor_worker(force: bool = False) -> Path:
     return _build_torch_ext("_tensor_worker", CSRC / "tensor_worker" / "worker_core.cpp", force)
 
 
+def build_allocator(force: bool = False) -> Path:
+    """The native process-allocator daemon (``csrc/tools/process_allocator.cpp``): a
+    standalone executable, ``monarch_b200/tools/process_allocator_native``."""
+    src = CSRC / "tools" / "process_allocator.cpp"
+    target = ROOT / "tools" / "process_allocator_native"
+    flags = ["-O2", "-std=c++17", "-pthread", "-Wall"]
+    stamp = _stamp([src], flags)
+    if not force and _up_to_date(target, stamp):
+        return target
+    _run([CXX, *flags, str(src), "-o", str(target)])
+    _write_stamp(target, stamp)
+    return target
+
+
 def build_all(force: bool = False) -> None:
+    build_allocator(force)
     build_kernels(force)
     build_kernels(force, checked=True)
     build_native(force)
@@ -236,5 +251,6 @@ if __name__ == "__main__":
     for w in what:
         {"kernels": build_kernels, "kernels_checked": lambda f: build_kernels(f, checked=True),
          "native": build_native, "gradgen": build_gradgen,
-         "tensor_worker": build_tensor_worker, "all": build_all}[w](force)
+         "tensor_worker": build_tensor_worker, "allocator": build_allocator,
+         "all": build_all}[w](force)
         print("built", w)

@@ -63,13 +63,23 @@ def _reachable(addr: str) -> bool:
         return False
 
 
+def _daemon_command(addr: str) -> list:
+    """The allocator daemon for ``addr``: the native executable where it can be built
+    (``MB200_ALLOCATOR_DAEMON=python`` forces the Python one; both speak one protocol)."""
+    if os.environ.get("MB200_ALLOCATOR_DAEMON", "native") != "python":
+        from .process_allocator import native_command
+        cmd = native_command(addr)
+        if cmd is not None:
+            return cmd
+    return [sys.executable, "-m", "monarch_b200.tools.process_allocator", "--addr", addr]
+
+
 def _start_local(n: int) -> tuple:
     addrs, pids = [], []
     for _ in range(n):
         port = _free_port()
         addr = f"tcp!127.0.0.1:{port}"
-        p = subprocess.Popen([sys.executable, "-m", "monarch_b200.tools.process_allocator",
-                              "--addr", addr], stdout=subprocess.DEVNULL,
+        p = subprocess.Popen(_daemon_command(addr), stdout=subprocess.DEVNULL,
                              stderr=subprocess.DEVNULL, start_new_session=True)
         addrs.append(addr)
         pids.append(p.pid)

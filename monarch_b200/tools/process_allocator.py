@@ -13,7 +13,8 @@ variables pass (prefixes ``HYPERACTOR_``, ``MONARCH_``, ``MB200_`` and the rank/
 names in ``ENV_ALLOW``); a request that names a program (``argv``) or a directory (``cwd``)
 is refused.  The default bind is the loopback interface; to serve other hosts bind another
 address and set ``MB200_ALLOCATOR_TOKEN`` on both sides: with a token configured, requests
-without the same token are refused.  It may send ``{"signal": n}``.
+without the same token are refused.  It may send ``{"signal": n}``.  ``--native`` runs the
+same daemon as a standalone executable (``csrc/tools/process_allocator.cpp``).
 Heartbeats ``{"hb": 1}`` flow both ways every ``--heartbeat`` seconds; when the client has
 been silent for 3 intervals, or its connection drops, the proc is killed (SIGTERM, then
 SIGKILL): a host never keeps orphans of a vanished client.
@@ -209,6 +210,25 @@ def serve(addr: str, heartbeat: float = 5.0, ready=None, program=None, token=Non
         _Session(conn, peer, heartbeat, sessions, program, token).start()
 
 
+def native_daemon() -> str | None:
+    """Path of the native daemon (``csrc/tools/process_allocator.cpp``, the same protocol in
+    a standalone executable), built on demand; None where no compiler is available."""
+    try:
+        from .. import _build
+        return str(_build.build_allocator())
+    except Exception:  # noqa: BLE001 - no compiler on this host: the Python daemon serves
+        return None
+
+
+def native_command(addr: str, heartbeat: float = 5.0, program=None) -> list | None:
+    """Command line that runs the native daemon with this module's defaults."""
+    exe = native_daemon()
+    if exe is None:
+        return None
+    return [exe, "--addr", addr, "--heartbeat", str(heartbeat), "--program",
+            shlex.join(list(program) if program else default_program())]
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("--addr", default="tcp!127.0.0.1:26600")
@@ -216,8 +236,17 @@ def main(argv=None) -> int:
     ap.add_argument("--program", default=None,
                     help="command line of the proc this daemon starts for its clients "
                          "(default: this interpreter -m monarch_b200.actor.bootstrap_main)")
+    ap.add_argument("--native", action="store_true",
+                    help="run the native daemon (same protocol, no Python in the serving path)")
     a = ap.parse_args(argv)
-    serve(a.addr, a.heartbeat, program=shlex.split(a.program) if a.program else None)
+    program = shlex.split(a.program) if a.program else None
+    if a.native:
+        cmd = native_command(a.addr, a.heartbeat, program)
+        if cmd is None:
+            print("process_allocator: the native daemon could not be built here", file=sys.stderr)
+            return 2
+        os.execv(cmd[0], cmd)
+    serve(a.addr, a.heartbeat, program=program)
     return 0
 
 

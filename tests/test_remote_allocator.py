@@ -22,10 +22,17 @@ class Where(Actor):
         return os.environ.get(k)
 
 
-@pytest.fixture()
-def job(tmp_path, monkeypatch):
+@pytest.fixture(params=["native", "python"])
+def job(tmp_path, monkeypatch, request):
     monkeypatch.setenv("MB200_JOBS_DIR", str(tmp_path))
+    monkeypatch.setenv("MB200_ALLOCATOR_DAEMON", request.param)
+    if request.param == "native":
+        from monarch_b200.tools.process_allocator import native_daemon
+        if native_daemon() is None:
+            pytest.skip("no compiler for the native daemon")
     j = cli.create("t", hosts=2)
+    exe = open(f"/proc/{j['pids'][0]}/cmdline", "rb").read().split(b"\0")[0].decode()
+    assert exe.endswith("process_allocator_native") == (request.param == "native"), exe
     yield j
     try:
         cli.stop("t")
@@ -85,20 +92,38 @@ def _ask(port, req):
     return {}
 
 
-def test_daemon_runs_only_its_own_program_and_checks_the_token():
+@pytest.mark.parametrize("daemon", ["native", "python"])
+def test_daemon_runs_only_its_own_program_and_checks_the_token(daemon):
     """A client cannot name the program, the working directory or arbitrary environment, and
     with a token configured a request without it is refused."""
     import threading
     from monarch_b200.tools import process_allocator as pa
-    ports = []
-    started = threading.Event()
     prog = [sys.executable, "-c", "import os,sys; print(os.environ.get('MB200_X'), "
             "os.environ.get('LD_PRELOAD'), os.environ.get('MB200_ALLOCATOR_TOKEN')); sys.exit(7)"]
+    if daemon == "native":
+        cmd = pa.native_command("tcp!127.0.0.1:0", 1.0, prog)
+        if cmd is None:
+            pytest.skip("no compiler for the native daemon")
+        proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, text=True,
+                                env=dict(os.environ, MB200_ALLOCATOR_TOKEN="s3cret"))
+        try:
+            line = proc.stdout.readline()            # "... listening on tcp!127.0.0.1:PORT"
+            port = int(line.rsplit(":", 1)[1])
+            _check_daemon_policy(port, pa)
+        finally:
+            proc.terminate()
+            proc.wait(10)
+        return
+    ports = []
+    started = threading.Event()
     threading.Thread(target=pa.serve, args=("tcp!127.0.0.1:0",), daemon=True,
                      kwargs=dict(heartbeat=1.0, ready=lambda p: (ports.append(p), started.set()),
                                  program=prog, token="s3cret")).start()
     assert started.wait(10)
-    port = ports[0]
+    _check_daemon_policy(ports[0], pa)
+
+
+def _check_daemon_policy(port, pa):
     assert _ask(port, {"start": 1, "env": {}})["exit"] == 126                 # no token
     assert _ask(port, {"start": 1, "token": "wrong"})["exit"] == 126
     r = _ask(port, {"start": 1, "token": "s3cret", "argv": ["/bin/sh", "-c", "id"]})
