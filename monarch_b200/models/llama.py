@@ -196,6 +196,24 @@ class LocalParamStore:
         init_params_(layout, self.master, seed, init_std)
         self.params.copy_(self.master)
         self.step_count = 0
+        # AdamW inside backward (see set_hyper): hyper-parameters of the coming step, the
+        # side stream the per-unit updates run on, how many units this step has updated
+        self._hyper: Optional[dict] = None
+        self._opt_stream = None
+        self._updating = False
+        self._updated_units = 0
+
+    def set_hyper(self, **kw) -> None:
+        """Hyper-parameters of the coming step.  Once they are known before the backward
+        pass (``Trainer.step`` sets them), every unit's AdamW update is issued on a side
+        stream as soon as that unit's gradients are final: the optimizer is bound by HBM
+        bandwidth (28 bytes per parameter), the GEMMs of the remaining backward by the
+        tensor cores, so the two overlap instead of the optimizer running alone at the end of
+        the step.  The same element-wise kernel runs either way: results are bit-identical.
+        ``optimizer_step`` then only joins the side stream."""
+        if self._hyper is None:
+            self._hyper = dict(lr=1e-4, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1, grad_scale=1.0)
+        self._hyper.update(kw)
 
     # --- unit access -----------------------------------------------------------------
     def unit_params(self, ui: int) -> dict:
@@ -206,12 +224,15 @@ class LocalParamStore:
         u = self.layout.units[ui]
         return self.layout.views(u, self.grads[u.offset: u.offset + u.size])
 
-    # --- hooks (no-ops for a resident store) -----------------------------------------
+    # --- hooks (a resident store has nothing to gather) ------------------------------
     def begin_step(self):
-        pass
+        self._updating = self._hyper is not None and self.device.type == "cuda"
+        self._updated_units = 0
+        if self._updating and self._opt_stream is None:
+            self._opt_stream = torch.cuda.Stream(device=self.device)
 
     def begin_eval(self):
-        pass
+        self._updating = False
 
     def pre_forward(self, ui: int):
         pass
@@ -223,10 +244,28 @@ class LocalParamStore:
         pass
 
     def post_backward(self, ui: int):
-        pass
+        if not self._updating:
+            return
+        u = self.layout.units[ui]
+        lo, hi = u.offset, u.offset + u.size
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream())
+        self._opt_stream.wait_event(ev)          # the unit's gradients are final
+        with torch.cuda.stream(self._opt_stream):
+            ops.adamw_(self.master[lo:hi], self.m[lo:hi], self.v[lo:hi], self.grads[lo:hi],
+                       self.params[lo:hi], step=self.step_count + 1, **self._hyper)
+        self._updated_units += 1
 
     def optimizer_step(self, lr, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1, grad_scale=1.0):
         self.step_count += 1
+        if self._updating and self._updated_units == len(self.layout.units):
+            # issued unit by unit during backward with the values given to set_hyper; these
+            # are recorded for the next step (the contract of the sharded stores)
+            self._updating = False
+            torch.cuda.current_stream().wait_stream(self._opt_stream)
+            self.set_hyper(lr=lr, beta1=beta1, beta2=beta2, eps=eps, wd=wd, grad_scale=grad_scale)
+            return
+        self._updating = False
         ops.adamw_(self.master, self.m, self.v, self.grads, self.params, lr=lr, beta1=beta1,
                    beta2=beta2, eps=eps, wd=wd, step=self.step_count, grad_scale=grad_scale)
 

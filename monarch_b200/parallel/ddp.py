@@ -95,6 +95,14 @@ class DDPParamStore(LocalParamStore):
                         dist.all_reduce(g, group=self.group)
                         if self.reduce_scale != 1.0:
                             g.mul_(self.reduce_scale)
+            if self._updating:
+                # hyper-parameters known before backward (set_hyper): the unit's AdamW update
+                # follows its all-reduce on the comm stream, under the rest of the backward
+                u = self.layout.units[ui]
+                lo, hi = u.offset, u.offset + u.size
+                ops.adamw_(self.master[lo:hi], self.m[lo:hi], self.v[lo:hi], self.grads[lo:hi],
+                           self.params[lo:hi], step=self.step_count + 1, **self._hyper)
+                self._updated_units += 1
 
     def optimizer_step(self, lr, **kw):
         if self._comm_stream is not None:
