@@ -17,6 +17,8 @@
 #include <torch/extension.h>
 #include <torch/csrc/Dtype.h>
 
+#include "messages.h"
+
 #include <ATen/core/dispatch/Dispatcher.h>
 #include <c10/core/Stream.h>
 #include <c10/core/impl/VirtualGuardImpl.h>
@@ -36,42 +38,10 @@
 #include <vector>
 
 namespace py = pybind11;
+using namespace mb::tensor;
 
 namespace {
 
-struct RemoteErr {
-  int64_t seq, rank;
-  std::string func, text, tb;
-  int64_t dependent_of;  // -1: original failure
-};
-using ErrPtr = std::shared_ptr<RemoteErr>;
-using Value = std::variant<std::monostate, at::Tensor, ErrPtr, py::object>;
-
-struct Arg {           // one positional or keyword argument of a recorded call
-  enum Kind { Const, RefOne, RefList } kind = Const;
-  c10::IValue constant;
-  std::vector<int64_t> refs;
-  std::string name;    // keyword name ("" = positional)
-};
-
-struct OpCall {
-  int64_t seq = 0;
-  std::vector<int64_t> results, mutates;
-  std::string name;
-  c10::OperatorHandle op;
-  std::vector<Arg> args;
-  int64_t stream = 0;
-  // torch.cuda.Stream to enter around the launch (borrowed: the core's stream table owns
-  // it), or null when the executing thread's current stream is already the right one
-  PyObject* py_stream = nullptr;
-  explicit OpCall(c10::OperatorHandle h) : op(std::move(h)) {}
-};
-
-struct RecItem {
-  std::unique_ptr<OpCall> call;  // null: not an operator call -> Python fallback
-  size_t index = 0;
-  std::vector<int64_t> drop;     // refs of the recording that are dead after this item
-};
 
 // One OS thread per named stream (monarch_tensor_worker/src/stream.rs:542-588 gives every
 // StreamActor a dedicated thread): the worker actor only routes messages; each stream's
@@ -375,16 +345,23 @@ class WorkerCore {
       py::tuple m = py::reinterpret_borrow<py::tuple>(h);
       bool done = false;
       if (!threads_.empty() && m.size() >= 2 && PyUnicode_Check(m[0].ptr())) {
-        const char* kind = PyUnicode_AsUTF8(m[0].ptr());
-        if (kind != nullptr && std::strcmp(kind, "call") == 0 && m.size() == 8) {
-          done = route_call(m);
-        } else if (kind != nullptr && std::strcmp(kind, "call") == 0 && m.size() == 9 &&
-                   null_device_ && !m[8].is_none()) {
-          done = route_null_call(m);
-        } else if (kind != nullptr && std::strcmp(kind, "delete") == 0 && m.size() == 2) {
-          auto ids = std::make_shared<std::vector<int64_t>>(m[1].cast<std::vector<int64_t>>());
-          fence_native([this, ids]() { erase_nogil(*ids); });
-          done = true;
+        switch (kind_of(PyUnicode_AsUTF8(m[0].ptr()))) {
+          case MessageKind::Call:
+            if (m.size() == 8)
+              done = route_call(m);
+            else if (m.size() == 9 && null_device_ && !m[8].is_none())
+              done = route_null_call(m);
+            break;
+          case MessageKind::Delete:
+            if (m.size() == 2) {
+              auto del = std::make_shared<DeleteRefs>();
+              del->ids = m[1].cast<std::vector<int64_t>>();
+              fence_native([this, del]() { erase_nogil(del->ids); });
+              done = true;
+            }
+            break;
+          default:
+            break;   // named and handled by the Python router
         }
       }
       if (done)
@@ -522,25 +499,21 @@ class WorkerCore {
   // Shape-only workers: the controller announces the results' metadata and nothing is
   // executed; zero tensors of those shapes stand in.
   bool route_null_call(const py::tuple& m) {
-    struct Meta {
-      std::vector<int64_t> shape;
-      at::ScalarType dtype;
-    };
-    auto metas = std::make_shared<std::vector<Meta>>();
-    std::vector<int64_t> results;
+    auto call = std::make_shared<ShapeOnlyCall>();
     StreamThread* thr = nullptr;
-    int64_t seq = 0;
     try {
-      seq = m[1].cast<int64_t>();
-      results = refs_of(m[2]);
-      auto it = threads_.find(m[7].cast<int64_t>());
+      call->seq = m[1].cast<int64_t>();
+      call->results = refs_of(m[2]);
+      call->stream = m[7].cast<int64_t>();
+      auto it = threads_.find(call->stream);
       if (it == threads_.end()) return false;
       thr = it->second.get();
       for (auto h : m[8]) {
         py::tuple mt = py::reinterpret_borrow<py::tuple>(h);
         if (!THPDtype_Check(mt[1].ptr())) return false;
-        metas->push_back(Meta{mt[0].cast<std::vector<int64_t>>(),
-                              reinterpret_cast<THPDtype*>(mt[1].ptr())->scalar_type});
+        call->metas.push_back(ShapeOnlyCall::Meta{
+            mt[0].cast<std::vector<int64_t>>(),
+            reinterpret_cast<THPDtype*>(mt[1].ptr())->scalar_type});
       }
     } catch (py::error_already_set& e) {
       e.restore();
@@ -549,13 +522,14 @@ class WorkerCore {
     } catch (const std::exception&) {
       return false;
     }
-    if (metas->size() != results.size()) return false;
-    thr->submit_native([this, metas, results, seq]() {
+    if (call->metas.size() != call->results.size()) return false;
+    thr->submit_native([this, call]() {
       int64_t prev = last_seq_.load();
-      while (prev < seq && !last_seq_.compare_exchange_weak(prev, seq)) {
+      while (prev < call->seq && !last_seq_.compare_exchange_weak(prev, call->seq)) {
       }
-      for (size_t i = 0; i < results.size(); ++i)
-        assign(results[i], at::zeros((*metas)[i].shape, at::TensorOptions().dtype((*metas)[i].dtype)));
+      for (size_t i = 0; i < call->results.size(); ++i)
+        assign(call->results[i], at::zeros(call->metas[i].shape,
+                                           at::TensorOptions().dtype(call->metas[i].dtype)));
     });
     return true;
   }
