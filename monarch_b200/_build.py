@@ -203,7 +203,7 @@ def _build_torch_ext(name: str, src: Path, force: bool) -> Path:
     from torch.utils import cpp_extension as ce
     flags = ["-O2", "-std=c++17", "-fPIC", f"-DTORCH_EXTENSION_NAME={name}",
              "-D_GLIBCXX_USE_CXX11_ABI=" + str(int(torch._C._GLIBCXX_USE_CXX11_ABI))]
-    stamp = _stamp([src], flags + [torch.__version__])
+    stamp = _stamp([src, *sorted(src.parent.glob("*.h"))], flags + [torch.__version__])
     if not force and _up_to_date(target, stamp):
         return target
     incs = []
