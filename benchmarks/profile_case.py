@@ -6,6 +6,7 @@
     python benchmarks/profile_case.py attn            # attention forward + backward, S=4096, 16q/4kv
     python benchmarks/profile_case.py step            # 2-layer Llama-3-8B-shaped training steps
     python benchmarks/profile_case.py collectives     # the NVLink kernels as a group of one rank
+    python benchmarks/profile_case.py fused           # the fused compute+collective kernels, one rank
 
 A profiler replays each captured launch many times, so kernels that wait for a peer cannot be
 captured in a multi-rank run; ``collectives`` runs them as a group of one rank on one GPU (the
@@ -132,6 +133,53 @@ def collectives_case():
     dist.destroy_process_group()
 
 
+def fused_case():
+    """The fused compute+collective kernels as a group of one rank: tensor-parallel
+    all-gather->GEMM and GEMM->reduce-scatter (TPComm), the FSDP step with the parameter
+    gather inside the GEMM launches, the MoE dispatch->GEMM / GEMM->combine pair (EPComm)."""
+    from dataclasses import replace
+    import torch.distributed as dist
+    from monarch_b200.models import PRESETS, LlamaEngine, ParamLayout
+    from monarch_b200.parallel.ep import EPComm
+    from monarch_b200.parallel.fsdp import FSDPParamStore
+    from monarch_b200.parallel.tp import TPComm
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29578")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
+    # tensor parallel: Llama-2-13B shapes at tp=1 (4096 rows, d 5120, ffn 13824)
+    T, d, F = 4096, 5120, 13824
+    tp = TPComm(dist.group.WORLD, dev, T, d)
+    x = torch.randn(T, d, device=dev, dtype=bf16)
+    w_gu = torch.randn(2 * F, d, device=dev, dtype=bf16) * 0.02
+    w_dn = torch.randn(d, F, device=dev, dtype=bf16) * 0.02
+    for _ in range(2):
+        gu, _ = tp.ag_gemm(x, w_gu)
+        h = ops.swiglu_fwd(gu)
+        tp.gemm_rs(h, w_dn, residual_local=x)
+    # FSDP, two layers of Llama-3-8B shape, gather inside the consuming GEMMs
+    cfg = replace(PRESETS["llama3-8b"], n_layers=2, vocab=32064)
+    st = FSDPParamStore(ParamLayout(cfg), dev, seed=0, gather="gemm")
+    eng = LlamaEngine(cfg, st, 8192)
+    tok = torch.randint(0, cfg.vocab, (1, 8192), device=dev)
+    st.set_hyper(lr=1e-4)
+    eng.forward_backward(tok, tok)
+    eng.optimizer_step(1e-4)
+    # expert parallel: Mixtral shapes, one expert on this rank
+    Tm, dm, Fm = 4096, 4096, 14336
+    ep = EPComm(dist.group.WORLD, dev, Tm, dm, Fm, top_k=1)
+    xm = torch.randn(Tm, dm, device=dev, dtype=bf16)
+    idx = torch.zeros(Tm, 1, dtype=torch.int32, device=dev)
+    wts = torch.ones(Tm, 1, device=dev)
+    e_gu = torch.randn(2 * Fm, dm, device=dev, dtype=bf16) * 0.02
+    e_dn = torch.randn(dm, Fm, device=dev, dtype=bf16) * 0.02
+    for _ in range(2):
+        ep.forward(xm, idx, wts, e_gu, e_dn, residual=xm)
+    torch.cuda.synchronize()
+    dist.destroy_process_group()
+
+
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
     if what == "gemm":
@@ -144,5 +192,7 @@ if __name__ == "__main__":
         step_case()
     elif what == "collectives":
         collectives_case()
+    elif what == "fused":
+        fused_case()
     K.check_status()
     print("ok", what)
