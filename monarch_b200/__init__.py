@@ -47,6 +47,8 @@ _LAZY = {
     "local_meshes": ("mesh_constructors", "local_meshes"),
     "sim_mesh": ("mesh_constructors", "sim_mesh"),
     "world_mesh": ("mesh_constructors", "world_mesh"),
+    "SocketType": ("mesh_constructors", "SocketType"),
+    "set_meta": ("simulator", "set_meta"),
     "ControllerRemoteClass": ("remote_class", "ControllerRemoteClass"),
     "WorkerRemoteClass": ("remote_class", "WorkerRemoteClass"),
     "ProcessAllocator": ("actor.allocator", "ProcessAllocator"),

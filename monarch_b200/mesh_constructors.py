@@ -10,6 +10,8 @@ those entry points find them.
 """
 from __future__ import annotations
 
+import enum
+
 import contextlib
 from typing import Iterator, List, Optional
 
@@ -87,3 +89,10 @@ def world_mesh(proc_mesh, use_cuda: Optional[bool] = None):
 
 
 __all__ = ["python_local_mesh", "local_mesh", "local_meshes", "sim_mesh", "world_mesh"]
+
+
+class SocketType(enum.Enum):
+    """Transport of a locally spawned mesh (python/monarch/rust_local_mesh.py ``SocketType``);
+    both map onto this runtime's channel addresses."""
+    TCP = "tcp"
+    UNIX = "unix"

@@ -17,6 +17,7 @@ bytes over NVLink bandwidth for collectives.
 """
 from __future__ import annotations
 
+import contextlib
 import json
 from typing import Any, Dict, List, Optional
 
@@ -52,6 +53,21 @@ class CostModel:
         return self.launch_us + vol / (self.link_gbs * 1e3)
 
 
+_META: List[Any] = []
+
+
+@contextlib.contextmanager
+def set_meta(value):
+    """Tag every simulated task issued inside the block: the tags show up under ``args.meta``
+    of the trace events (nested blocks stack).  Parity: python/monarch/simulator/config.py
+    (``set_meta``)."""
+    _META.append(value)
+    try:
+        yield
+    finally:
+        _META.pop()
+
+
 class SimWorker:
     """One simulated rank: executes worker messages on meta tensors."""
 
@@ -83,8 +99,10 @@ class SimWorker:
         t0 = self.clock.setdefault(stream, 0.0)
         self.clock[stream] = t0 + dur
         if self.events is not None:
-            self.events.append({"name": name, "ph": "X", "pid": self.rank, "tid": stream,
-                                "ts": t0, "dur": dur})
+            ev = {"name": name, "ph": "X", "pid": self.rank, "tid": stream, "ts": t0, "dur": dur}
+            if _META:
+                ev["args"] = {"meta": list(_META)}
+            self.events.append(ev)
 
     # -------------------------------------------------------------------- messages
     def handle(self, msgs: List[tuple]) -> None:
@@ -266,6 +284,11 @@ class Simulator:
 
     def stream_clocks(self, rank: int = 0) -> Dict[int, float]:
         return dict(self._w._all[rank].clock)
+
+    def events(self) -> List[dict]:
+        """The trace events recorded so far (chrome-trace "X" events; tasks issued under
+        :func:`set_meta` carry ``args.meta``)."""
+        return list(self._w.events or [])
 
     def dump_chrome_trace(self, path: str) -> None:
         with open(path, "w") as f:

@@ -27,6 +27,9 @@ PATHS = {
     "monarch_extension.mesh_controller": ["_Controller"],
     "monarch_extension.tensor_worker": ["Ref", "CallFunction", "Reduce", "SendTensor",
                                         "BorrowCreate", "DefineRecording", "CallRecording"],
+    "monarch_extension.client": ["Error", "Failure", "WorkerResponse", "LogMessage", "LogLevel",
+                                 "DebuggerMessage", "WorldState"],
+    "monarch_extension.controller": ["Node", "Send"],
     "monarch_extension.code_sync": ["CodeSyncMeshClient"],
     "monarch_extension.debugger": ["PdbActor"],
     "monarch_extension.logging": ["LoggingMeshClient"],
@@ -72,3 +75,36 @@ def test_the_names_are_the_runtimes_own_objects():
     assert st.is_simulator_active()
     st.sleep(5.0)
     st.stop()
+
+
+def test_client_and_controller_value_types():
+    from monarch._rust_bindings.monarch_extension.client import Error, Failure, WorkerResponse
+    from monarch._rust_bindings.monarch_extension.controller import Node, Send
+    from monarch_b200 import _native as N
+    from monarch_b200.tensor_engine import RemoteException
+    e = Error.from_remote(RemoteException(7, 2, "aten.add", "RuntimeError: boom", "tb", 5))
+    assert (e.seq, e.caused_by_seq, e.actor_id) == (7, 5, 2) and "boom" in e.backtrace
+    r = WorkerResponse.new_for_unit_test(seq=7, response=e)
+    assert r.is_exception() and r.exception() is e and r.result() is None
+    assert WorkerResponse(8, 41).result() == 41 and not WorkerResponse(8, 41).is_exception()
+    assert isinstance(Failure.new_for_unit_test("w[0]"), type(e).__mro__[1])
+    n = Node.from_serialized(Node(seq=3, defs=[10], uses=[1, 2]).serialize())
+    h = N.ControllerHistory(1)
+    assert n.record(h) == -1 and h.describe(3) == ("node", -1)
+    s = Send.from_serialized(Send(ranks=[0, 1], message=("delete", [10])).serialize())
+    assert s.ranks == [0, 1] and s.message == ("delete", [10])
+
+
+def test_top_level_names_of_the_reference():
+    import monarch_b200 as m
+    assert m.SocketType.TCP.value == "tcp" and m.SocketType.UNIX.value == "unix"
+    from monarch_b200.simulator import mock_mesh
+    import torch
+    mesh, sim = mock_mesh(hosts=1, gpus=1)
+    with mesh.activate():
+        x = torch.ones(4, 4)
+        with m.set_meta("phase-1"):
+            y = x + 1
+        z = y * 2
+    tagged = [e for e in sim.events() if e.get("args", {}).get("meta") == ["phase-1"]]
+    assert tagged and len(tagged) < len(sim.events())
