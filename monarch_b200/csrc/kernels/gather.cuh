@@ -25,6 +25,9 @@ struct GatherParams {
   int wait_slot;
   uint32_t wait_epoch;
   int* status;
+  // Visit the chunks of [c_begin, c_end) starting c_rot chunks into the range and wrapping
+  // around: every rank then starts with its own rows and reads a different peer at any time.
+  long long c_rot;
 };
 
 __device__ __forceinline__ void gather_chunks(const GatherParams& g, int cta, int n_cta) {
@@ -92,20 +95,25 @@ struct BulkPiece {
 struct PieceIter {
   const GatherParams& g;
   int cta, n_cta;
-  long long c, e, e1;
+  long long k, c, e, e1;   // k: position in the visiting order, c: the chunk visited there
   __device__ PieceIter(const GatherParams& gp, int cta_, int n) : g(gp), cta(cta_), n_cta(n) {
-    c = g.c_begin + cta;
+    k = g.c_begin + cta;
     start_chunk();
   }
   __device__ void start_chunk() {
-    if (c < g.c_end) {
+    c = k;
+    if (k < g.c_end) {
+      if (g.c_rot > 0) {
+        c = k + g.c_rot;
+        if (c >= g.c_end) c -= (g.c_end - g.c_begin);
+      }
       e = c * g.chunk_elems;
       e1 = e + g.chunk_elems;
       if (e1 > g.total_elems) e1 = g.total_elems;
     }
   }
   __device__ bool next(BulkPiece& out) {
-    if (c >= g.c_end) return false;
+    if (k >= g.c_end) return false;
     long long n = kBulkPiece / 2;
     if (e + n > e1) n = e1 - e;
     const long long p = e / g.shard_elems;
@@ -117,7 +125,7 @@ struct PieceIter {
     e += n;
     out.last = (e >= e1);
     if (out.last) {
-      c += n_cta;
+      k += n_cta;
       start_chunk();
     }
     return true;

@@ -41,19 +41,22 @@ constexpr int G2_SMEM_BYTES = G2_STAGES * G2_STAGE_BYTES + 1024 /*align*/ + 256 
 // order in which the chunks land, rotated by `rot`.
 constexpr int G2_GROUP_M = 8;
 __device__ __forceinline__ void tile_coords(int t, int m_blocks, int n_blocks, int rot,
-                                            bool ordered, int& m_blk, int& n_blk) {
+                                            bool ordered, int m_group, int m_rot, int& m_blk,
+                                            int& n_blk) {
   if (ordered) {
     m_blk = t % m_blocks;
     n_blk = t / m_blocks + rot;
     if (n_blk >= n_blocks) n_blk -= n_blocks;
     return;
   }
-  const int per_group = G2_GROUP_M * n_blocks;
+  const int group_m = m_group > 0 ? m_group : G2_GROUP_M;
+  const int per_group = group_m * n_blocks;
   const int group = t / per_group;
-  const int first_m = group * G2_GROUP_M;
-  const int gm = (m_blocks - first_m) < G2_GROUP_M ? (m_blocks - first_m) : G2_GROUP_M;
+  const int first_m = group * group_m;
+  const int gm = (m_blocks - first_m) < group_m ? (m_blocks - first_m) : group_m;
   const int in_group = t - group * per_group;
-  m_blk = first_m + in_group % gm;
+  m_blk = first_m + in_group % gm + m_rot;
+  if (m_blk >= m_blocks) m_blk -= m_blocks;
   n_blk = in_group / gm;
 }
 
@@ -117,7 +120,8 @@ __device__ __forceinline__ void gemm2_cta_body(const CUtensorMap* tmA, const CUt
       uint32_t phase = 0;
       for (int t = vpair; t < num_tiles; t += npairs) {
         int m_blk, n_blk;
-        tile_coords(t, m_blocks, n_blocks, p.n_blk_rot, p.b_ready != nullptr, m_blk, n_blk);
+        tile_coords(t, m_blocks, n_blocks, p.n_blk_rot, p.b_ready != nullptr, p.m_group, p.m_rot,
+                    m_blk, n_blk);
         const int m0 = m_blk * G2_BM + (int)cta * G2_HALF;
         const int n0 = n_blk * G2_BN + (int)cta * G2_HALF;
         bool ok = true;
@@ -224,7 +228,8 @@ __device__ __forceinline__ void gemm2_cta_body(const CUtensorMap* tmA, const CUt
     const uint32_t empty0 = mapa_u32(smem_u32(&sh->tmem_empty[0]), 0);
     for (int t = vpair; t < num_tiles; t += npairs) {
       int m_blk, n_blk;
-      tile_coords(t, m_blocks, n_blocks, p.n_blk_rot, p.b_ready != nullptr, m_blk, n_blk);
+      tile_coords(t, m_blocks, n_blocks, p.n_blk_rot, p.b_ready != nullptr, p.m_group, p.m_rot,
+                    m_blk, n_blk);
       const int row = m_blk * G2_BM + (int)cta * G2_HALF + quad * 32 + lane;
       const int n0 = n_blk * G2_BN;
       if (!mbar_wait(&sh->tmem_full[acc], acc_phase, abort_word, p.status)) break;

@@ -52,6 +52,11 @@ struct GemmParams {
   long long a_flag_chunk_elems;
   long long a_flag_elem0;
   int lda;
+  // Tile order of the CTA-pair kernel when A arrives rank by rank: groups of m_group
+  // m-blocks (0: the default group size), the whole order rotated by m_rot m-blocks so
+  // that the rows this rank already holds are multiplied first.
+  int m_group;
+  int m_rot;
   // Reduce-scatter epilogue (row-parallel GEMM -> sequence-parallel output): when
   // rs_rows_per_rank > 0 the bf16 partial tile is stored over NVLink into the staging
   // buffer of the rank that owns the row, in the slot of the producing rank:

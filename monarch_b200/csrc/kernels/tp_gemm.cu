@@ -128,6 +128,15 @@ extern "C" int mb200_ag_a_gemm(void* a_full, const void* const* shard_ptrs, long
   GatherParams g = make_gather(a_full, shard_ptrs, shard_elems, rank, world, 0, n_chunks,
                                chunk_elems, chunk_flags, chunk_epoch, my_flags, wait_slot,
                                wait_epoch, status);
+  // own rows first, then the peers in ring order -- for the copies (every rank reads a
+  // different peer at any time) and for the GEMM's tiles (the rows already here are
+  // multiplied while the others travel); one rank's rows form one group of the tile order
+  g.c_rot = ((long long)rank * shard_elems) / chunk_elems;
+  const int rows_per_rank = M / world;
+  p.m_rot = (int)(((long long)rank * rows_per_rank) / G2_BM);
+  p.m_group = rows_per_rank / G2_BM;
+  if (p.m_group < 1) p.m_group = 1;
+  if (p.m_group > 8) p.m_group = 8;
   const int sms = sm_count();
   if (n_comm <= 0) n_comm = 16;
   if (n_comm > sms / 2) n_comm = sms / 2;
