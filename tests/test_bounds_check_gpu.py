@@ -29,6 +29,7 @@ SCRIPT = textwrap.dedent("""
     # a stale "peer" pointer: valid memory, but not a range the communicator registered
     stray = torch.zeros_like(local)
     comm.ptrs[0] = stray.data_ptr()
+    comm._at_cache.clear()                    # (pointer arrays are cached per offset)
     y = comm.all_reduce(x, "sum")
     torch.cuda.synchronize()
     st = K.status_word(dev)
@@ -43,6 +44,7 @@ SCRIPT = textwrap.dedent("""
         assert "bounds" in str(e), e
     # the word is cleared and the device keeps working
     comm.ptrs[0] = local.data_ptr()
+    comm._at_cache.clear()
     st[2:].zero_()
     # (the aborted collective left its epoch published on the stray buffer: start afresh)
     comm2_buf = MeshComm.allocate_local(dev, cap)
