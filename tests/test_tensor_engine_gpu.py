@@ -73,8 +73,9 @@ def test_reduce_variants_use_the_nvlink_kernels(dm):
     assert r_stack.shape == (1, 1, 6) and torch.equal(r_stack[0], ref)
     assert r_rs.shape == (6,) and torch.equal(r_rs, ref[0])
     assert r_a2a.shape == (1, 6) and torch.equal(r_a2a, ref)
-    # stage + reduce (or gather) per collective, launched by the tensor worker
-    assert after - before >= 16, (before, after)
+    # launched by the tensor worker: one kernel per small all-reduce (it stages, handshakes and
+    # combines), stage + reduce or stage + gather for the other five collectives
+    assert after - before >= 11, (before, after)
 
 
 def test_borrow_between_two_cuda_streams(dm):
