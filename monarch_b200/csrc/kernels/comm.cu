@@ -474,6 +474,25 @@ extern "C" int mb200_memcpy_d2d_async(void* dst, const void* src, int64_t nbytes
   return (int)cudaMemcpyAsync(dst, src, (size_t)nbytes, cudaMemcpyDeviceToDevice, ST(stream));
 }
 
+// Asynchronous fill of `count` 32-bit words with `value` (the driver's cuMemsetD32Async): used
+// to raise a range of readiness flags behind a copy-engine transfer on the same stream.
+extern "C" int mb200_memset_d32_async(void* dst, uint32_t value, int64_t count, void* stream) {
+  using Fn = CUresult (*)(CUdeviceptr, unsigned int, size_t, CUstream);
+  static Fn fn = nullptr;
+  if (!fn) {
+    void* fp = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuMemsetD32Async", &fp, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return 1004;
+    fn = reinterpret_cast<Fn>(fp);
+  }
+  if (count <= 0) return 0;
+  const CUresult r = fn(reinterpret_cast<CUdeviceptr>(dst), value, (size_t)count,
+                        reinterpret_cast<CUstream>(stream));
+  return r == CUDA_SUCCESS ? 0 : 1007;
+}
+
 // Let kernels running on device `dev` dereference memory that lives on device `peer` (memory
 // opened through CUDA IPC or allocated by this process).  Idempotent.  Returns 0, or 1003 when
 // the two devices have no peer path.

@@ -138,12 +138,16 @@ extern "C" int mb200_ag_a_gemm(void* a_full, const void* const* shard_ptrs, long
   if (p.m_group < 1) p.m_group = 1;
   if (p.m_group > 8) p.m_group = 8;
   const int sms = sm_count();
-  if (n_comm <= 0) n_comm = 16;
+  // n_comm < 0: the rows are brought in from outside the kernel (copy engines on another
+  // stream, which raise the same chunk flags): no copy CTAs, every SM multiplies
+  const bool external = n_comm < 0;
+  if (n_comm == 0) n_comm = 16;
   if (n_comm > sms / 2) n_comm = sms / 2;
+  if (external) n_comm = 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (mb200_gemm_get_impl() == 2) {
     n_comm &= ~1;
-    if (n_comm < 2) n_comm = 2;
+    if (n_comm < 2 && !external) n_comm = 2;
     CUtensorMap ta2, tb2;
     r = make_gemm2_tmaps(&ta2, &tb2, a_full, B, M, N, K, K, ldb, 0, b_mn);
     if (r) return 1000 - r;

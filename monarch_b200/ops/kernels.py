@@ -97,6 +97,7 @@ _OPTIONAL: dict[str, list] = {
     "mb200_peer_copy": [_vp, _vp, _i64, _vp, ctypes.c_uint32, _vp, _i, _vp],
     "mb200_peer_copy_sync": [_vp, _vp, _i64, _i, _vp],
     "mb200_memcpy_d2d_async": [_vp, _vp, _i64, _vp],
+    "mb200_memset_d32_async": [_vp, ctypes.c_uint32, _i64, _vp],
     "mb200_enable_peer_access": [_i, _i],
     "mb200_ipc_export": [_vp, _vp, _vp, _vp],
     "mb200_ipc_open": [_vp, _i, _vp],

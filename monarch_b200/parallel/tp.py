@@ -26,6 +26,7 @@ is the net-new part that the ``{pp: 2, tp: 4}`` configuration needs.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -59,6 +60,10 @@ class TPComm:
         self._n_rs = 0
         self._epoch = 0
         self._rs_epoch = 0
+        self._side = None
+        # how the peers' rows reach the gather-GEMM: "kernel" (copy CTAs inside the GEMM
+        # launch) or "dma" (copy engines on a side stream, no copy CTAs)
+        self.gather = os.environ.get("MB200_TP_GATHER", "kernel")
         if comm == "fused":
             from .symm import FlagArray, SymmBuffer
             n = rows_local * d
@@ -100,12 +105,43 @@ class TPComm:
             self._flags.barrier(0)  # every rank's rows are in place
             wait_slot, wait_epoch = 0, 0
         out = torch.empty(T, N, dtype=bf16, device=x_local.device)
+        n_comm = 12
+        shard = self.rows_local * d
+        if self.gather == "dma" and wait_epoch and shard % self.CHUNK == 0:
+            # the rows travel on the copy engines (a side stream: bounded flag wait, one copy
+            # per rank in ring order starting with the own rows, the rows' chunk flags raised
+            # behind each copy) while every SM of the GEMM launch multiplies
+            self._dma_rows(sb, x_full, shard)
+            n_comm, wait_slot, wait_epoch = -1, 0, 0
         K.check(K.lib().mb200_ag_a_gemm(
-            x_full.data_ptr(), sb.ptrs_at(0), self.rows_local * d, self.rank, self.world, T, d,
+            x_full.data_ptr(), sb.ptrs_at(0), shard, self.rank, self.world, T, d,
             w.data_ptr(), w.stride(0), int(b_mn), N, out.data_ptr(), N, None, 0, self.CHUNK,
             self._chunk_flags.data_ptr(), self._epoch, self._flags.my_ptr, wait_slot, wait_epoch,
-            12, K.status_word(self.device).data_ptr(), K.stream_ptr()), "ag_a_gemm")
+            n_comm, K.status_word(self.device).data_ptr(), K.stream_ptr()), "ag_a_gemm")
+        if n_comm < 0:
+            torch.cuda.current_stream().wait_stream(self._side)   # later readers of x_full
         return out, x_full
+
+    def _dma_rows(self, sb, x_full: torch.Tensor, shard: int) -> None:
+        main = torch.cuda.current_stream()
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=self.device)
+        side = self._side
+        side.wait_stream(main)                 # the staging copy and x_full's allocation
+        x_full.record_stream(side)
+        lib, per = K.lib(), shard // self.CHUNK
+        with torch.cuda.stream(side):
+            st = K.stream_ptr()
+            K.check(lib.mb200_wait_flags(self._flags.my_ptr, self.world, self.SLOT_ROWS,
+                                         self._epoch, K.status_word(self.device).data_ptr(), st),
+                    "wait_flags")
+            base, flags = x_full.data_ptr(), self._chunk_flags.data_ptr()
+            for k in range(self.world):
+                p = (self.rank + k) % self.world
+                K.check(lib.mb200_memcpy_d2d_async(base + p * shard * 2, sb.ptrs[p], shard * 2, st),
+                        "memcpy_d2d", 0)
+                K.check(lib.mb200_memset_d32_async(flags + p * per * 4, self._epoch, per, st),
+                        "memset_d32", 0)
 
     # ------------------------------------------------------------ GEMM -> reduce-scatter
     def gemm_rs(self, a: torch.Tensor, w: torch.Tensor, b_mn: bool = False,

@@ -46,6 +46,12 @@ def main() -> int:
         y, x_full = tp.ag_gemm(x, w)
     assert torch.equal(x_full, x)
     out["ag_gemm_rel"] = _rel(y, x.float() @ w.float().t())
+    tp.gather = "dma"                        # rows by the copy engines, no copy CTAs
+    for _ in range(3):
+        y2, x_full2 = tp.ag_gemm(x, w)
+    torch.cuda.synchronize()
+    assert torch.equal(x_full2, x) and torch.equal(y2, y)
+    tp.gather = "kernel"
     a = torch.randn(T, N, device=dev, dtype=bf16)
     w2 = torch.randn(d, N, device=dev, dtype=bf16) * 0.05
     for _ in range(3):
