@@ -391,15 +391,20 @@ def main() -> int:
 
     # ------------------------------- tensor x pipeline parallel: fused == library path ----
     from monarch_b200.parallel.pipelining import PipelineTrainer
+    # tp=2 x pp=world/2 up to 4 ranks; 8 ranks run {pp:2, tp:4} like the 13B configuration, on a
+    # variant of the tiny model with enough heads for four tensor-parallel ranks
     tp_n = 2 if world < 8 else 4
     pp_n = world // tp_n
     if pp_n * tp_n == world:
+        from dataclasses import replace as _replace
+        pcfg = cfg if tp_n == 2 else _replace(cfg, d=512, n_heads=8, n_kv_heads=4,
+                                              name="tiny-tp4")       # head dim stays 64
         Sp, Mp = 256, 4
         gp = torch.Generator().manual_seed(4242)
         ptok = torch.randint(0, cfg.vocab, (3, Mp, 1, Sp), generator=gp).to(dev)
         plosses = {}
         for mode in ("fused", "nccl"):
-            tr = PipelineTrainer(cfg, pp_n, tp_n, Sp, 1, Mp, device=dev, comm=mode, lr=1e-2,
+            tr = PipelineTrainer(pcfg, pp_n, tp_n, Sp, 1, Mp, device=dev, comm=mode, lr=1e-2,
                                  seed=11, init_std=0.05)
             ls = []
             for step in range(2):
