@@ -6,9 +6,11 @@ A column-parallel GEMM (QKV, gate|up) first needs all rows of its normalised inp
 row-parallel GEMM (out, down) produces partial sums of all rows that must be summed and
 scattered back to T/tp rows per rank.  With ``comm="fused"`` both are one kernel each:
 
-* ``ag_gemm``  = ``mb200_ag_a_gemm``: copy CTAs pull the peers' rows over NVLink while the
-  tcgen05 GEMM CTAs consume row blocks as they land; the gathered input stays resident
-  for the weight-gradient GEMM of the backward pass.
+* ``ag_gemm``  = ``mb200_ag_a_gemm``: the peers' rows arrive over NVLink while the tcgen05
+  GEMM CTAs consume row blocks as they land (own rows first, then the peers in ring order);
+  the rows are moved by the copy engines on a side stream, which raise the same per-chunk
+  flags that the kernel's own copy CTAs raise in the ``MB200_TP_GATHER=kernel`` mode; the
+  gathered input stays resident for the weight-gradient GEMM of the backward pass.
 * ``gemm_rs``  = ``mb200_gemm_rs`` + ``mb200_rs_finish_sync``: the GEMM epilogue stores each
   bf16 partial tile straight into the owner rank's staging slot; the owner's next launch is
   the flag barrier and the fp32 sum of the slots together with the residual.
@@ -61,9 +63,11 @@ class TPComm:
         self._epoch = 0
         self._rs_epoch = 0
         self._side = None
-        # how the peers' rows reach the gather-GEMM: "kernel" (copy CTAs inside the GEMM
-        # launch) or "dma" (copy engines on a side stream, no copy CTAs)
-        self.gather = os.environ.get("MB200_TP_GATHER", "kernel")
+        # how the peers' rows reach the gather-GEMM: "dma" (copy engines on a side stream raise
+        # the rows' chunk flags, the GEMM launch has no copy CTAs; Llama-2-13B tp=4 on 4 GPUs:
+        # 2,125 ms/step) or "kernel" (copy CTAs inside the GEMM launch: 2,314 ms; the same
+        # schedule over NCCL: 2,337 ms)
+        self.gather = os.environ.get("MB200_TP_GATHER", "dma")
         if comm == "fused":
             from .symm import FlagArray, SymmBuffer
             n = rows_local * d
