@@ -151,6 +151,8 @@ def fused_case():
     # tensor parallel: Llama-2-13B shapes at tp=1 (4096 rows, d 5120, ffn 13824)
     T, d, F = 4096, 5120, 13824
     tp = TPComm(dist.group.WORLD, dev, T, d)
+    tp.gather = "kernel"      # the form with copy CTAs inside the GEMM launch (the default,
+    #                           "dma", moves the rows with the copy engines: nothing to capture)
     x = torch.randn(T, d, device=dev, dtype=bf16)
     w_gu = torch.randn(2 * F, d, device=dev, dtype=bf16) * 0.02
     w_dn = torch.randn(d, F, device=dev, dtype=bf16) * 0.02
