@@ -148,3 +148,57 @@ def _check_daemon_policy(port, pa):
             break
     c.close()
     assert code == 7 and out.split() == ["hello", "None", "None"], (code, out)
+
+
+@pytest.mark.parametrize("daemon", ["native", "python"])
+@pytest.mark.parametrize("how", ["close", "silence"])
+def test_a_vanished_client_leaves_no_orphan(daemon, how):
+    """The proc of a client that closes its connection, or stays connected but goes silent
+    for three heartbeat intervals, is killed by the daemon (its whole process group)."""
+    import json
+    import socket
+    import threading
+    from monarch_b200.tools import process_allocator as pa
+    prog = [sys.executable, "-c", "import time; print('up', flush=True); time.sleep(600)"]
+    proc = None
+    if daemon == "native":
+        cmd = pa.native_command("tcp!127.0.0.1:0", 0.5, prog)
+        if cmd is None:
+            pytest.skip("no compiler for the native daemon")
+        proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, text=True)
+        port = int(proc.stdout.readline().rsplit(":", 1)[1])
+    else:
+        ports, started = [], threading.Event()
+        threading.Thread(target=pa.serve, args=("tcp!127.0.0.1:0",), daemon=True,
+                         kwargs=dict(heartbeat=0.5, program=prog, token="",
+                                     ready=lambda p: (ports.append(p), started.set()))).start()
+        assert started.wait(10)
+        port = ports[0]
+    try:
+        c = socket.create_connection(("127.0.0.1", port), timeout=10)
+        c.sendall((json.dumps({"start": 1, "env": {}}) + "\n").encode())
+        f = c.makefile("rb")
+        pid = None
+        for line in f:
+            msg = json.loads(line)
+            if "pid" in msg:
+                pid = msg["pid"]
+            if msg.get("out", "").startswith("up"):
+                break
+        assert pid and os.path.exists(f"/proc/{pid}")
+        if how == "close":
+            c.close()
+        # "silence": the connection stays open and nothing (no heartbeat) is sent any more
+        deadline = time.time() + 15
+        while time.time() < deadline and os.path.exists(f"/proc/{pid}") and \
+                open(f"/proc/{pid}/stat").read().split(")")[1].split()[0] != "Z":
+            time.sleep(0.1)
+        gone = not os.path.exists(f"/proc/{pid}") or \
+            open(f"/proc/{pid}/stat").read().split(")")[1].split()[0] == "Z"
+        assert gone, f"proc {pid} outlived its client ({how})"
+        if how == "silence":
+            c.close()
+    finally:
+        if proc is not None:
+            proc.terminate()
+            proc.wait(10)
