@@ -188,6 +188,7 @@ class Client:
         self.eager_batch = eager_batch
         self._pending: List[Tuple[Any, tuple]] = []
         self._pending_cmds = 0          # commands in _pending (ref deletions do not count)
+        self._pending_since = 0.0       # when the oldest of them was queued
         self._plock = threading.RLock()
         self._flusher: Optional[threading.Thread] = None
         self._flush_event = threading.Event()
@@ -267,7 +268,11 @@ class Client:
             self._pending_cmds += 1
             if self._pending_cmds >= self.eager_batch:
                 self._flush_locked()
-            else:
+            elif self._pending_cmds == 1:
+                # the first command of a batch starts the clock; while the program keeps
+                # issuing, batches fill up and leave from here, and the flusher only sees to
+                # a batch that has been waiting for a millisecond
+                self._pending_since = time.monotonic()
                 self._kick_flusher()
 
     def flush(self) -> None:
@@ -309,11 +314,18 @@ class Client:
         while not self._closed:
             self._flush_event.wait()
             self._flush_event.clear()
-            time.sleep(0.001)           # let a burst of commands accumulate
-            try:
-                self.flush()
-            except Exception as e:  # noqa: BLE001 - surfaces at the caller's next command
-                self._failed = e
+            while not self._closed:
+                with self._plock:
+                    if not self._pending:
+                        break
+                    age = time.monotonic() - self._pending_since
+                    if age >= 0.001:
+                        try:
+                            self._flush_locked()
+                        except Exception as e:  # noqa: BLE001 - surfaces at the next command
+                            self._failed = e
+                        break
+                time.sleep(0.0011 - age)        # let the burst of commands accumulate
 
     def _watch(self) -> None:
         """Progress watchdog step; called from the command path and from waits, so it needs
