@@ -49,6 +49,9 @@ int64_t ControllerHistory::add_invocation(int64_t seq, const std::string& name,
   }
   const int64_t r = inv.failed_by;
   live_.push_back(std::move(inv));
+  // without progress reports (watchdog off, simulated workers) nothing retires: keep the
+  // table bounded by forgetting the oldest invocations
+  while (live_.size() > kMaxLive) live_.pop_front();
   return r;
 }
 

@@ -78,6 +78,7 @@ class ControllerHistory {
   uint32_t intern(const std::string& name);
   void retire_locked();
 
+  static constexpr size_t kMaxLive = 1u << 20;
   const int world_;
   mutable std::mutex mu_;
   int64_t seq_ = 0, ref_ = 0;
