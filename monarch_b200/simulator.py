@@ -113,13 +113,27 @@ class SimWorker:
     def _m_other(self, *a) -> None:
         pass
 
-    def _m_call(self, seq, results, mutates, fspec, args, kwargs, stream) -> None:
+    def _m_call(self, seq, results, mutates, fspec, args, kwargs, stream, metas=None) -> None:
         name = fspec[1] if isinstance(fspec[1], str) else getattr(fspec[1], "__name__", "udf")
         a = _map_refs(args, lambda r: self.env.get(r.id))
         k = _map_refs(kwargs, lambda r: self.env.get(r.id))
         ins = [t for t in _flatten_tensors((a, k))]
         try:
-            if fspec[0] == "op":
+            if metas is not None and len(metas) == len(results) and \
+                    not any(isinstance(t, RemoteError) for t in ins):
+                # the controller announced the results' shapes (it propagated them already):
+                # no need to run the operator on meta tensors a second time
+                # (the simulated workers run inside the controller's process: keep the active
+                # mesh's dispatch mode from taking these factory calls for mesh operations)
+                from .tensor_engine import device_mesh as _dm
+                prev = getattr(_dm._tls, "propagating", False)
+                _dm._tls.propagating = True
+                try:
+                    flat = [torch.empty(shape, dtype=dtype, device="meta")
+                            for shape, dtype in metas]
+                finally:
+                    _dm._tls.propagating = prev
+            elif fspec[0] == "op":
                 with torch.device("meta"):
                     out = _resolve_function(fspec)(*a, **k)
                 flat = _flatten_tensors(out)
@@ -326,6 +340,7 @@ def mock_mesh(hosts: int = 1, gpus: int = 1, cost: Optional[CostModel] = None,
     client._closed = False
     client._err_rx = None
     client._init_watchdog(0.0)   # simulated workers cannot stall
+    client.send_metas = True     # results' shapes travel with the calls (see SimWorker._m_call)
     dm = DeviceMesh(client, shape, workers)
     client.root_mesh = dm
     return dm, Simulator(workers)

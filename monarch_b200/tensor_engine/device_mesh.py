@@ -875,7 +875,7 @@ def _send_call(fspec, args, kwargs, fake_out, mesh: "DeviceMesh", mutates: Seque
         [r.id for r in refs] + [t.ref for t in mutates], [t.ref for t in uses])
     msg = ("call", seq, refs, [Ref(t.ref) for t in mutates], fspec, _to_wire(args),
            _to_wire(kwargs), stream.id)
-    if getattr(client, "null_device", False):
+    if getattr(client, "null_device", False) or getattr(client, "send_metas", False):
         # shape-only workers do not run the function: they need the results' metadata
         flat: List[Tensor] = []
         _collect(out, flat)
