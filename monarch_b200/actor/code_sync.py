@@ -10,12 +10,11 @@ Parity: monarch_hyperactor/src/code_sync (manager.rs:71-341 ``CodeSyncManager``,
 the file mover, auto_reload.rs + python/monarch/_src/actor/code_sync/auto_reload.py: the
 ``AutoReloader`` that snapshots module sources by hash and reloads the changed ones),
 python/monarch/_src/actor/proc_mesh.py ``sync_workspace``.  Files travel as message parts
-over the actor channels (content-hash manifest, only changed files), not through an rsync
-daemon.  Environment (conda / virtualenv) sync lives in ``env_sync.py``.
+over the actor channels (content-hash manifest computed by the native runtime --
+``csrc/mesh/tree_manifest.cpp`` --, only changed files), not through an rsync daemon.  Environment (conda / virtualenv) sync lives in ``env_sync.py``.
 """
 from __future__ import annotations
 
-import hashlib
 import importlib
 import os
 import sys
@@ -28,27 +27,25 @@ _SKIP_DIRS = {".git", "__pycache__", ".pytest_cache", "build", ".hypothesis"}
 _MAX_FILE = 64 << 20
 
 
+_SKIP_SUFFIXES = (".pyc", ".so", ".o")
+
+
 def _hash_file(path: str) -> str:
-    h = hashlib.sha256()
-    with open(path, "rb") as f:
-        for blk in iter(lambda: f.read(1 << 20), b""):
-            h.update(blk)
-    return h.hexdigest()
+    """Content hash of one file: the native 128-bit hash (the one ``manifest`` uses)."""
+    from .. import _native as N
+    h = N.hash_file_128(path)
+    if h is None:
+        raise OSError(f"cannot read {path}")
+    return h
 
 
 def manifest(root: str) -> Dict[str, str]:
-    """{relative path: sha256} of the regular files under ``root``."""
-    out: Dict[str, str] = {}
-    for d, dirs, files in os.walk(root):
-        dirs[:] = [x for x in dirs if x not in _SKIP_DIRS]
-        for fn in files:
-            p = os.path.join(d, fn)
-            if fn.endswith((".pyc", ".so", ".o")) or not os.path.isfile(p):
-                continue
-            if os.path.getsize(p) > _MAX_FILE:
-                continue
-            out[os.path.relpath(p, root)] = _hash_file(p)
-    return out
+    """{relative path: content hash} of the regular files under ``root``: the walk and the
+    hashing run in the native runtime, on a few threads, without the GIL (a workspace of
+    thousands of files is compared on every sync, on the client and on every proc)."""
+    from .. import _native as N
+    return N.tree_manifest(root, sorted(_SKIP_DIRS), list(_SKIP_SUFFIXES), _MAX_FILE,
+                           min(8, os.cpu_count() or 1))
 
 
 class AutoReloader:

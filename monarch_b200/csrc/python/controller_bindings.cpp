@@ -2,12 +2,41 @@
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
+#include "mesh/tree_manifest.h"
 #include "tensor/controller_history.h"
 
 namespace py = pybind11;
 using namespace mb;
 
 void bind_controller(py::module_& m) {
+  // workspace synchronisation: {relative path: content hash} of a directory tree, hashed by
+  // a few threads with the GIL released
+  m.def(
+      "tree_manifest",
+      [](const std::string& root, const std::vector<std::string>& skip_dirs,
+         const std::vector<std::string>& skip_suffixes, uint64_t max_file_bytes, int threads) {
+        std::vector<ManifestEntry> entries;
+        {
+          py::gil_scoped_release rel;
+          entries = tree_manifest(root, skip_dirs, skip_suffixes, max_file_bytes, threads);
+        }
+        py::dict out;
+        for (auto& e : entries) out[py::str(e.rel)] = py::str(e.hash);
+        return out;
+      },
+      py::arg("root"), py::arg("skip_dirs"), py::arg("skip_suffixes"),
+      py::arg("max_file_bytes") = (uint64_t)64 << 20, py::arg("threads") = 4);
+  m.def("hash_file_128", [](const std::string& path) -> py::object {
+    bool ok = false;
+    std::string h;
+    {
+      py::gil_scoped_release rel;
+      h = hash_file_128(path, &ok);
+    }
+    if (!ok) return py::none();
+    return py::str(h);
+  });
+
   py::class_<ControllerHistory, std::shared_ptr<ControllerHistory>>(m, "ControllerHistory")
       .def(py::init<int>(), py::arg("world"))
       .def("next_seq", &ControllerHistory::next_seq)
