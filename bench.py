@@ -171,7 +171,9 @@ def main():
                    "parallelism": par,
                    "activation_checkpointing": True if args.recompute_layers is None else
                    f"first {args.recompute_layers} layers recomputed, the rest kept",
-                   "optimizer": "AdamW fp32 master", "comm": args.comm,
+                   "optimizer": "AdamW fp32 master",
+                   # what the parameter store actually runs (CPU ranks fall back to the library)
+                   "comm": res["info"].get("comm") or args.comm,
                    **({"fsdp_gather": res["info"]["fsdp_gather"]} if par.startswith("fsdp") else {}),
                    "driven_by": "actor mesh over the launch's processes (attach_proc_mesh); "
                                 "TrainerActor.timed_steps",

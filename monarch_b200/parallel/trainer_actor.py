@@ -171,7 +171,8 @@ class TrainerActor(Actor):
                 "tokens_per_step": self.tokens_per_step, "device": str(self.device),
                 "pid": os.getpid(), "h2d_bytes_per_step": t.h2d_bytes_per_step,
                 "d2h_bytes_per_step": t.d2h_bytes_per_step,
-                "fsdp_gather": getattr(getattr(t, "store", None), "gather", None)}
+                "fsdp_gather": getattr(getattr(t, "store", None), "gather", None),
+                "comm": getattr(getattr(t, "store", None), "comm", None)}
 
     @endpoint
     def release(self) -> None:
