@@ -227,11 +227,24 @@ def build_allocator(force: bool = False) -> Path:
     standalone executable, ``monarch_b200/tools/process_allocator_native``."""
     src = CSRC / "tools" / "process_allocator.cpp"
     target = ROOT / "tools" / "process_allocator_native"
+    _build_tool(src, target, force)
+    build_remote_exec(force)
+    return target
+
+
+def build_remote_exec(force: bool = False) -> Path:
+    """The native client stub of a remote proc (``csrc/tools/remote_exec.cpp``):
+    ``monarch_b200/tools/remote_exec_native``."""
+    return _build_tool(CSRC / "tools" / "remote_exec.cpp", ROOT / "tools" / "remote_exec_native",
+                       force)
+
+
+def _build_tool(src: Path, target: Path, force: bool) -> Path:
     flags = ["-O2", "-std=c++17", "-pthread", "-Wall"]
-    stamp = _stamp([src], flags)
+    stamp = _stamp([src, *sorted(src.parent.glob("*.h"))], flags)
     if not force and _up_to_date(target, stamp):
         return target
-    _run([CXX, *flags, str(src), "-o", str(target)])
+    _run([CXX, *flags, "-I", str(src.parent), str(src), "-o", str(target)])
     _write_stamp(target, stamp)
     return target
 

@@ -422,9 +422,10 @@ def _allocate(dims: Dict[str, int], *, in_process: bool, env: Optional[Dict[str,
         e.setdefault("MB200_CONTROLLER_REF", os.environ.get("MB200_CONTROLLER_REF", ""))
         if remote_hosts:
             # every proc is started by the allocator daemon of its host; a local stub per
-            # proc relays its output and lifetime (tools/remote_exec.py)
+            # proc relays its output and lifetime: the native executable
+            # (csrc/tools/remote_exec.cpp) where it can be built, else tools/remote_exec.py
             # (the daemon runs its own program: nothing of `argv` travels)
-            argv = [sys.executable, "-m", "monarch_b200.tools.remote_exec"]
+            argv = _remote_stub_command()
             e["MB200_REMOTE_HOSTS"] = ",".join(remote_hosts)
             e["MB200_PROCS_PER_HOST"] = str(procs_per_host)
             transport = "tcp"
@@ -435,6 +436,16 @@ def _allocate(dims: Dict[str, int], *, in_process: bool, env: Optional[Dict[str,
         native = N.ProcMesh.allocate_process(world, n, argv, e, gpu_env, _make_log_sink(world),
                                              transport)
     return ProcMesh(native, _shape_from_dims(dims), in_process=in_process)
+
+
+def _remote_stub_command() -> List[str]:
+    if os.environ.get("MB200_REMOTE_EXEC", "native") != "python":
+        try:
+            from .. import _build
+            return [str(_build.build_remote_exec())]
+        except Exception:  # noqa: BLE001 - no compiler on this host
+            pass
+    return [sys.executable, "-m", "monarch_b200.tools.remote_exec"]
 
 
 # ---------------------------------------------------------------------------- hosts ----

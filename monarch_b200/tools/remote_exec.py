@@ -1,4 +1,6 @@
-"""Local stand-in of a proc that runs on another host's process-allocator daemon.
+"""Local stand-in of a proc that runs on another host's process-allocator daemon (the
+Python form; ``csrc/tools/remote_exec.cpp`` is the same program as a native executable and is
+what the process allocator starts where it can be built).
 
 The process allocator of the client starts one of these per remote proc:
 

@@ -26,6 +26,7 @@ class Where(Actor):
 def job(tmp_path, monkeypatch, request):
     monkeypatch.setenv("MB200_JOBS_DIR", str(tmp_path))
     monkeypatch.setenv("MB200_ALLOCATOR_DAEMON", request.param)
+    monkeypatch.setenv("MB200_REMOTE_EXEC", request.param)   # the client-side stub likewise
     if request.param == "native":
         from monarch_b200.tools.process_allocator import native_daemon
         if native_daemon() is None:
@@ -40,12 +41,28 @@ def job(tmp_path, monkeypatch, request):
         pass
 
 
+def _children_of(pid):
+    out = []
+    for d in os.listdir("/proc"):
+        if d.isdigit():
+            try:
+                if int(open(f"/proc/{d}/stat").read().split(")")[1].split()[1]) == pid:
+                    out.append(int(d))
+            except (OSError, ValueError, IndexError):
+                pass
+    return out
+
+
 def test_procs_run_under_the_daemons(job):
     assert cli.info("t")["running"]
     hosts = hosts_from_config("t")
     assert hosts.sizes == {"hosts": 2}
     pm = hosts.spawn_procs(per_host={"gpus": 2})
     assert pm.sizes == {"hosts": 2, "gpus": 2}
+    stubs = [open(f"/proc/{c}/cmdline", "rb").read().split(b"\0")[0].decode()
+             for c in _children_of(os.getpid())]
+    native_stub = any(x.endswith("remote_exec_native") for x in stubs)
+    assert native_stub == (os.environ["MB200_REMOTE_EXEC"] == "native"), stubs
     a = pm.spawn("w", Where)
     pids = [v for _, v in a.pid.call().get(timeout=60).items()]
     assert len(set(pids)) == 4 and os.getpid() not in pids
