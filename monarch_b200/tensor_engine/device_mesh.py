@@ -1047,16 +1047,17 @@ def _info_of(func) -> tuple:
     return info
 
 
-def _dispatch(func, args, kwargs):
+def _dispatch(func, args, kwargs, ts: Optional[List["Tensor"]] = None):
     data_dependent, name, writes = _info_of(func)
     if data_dependent:
         raise RuntimeError(
             f"{func._schema.name} needs the values of a distributed tensor, which live on the "
             "workers.  Bring them to the controller with fetch_shard(t).get() or inspect(t), "
             "or compute on the workers inside a remote function.")
-    ts: List[Tensor] = []
-    _collect(args, ts)
-    _collect(kwargs, ts)
+    if ts is None:                      # (the active-mesh mode has collected them already)
+        ts = []
+        _collect(args, ts)
+        _collect(kwargs, ts)
     if ts:
         mesh = _mesh_of(ts)
         for t in ts:
@@ -1120,6 +1121,13 @@ class _NoDispatch(TorchDispatchMode):
 class _ActiveMeshMode(TorchDispatchMode):
     """Routes factory functions (no tensor arguments) to the active mesh."""
 
+    @classmethod
+    def _should_skip_dynamo(cls) -> bool:
+        # torch wraps a mode's __torch_dispatch__ in a "disable dynamo" guard unless this says
+        # otherwise: two extra Python frames on every dispatched operator.  Nothing under an
+        # active device mesh is compiled by dynamo.
+        return False
+
     def __torch_dispatch__(self, func, types, args=(), kwargs=None):
         kwargs = kwargs or {}
         if getattr(_tls, "propagating", False):
@@ -1128,9 +1136,9 @@ class _ActiveMeshMode(TorchDispatchMode):
         _collect(args, ts)
         _collect(kwargs, ts)
         if not ts and get_active_mesh() is not None and not _has_plain_tensor(args, kwargs):
-            return _dispatch(func, args, kwargs)
+            return _dispatch(func, args, kwargs, ts)
         if ts:
-            return _dispatch(func, args, kwargs)
+            return _dispatch(func, args, kwargs, ts)
         return func(*args, **kwargs)
 
 
